@@ -1,0 +1,130 @@
+/*
+ * lancelot_b200 - C ABI of the B200 (sm_100a) CKKS encrypted-aggregation path.
+ *
+ * This is the boundary a binding of the reference's C++ API (cahel-main/include/*.h) or of
+ * its Python module (cahel-main/python/src/binding.cu) calls instead of launching the
+ * reference's own kernels.  Plain pointers and sizes only.  Unless stated otherwise every
+ * `uint64_t *` argument is DEVICE memory holding residues in [0, q) in the reference's
+ * layouts (cahel-main/include/ciphertext.h:7, plaintext.h:11):
+ *
+ *   polynomial  [limb][N]            ciphertext  [poly][limb][N]
+ *   key pair    [2][size_QP][N]      switch key  [dnum][2][size_QP][N]   (b then a)
+ *   mod-up      [beta][size_l + size_P][N]
+ *
+ * `size_l` is the number of data primes of the operand's level (size_Q at chain index 1,
+ * one fewer per rescale).  All calls are asynchronous on `stream` (a cudaStream_t passed as
+ * void *, NULL = default stream) and return 0 on success or one of the LB_ERR_* codes; the
+ * message of the last failure on the calling thread is available from lb_last_error().
+ * LB_ERR_INVALID_ARG marks the conditions where the reference throws std::invalid_argument,
+ * LB_ERR_LOGIC / LB_ERR_CUDA where it throws std::logic_error (cahel-main/include/common.h:50-62).
+ * The library never falls back to the CPU: without a usable GPU every compute call fails.
+ */
+#ifndef LANCELOT_B200_H
+#define LANCELOT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define LB_API __attribute__((visibility("default")))
+#else
+#define LB_API
+#endif
+
+#define LB_OK 0
+#define LB_ERR_INVALID_ARG 1
+#define LB_ERR_LOGIC 2
+#define LB_ERR_CUDA 3
+#define LB_ERR_NO_MEMORY 4
+
+typedef struct lb_context lb_context;
+
+LB_API const char *lb_last_error(void);
+
+/* ---- host-only parameter helpers (no GPU needed) ---------------------------------------- */
+
+/* cahel::CoeffModulus::Create (cahel-main/src/modulus.cu:93-125; pyCAHEL coeff_modulus_create,
+ * binding.cu:34): one NTT-friendly prime per requested bit size, largest first. */
+LB_API int lb_coeff_modulus_create(uint64_t poly_modulus_degree, const int *bit_sizes, int count, uint64_t *out_moduli);
+/* get_elts_from_steps (cahel-main/include/galois.cuh:155-192; binding.cu:77). */
+LB_API int lb_galois_elts_from_steps(const int *steps, int count, uint64_t poly_modulus_degree, uint32_t *out_elts);
+/* Minimal primitive 2N-th root used for the NTT tables (cahel-main/src/util/numth.cu:311-333). */
+LB_API uint64_t lb_minimal_primitive_root(uint64_t degree, uint64_t modulus);
+/* CoeffModulus::MaxBitCount for sec_level_type::tc128 (cahel-main/include/util/hestdparms.h:16-38). */
+LB_API int lb_max_bit_count_tc128(uint64_t poly_modulus_degree);
+
+/* ---- context (replaces CAHELGPUContext, cahel-main/include/gpucontext.h:15-136) ------------ */
+
+/* moduli: the key-level list Q || P as returned by lb_coeff_modulus_create; the last
+ * special_modulus_size entries are the special primes.  galois_elts may be NULL.
+ * check_tc128 != 0 rejects parameter sets above the 128-bit bound like
+ * cahel-main/src/context.cu:181-186. */
+LB_API int lb_context_create(int log_n, const uint64_t *moduli, int n_moduli, int special_modulus_size,
+                      const uint32_t *galois_elts, int n_galois_elts, int check_tc128, int device, lb_context **out);
+LB_API void lb_context_destroy(lb_context *ctx);
+/* host copies of context constants */
+LB_API int lb_context_get_modulus(const lb_context *ctx, int index, uint64_t *out);
+LB_API int lb_context_get_root(const lb_context *ctx, int index, uint64_t *out);
+LB_API int lb_context_get_galois_table(const lb_context *ctx, int elt_index, uint32_t *out_host_table);
+/* bytes of context-owned scratch a key switch at this level uses */
+LB_API size_t lb_keyswitch_workspace_bytes(const lb_context *ctx, int size_l);
+
+/* ---- negacyclic NTT (cahel-main/src/ntt/fntt_2d.cu:872, intt_2d.cu:693) --------------------- */
+
+/* data: n_groups x (size_l + size_p) limbs; inside a group the first size_l limbs use data
+ * primes 0..size_l-1 and the next size_p the special primes.  In place. */
+LB_API int lb_ntt_forward(lb_context *ctx, uint64_t *data, int n_groups, int size_l, int size_p, void *stream);
+LB_API int lb_ntt_inverse(lb_context *ctx, uint64_t *data, int n_groups, int size_l, int size_p, void *stream);
+
+/* ---- element-wise evaluator ops (cahel-main/src/evaluate.cu:15,42,199; polymath.cu:16-227) ---- */
+
+/* out = a (+|-|*) b over n_polys polynomials of size_l limbs each; out may alias a or b. */
+LB_API int lb_add(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream);
+LB_API int lb_sub(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream);
+LB_API int lb_multiply_poly(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream);
+LB_API int lb_negate(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, uint64_t *out, void *stream);
+/* ckks_multiply / ckks_square (cahel-main/src/evaluate.cu:447,1433): batch of size-2 ciphertexts -> size-3 */
+LB_API int lb_multiply(lb_context *ctx, int size_l, int batch, const uint64_t *a, const uint64_t *b, uint64_t *out3, void *stream);
+LB_API int lb_square(lb_context *ctx, int size_l, int batch, const uint64_t *a, uint64_t *out3, void *stream);
+/* mod_switch_drop_to_next (cahel-main/src/evaluate.cu:2253): drop the last limb of every polynomial */
+LB_API int lb_mod_switch_drop(lb_context *ctx, int size_l, int n_polys, const uint64_t *in, uint64_t *out, void *stream);
+/* apply_galois_ntt (cahel-main/src/galois.cu:153) on n_limbs limbs */
+LB_API int lb_galois_permute(lb_context *ctx, int elt_index, int n_limbs, const uint64_t *in, uint64_t *out, void *stream);
+
+/* ---- key switching (cahel-main/src/eval_key_switch.cu:80-216, rns_bconv.cu:668,965) ---------- */
+
+LB_API int lb_modup(lb_context *ctx, int size_l, const uint64_t *cks, uint64_t *digits, void *stream);
+LB_API int lb_keyswitch_inner_product(lb_context *ctx, int size_l, const uint64_t *digits, const uint64_t *evk, uint64_t *cx, void *stream);
+LB_API int lb_moddown(lb_context *ctx, int size_l, const uint64_t *cx, uint64_t *out, void *stream);
+/* switch_key_inplace: ct[2][size_l][N] += KS(cks) */
+LB_API int lb_keyswitch(lb_context *ctx, int size_l, uint64_t *ct, const uint64_t *cks, const uint64_t *evk, void *stream);
+/* relinearize_inplace (cahel-main/src/evaluate.cu:2019): ct3[3][size_l][N]; result in the first two polynomials */
+LB_API int lb_relinearize(lb_context *ctx, int size_l, uint64_t *ct3, const uint64_t *relin_key, void *stream);
+/* rescale_to_next (cahel-main/src/evaluate.cu:2059,2307; rns.cu:544): in [n_polys][size_l][N] -> out [n_polys][size_l-1][N] */
+LB_API int lb_rescale(lb_context *ctx, int size_l, int n_polys, const uint64_t *in, uint64_t *out, void *stream);
+/* apply_galois_inplace / rotate_vector for one Galois element that has a key (cahel-main/src/evaluate.cu:2364,2631) */
+LB_API int lb_rotate(lb_context *ctx, int size_l, uint64_t *ct, int elt_index, const uint64_t *galois_key, void *stream);
+/* hoisting_inplace (cahel-main/src/evaluate.cu:2412): ct <- sum over steps of rot(ct, step).
+ * galois_keys: HOST array of n_steps device pointers, key of elt_indices[i] at [i]. */
+LB_API int lb_hoisting(lb_context *ctx, int size_l, uint64_t *ct, int n_steps, const int *elt_indices,
+                const uint64_t *const *galois_keys, void *stream);
+
+/* ---- Krum pairwise distance inner loop (lancelot-main-GPU/utils/byzantine_fl.py:201-223) ------- */
+
+/* acc[3][size_l][N] (+)= sum over chunks c of square(b_c - a_c); a, b: chunk c of a client at
+ * a + c * chunk_stride (in uint64 units), each chunk a size-2 ciphertext. */
+LB_API int lb_krum_accumulate(lb_context *ctx, int size_l, int n_chunks, const uint64_t *a, const uint64_t *b,
+                       size_t chunk_stride_a, size_t chunk_stride_b, uint64_t *acc, int accumulate, void *stream);
+
+/* ---- decryption (cahel-main/src/secretkey.cu:594-654 without the noise-flooding term) --------- */
+
+LB_API int lb_decrypt(lb_context *ctx, int size_l, int n_polys, const uint64_t *ct, const uint64_t *secret_key, uint64_t *pt, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

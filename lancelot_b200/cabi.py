@@ -1,0 +1,203 @@
+"""Thin typed wrapper over the C ABI (include/lancelot_b200.h).
+
+Device buffers are ``torch`` tensors of dtype ``int64`` on a CUDA device, holding the
+bit patterns of the ``uint64`` residues; torch only provides the memory and the stream.
+Every method forwards to exactly one ``lb_*`` entry point.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from ._lib import check, lib
+
+_u64p = C.POINTER(C.c_uint64)
+
+
+def _p(t):
+    """Device pointer of a CUDA int64 tensor (or None)."""
+    if t is None:
+        return None
+    assert t.is_cuda and t.dtype == torch.int64 and t.is_contiguous(), "need a contiguous CUDA int64 tensor"
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def to_device(a, device="cuda"):
+    """numpy uint64 array -> CUDA int64 tensor with the same bits."""
+    a = np.ascontiguousarray(a, dtype=np.uint64)
+    return torch.from_numpy(a.view(np.int64)).to(device)
+
+
+def to_host(t):
+    """CUDA int64 tensor -> numpy uint64 array with the same bits."""
+    return t.detach().cpu().numpy().view(np.uint64)
+
+
+def coeff_modulus_create(n, bit_sizes):
+    k = len(bit_sizes)
+    out = (C.c_uint64 * k)()
+    check(lib.lb_coeff_modulus_create(C.c_uint64(n), (C.c_int * k)(*bit_sizes), k, out))
+    return [int(x) for x in out]
+
+
+def galois_elts_from_steps(steps, n):
+    k = len(steps)
+    out = (C.c_uint32 * max(k, 1))()
+    check(lib.lb_galois_elts_from_steps((C.c_int * max(k, 1))(*steps), k, C.c_uint64(n), out))
+    return [int(out[i]) for i in range(k)]
+
+
+class Context:
+    """Owns one ``lb_context`` (tables on the device, scratch)."""
+
+    def __init__(self, log_n, moduli, special_modulus_size, galois_elts=(), check_tc128=False, device=0):
+        self.log_n, self.N = log_n, 1 << log_n
+        self.moduli = [int(m) for m in moduli]
+        self.size_QP = len(self.moduli)
+        self.size_P = special_modulus_size
+        self.size_Q = self.size_QP - self.size_P
+        self.galois_elts = [int(e) for e in galois_elts]
+        self.device = device
+        m = (C.c_uint64 * self.size_QP)(*self.moduli)
+        ne = len(self.galois_elts)
+        e = (C.c_uint32 * max(ne, 1))(*self.galois_elts)
+        h = C.c_void_p()
+        check(lib.lb_context_create(log_n, m, self.size_QP, special_modulus_size, e, ne, int(check_tc128), device,
+                                    C.byref(h)))
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib.lb_context_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def beta(self, size_l):
+        return (size_l + self.size_P - 1) // self.size_P
+
+    def empty(self, *shape):
+        return torch.empty(shape, dtype=torch.int64, device="cuda:%d" % self.device)
+
+    def root(self, i):
+        out = C.c_uint64()
+        check(lib.lb_context_get_root(self.h, i, C.byref(out)))
+        return int(out.value)
+
+    def galois_table(self, i):
+        out = np.empty(self.N, dtype=np.uint32)
+        check(lib.lb_context_get_galois_table(self.h, i, out.ctypes.data_as(C.POINTER(C.c_uint32))))
+        return out
+
+    # -- transforms
+    def ntt_forward(self, data, n_groups, size_l, size_p):
+        check(lib.lb_ntt_forward(self.h, _p(data), n_groups, size_l, size_p, _stream()))
+
+    def ntt_inverse(self, data, n_groups, size_l, size_p):
+        check(lib.lb_ntt_inverse(self.h, _p(data), n_groups, size_l, size_p, _stream()))
+
+    # -- element-wise
+    def add(self, size_l, a, b, out=None):
+        out = torch.empty_like(a) if out is None else out
+        check(lib.lb_add(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(b), _p(out), _stream()))
+        return out
+
+    def sub(self, size_l, a, b, out=None):
+        out = torch.empty_like(a) if out is None else out
+        check(lib.lb_sub(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(b), _p(out), _stream()))
+        return out
+
+    def multiply_poly(self, size_l, a, b, out=None):
+        out = torch.empty_like(a) if out is None else out
+        check(lib.lb_multiply_poly(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(b), _p(out), _stream()))
+        return out
+
+    def negate(self, size_l, a, out=None):
+        out = torch.empty_like(a) if out is None else out
+        check(lib.lb_negate(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(out), _stream()))
+        return out
+
+    def multiply(self, size_l, a, b, batch=1):
+        out = self.empty(batch, 3, size_l, self.N) if batch > 1 else self.empty(3, size_l, self.N)
+        check(lib.lb_multiply(self.h, size_l, batch, _p(a), _p(b), _p(out), _stream()))
+        return out
+
+    def square(self, size_l, a, batch=1):
+        out = self.empty(batch, 3, size_l, self.N) if batch > 1 else self.empty(3, size_l, self.N)
+        check(lib.lb_square(self.h, size_l, batch, _p(a), _p(out), _stream()))
+        return out
+
+    def mod_switch_drop(self, size_l, ct):
+        n_polys = ct.numel() // (size_l * self.N)
+        out = self.empty(n_polys, size_l - 1, self.N)
+        check(lib.lb_mod_switch_drop(self.h, size_l, n_polys, _p(ct), _p(out), _stream()))
+        return out
+
+    def galois_permute(self, elt_index, data):
+        out = torch.empty_like(data)
+        check(lib.lb_galois_permute(self.h, elt_index, data.numel() // self.N, _p(data), _p(out), _stream()))
+        return out
+
+    # -- key switching
+    def modup(self, size_l, cks):
+        out = self.empty(self.beta(size_l), size_l + self.size_P, self.N)
+        check(lib.lb_modup(self.h, size_l, _p(cks), _p(out), _stream()))
+        return out
+
+    def inner_product(self, size_l, digits, evk):
+        out = self.empty(2, size_l + self.size_P, self.N)
+        check(lib.lb_keyswitch_inner_product(self.h, size_l, _p(digits), _p(evk), _p(out), _stream()))
+        return out
+
+    def moddown(self, size_l, cx):
+        out = self.empty(size_l, self.N)
+        check(lib.lb_moddown(self.h, size_l, _p(cx), _p(out), _stream()))
+        return out
+
+    def keyswitch(self, size_l, ct, cks, evk):
+        check(lib.lb_keyswitch(self.h, size_l, _p(ct), _p(cks), _p(evk), _stream()))
+        return ct
+
+    def relinearize(self, size_l, ct3, rlk):
+        check(lib.lb_relinearize(self.h, size_l, _p(ct3), _p(rlk), _stream()))
+        return ct3[:2]
+
+    def rescale(self, size_l, ct):
+        n_polys = ct.numel() // (size_l * self.N)
+        out = self.empty(n_polys, size_l - 1, self.N)
+        check(lib.lb_rescale(self.h, size_l, n_polys, _p(ct), _p(out), _stream()))
+        return out
+
+    def rotate(self, size_l, ct, elt_index, glk):
+        check(lib.lb_rotate(self.h, size_l, _p(ct), elt_index, _p(glk), _stream()))
+        return ct
+
+    def hoisting(self, size_l, ct, elt_indices, glks):
+        n = len(elt_indices)
+        idx = (C.c_int * n)(*elt_indices)
+        ptrs = (C.c_void_p * n)(*[g.data_ptr() for g in glks])
+        check(lib.lb_hoisting(self.h, size_l, _p(ct), n, idx, ptrs, _stream()))
+        return ct
+
+    def krum_accumulate(self, size_l, a, b, acc, accumulate=False, n_chunks=None, stride_a=None, stride_b=None):
+        ct_words = 2 * size_l * self.N
+        n_chunks = a.numel() // ct_words if n_chunks is None else n_chunks
+        stride_a = ct_words if stride_a is None else stride_a
+        stride_b = ct_words if stride_b is None else stride_b
+        check(lib.lb_krum_accumulate(self.h, size_l, n_chunks, _p(a), _p(b), C.c_size_t(stride_a), C.c_size_t(stride_b),
+                                     _p(acc), int(accumulate), _stream()))
+        return acc
+
+    def decrypt(self, size_l, ct, sk):
+        n_polys = ct.numel() // (size_l * self.N)
+        pt = self.empty(size_l, self.N)
+        check(lib.lb_decrypt(self.h, size_l, n_polys, _p(ct), _p(sk), _p(pt), _stream()))
+        return pt

@@ -1,0 +1,315 @@
+// extern "C" surface declared in include/lancelot_b200.h.  Argument validation lives here
+// (the kernels trust their launchers); nothing below ever computes on the CPU.
+#include <cstring>
+
+#include "context.h"
+
+namespace lb {
+const std::string &last_error();
+int context_create(int logN, const std::vector<u64> &moduli, int size_P, const std::vector<uint32_t> &elts, int device,
+                   Context **out);
+void context_destroy(Context *ctx);
+} // namespace lb
+
+using namespace lb;
+
+struct lb_context {
+    Context *c;
+};
+
+static inline Context *C(lb_context *h) { return h ? h->c : nullptr; }
+static inline const Context *C(const lb_context *h) { return h ? h->c : nullptr; }
+static inline cudaStream_t S(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+#define REQUIRE(cond, msg)             \
+    do {                               \
+        if (!(cond)) {                 \
+            set_error(msg);            \
+            return LB_ERR_INVALID_ARG; \
+        }                              \
+    } while (0)
+
+static int bind(lb_context *h)
+{
+    if (!h || !h->c) {
+        set_error("context is null");
+        return LB_ERR_INVALID_ARG;
+    }
+    LB_CUDA(cudaSetDevice(h->c->device));
+    return LB_OK;
+}
+
+static int level_ok(const Context *c, int size_l)
+{
+    REQUIRE(size_l >= 1 && size_l <= c->hp.size_Q, "size_l is out of range for this context");
+    return LB_OK;
+}
+
+extern "C" {
+
+const char *lb_last_error(void) { return last_error().c_str(); }
+
+int lb_coeff_modulus_create(uint64_t n, const int *bit_sizes, int count, uint64_t *out)
+{
+    REQUIRE(bit_sizes && out && count >= 1 && count <= 64, "bit_sizes is invalid");
+    REQUIRE(n >= 16 && n <= 131072 && (n & (n - 1)) == 0, "poly_modulus_degree is invalid");
+    std::vector<int> bits(bit_sizes, bit_sizes + count);
+    for (int b : bits) REQUIRE(b >= 2 && b <= 60, "bit_sizes is invalid");
+    std::vector<u64> m = coeff_modulus_create(n, bits);
+    if (m.empty()) {
+        set_error("failed to find enough qualifying primes");
+        return LB_ERR_LOGIC;
+    }
+    std::memcpy(out, m.data(), sizeof(u64) * count);
+    return LB_OK;
+}
+
+int lb_galois_elts_from_steps(const int *steps, int count, uint64_t n, uint32_t *out)
+{
+    REQUIRE(steps && out && count >= 0, "steps is invalid");
+    for (int i = 0; i < count; ++i) {
+        const long a = steps[i] < 0 ? -(long)steps[i] : steps[i];
+        REQUIRE(a < (long)(n >> 1), "step count too large");
+        out[i] = galois_elt_from_step(steps[i], n);
+    }
+    return LB_OK;
+}
+
+uint64_t lb_minimal_primitive_root(uint64_t degree, uint64_t modulus) { return minimal_primitive_root(degree, modulus); }
+
+int lb_max_bit_count_tc128(uint64_t n) { return max_bit_count_tc128(n); }
+
+int lb_context_create(int log_n, const uint64_t *moduli, int n_moduli, int special, const uint32_t *elts, int n_elts,
+                      int check_tc128, int device, lb_context **out)
+{
+    REQUIRE(out, "out is null");
+    *out = nullptr;
+    REQUIRE(moduli && n_moduli >= 1 && n_moduli <= 64, "coeff_modulus size is invalid");
+    REQUIRE(n_elts >= 0 && (n_elts == 0 || elts), "galois_elts is invalid");
+    std::vector<u64> m(moduli, moduli + n_moduli);
+    std::vector<uint32_t> e(elts, elts + n_elts);
+    if (check_tc128) {
+        int bits = 0;
+        for (u64 v : m) bits += 64 - __builtin_clzll(v);
+        const int bound = max_bit_count_tc128(u64(1) << log_n);
+        REQUIRE(bound > 0 && bits <= bound, "invalid parameters_insecure");
+    }
+    Context *c = nullptr;
+    int rc = context_create(log_n, m, special, e, device, &c);
+    if (rc) return rc;
+    *out = new lb_context{c};
+    return LB_OK;
+}
+
+void lb_context_destroy(lb_context *h)
+{
+    if (!h) return;
+    context_destroy(h->c);
+    delete h;
+}
+
+int lb_context_get_modulus(const lb_context *h, int i, uint64_t *out)
+{
+    const Context *c = C(h);
+    REQUIRE(c && out && i >= 0 && i < c->hp.size_QP, "modulus index is out of range");
+    *out = c->hp.q[i];
+    return LB_OK;
+}
+
+int lb_context_get_root(const lb_context *h, int i, uint64_t *out)
+{
+    const Context *c = C(h);
+    REQUIRE(c && out && i >= 0 && i < c->hp.size_QP, "modulus index is out of range");
+    *out = c->hp.psi[i];
+    return LB_OK;
+}
+
+int lb_context_get_galois_table(const lb_context *h, int e, uint32_t *out)
+{
+    const Context *c = C(h);
+    REQUIRE(c && out && e >= 0 && e < (int)c->hp.galois_elts.size(), "Galois element index is out of range");
+    std::memcpy(out, &c->hp.perm[(size_t)e * c->hp.N], c->hp.N * sizeof(uint32_t));
+    return LB_OK;
+}
+
+size_t lb_keyswitch_workspace_bytes(const lb_context *h, int size_l)
+{
+    const Context *c = C(h);
+    if (!c || size_l < 1 || size_l > c->hp.size_Q || c->hp.size_P < 1) return 0;
+    return keyswitch_workspace_bytes(c, size_l);
+}
+
+static int ntt_rows(lb_context *h, uint64_t *data, int n_groups, int size_l, int size_p, bool fwd, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    Context *c = C(h);
+    REQUIRE(data || n_groups == 0, "data is null");
+    REQUIRE(n_groups >= 0 && size_l >= 0 && size_l <= c->hp.size_Q && size_p >= 0 && size_p <= c->hp.size_P && size_l + size_p >= 1,
+            "limb counts are out of range for this context");
+    NttJob job;
+    job.src = data;
+    job.dst = data;
+    job.n_groups = n_groups;
+    job.per_group = size_l + size_p;
+    job.size_l = size_l;
+    return fwd ? ntt_forward(c, job, S(stream)) : ntt_inverse(c, job, S(stream));
+}
+
+int lb_ntt_forward(lb_context *h, uint64_t *data, int n_groups, int size_l, int size_p, void *stream)
+{
+    return ntt_rows(h, data, n_groups, size_l, size_p, true, stream);
+}
+
+int lb_ntt_inverse(lb_context *h, uint64_t *data, int n_groups, int size_l, int size_p, void *stream)
+{
+    return ntt_rows(h, data, n_groups, size_l, size_p, false, stream);
+}
+
+static int binary(lb_context *h, int op, int size_l, int n_polys, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    if ((rc = level_ok(C(h), size_l))) return rc;
+    REQUIRE(n_polys >= 0 && a && out && (b || op == OP_NEG), "operand is null");
+    return poly_binary(C(h), op, size_l, (long)n_polys * size_l, a, b, out, S(stream));
+}
+
+int lb_add(lb_context *h, int size_l, int n, const uint64_t *a, const uint64_t *b, uint64_t *out, void *s) { return binary(h, OP_ADD, size_l, n, a, b, out, s); }
+int lb_sub(lb_context *h, int size_l, int n, const uint64_t *a, const uint64_t *b, uint64_t *out, void *s) { return binary(h, OP_SUB, size_l, n, a, b, out, s); }
+int lb_multiply_poly(lb_context *h, int size_l, int n, const uint64_t *a, const uint64_t *b, uint64_t *out, void *s) { return binary(h, OP_MUL, size_l, n, a, b, out, s); }
+int lb_negate(lb_context *h, int size_l, int n, const uint64_t *a, uint64_t *out, void *s) { return binary(h, OP_NEG, size_l, n, a, nullptr, out, s); }
+
+int lb_multiply(lb_context *h, int size_l, int batch, const uint64_t *a, const uint64_t *b, uint64_t *out3, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    if ((rc = level_ok(C(h), size_l))) return rc;
+    REQUIRE(a && b && out3 && batch >= 0, "operand is null");
+    REQUIRE(out3 != a && out3 != b, "the size-3 result cannot alias an input");
+    return poly_tensor(C(h), size_l, batch, a, b, out3, S(stream));
+}
+
+int lb_square(lb_context *h, int size_l, int batch, const uint64_t *a, uint64_t *out3, void *stream)
+{
+    return lb_multiply(h, size_l, batch, a, a, out3, stream);
+}
+
+int lb_mod_switch_drop(lb_context *h, int size_l, int n_polys, const uint64_t *in, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(size_l >= 2 && size_l <= C(h)->hp.size_Q, "end of modulus switching chain reached");
+    REQUIRE(in && out && n_polys >= 1, "operand is null");
+    return poly_drop_last(C(h), size_l, n_polys, in, out, S(stream));
+}
+
+int lb_galois_permute(lb_context *h, int elt, int n_limbs, const uint64_t *in, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(in && out && in != out && n_limbs >= 0, "operand is null or aliased");
+    return poly_galois(C(h), elt, n_limbs, in, out, S(stream));
+}
+
+int lb_modup(lb_context *h, int size_l, const uint64_t *cks, uint64_t *digits, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(cks && digits, "operand is null");
+    return modup(C(h), size_l, cks, digits, S(stream));
+}
+
+int lb_keyswitch_inner_product(lb_context *h, int size_l, const uint64_t *digits, const uint64_t *evk, uint64_t *cx, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(digits && evk && cx, "operand is null");
+    // digits carries its own limbs here, so the "own" source is the digit buffer itself:
+    // pass a pointer the kernel never dereferences differently by materialising the rows
+    Context *c = C(h);
+    if ((rc = level_ok(c, size_l))) return rc;
+    // own limbs of digit j sit at digits[j][j*alpha ..]; gather them into the workspace tail
+    const HostParams &hp = c->hp;
+    const int LP = size_l + hp.size_P, alpha = hp.size_P;
+    REQUIRE(alpha >= 1, "key switching needs at least one special prime");
+    if ((rc = c->ensure_workspace(keyswitch_workspace_bytes(c, size_l)))) return rc;
+    u64 *own = reinterpret_cast<u64 *>(c->ws); // the coefficient scratch is free at this point
+    for (int j = 0; j < hp.level[size_l].beta; ++j) {
+        const int s = j * alpha, e = s + alpha < size_l ? s + alpha : size_l;
+        LB_CUDA(cudaMemcpyAsync(own + (size_t)s * hp.N, digits + ((size_t)j * LP + s) * hp.N, (size_t)(e - s) * hp.N * 8,
+                                cudaMemcpyDeviceToDevice, S(stream)));
+    }
+    return inner_product(c, size_l, digits, own, evk, cx, S(stream));
+}
+
+int lb_moddown(lb_context *h, int size_l, const uint64_t *cx, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(cx && out, "operand is null");
+    return moddown(C(h), size_l, cx, out, S(stream));
+}
+
+int lb_keyswitch(lb_context *h, int size_l, uint64_t *ct, const uint64_t *cks, const uint64_t *evk, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(ct && cks && evk, "operand is null");
+    const size_t poly = (size_t)size_l * C(h)->hp.N;
+    return keyswitch(C(h), size_l, cks, evk, ct, ct + poly, ct, S(stream));
+}
+
+int lb_relinearize(lb_context *h, int size_l, uint64_t *ct3, const uint64_t *rlk, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(ct3 && rlk, "operand is null");
+    return relinearize(C(h), size_l, ct3, rlk, S(stream));
+}
+
+int lb_rescale(lb_context *h, int size_l, int n_polys, const uint64_t *in, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(in && out && n_polys >= 1, "operand is null");
+    return rescale(C(h), size_l, n_polys, in, out, S(stream));
+}
+
+int lb_rotate(lb_context *h, int size_l, uint64_t *ct, int elt, const uint64_t *glk, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(ct && glk, "operand is null");
+    return rotate(C(h), size_l, ct, elt, glk, S(stream));
+}
+
+int lb_hoisting(lb_context *h, int size_l, uint64_t *ct, int n_steps, const int *elts, const uint64_t *const *keys, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(ct && elts && keys, "operand is null");
+    return hoisting(C(h), size_l, ct, n_steps, elts, keys, S(stream));
+}
+
+int lb_krum_accumulate(lb_context *h, int size_l, int n_chunks, const uint64_t *a, const uint64_t *b, size_t sa, size_t sb,
+                       uint64_t *acc, int accumulate, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    if ((rc = level_ok(C(h), size_l))) return rc;
+    REQUIRE(a && b && acc && n_chunks >= 0, "operand is null");
+    REQUIRE(sa % 2 == 0 && sb % 2 == 0, "chunk strides must be even");
+    return krum_accumulate(C(h), size_l, n_chunks, a, b, (long)sa, (long)sb, acc, accumulate, S(stream));
+}
+
+int lb_decrypt(lb_context *h, int size_l, int n_polys, const uint64_t *ct, const uint64_t *sk, uint64_t *pt, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    if ((rc = level_ok(C(h), size_l))) return rc;
+    REQUIRE(ct && sk && pt && n_polys >= 1, "operand is null");
+    return poly_decrypt(C(h), size_l, n_polys, ct, sk, pt, S(stream));
+}
+
+} // extern "C"

@@ -1,0 +1,120 @@
+// Device-resident context: constant tables uploaded once, a reusable workspace, and the
+// launch helpers every kernel file shares.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/lancelot_b200.h"
+#include "params.h"
+
+namespace lb {
+
+struct DevLevel {
+    u64 *qlast_inv = nullptr, *qlast_inv_s = nullptr;
+    u64 *p_inv = nullptr, *p_inv_s = nullptr;
+    u64 *hat_inv = nullptr, *hat_inv_s = nullptr, *hat_mod = nullptr;
+    u64 *phat_inv = nullptr, *phat_inv_s = nullptr, *phat_mod = nullptr;
+    // inverse-NTT closing constants with the mod-up factor folded in: N^-1 * hat_inv and
+    // psi^-bitrev(1) * N^-1 * hat_inv (value, Shoup quotient) per limb
+    u64 *fold = nullptr; // [size_l][4]
+    // same for the special limbs with phat_inv folded in: [size_p][4]
+    u64 *pfold = nullptr;
+};
+
+struct Context {
+    HostParams hp;
+    int device = 0;
+    int sm_count = 0;
+    ModConst *d_mc = nullptr;
+    ulonglong2 *d_tw = nullptr, *d_itw = nullptr;
+    uint32_t *d_perm = nullptr;
+    u64 *d_p_mod_q = nullptr, *d_p_mod_q_s = nullptr;
+    std::vector<DevLevel> d_level;
+    // encoder tables
+    double2 *d_croots = nullptr; // [2N] complex roots of unity
+    uint32_t *d_rot_group = nullptr; // [N/4] powers of 5 mod 2N
+    // scratch owned by the context, grown on demand between operations
+    void *ws = nullptr;
+    size_t ws_bytes = 0;
+    std::vector<void *> owned; // device allocations released with the context
+
+    int ensure_workspace(size_t bytes);
+};
+
+void set_error(const std::string &msg);
+int cuda_fail(cudaError_t e, const char *what);
+
+#define LB_CUDA(call)                                         \
+    do {                                                      \
+        cudaError_t e__ = (call);                             \
+        if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
+    } while (0)
+
+// ---- kernels (one launcher per step; all asynchronous on `stream`) ----------------------
+
+struct NttJob {
+    const u64 *src = nullptr; // rows of N residues
+    u64 *dst = nullptr;
+    int n_groups = 1;    // number of row groups
+    int per_group = 1;   // limb rows per group
+    int size_l = 1;      // rows [0,size_l) use table tbl_off + row, the rest size_Q + (row - size_l)
+    int tbl_off = 0;
+    long src_group_stride = -1, dst_group_stride = -1; // in rows; -1: per_group
+    int src_row_off = 0;   // first source row inside a group
+    int skip_lo = 0, skip_hi = 0; // rows [skip_lo, skip_hi) of each group are left untouched
+    // Forward prologue (fast base conversion fused into the load): the transform input of
+    // row r is  sum_{i < bconv_n} src_row(i)[k] * mat[i]  mod q_r,  where src_row(i) is row
+    // src_row_off + i of the group's source block.  mat == nullptr means all-ones with
+    // bconv_n == 1, i.e. "x mod q_r" of a single source row.
+    int bconv_n = 0;
+    const u64 *bconv_mat = nullptr;     // entries of row r start at (grp * mat_group_stride + r * mat_row_stride)
+    long mat_group_stride = 0, mat_row_stride = 0;
+    int digit_alpha = 0; // > 0: mod-up mode. Group g converts digit g: source rows [g*alpha, min((g+1)*alpha, size_l)),
+                         // and the digit's own rows are skipped
+    // Forward epilogue: dst = (aux - NTT(x)) * scal[row] (+ add), the closing step of mod-down and rescale
+    const u64 *aux = nullptr;
+    long aux_group_stride = -1;
+    const u64 *scal = nullptr, *scal_s = nullptr;
+    const u64 *add = nullptr; // optional addend rows, same shape as dst; only groups < add_groups have one
+    long add_group_stride = -1;
+    int add_groups = 0;
+    // Inverse epilogue: closing constants per row replaced by fold[row][4]
+    const u64 *fold = nullptr;
+};
+
+int ntt_forward(Context *ctx, const NttJob &job, cudaStream_t stream);
+int ntt_inverse(Context *ctx, const NttJob &job, cudaStream_t stream);
+
+// element-wise kernels (poly.cu).  Rows are limbs of N residues; row r uses prime r % size_l.
+enum PolyOp { OP_ADD = 0, OP_SUB = 1, OP_MUL = 2, OP_NEG = 3 };
+int poly_binary(Context *ctx, int op, int size_l, long rows, const u64 *a, const u64 *b, u64 *out, cudaStream_t stream);
+// out[3][L][N] = a[2][L][N] (x) b[2][L][N], batched over `batch` ciphertexts
+int poly_tensor(Context *ctx, int size_l, int batch, const u64 *a, const u64 *b, u64 *out, cudaStream_t stream);
+// dst[i] = src[perm[i]] for `rows` limbs
+int poly_galois(Context *ctx, int elt_idx, long rows, const u64 *src, u64 *dst, cudaStream_t stream);
+// acc[3][L][N] (+)= sum_c square(b_c - a_c) over n_chunks ciphertext pairs [2][L][N]
+int krum_accumulate(Context *ctx, int size_l, int n_chunks, const u64 *a, const u64 *b, long chunk_stride_a,
+                    long chunk_stride_b, u64 *acc, int accumulate, cudaStream_t stream);
+// drop the last limb of each polynomial: in [polys][L][N] -> out [polys][L-1][N]
+int poly_drop_last(Context *ctx, int size_l, int n_polys, const u64 *in, u64 *out, cudaStream_t stream);
+// pt = c0 + c1 s + c2 s^2 ...
+int poly_decrypt(Context *ctx, int size_l, int n_polys, const u64 *ct, const u64 *sk, u64 *pt, cudaStream_t stream);
+
+// key switching (keyswitch.cu); all buffers in NTT form, evk [dnum][2][size_QP][N]
+size_t keyswitch_workspace_bytes(const Context *ctx, int size_l);
+// ct[2][L][N]: out_i = (add_i ? add_i : 0) + moddown(<modup(cks), evk>)_i ; add0/add1 may alias out
+int keyswitch(Context *ctx, int size_l, const u64 *cks, const u64 *evk, const u64 *add0, const u64 *add1, u64 *out,
+              cudaStream_t stream);
+int relinearize(Context *ctx, int size_l, u64 *ct3, const u64 *rlk, cudaStream_t stream);
+int rescale(Context *ctx, int size_l, int n_polys, const u64 *in, u64 *out, cudaStream_t stream);
+int rotate(Context *ctx, int size_l, u64 *ct, int elt_idx, const u64 *glk, cudaStream_t stream);
+int hoisting(Context *ctx, int size_l, u64 *ct, int n_steps, const int *elt_idx, const u64 *const *glks,
+             cudaStream_t stream);
+// exposed pieces of the key switch for per-stage parity tests
+int modup(Context *ctx, int size_l, const u64 *cks, u64 *digits, cudaStream_t stream);
+int inner_product(Context *ctx, int size_l, const u64 *digits, const u64 *cks, const u64 *evk, u64 *cx, cudaStream_t stream);
+int moddown(Context *ctx, int size_l, const u64 *cx, u64 *out, cudaStream_t stream);
+
+} // namespace lb

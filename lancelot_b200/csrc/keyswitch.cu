@@ -1,0 +1,360 @@
+// Hybrid key switching, rescale, rotation and hoisted rotation sums.
+//
+// Reference flow (cahel-main/src/eval_key_switch.cu:80-216): modup (INTT, per-digit base
+// conversion, per-digit NTT) -> inner product with the key -> two moddowns (INTT of the
+// special limbs, base conversion, NTT, (cx - delta) P^-1) -> add to the ciphertext; about
+// fourteen launches with every intermediate written to HBM.
+//
+// Here the base conversions live inside the forward transform's load stage and the
+// moddown / rescale closing arithmetic (and the final addition to the ciphertext) inside
+// its store stage, so a key switch is five launches:
+//   1 INTT of the L input limbs (mod-up scaling folded into the closing constants)
+//   2 NTT of all beta x (L + P) digit limbs with the base conversion fused into the load;
+//     a digit's own limbs are never copied: the inner product reads them from the input
+//   3 inner product over digits (128-bit lazy accumulation, one reduction per output)
+//   4 INTT of the 2 x P special limbs (mod-down scaling folded in)
+//   5 NTT of 2 x L limbs: load = P->Ql conversion, store = (cx - delta) P^-1 + ct
+#include "context.h"
+
+namespace lb {
+
+constexpr int kKsThreads = 256;
+constexpr int kMaxSteps = 16;
+
+struct KsWs {
+    u64 *coef, *digits, *cx, *pc, *tmp;
+};
+
+size_t keyswitch_workspace_bytes(const Context *ctx, int L)
+{
+    const HostParams &hp = ctx->hp;
+    const size_t N = hp.N, P = hp.size_P, LP = L + P;
+    const size_t beta = hp.level[L].beta;
+    // coef[L] + digits[beta][LP] + cx[2][LP] + pc[2][P] + tmp[3][L] rows
+    return (L + beta * LP + 2 * LP + 2 * P + 3 * (size_t)L) * N * sizeof(u64);
+}
+
+static int get_ws(Context *ctx, int L, KsWs &w)
+{
+    const HostParams &hp = ctx->hp;
+    const size_t N = hp.N, P = hp.size_P, LP = L + P;
+    const size_t beta = hp.level[L].beta;
+    int rc = ctx->ensure_workspace(keyswitch_workspace_bytes(ctx, L));
+    if (rc) return rc;
+    u64 *p = reinterpret_cast<u64 *>(ctx->ws);
+    w.coef = p; p += L * N;
+    w.digits = p; p += beta * LP * N;
+    w.cx = p; p += 2 * LP * N;
+    w.pc = p; p += 2 * P * N;
+    w.tmp = p;
+    return LB_OK;
+}
+
+static int check_level(const Context *ctx, int L)
+{
+    if (ctx->hp.size_P < 1) { set_error("key switching needs at least one special prime"); return LB_ERR_INVALID_ARG; }
+    if (L < 1 || L > ctx->hp.size_Q) { set_error("ciphertext level is out of range"); return LB_ERR_INVALID_ARG; }
+    if (ctx->hp.size_Q % ctx->hp.size_P != 0) {
+        // the reference sizes keys by floor(size_Q / size_P) digits but switches with ceil(size_Ql / size_P)
+        set_error("special_modulus_size must divide the number of data primes");
+        return LB_ERR_INVALID_ARG;
+    }
+    return LB_OK;
+}
+
+// ---- step 1+2: mod-up (cahel-main/src/rns_bconv.cu:668-792) -----------------------------
+
+static int modup_into(Context *ctx, int L, const u64 *cks, u64 *coef, u64 *digits, cudaStream_t stream)
+{
+    const HostParams &hp = ctx->hp;
+    const int P = hp.size_P, LP = L + P, alpha = P;
+    const DevLevel &dl = ctx->d_level[L];
+    NttJob inv;
+    inv.src = cks;
+    inv.dst = coef;
+    inv.n_groups = 1;
+    inv.per_group = L;
+    inv.size_l = L;
+    inv.fold = alpha > 1 ? dl.fold : nullptr;
+    int rc = ntt_inverse(ctx, inv, stream);
+    if (rc) return rc;
+    NttJob fwd;
+    fwd.src = coef;
+    fwd.dst = digits;
+    fwd.n_groups = hp.level[L].beta;
+    fwd.per_group = LP;
+    fwd.size_l = L;
+    fwd.src_group_stride = 0;
+    fwd.digit_alpha = alpha;
+    fwd.bconv_n = alpha;
+    fwd.bconv_mat = alpha > 1 ? dl.hat_mod : nullptr;
+    fwd.mat_group_stride = (long)LP * alpha;
+    fwd.mat_row_stride = alpha;
+    return ntt_forward(ctx, fwd, stream);
+}
+
+// ---- step 3: inner product (cahel-main/src/eval_key_switch.cu:13-76; with a gather and a
+// loop over steps it is also the hoisting accumulation of cahel-main/src/evaluate.cu:2572-2599)
+
+struct IpArgs {
+    const u64 *evk[kMaxSteps];
+    const uint32_t *perm[kMaxSteps];
+    int n_steps;
+};
+
+__global__ void __launch_bounds__(kKsThreads) inner_product_kernel(const u64 *__restrict__ digits, const u64 *__restrict__ own,
+                                                                   u64 *__restrict__ cx, const ModConst *__restrict__ mc,
+                                                                   const IpArgs args, const int logN, const int L, const int LP,
+                                                                   const int size_Q, const int size_QP, const int alpha,
+                                                                   const int beta)
+{
+    const long total = (long)LP << logN;
+    const long n_mask = (1L << logN) - 1;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const int r = (int)(i >> logN);
+        const long k = i & n_mask;
+        const int tbl = r < L ? r : size_Q + (r - L);
+        const ModConst m = mc[tbl];
+        const int own_digit = r < L ? r / alpha : -1;
+        u128d a0 = {0, 0}, a1 = {0, 0};
+        u64 r0 = 0, r1 = 0;
+        int pending = 0;
+        for (int s = 0; s < args.n_steps; ++s) {
+            const long kk = args.perm[s] ? (long)args.perm[s][k] : k;
+            const u64 *key = args.evk[s];
+            for (int j = 0; j < beta; ++j) {
+                const u64 d = (j == own_digit) ? own[((long)r << logN) + kk] : digits[(((long)j * LP + r) << logN) + kk];
+                const u64 *kb = key + ((((long)j * 2) * size_QP + tbl) << logN) + k;
+                mac_wide(a0, d, kb[0]);
+                mac_wide(a1, d, kb[(long)size_QP << logN]);
+                if (++pending == 32) {
+                    r0 = add_mod(r0, barrett128(a0, m.q, m.r0, m.r1), m.q);
+                    r1 = add_mod(r1, barrett128(a1, m.q, m.r0, m.r1), m.q);
+                    a0.lo = a0.hi = a1.lo = a1.hi = 0;
+                    pending = 0;
+                }
+            }
+        }
+        r0 = add_mod(r0, barrett128(a0, m.q, m.r0, m.r1), m.q);
+        r1 = add_mod(r1, barrett128(a1, m.q, m.r0, m.r1), m.q);
+        cx[i] = r0;
+        cx[total + i] = r1;
+    }
+}
+
+static int inner_product_steps(Context *ctx, int L, const u64 *digits, const u64 *own, const IpArgs &args, u64 *cx,
+                               cudaStream_t stream)
+{
+    const HostParams &hp = ctx->hp;
+    const int LP = L + hp.size_P;
+    const long total = (long)LP << hp.logN;
+    long blocks = (total + kKsThreads - 1) / kKsThreads;
+    const long cap = (long)ctx->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    inner_product_kernel<<<(int)blocks, kKsThreads, 0, stream>>>(digits, own, cx, ctx->d_mc, args, hp.logN, L, LP, hp.size_Q,
+                                                                 hp.size_QP, hp.size_P, hp.level[L].beta);
+    LB_CUDA(cudaGetLastError());
+    return LB_OK;
+}
+
+// ---- step 4+5: mod-down (cahel-main/src/rns_bconv.cu:965-1053, ntt_moddown.cu:244-252) -----
+
+static int moddown_into(Context *ctx, int L, int n_polys, const u64 *cx, u64 *pc, u64 *out, const u64 *add, int add_groups,
+                        cudaStream_t stream)
+{
+    const HostParams &hp = ctx->hp;
+    const int P = hp.size_P, LP = L + P;
+    const DevLevel &dl = ctx->d_level[L];
+    NttJob inv;
+    inv.src = cx;
+    inv.dst = pc;
+    inv.n_groups = n_polys;
+    inv.per_group = P;
+    inv.size_l = 0; // every row is a special limb
+    inv.src_group_stride = LP;
+    inv.src_row_off = L;
+    inv.dst_group_stride = P;
+    inv.fold = P > 1 ? dl.pfold : nullptr;
+    int rc = ntt_inverse(ctx, inv, stream);
+    if (rc) return rc;
+    NttJob fwd;
+    fwd.src = pc;
+    fwd.dst = out;
+    fwd.n_groups = n_polys;
+    fwd.per_group = L;
+    fwd.size_l = L;
+    fwd.src_group_stride = P;
+    fwd.dst_group_stride = L;
+    fwd.bconv_n = P;
+    fwd.bconv_mat = P > 1 ? dl.phat_mod : nullptr;
+    fwd.mat_group_stride = 0;
+    fwd.mat_row_stride = P;
+    fwd.aux = cx;
+    fwd.aux_group_stride = LP;
+    fwd.scal = dl.p_inv;
+    fwd.scal_s = dl.p_inv_s;
+    fwd.add = add;
+    fwd.add_group_stride = L;
+    fwd.add_groups = add ? add_groups : 0;
+    return ntt_forward(ctx, fwd, stream);
+}
+
+// ---- public pieces ----------------------------------------------------------------------
+
+int modup(Context *ctx, int L, const u64 *cks, u64 *digits, cudaStream_t stream)
+{
+    int rc = check_level(ctx, L);
+    if (rc) return rc;
+    KsWs w;
+    if ((rc = get_ws(ctx, L, w))) return rc;
+    if ((rc = modup_into(ctx, L, cks, w.coef, digits, stream))) return rc;
+    // materialise the digit's own limbs for callers that want the reference layout
+    const HostParams &hp = ctx->hp;
+    const int LP = L + hp.size_P, alpha = hp.size_P;
+    for (int j = 0; j < hp.level[L].beta; ++j) {
+        const int s = j * alpha, e = s + alpha < L ? s + alpha : L;
+        LB_CUDA(cudaMemcpyAsync(digits + ((size_t)j * LP + s) * hp.N, cks + (size_t)s * hp.N, (size_t)(e - s) * hp.N * 8,
+                                cudaMemcpyDeviceToDevice, stream));
+    }
+    return LB_OK;
+}
+
+int inner_product(Context *ctx, int L, const u64 *digits, const u64 *cks, const u64 *evk, u64 *cx, cudaStream_t stream)
+{
+    int rc = check_level(ctx, L);
+    if (rc) return rc;
+    IpArgs args = {};
+    args.evk[0] = evk;
+    args.perm[0] = nullptr;
+    args.n_steps = 1;
+    return inner_product_steps(ctx, L, digits, cks, args, cx, stream);
+}
+
+int moddown(Context *ctx, int L, const u64 *cx, u64 *out, cudaStream_t stream)
+{
+    int rc = check_level(ctx, L);
+    if (rc) return rc;
+    KsWs w;
+    if ((rc = get_ws(ctx, L, w))) return rc;
+    return moddown_into(ctx, L, 1, cx, w.pc, out, nullptr, 0, stream);
+}
+
+static int keyswitch_add(Context *ctx, int L, const u64 *cks, const u64 *evk, const u64 *add, int add_groups, u64 *out,
+                         cudaStream_t stream)
+{
+    int rc = check_level(ctx, L);
+    if (rc) return rc;
+    KsWs w;
+    if ((rc = get_ws(ctx, L, w))) return rc;
+    if ((rc = modup_into(ctx, L, cks, w.coef, w.digits, stream))) return rc;
+    IpArgs args = {};
+    args.evk[0] = evk;
+    args.n_steps = 1;
+    if ((rc = inner_product_steps(ctx, L, w.digits, cks, args, w.cx, stream))) return rc;
+    return moddown_into(ctx, L, 2, w.cx, w.pc, out, add, add_groups, stream);
+}
+
+int keyswitch(Context *ctx, int L, const u64 *cks, const u64 *evk, const u64 *add0, const u64 *add1, u64 *out, cudaStream_t stream)
+{
+    const size_t poly = (size_t)L * ctx->hp.N;
+    if (add0 && add1 && add1 != add0 + poly) { set_error("addends must be the two polynomials of one ciphertext"); return LB_ERR_INVALID_ARG; }
+    if (!add0 && add1) { set_error("an addend for the second polynomial alone is not supported"); return LB_ERR_INVALID_ARG; }
+    return keyswitch_add(ctx, L, cks, evk, add0, add0 ? (add1 ? 2 : 1) : 0, out, stream);
+}
+
+// cahel-main/src/evaluate.cu:2019-2056
+int relinearize(Context *ctx, int L, u64 *ct3, const u64 *rlk, cudaStream_t stream)
+{
+    const size_t poly = (size_t)L * ctx->hp.N;
+    return keyswitch_add(ctx, L, ct3 + 2 * poly, rlk, ct3, 2, ct3, stream);
+}
+
+// cahel-main/src/rns.cu:544-570 (floors): two launches for all polynomials
+int rescale(Context *ctx, int L, int n_polys, const u64 *in, u64 *out, cudaStream_t stream)
+{
+    if (L < 2 || L > ctx->hp.size_Q) { set_error("cannot rescale: no next level"); return LB_ERR_INVALID_ARG; }
+    int rc = ctx->ensure_workspace((size_t)n_polys * ctx->hp.N * 8);
+    if (rc) return rc;
+    u64 *last = reinterpret_cast<u64 *>(ctx->ws);
+    NttJob inv;
+    inv.src = in;
+    inv.dst = last;
+    inv.n_groups = n_polys;
+    inv.per_group = 1;
+    inv.size_l = 1;
+    inv.tbl_off = L - 1;
+    inv.src_group_stride = L;
+    inv.src_row_off = L - 1;
+    inv.dst_group_stride = 1;
+    if ((rc = ntt_inverse(ctx, inv, stream))) return rc;
+    const DevLevel &dl = ctx->d_level[L];
+    NttJob fwd;
+    fwd.src = last;
+    fwd.dst = out;
+    fwd.n_groups = n_polys;
+    fwd.per_group = L - 1;
+    fwd.size_l = L - 1;
+    fwd.src_group_stride = 1;
+    fwd.dst_group_stride = L - 1;
+    fwd.bconv_n = 1;
+    fwd.aux = in;
+    fwd.aux_group_stride = L;
+    fwd.scal = dl.qlast_inv;
+    fwd.scal_s = dl.qlast_inv_s;
+    return ntt_forward(ctx, fwd, stream);
+}
+
+// cahel-main/src/evaluate.cu:2631-2686: permute both polynomials, then switch the permuted c1
+int rotate(Context *ctx, int L, u64 *ct, int elt_idx, const u64 *glk, cudaStream_t stream)
+{
+    int rc = check_level(ctx, L);
+    if (rc) return rc;
+    KsWs w;
+    if ((rc = get_ws(ctx, L, w))) return rc;
+    if ((rc = poly_galois(ctx, elt_idx, 2L * L, ct, w.tmp, stream))) return rc;
+    const size_t poly = (size_t)L * ctx->hp.N;
+    return keyswitch_add(ctx, L, w.tmp + poly, glk, w.tmp, 1, ct, stream);
+}
+
+// sum over steps of the permuted c0 (cahel-main/src/evaluate.cu:2560-2568)
+__global__ void __launch_bounds__(kKsThreads) galois_sum_kernel(const u64 *__restrict__ src, u64 *__restrict__ dst,
+                                                                const ModConst *__restrict__ mc, const IpArgs args, const int logN,
+                                                                const long total)
+{
+    const long n_mask = (1L << logN) - 1;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long row = i >> logN, k = i & n_mask;
+        const u64 q = mc[row].q;
+        u64 acc = 0;
+        for (int s = 0; s < args.n_steps; ++s) acc = add_mod(acc, src[(row << logN) + args.perm[s][k]], q);
+        dst[i] = acc;
+    }
+}
+
+// cahel-main/src/evaluate.cu:2412-2629: one mod-up, per step a permuted inner product, two mod-downs
+int hoisting(Context *ctx, int L, u64 *ct, int n_steps, const int *elt_idx, const u64 *const *glks, cudaStream_t stream)
+{
+    int rc = check_level(ctx, L);
+    if (rc) return rc;
+    if (n_steps < 1 || n_steps > kMaxSteps) { set_error("hoisting supports 1 to 16 steps per call"); return LB_ERR_INVALID_ARG; }
+    const HostParams &hp = ctx->hp;
+    IpArgs args = {};
+    args.n_steps = n_steps;
+    for (int s = 0; s < n_steps; ++s) {
+        if (elt_idx[s] < 0 || elt_idx[s] >= (int)hp.galois_elts.size()) { set_error("Galois key not present in hoisting"); return LB_ERR_LOGIC; }
+        args.evk[s] = glks[s];
+        args.perm[s] = ctx->d_perm + ((size_t)elt_idx[s] << hp.logN);
+    }
+    KsWs w;
+    if ((rc = get_ws(ctx, L, w))) return rc;
+    const size_t poly = (size_t)L * hp.N;
+    if ((rc = modup_into(ctx, L, ct + poly, w.coef, w.digits, stream))) return rc;
+    if ((rc = inner_product_steps(ctx, L, w.digits, ct + poly, args, w.cx, stream))) return rc;
+    const long total = (long)L << hp.logN;
+    long blocks = (total + kKsThreads - 1) / kKsThreads;
+    galois_sum_kernel<<<(int)blocks, kKsThreads, 0, stream>>>(ct, w.tmp, ctx->d_mc, args, hp.logN, total);
+    LB_CUDA(cudaGetLastError());
+    return moddown_into(ctx, L, 2, w.cx, w.pc, ct, w.tmp, 1, stream);
+}
+
+} // namespace lb

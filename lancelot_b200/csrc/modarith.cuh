@@ -1,0 +1,118 @@
+// 64-bit modular arithmetic shared by host precompute and device kernels.
+//
+// Device code keeps residues lazily reduced inside a kernel (forward butterflies in
+// [0,4q), inverse in [0,2q)) and always stores the canonical residue in [0,q), which is
+// what every stage of the reference library leaves in memory
+// (cahel-main/src/ntt/fntt_2d.cu:860-866, cahel-main/include/uintmodmath.cuh:112-259).
+#pragma once
+#include <cstdint>
+
+namespace lb {
+
+typedef uint64_t u64;
+typedef unsigned __int128 u128;
+
+#if defined(__CUDACC__)
+#define LB_HD __host__ __device__ __forceinline__
+#define LB_D __device__ __forceinline__
+#else
+#define LB_HD inline
+#define LB_D inline
+#endif
+
+// ---- host-only helpers (precompute) ---------------------------------------------------
+inline u64 h_mulmod(u64 a, u64 b, u64 q) { return (u64)((u128)a * b % q); }
+inline u64 h_powmod(u64 b, u64 e, u64 q)
+{
+    u64 r = 1 % q;
+    b %= q;
+    for (; e; e >>= 1) {
+        if (e & 1) r = h_mulmod(r, b, q);
+        b = h_mulmod(b, b, q);
+    }
+    return r;
+}
+inline u64 h_invmod(u64 a, u64 q) { return h_powmod(a % q, q - 2, q); } // q prime
+inline u64 h_shoup(u64 w, u64 q) { return (u64)(((u128)w << 64) / q); }
+
+#if defined(__CUDACC__)
+// ---- device arithmetic ----------------------------------------------------------------
+
+// x * w mod q in [0, 2q) for any 64-bit x, given ws = floor(w 2^64 / q), w < q.
+LB_D u64 shoup_lazy(u64 x, u64 w, u64 ws, u64 q)
+{
+    u64 hi = __umul64hi(x, ws);
+    return x * w - hi * q;
+}
+
+LB_D u64 shoup_mul(u64 x, u64 w, u64 ws, u64 q)
+{
+    u64 r = shoup_lazy(x, w, ws, q);
+    return r >= q ? r - q : r;
+}
+
+LB_D u64 csub(u64 x, u64 q) { return x >= q ? x - q : x; }
+
+LB_D u64 add_mod(u64 a, u64 b, u64 q) { return csub(a + b, q); }
+LB_D u64 sub_mod(u64 a, u64 b, u64 q) { return a >= b ? a - b : a + q - b; }
+
+// x mod q for any 64-bit x, bhi = floor(2^64 / q)
+LB_D u64 barrett64(u64 x, u64 q, u64 bhi)
+{
+    u64 s = __umul64hi(x, bhi);
+    u64 r = x - s * q;
+    return r >= q ? r - q : r;
+}
+
+struct u128d {
+    u64 lo, hi;
+};
+
+LB_D u128d mul_wide(u64 a, u64 b)
+{
+    u128d r;
+    r.lo = a * b;
+    r.hi = __umul64hi(a, b);
+    return r;
+}
+
+LB_D void mac_wide(u128d &acc, u64 a, u64 b)
+{
+    u64 lo = a * b, hi = __umul64hi(a, b);
+    acc.lo += lo;
+    acc.hi += hi + (acc.lo < lo);
+}
+
+// (hi:lo) mod q with the two-word ratio floor(2^128 / q) = (r1:r0); exact for q < 2^62.
+LB_D u64 barrett128(u128d z, u64 q, u64 r0, u64 r1)
+{
+    // quotient estimate: floor(z * ratio / 2^128), dropping the lowest partial product
+    u64 carry = __umul64hi(z.lo, r0);
+    u64 t_lo = z.lo * r1;
+    u64 t_hi = __umul64hi(z.lo, r1);
+    u64 s = t_lo + carry;
+    u64 c1 = t_hi + (s < t_lo);
+    u64 u_lo = z.hi * r0;
+    u64 u_hi = __umul64hi(z.hi, r0);
+    u64 s2 = s + u_lo;
+    u64 c2 = u_hi + (s2 < u_lo);
+    u64 qhat = z.hi * r1 + c1 + c2;
+    u64 r = z.lo - qhat * q;
+    // the estimate is short by at most 2
+    r = csub(r, q << 1);
+    return csub(r, q);
+}
+
+LB_D u64 mul_mod(u64 a, u64 b, u64 q, u64 r0, u64 r1) { return barrett128(mul_wide(a, b), q, r0, r1); }
+#endif
+
+// Per-modulus constants as laid out in device memory (one entry per prime of QP).
+struct ModConst {
+    u64 q;
+    u64 r0, r1;      // floor(2^128 / q), low and high word
+    u64 ninv, ninvs; // N^-1 mod q and its Shoup quotient
+    u64 iw1n, iw1ns; // psi^-bitrev(1) * N^-1 (last inverse stage fused with the scaling)
+    u64 pad;
+};
+
+} // namespace lb

@@ -1,0 +1,476 @@
+// Batched negacyclic NTT / inverse NTT over RNS limbs for sm_100a.
+//
+// Mathematical definition (must equal the reference's, cahel-main/src/ntt/ntt_1d.cu:38-74,
+// :129-171 and butterfly.cuh:10-43; its production path is the two-kernel radix-8 pair in
+// cahel-main/src/ntt/fntt_2d.cu:8,126,872 and intt_2d.cu:8,103,693):
+//   forward: stages m = 1,2,..,N/2, butterfly (x,y) -> (x + w y, x - w y), w = psi^bitrev(m+k);
+//            natural order in, bit-reversed order out, canonical residues out.
+//   inverse: the exact inverse map (the reference halves in every butterfly; here N^-1 is
+//            folded into the last stage).
+//
+// Schedule (new): ONE kernel per transform and one pass over HBM.  A limb of N = 2^16
+// coefficients (512 KiB) does not fit one SM, so a thread-block cluster of C = N / 8192 CTAs
+// owns a limb.  The first log2(C) stages run in registers on coalesced strided global loads;
+// their outputs are scattered to the owning CTA through distributed shared memory; each
+// CTA then finishes an independent 8192-point transform in its own shared memory with
+// register-blocked radix-8 passes and writes its contiguous part of the result with
+// 16-byte stores.  The inverse mirrors this (contiguous loads, local passes, DSMEM gather,
+// last log2(C) stages in registers, coalesced strided stores).  Algorithmic traffic is
+// 16 bytes per coefficient per transform; twiddles (16 B each, value + Shoup quotient) are
+// read through L2.
+#include <cooperative_groups.h>
+
+#include "context.h"
+
+namespace cg = cooperative_groups;
+
+namespace lb {
+
+constexpr int kNttThreads = 256;
+constexpr int kMaxLocalLog = 13; // 8192 points (64 KiB + padding) per CTA
+
+struct NttK {
+    const u64 *src;
+    u64 *dst;
+    const ulonglong2 *tw;
+    const ModConst *mc;
+    int logN, per_group, size_l, size_Q, tbl_off;
+    long src_group_stride, dst_group_stride, aux_group_stride, add_group_stride;
+    int src_row_off, skip_lo, skip_hi;
+    int bconv_n, digit_alpha, add_groups;
+    const u64 *bconv_mat;
+    long mat_group_stride, mat_row_stride;
+    const u64 *aux, *scal, *scal_s, *add, *fold;
+    int npass;
+    unsigned char S[8];
+};
+
+// one spare word per 16 keeps the stride-8 and stride-1 passes off the same banks
+LB_D int sidx(int i) { return i + (i >> 4); }
+
+LB_D void fwd_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
+{
+    x = csub(x, q2);
+    const u64 t = shoup_lazy(y, w.x, w.y, q);
+    y = x + q2 - t;
+    x = x + t;
+}
+
+LB_D void inv_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
+{
+    const u64 s = csub(x + y, q2);
+    const u64 d = x + q2 - y;
+    x = s;
+    y = shoup_lazy(d, w.x, w.y, q);
+}
+
+// S consecutive forward stages on 2^S register values; stage u uses twiddle (t0 << u) + block
+template <int S>
+LB_D void fwd_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ tw, const unsigned t0, const u64 q, const u64 q2)
+{
+#pragma unroll
+    for (int u = 0; u < S; ++u) {
+        const int half = 1 << (S - 1 - u);
+#pragma unroll
+        for (int b = 0; b < (1 << u); ++b) {
+            const ulonglong2 w = __ldg(tw + ((t0 << u) + b));
+#pragma unroll
+            for (int i = 0; i < half; ++i) fwd_bf(v[b * 2 * half + i], v[b * 2 * half + i + half], w, q, q2);
+        }
+    }
+}
+
+// S consecutive inverse stages; stage u pairs distance 2^u and uses twiddle (tb >> u) + block.
+// CLOSE: the last of them is the transform's last stage and carries the N^-1 scaling.
+template <int S, bool CLOSE>
+LB_D void inv_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ itw, const unsigned tb, const u64 q, const u64 q2,
+                   const u64 cn, const u64 cns, const u64 cw, const u64 cws)
+{
+#pragma unroll
+    for (int u = 0; u < S; ++u) {
+        const int dist = 1 << u;
+#pragma unroll
+        for (int b = 0; b < (1 << (S - 1 - u)); ++b) {
+            if (CLOSE && u == S - 1) {
+#pragma unroll
+                for (int i = 0; i < dist; ++i) {
+                    u64 &x = v[b * 2 * dist + i], &y = v[b * 2 * dist + i + dist];
+                    const u64 s = x + y, d = x + q2 - y;
+                    x = shoup_mul(s, cn, cns, q);
+                    y = shoup_mul(d, cw, cws, q);
+                }
+            } else {
+                const ulonglong2 w = __ldg(itw + ((tb >> u) + b));
+#pragma unroll
+                for (int i = 0; i < dist; ++i) inv_bf(v[b * 2 * dist + i], v[b * 2 * dist + i + dist], w, q, q2);
+            }
+        }
+    }
+}
+
+template <int R>
+LB_D void load_contig(u64 (&v)[R], const u64 *p)
+{
+    if (R == 1) {
+        v[0] = p[0];
+    } else {
+#pragma unroll
+        for (int i = 0; i < R; i += 2) {
+            const ulonglong2 t = *reinterpret_cast<const ulonglong2 *>(p + i);
+            v[i] = t.x;
+            v[i + 1] = t.y;
+        }
+    }
+}
+
+template <int R>
+LB_D void store_contig(const u64 (&v)[R], u64 *p)
+{
+#pragma unroll
+    for (int i = 0; i < R; i += 2) *reinterpret_cast<ulonglong2 *>(p + i) = make_ulonglong2(v[i], v[i + 1]);
+}
+
+// ---- forward --------------------------------------------------------------------------
+
+// Where a transform input comes from: a plain row, one row reduced into this row's prime,
+// or an approximate fast base conversion of up to alpha rows (cahel-main/src/rns_bconv.cu:
+// 562-623 for mod-up, :847-866 and :166-199 for mod-down), evaluated while loading.
+struct FwdIn {
+    const u64 *src;
+    const u64 *mat;
+    int n, logN;
+    u64 q, r0, r1;
+};
+
+LB_D u64 load_in(const FwdIn &in, const int idx)
+{
+    if (in.n == 0) return in.src[idx];
+    if (in.mat == nullptr) return barrett64(in.src[idx], in.q, in.r1);
+    u128d acc;
+    acc.lo = 0;
+    acc.hi = 0;
+    for (int i = 0; i < in.n; ++i) mac_wide(acc, in.src[((size_t)i << in.logN) + idx], __ldg(in.mat + i));
+    return barrett128(acc, in.q, in.r0, in.r1);
+}
+
+struct FwdEpi {
+    const u64 *aux; // nullptr: plain store
+    const u64 *add; // optional addend
+    u64 scal, scal_s;
+};
+
+template <int S>
+LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, const int logn_loc, const int logt,
+                   const unsigned cc, const ulonglong2 *tw, const u64 q, const u64 q2, const FwdEpi &epi)
+{
+    constexpr int R = 1 << S;
+    const int logst = logt - (S - 1);
+    const int groups = 1 << (logn_loc - S);
+    const int logm0 = logn_loc - 1 - logt;
+    for (int g = threadIdx.x; g < groups; g += kNttThreads) {
+        const int lo = g & ((1 << logst) - 1), hi = g >> logst;
+        const int base = (hi << (logt + 1)) + lo;
+        u64 v[R];
+        if (from_global) {
+#pragma unroll
+            for (int i = 0; i < R; ++i) v[i] = load_in(in, base + (i << logst));
+        } else {
+#pragma unroll
+            for (int i = 0; i < R; ++i) v[i] = sm[sidx(base + (i << logst))];
+        }
+        fwd_core<S>(v, tw, (cc << logm0) + hi, q, q2);
+        if (gdst) { // closing pass: logst == 0, the 2^S results are contiguous
+#pragma unroll
+            for (int i = 0; i < R; ++i) v[i] = csub(csub(v[i], q2), q);
+            if (epi.aux) {
+                u64 t[R];
+                load_contig<R>(t, epi.aux + base);
+#pragma unroll
+                for (int i = 0; i < R; ++i) v[i] = shoup_mul(sub_mod(t[i], v[i], q), epi.scal, epi.scal_s, q);
+                if (epi.add) {
+                    load_contig<R>(t, epi.add + base);
+#pragma unroll
+                    for (int i = 0; i < R; ++i) v[i] = add_mod(v[i], t[i], q);
+                }
+            }
+            store_contig<R>(v, gdst + base);
+        } else {
+#pragma unroll
+            for (int i = 0; i < R; ++i) sm[sidx(base + (i << logst))] = v[i];
+        }
+    }
+}
+
+template <int LOGC>
+__global__ void __launch_bounds__(kNttThreads, 3) ntt_fwd_kernel(const NttK a)
+{
+    extern __shared__ __align__(16) u64 sm[];
+    constexpr int C = 1 << LOGC;
+    const int row = blockIdx.x >> LOGC;
+    const int grp = row / a.per_group, rr = row - grp * a.per_group;
+    if (rr >= a.skip_lo && rr < a.skip_hi) return; // uniform over the cluster
+    int first_src = a.src_row_off, n_in = a.bconv_n;
+    if (a.digit_alpha > 0) {
+        const int s = grp * a.digit_alpha;
+        const int e = min(s + a.digit_alpha, a.size_l);
+        if (rr >= s && rr < e) return; // the digit's own limbs stay in NTT form
+        first_src += s;
+        n_in = e - s;
+    }
+    const int tbl = rr < a.size_l ? rr + a.tbl_off : a.size_Q + (rr - a.size_l);
+    const ModConst mc = a.mc[tbl];
+    const u64 q = mc.q, q2 = q << 1;
+    const int logN = a.logN, logn_loc = logN - LOGC, n_loc = 1 << logn_loc;
+    const ulonglong2 *tw = a.tw + ((size_t)tbl << logN);
+    FwdIn in;
+    in.n = n_in;
+    in.logN = logN;
+    in.q = q;
+    in.r0 = mc.r0;
+    in.r1 = mc.r1;
+    in.src = a.src + (((size_t)grp * a.src_group_stride + first_src + (n_in == 0 ? rr : 0)) << logN);
+    in.mat = a.bconv_mat ? a.bconv_mat + (size_t)grp * a.mat_group_stride + (size_t)rr * a.mat_row_stride : nullptr;
+    u64 *dst = a.dst + (((size_t)grp * a.dst_group_stride + rr) << logN);
+    FwdEpi epi;
+    epi.aux = a.aux ? a.aux + (((size_t)grp * a.aux_group_stride + rr) << logN) : nullptr;
+    epi.add = (a.add && grp < a.add_groups) ? a.add + (((size_t)grp * a.add_group_stride + rr) << logN) : nullptr;
+    epi.scal = a.aux ? a.scal[rr] : 0;
+    epi.scal_s = a.aux ? a.scal_s[rr] : 0;
+
+    unsigned c = 0;
+    if constexpr (LOGC > 0) {
+        cg::cluster_group cluster = cg::this_cluster();
+        c = cluster.block_rank();
+        cluster.sync(); // every CTA of the cluster is running before its shared memory is written
+        u64 *remote[C];
+#pragma unroll
+        for (int k = 0; k < C; ++k) remote[k] = cluster.map_shared_rank(sm, k);
+        const int share = n_loc >> LOGC;
+        for (int jj = threadIdx.x; jj < share; jj += kNttThreads) {
+            const int j = c * share + jj;
+            u64 v[C];
+#pragma unroll
+            for (int k = 0; k < C; ++k) v[k] = load_in(in, j + k * n_loc);
+            fwd_core<LOGC>(v, tw, 1u, q, q2);
+#pragma unroll
+            for (int k = 0; k < C; ++k) remote[k][sidx(j)] = v[k];
+        }
+        cluster.sync();
+        const size_t off = (size_t)c * n_loc;
+        if (epi.aux) epi.aux += off;
+        if (epi.add) epi.add += off;
+    }
+
+    int logt = logn_loc - 1;
+    const unsigned cc = C + c;
+    for (int p = 0; p < a.npass; ++p) {
+        const int S = a.S[p];
+        const bool from_global = (LOGC == 0 && p == 0);
+        u64 *gdst = (p == a.npass - 1) ? dst + (size_t)c * n_loc : nullptr;
+        if (S == 3) fwd_pass<3>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+        else if (S == 2) fwd_pass<2>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+        else fwd_pass<1>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+        logt -= S;
+        if (p + 1 < a.npass) __syncthreads();
+    }
+    if constexpr (LOGC > 0) cg::this_cluster().sync(); // nobody leaves while a peer may still write here
+}
+
+// ---- inverse --------------------------------------------------------------------------
+
+template <int S, bool CLOSE>
+LB_D void inv_pass(u64 *sm, const u64 *gsrc, u64 *gdst, const int logn_loc, const int logt, const unsigned cc,
+                   const ulonglong2 *itw, const u64 q, const u64 q2, const u64 cn, const u64 cns, const u64 cw,
+                   const u64 cws)
+{
+    constexpr int R = 1 << S;
+    const int logst = logt;
+    const int groups = 1 << (logn_loc - S);
+    const int logm0 = logn_loc - 1 - logt;
+    for (int g = threadIdx.x; g < groups; g += kNttThreads) {
+        const int lo = g & ((1 << logst) - 1), hi = g >> logst;
+        const int base = (hi << (logst + S)) + lo;
+        u64 v[R];
+        if (gsrc) { // opening pass: logst == 0, contiguous
+            load_contig<R>(v, gsrc + base);
+        } else {
+#pragma unroll
+            for (int i = 0; i < R; ++i) v[i] = sm[sidx(base + (i << logst))];
+        }
+        inv_core<S, CLOSE>(v, itw, (cc << logm0) + (hi << (S - 1)), q, q2, cn, cns, cw, cws);
+        if (gdst) {
+#pragma unroll
+            for (int i = 0; i < R; ++i) gdst[base + (i << logst)] = v[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < R; ++i) sm[sidx(base + (i << logst))] = v[i];
+        }
+    }
+}
+
+template <int LOGC>
+__global__ void __launch_bounds__(kNttThreads, 3) ntt_inv_kernel(const NttK a)
+{
+    extern __shared__ __align__(16) u64 sm[];
+    constexpr int C = 1 << LOGC;
+    const int row = blockIdx.x >> LOGC;
+    const int grp = row / a.per_group, rr = row - grp * a.per_group;
+    if (rr >= a.skip_lo && rr < a.skip_hi) return;
+    const int tbl = rr < a.size_l ? rr + a.tbl_off : a.size_Q + (rr - a.size_l);
+    const ModConst mc = a.mc[tbl];
+    const u64 q = mc.q, q2 = q << 1;
+    const int logN = a.logN, logn_loc = logN - LOGC, n_loc = 1 << logn_loc;
+    const ulonglong2 *itw = a.tw + ((size_t)tbl << logN);
+    const u64 *src = a.src + (((size_t)grp * a.src_group_stride + rr + a.src_row_off) << logN);
+    u64 *dst = a.dst + (((size_t)grp * a.dst_group_stride + rr) << logN);
+    u64 cn = mc.ninv, cns = mc.ninvs, cw = mc.iw1n, cws = mc.iw1ns;
+    if (a.fold) {
+        const u64 *f = a.fold + 4 * rr;
+        cn = f[0]; cns = f[1]; cw = f[2]; cws = f[3];
+    }
+    unsigned c = 0;
+    if constexpr (LOGC > 0) {
+        c = cg::this_cluster().block_rank();
+        cg::this_cluster().sync();
+    }
+    const unsigned cc = C + c;
+    int logt = 0;
+    for (int p = 0; p < a.npass; ++p) {
+        const int S = a.S[p];
+        const u64 *gsrc = (p == 0) ? src + (size_t)c * n_loc : nullptr;
+        const bool closing = (LOGC == 0 && p == a.npass - 1);
+        u64 *gdst = closing ? dst : nullptr;
+        if (p > 0) __syncthreads();
+        if (closing) {
+            if (S == 3) inv_pass<3, true>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
+            else if (S == 2) inv_pass<2, true>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
+            else inv_pass<1, true>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
+        } else {
+            if (S == 3) inv_pass<3, false>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
+            else if (S == 2) inv_pass<2, false>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
+            else inv_pass<1, false>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
+        }
+        logt += S;
+    }
+    if constexpr (LOGC > 0) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync(); // all local transforms of the cluster are in shared memory
+        const u64 *remote[C];
+#pragma unroll
+        for (int k = 0; k < C; ++k) remote[k] = cluster.map_shared_rank(sm, k);
+        const int share = n_loc >> LOGC;
+        for (int jj = threadIdx.x; jj < share; jj += kNttThreads) {
+            const int j = c * share + jj;
+            u64 v[C];
+#pragma unroll
+            for (int k = 0; k < C; ++k) v[k] = remote[k][sidx(j)];
+            inv_core<LOGC, true>(v, itw, C / 2, q, q2, cn, cns, cw, cws);
+#pragma unroll
+            for (int k = 0; k < C; ++k) dst[j + k * n_loc] = v[k];
+        }
+        cluster.sync(); // shared memory stays alive until every peer has read it
+    }
+}
+
+// ---- launchers ------------------------------------------------------------------------
+
+static int plan_passes(int logn_loc, bool forward, unsigned char *S)
+{
+    // Radix-8 wherever possible; the pass that touches global memory with contiguous
+    // per-thread data (forward: last, inverse: first) is kept at radix 8 when it fits.
+    int n = 0, rem = logn_loc;
+    int edge = rem >= 3 ? 3 : rem;
+    rem -= edge;
+    unsigned char mid[8];
+    int nm = 0;
+    while (rem > 0) {
+        if (rem == 4) { mid[nm++] = 2; mid[nm++] = 2; rem = 0; }
+        else if (rem >= 3) { mid[nm++] = 3; rem -= 3; }
+        else { mid[nm++] = (unsigned char)rem; rem = 0; }
+    }
+    if (forward) {
+        for (int i = 0; i < nm; ++i) S[n++] = mid[i];
+        S[n++] = (unsigned char)edge;
+    } else {
+        S[n++] = (unsigned char)edge;
+        for (int i = nm - 1; i >= 0; --i) S[n++] = mid[i];
+    }
+    return n;
+}
+
+template <int LOGC>
+static int launch(bool forward, const NttK &k, int rows, size_t smem, cudaStream_t stream)
+{
+    auto kern = forward ? ntt_fwd_kernel<LOGC> : ntt_inv_kernel<LOGC>;
+    static bool configured[2] = {false, false};
+    if (!configured[forward]) {
+        LB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem > 48 * 1024 ? 72 * 1024 : 48 * 1024));
+        configured[forward] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)rows << LOGC);
+    cfg.blockDim = dim3(kNttThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1 << LOGC;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    LB_CUDA(cudaLaunchKernelEx(&cfg, kern, k));
+    return LB_OK;
+}
+
+static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t stream)
+{
+    const HostParams &hp = ctx->hp;
+    const int rows = job.n_groups * job.per_group;
+    if (rows <= 0) return LB_OK;
+    NttK k;
+    k.src = job.src;
+    k.dst = job.dst;
+    k.tw = forward ? ctx->d_tw : ctx->d_itw;
+    k.mc = ctx->d_mc;
+    k.logN = hp.logN;
+    k.per_group = job.per_group;
+    k.size_l = job.size_l;
+    k.size_Q = hp.size_Q;
+    k.tbl_off = job.tbl_off;
+    k.src_group_stride = job.src_group_stride >= 0 ? job.src_group_stride : job.per_group;
+    k.dst_group_stride = job.dst_group_stride >= 0 ? job.dst_group_stride : job.per_group;
+    k.aux_group_stride = job.aux_group_stride >= 0 ? job.aux_group_stride : job.per_group;
+    k.add_group_stride = job.add_group_stride >= 0 ? job.add_group_stride : job.per_group;
+    k.src_row_off = job.src_row_off;
+    k.skip_lo = job.skip_lo;
+    k.skip_hi = job.skip_hi;
+    k.bconv_n = job.bconv_n;
+    k.digit_alpha = job.digit_alpha;
+    k.add_groups = job.add_groups;
+    k.bconv_mat = job.bconv_mat;
+    k.mat_group_stride = job.mat_group_stride;
+    k.mat_row_stride = job.mat_row_stride;
+    k.aux = job.aux;
+    k.scal = job.scal;
+    k.scal_s = job.scal_s;
+    k.add = job.add;
+    k.fold = job.fold;
+    const int logc = hp.logN > kMaxLocalLog ? hp.logN - kMaxLocalLog : 0;
+    const int logn_loc = hp.logN - logc;
+    k.npass = plan_passes(logn_loc, forward, k.S);
+    const size_t n_loc = size_t(1) << logn_loc;
+    const size_t smem = (n_loc + (n_loc >> 4) + 2) * sizeof(u64);
+    switch (logc) {
+    case 0: return launch<0>(forward, k, rows, smem, stream);
+    case 1: return launch<1>(forward, k, rows, smem, stream);
+    case 2: return launch<2>(forward, k, rows, smem, stream);
+    case 3: return launch<3>(forward, k, rows, smem, stream);
+    default: set_error("poly_modulus_degree above 65536 is not supported"); return LB_ERR_INVALID_ARG;
+    }
+}
+
+int ntt_forward(Context *ctx, const NttJob &job, cudaStream_t stream) { return run(ctx, job, true, stream); }
+int ntt_inverse(Context *ctx, const NttJob &job, cudaStream_t stream) { return run(ctx, job, false, stream); }
+
+} // namespace lb

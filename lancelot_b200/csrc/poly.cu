@@ -1,0 +1,242 @@
+// Element-wise RNS polynomial kernels: HBM-streaming integer work, two coefficients per
+// thread through 16-byte loads, grids sized in multiples of the SM count.
+// They replace the one-launch-per-polynomial kernels of cahel-main/src/polymath.cu:16-227
+// (add/sub/negate/multiply), :531-600 (2x2 tensor and square), cahel-main/src/galois.cu:20-29
+// (NTT-domain automorphism) and the per-chunk sub / square / add sequence of the Krum inner
+// loop (lancelot-main-GPU/utils/byzantine_fl.py:221-223).
+#include "context.h"
+
+namespace lb {
+
+constexpr int kPolyThreads = 256;
+
+static inline int grid_for(const Context *ctx, long work_items, int per_block)
+{
+    long need = (work_items + per_block - 1) / per_block;
+    long cap = (long)ctx->sm_count * 16;
+    if (need < 1) need = 1;
+    return (int)(need < cap ? need : cap);
+}
+
+// ---- add / sub / mul / neg --------------------------------------------------------------
+
+template <int OP>
+__global__ void __launch_bounds__(kPolyThreads) binary_kernel(const ulonglong2 *__restrict__ a, const ulonglong2 *__restrict__ b,
+                                                              ulonglong2 *__restrict__ out, const ModConst *__restrict__ mc,
+                                                              const int size_l, const int log_half_n, const long total)
+{
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const int row = (int)(i >> log_half_n);
+        const ModConst m = mc[row % size_l];
+        const ulonglong2 x = a[i];
+        ulonglong2 y = make_ulonglong2(0, 0), r;
+        if (OP != OP_NEG) y = b[i];
+        if (OP == OP_ADD) {
+            r.x = add_mod(x.x, y.x, m.q);
+            r.y = add_mod(x.y, y.y, m.q);
+        } else if (OP == OP_SUB) {
+            r.x = sub_mod(x.x, y.x, m.q);
+            r.y = sub_mod(x.y, y.y, m.q);
+        } else if (OP == OP_MUL) {
+            r.x = mul_mod(x.x, y.x, m.q, m.r0, m.r1);
+            r.y = mul_mod(x.y, y.y, m.q, m.r0, m.r1);
+        } else {
+            r.x = x.x ? m.q - x.x : 0;
+            r.y = x.y ? m.q - x.y : 0;
+        }
+        out[i] = r;
+    }
+}
+
+int poly_binary(Context *ctx, int op, int size_l, long rows, const u64 *a, const u64 *b, u64 *out, cudaStream_t stream)
+{
+    if (rows <= 0) return LB_OK;
+    const int log_half_n = ctx->hp.logN - 1;
+    const long total = rows << log_half_n;
+    const int grid = grid_for(ctx, total, kPolyThreads);
+    const ulonglong2 *pa = reinterpret_cast<const ulonglong2 *>(a), *pb = reinterpret_cast<const ulonglong2 *>(b);
+    ulonglong2 *po = reinterpret_cast<ulonglong2 *>(out);
+    switch (op) {
+    case OP_ADD: binary_kernel<OP_ADD><<<grid, kPolyThreads, 0, stream>>>(pa, pb, po, ctx->d_mc, size_l, log_half_n, total); break;
+    case OP_SUB: binary_kernel<OP_SUB><<<grid, kPolyThreads, 0, stream>>>(pa, pb, po, ctx->d_mc, size_l, log_half_n, total); break;
+    case OP_MUL: binary_kernel<OP_MUL><<<grid, kPolyThreads, 0, stream>>>(pa, pb, po, ctx->d_mc, size_l, log_half_n, total); break;
+    case OP_NEG: binary_kernel<OP_NEG><<<grid, kPolyThreads, 0, stream>>>(pa, pb, po, ctx->d_mc, size_l, log_half_n, total); break;
+    default: set_error("unknown element-wise operation"); return LB_ERR_INVALID_ARG;
+    }
+    LB_CUDA(cudaGetLastError());
+    return LB_OK;
+}
+
+// ---- tensor product ---------------------------------------------------------------------
+
+LB_D u64 tensor_mid(u64 a0, u64 b1, u64 a1, u64 b0, const ModConst &m)
+{
+    u128d acc = mul_wide(a0, b1);
+    mac_wide(acc, a1, b0);
+    return barrett128(acc, m.q, m.r0, m.r1);
+}
+
+__global__ void __launch_bounds__(kPolyThreads) tensor_kernel(const ulonglong2 *__restrict__ a, const ulonglong2 *__restrict__ b,
+                                                              ulonglong2 *__restrict__ out, const ModConst *__restrict__ mc,
+                                                              const int size_l, const int log_half_n, const long per_ct,
+                                                              const long total)
+{
+    // per_ct = size_l * N / 2 vector elements per polynomial
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long ct = i / per_ct, e = i - ct * per_ct;
+        const ModConst m = mc[(int)(e >> log_half_n)];
+        const ulonglong2 a0 = a[ct * 2 * per_ct + e], a1 = a[ct * 2 * per_ct + per_ct + e];
+        const ulonglong2 b0 = b[ct * 2 * per_ct + e], b1 = b[ct * 2 * per_ct + per_ct + e];
+        ulonglong2 d0, d1, d2;
+        d0.x = mul_mod(a0.x, b0.x, m.q, m.r0, m.r1);
+        d0.y = mul_mod(a0.y, b0.y, m.q, m.r0, m.r1);
+        d1.x = tensor_mid(a0.x, b1.x, a1.x, b0.x, m);
+        d1.y = tensor_mid(a0.y, b1.y, a1.y, b0.y, m);
+        d2.x = mul_mod(a1.x, b1.x, m.q, m.r0, m.r1);
+        d2.y = mul_mod(a1.y, b1.y, m.q, m.r0, m.r1);
+        out[ct * 3 * per_ct + e] = d0;
+        out[ct * 3 * per_ct + per_ct + e] = d1;
+        out[ct * 3 * per_ct + 2 * per_ct + e] = d2;
+    }
+}
+
+int poly_tensor(Context *ctx, int size_l, int batch, const u64 *a, const u64 *b, u64 *out, cudaStream_t stream)
+{
+    if (batch <= 0) return LB_OK;
+    const int log_half_n = ctx->hp.logN - 1;
+    const long per_ct = (long)size_l << log_half_n;
+    const long total = per_ct * batch;
+    tensor_kernel<<<grid_for(ctx, total, kPolyThreads), kPolyThreads, 0, stream>>>(
+        reinterpret_cast<const ulonglong2 *>(a), reinterpret_cast<const ulonglong2 *>(b), reinterpret_cast<ulonglong2 *>(out),
+        ctx->d_mc, size_l, log_half_n, per_ct, total);
+    LB_CUDA(cudaGetLastError());
+    return LB_OK;
+}
+
+// ---- Galois automorphism in NTT form ---------------------------------------------------
+
+__global__ void __launch_bounds__(kPolyThreads) galois_kernel(const u64 *__restrict__ src, u64 *__restrict__ dst,
+                                                              const uint32_t *__restrict__ perm, const int logN, const long total)
+{
+    const long n_mask = (1L << logN) - 1;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long row = i >> logN;
+        dst[i] = src[(row << logN) + perm[i & n_mask]];
+    }
+}
+
+int poly_galois(Context *ctx, int elt_idx, long rows, const u64 *src, u64 *dst, cudaStream_t stream)
+{
+    if (elt_idx < 0 || elt_idx >= (int)ctx->hp.galois_elts.size()) {
+        set_error("Galois key not present");
+        return LB_ERR_LOGIC;
+    }
+    const long total = rows << ctx->hp.logN;
+    galois_kernel<<<grid_for(ctx, total, kPolyThreads), kPolyThreads, 0, stream>>>(
+        src, dst, ctx->d_perm + ((size_t)elt_idx << ctx->hp.logN), ctx->hp.logN, total);
+    LB_CUDA(cudaGetLastError());
+    return LB_OK;
+}
+
+// ---- Krum inner loop: acc += sum_c (b_c - a_c)^2 as a size-3 ciphertext ---------------------
+
+// One thread owns two coefficients of one limb and walks all chunks with 128-bit lazy
+// accumulators (products of residues below 2^61 leave room for 64 terms between reductions).
+__global__ void __launch_bounds__(kPolyThreads) krum_accumulate_kernel(const ulonglong2 *__restrict__ a, const ulonglong2 *__restrict__ b,
+                                                                       ulonglong2 *__restrict__ acc, const ModConst *__restrict__ mc,
+                                                                       const int log_half_n, const long per_poly,
+                                                                       const long stride_a, const long stride_b,
+                                                                       const int n_chunks, const int accumulate)
+{
+    // per_poly = size_l * N / 2 vector elements; strides in vector elements between chunks
+    for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < per_poly; e += (long)gridDim.x * blockDim.x) {
+        const ModConst m = mc[(int)(e >> log_half_n)];
+        u64 r0x = 0, r0y = 0, r1x = 0, r1y = 0, r2x = 0, r2y = 0;
+        for (int c0 = 0; c0 < n_chunks; c0 += 64) {
+            const int c1 = min(c0 + 64, n_chunks);
+            u128d s0x = {0, 0}, s0y = {0, 0}, s1x = {0, 0}, s1y = {0, 0}, s2x = {0, 0}, s2y = {0, 0};
+#pragma unroll 2
+            for (int c = c0; c < c1; ++c) {
+                const ulonglong2 a0 = a[c * stride_a + e], a1 = a[c * stride_a + per_poly + e];
+                const ulonglong2 b0 = b[c * stride_b + e], b1 = b[c * stride_b + per_poly + e];
+                const u64 x0 = sub_mod(b0.x, a0.x, m.q), y0 = sub_mod(b0.y, a0.y, m.q);
+                const u64 x1 = sub_mod(b1.x, a1.x, m.q), y1 = sub_mod(b1.y, a1.y, m.q);
+                mac_wide(s0x, x0, x0);
+                mac_wide(s0y, y0, y0);
+                mac_wide(s1x, x0, x1);
+                mac_wide(s1y, y0, y1);
+                mac_wide(s2x, x1, x1);
+                mac_wide(s2y, y1, y1);
+            }
+            r0x = add_mod(r0x, barrett128(s0x, m.q, m.r0, m.r1), m.q);
+            r0y = add_mod(r0y, barrett128(s0y, m.q, m.r0, m.r1), m.q);
+            r1x = add_mod(r1x, barrett128(s1x, m.q, m.r0, m.r1), m.q);
+            r1y = add_mod(r1y, barrett128(s1y, m.q, m.r0, m.r1), m.q);
+            r2x = add_mod(r2x, barrett128(s2x, m.q, m.r0, m.r1), m.q);
+            r2y = add_mod(r2y, barrett128(s2y, m.q, m.r0, m.r1), m.q);
+        }
+        // middle term is 2 x0 x1
+        r1x = add_mod(r1x, r1x, m.q);
+        r1y = add_mod(r1y, r1y, m.q);
+        if (accumulate) {
+            const ulonglong2 o0 = acc[e], o1 = acc[per_poly + e], o2 = acc[2 * per_poly + e];
+            r0x = add_mod(r0x, o0.x, m.q); r0y = add_mod(r0y, o0.y, m.q);
+            r1x = add_mod(r1x, o1.x, m.q); r1y = add_mod(r1y, o1.y, m.q);
+            r2x = add_mod(r2x, o2.x, m.q); r2y = add_mod(r2y, o2.y, m.q);
+        }
+        acc[e] = make_ulonglong2(r0x, r0y);
+        acc[per_poly + e] = make_ulonglong2(r1x, r1y);
+        acc[2 * per_poly + e] = make_ulonglong2(r2x, r2y);
+    }
+}
+
+int krum_accumulate(Context *ctx, int size_l, int n_chunks, const u64 *a, const u64 *b, long chunk_stride_a,
+                    long chunk_stride_b, u64 *acc, int accumulate, cudaStream_t stream)
+{
+    const int log_half_n = ctx->hp.logN - 1;
+    const long per_poly = (long)size_l << log_half_n;
+    long blocks = (per_poly + kPolyThreads - 1) / kPolyThreads;
+    krum_accumulate_kernel<<<(int)blocks, kPolyThreads, 0, stream>>>(
+        reinterpret_cast<const ulonglong2 *>(a), reinterpret_cast<const ulonglong2 *>(b), reinterpret_cast<ulonglong2 *>(acc),
+        ctx->d_mc, log_half_n, per_poly, chunk_stride_a / 2, chunk_stride_b / 2, n_chunks, accumulate);
+    LB_CUDA(cudaGetLastError());
+    return LB_OK;
+}
+
+// ---- level drop and decryption ---------------------------------------------------------
+
+int poly_drop_last(Context *ctx, int size_l, int n_polys, const u64 *in, u64 *out, cudaStream_t stream)
+{
+    const size_t N = ctx->hp.N;
+    LB_CUDA(cudaMemcpy2DAsync(out, (size_t)(size_l - 1) * N * 8, in, (size_t)size_l * N * 8, (size_t)(size_l - 1) * N * 8,
+                              n_polys, cudaMemcpyDeviceToDevice, stream));
+    return LB_OK;
+}
+
+// cahel-main/src/secretkey.cu:594-631 without the noise-flooding term
+__global__ void __launch_bounds__(kPolyThreads) decrypt_kernel(const u64 *__restrict__ ct, const u64 *__restrict__ sk,
+                                                               u64 *__restrict__ pt, const ModConst *__restrict__ mc,
+                                                               const int logN, const int n_polys, const long per_poly)
+{
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < per_poly; i += (long)gridDim.x * blockDim.x) {
+        const ModConst m = mc[(int)(i >> logN)];
+        const u64 s = sk[i];
+        u64 sp = s, r = ct[i];
+        for (int p = 1; p < n_polys; ++p) {
+            r = add_mod(r, mul_mod(ct[p * per_poly + i], sp, m.q, m.r0, m.r1), m.q);
+            sp = mul_mod(sp, s, m.q, m.r0, m.r1);
+        }
+        pt[i] = r;
+    }
+}
+
+int poly_decrypt(Context *ctx, int size_l, int n_polys, const u64 *ct, const u64 *sk, u64 *pt, cudaStream_t stream)
+{
+    const long per_poly = (long)size_l << ctx->hp.logN;
+    decrypt_kernel<<<grid_for(ctx, per_poly, kPolyThreads), kPolyThreads, 0, stream>>>(ct, sk, pt, ctx->d_mc, ctx->hp.logN, n_polys,
+                                                                                       per_poly);
+    LB_CUDA(cudaGetLastError());
+    return LB_OK;
+}
+
+} // namespace lb

@@ -1,0 +1,61 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every symbol the header
+declares, and its host-only parameter helpers agree with the oracle."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "lancelot_b200.h")).read()
+    return sorted(set(re.findall(r"LB_API[^;(]*?\b(lb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from lancelot_b200 import lib
+
+    names = _declared_symbols()
+    assert len(names) >= 30
+    for name in names:
+        assert hasattr(lib, name), "missing export: " + name
+
+
+def test_prime_generation_matches_oracle():
+    from lancelot_b200 import cabi
+    from oracle import binding
+
+    for n, bits in [(1 << 13, [60, 40, 40, 60]), (1 << 15, [60, 40, 40, 60]), (1 << 16, [60] + [50] * 23 + [60] * 8),
+                    (1 << 12, [50, 40, 40, 40, 40, 40, 50, 50])]:
+        assert cabi.coeff_modulus_create(n, bits) == binding.coeff_modulus_create(n, bits)
+
+
+def test_roots_and_galois_elements_match_oracle():
+    from lancelot_b200 import cabi, lib
+    from oracle import binding
+
+    n = 1 << 12
+    mods = binding.coeff_modulus_create(n, [60, 40, 60])
+    for q in mods:
+        assert lib.lb_minimal_primitive_root(2 * n, q) == binding.lib.orc_minimal_primitive_root(2 * n, q)
+    steps = [0, 1, 2, 3, 15, 16, 1024, -1, -7]
+    assert cabi.galois_elts_from_steps(steps, n) == binding.elts_from_steps(steps, n)
+    with pytest.raises(ValueError):
+        cabi.galois_elts_from_steps([n // 2], n)
+
+
+def test_invalid_arguments_are_reported_not_crashed():
+    from lancelot_b200 import cabi, lib
+    from lancelot_b200._lib import InvalidArgument
+
+    with pytest.raises(InvalidArgument):
+        cabi.coeff_modulus_create(1000, [40])  # not a power of two
+    with pytest.raises(InvalidArgument):
+        cabi.coeff_modulus_create(1 << 12, [61])  # above the 60-bit limit of the reference
+    assert lib.lb_max_bit_count_tc128(65536) == 1777 and lib.lb_max_bit_count_tc128(8192) == 218
+    # a null context is refused by every compute entry point
+    assert lib.lb_ntt_forward(None, None, 1, 1, 0, None) == 1
+    assert b"context" in lib.lb_last_error()

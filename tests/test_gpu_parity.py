@@ -1,0 +1,203 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle: bit-exact on the
+same seeded inputs.  Needs a B200; run with -m gpu."""
+import numpy as np
+import pytest
+
+from gpu_util import rand_rows, row_moduli, seeds
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device; there is no CPU fallback")
+    return torch
+
+
+def make(logn, bits, size_p, steps=()):
+    from lancelot_b200 import cabi
+    from oracle import binding
+
+    n = 1 << logn
+    mods = binding.coeff_modulus_create(n, bits)
+    elts = binding.elts_from_steps(list(steps), n)
+    return binding.Oracle(logn, mods, size_p, elts), cabi.Context(logn, mods, size_p, elts), mods
+
+
+@pytest.mark.parametrize("logn", [4, 5, 7, 10, 12, 13, 14, 15, 16])
+def test_ntt_matches_oracle(torch_cuda, logn):
+    from lancelot_b200 import cabi
+
+    o, ctx, mods = make(logn, [60, 40, 50, 60], 1)
+    rng = np.random.default_rng(logn)
+    groups = 3 if logn <= 13 else 2
+    data = rand_rows(rng, row_moduli(mods, 3, 3, 1, groups), 1 << logn)
+    d = cabi.to_device(data)
+    ctx.ntt_forward(d, groups, 3, 1)
+    want = o.ntt_rows(data, groups, 3, 1)
+    got = cabi.to_host(d)
+    assert np.array_equal(got, want)
+    ctx.ntt_inverse(d, groups, 3, 1)
+    assert np.array_equal(cabi.to_host(d), data)
+    # inverse alone, from the oracle's forward output
+    d2 = cabi.to_device(want)
+    ctx.ntt_inverse(d2, groups, 3, 1)
+    assert np.array_equal(cabi.to_host(d2), data)
+
+
+def test_ntt_edge_values(torch_cuda):
+    """all-zero, all q-1 and a single one: the extremes of the lazy-reduction ranges"""
+    from lancelot_b200 import cabi
+
+    logn = 13
+    o, ctx, mods = make(logn, [60, 40, 60], 1)
+    n = 1 << logn
+    rows = []
+    for q in [mods[0], mods[1], mods[2]]:
+        rows += [np.zeros(n, np.uint64), np.full(n, q - 1, np.uint64)]
+    # layout: groups of (2 data + 1 special); build 2 groups: zeros and q-1
+    data = np.stack([np.zeros(n, np.uint64)] * 3 + [np.full(n, mods[0] - 1, np.uint64), np.full(n, mods[1] - 1, np.uint64),
+                                                    np.full(n, mods[2] - 1, np.uint64)])
+    d = cabi.to_device(data)
+    ctx.ntt_forward(d, 2, 2, 1)
+    assert np.array_equal(cabi.to_host(d), o.ntt_rows(data, 2, 2, 1))
+    ctx.ntt_inverse(d, 2, 2, 1)
+    assert np.array_equal(cabi.to_host(d), data)
+
+
+def test_ntt_special_limbs_only_and_empty(torch_cuda):
+    from lancelot_b200 import cabi
+
+    logn = 12
+    o, ctx, mods = make(logn, [50, 40, 40, 50, 50], 2)
+    rng = np.random.default_rng(5)
+    data = rand_rows(rng, row_moduli(mods, 3, 0, 2, 2), 1 << logn)
+    d = cabi.to_device(data)
+    ctx.ntt_forward(d, 2, 0, 2)
+    assert np.array_equal(cabi.to_host(d), o.ntt_rows(data, 2, 0, 2))
+    ctx.ntt_forward(d, 0, 0, 2)  # empty batch is a no-op
+    assert np.array_equal(cabi.to_host(d), o.ntt_rows(data, 2, 0, 2))
+
+
+@pytest.mark.parametrize("logn", [10, 13])
+def test_elementwise_and_tensor(torch_cuda, logn):
+    from lancelot_b200 import cabi
+
+    o, ctx, mods = make(logn, [60, 40, 40, 60], 1)
+    rng = np.random.default_rng(7)
+    n = 1 << logn
+    a = rand_rows(rng, row_moduli(mods, 3, 3, 0, 2), n)
+    b = rand_rows(rng, row_moduli(mods, 3, 3, 0, 2), n)
+    da, db = cabi.to_device(a), cabi.to_device(b)
+    assert np.array_equal(cabi.to_host(ctx.add(3, da, db)), o.poly_op("add", 3, a, b))
+    assert np.array_equal(cabi.to_host(ctx.sub(3, da, db)), o.poly_op("sub", 3, a, b))
+    assert np.array_equal(cabi.to_host(ctx.multiply_poly(3, da, db)), o.poly_op("mul", 3, a, b))
+    assert np.array_equal(cabi.to_host(ctx.negate(3, da)), o.poly_op("neg", 3, a))
+    assert np.array_equal(cabi.to_host(ctx.multiply(3, da, db)).reshape(3, 3, n), o.tensor(3, a.reshape(2, 3, n), b.reshape(2, 3, n)))
+    assert np.array_equal(cabi.to_host(ctx.square(3, da)).reshape(3, 3, n), o.square(3, a.reshape(2, 3, n)))
+    # in place
+    ctx.add(3, da, db, out=da)
+    assert np.array_equal(cabi.to_host(da), o.poly_op("add", 3, a, b))
+    # level drop
+    assert np.array_equal(cabi.to_host(ctx.mod_switch_drop(3, db)).reshape(2, 2, n), o.drop_last(3, b))
+
+
+def _keys(o, rng, n_elts):
+    sk = o.gen_sk(seeds(rng, 1))
+    dnum = o.size_Q // o.size_P
+    rlk = o.gen_ksk(sk, o.sk_square(sk), seeds(rng, 2 * dnum))
+    glk = [o.gen_ksk(sk, o.galois(i, sk), seeds(rng, 2 * dnum)) for i in range(n_elts)]
+    return sk, rlk, glk
+
+
+CASES = [
+    # logn, bits, size_P, levels to test
+    (10, [60, 40, 40, 60], 1, [3, 2]),
+    (13, [60, 40, 40, 60], 1, [3, 2]),
+    (11, [50, 40, 40, 40, 40, 40, 50, 50], 2, [6, 5, 3]),
+    (12, [50] + [40] * 8 + [50, 50, 50], 3, [9, 7]),
+    (14, [60, 40, 40, 60], 1, [3]),
+]
+
+
+@pytest.mark.parametrize("logn,bits,size_p,levels", CASES)
+def test_keyswitch_pieces_and_whole(torch_cuda, logn, bits, size_p, levels):
+    from lancelot_b200 import cabi
+
+    steps = [1, 2, 3]
+    o, ctx, mods = make(logn, bits, size_p, steps)
+    rng = np.random.default_rng(100 + logn)
+    n = 1 << logn
+    size_Q = len(bits) - size_p
+    sk, rlk, glk = _keys(o, rng, len(steps))
+    d_rlk = cabi.to_device(rlk)
+    d_glk = [cabi.to_device(g) for g in glk]
+    for L in levels:
+        cks = rand_rows(rng, row_moduli(mods, size_Q, L, 0), n)
+        dig = o.modup(L, cks)
+        got_dig = cabi.to_host(ctx.modup(L, cabi.to_device(cks)))
+        assert np.array_equal(got_dig, dig), "modup L=%d" % L
+        cx = o.inner_product(L, dig, rlk)
+        got_cx = cabi.to_host(ctx.inner_product(L, cabi.to_device(dig), d_rlk))
+        assert np.array_equal(got_cx, cx), "inner product L=%d" % L
+        md = o.moddown(L, cx[0])
+        assert np.array_equal(cabi.to_host(ctx.moddown(L, cabi.to_device(cx[0]))), md), "moddown L=%d" % L
+        ct = rand_rows(rng, row_moduli(mods, size_Q, L, 0, 2), n).reshape(2, L, n)
+        want = o.keyswitch(L, ct, cks, rlk)
+        got = cabi.to_host(ctx.keyswitch(L, cabi.to_device(ct), cabi.to_device(cks), d_rlk))
+        assert np.array_equal(got, want), "keyswitch L=%d" % L
+        ct3 = rand_rows(rng, row_moduli(mods, size_Q, L, 0, 3), n).reshape(3, L, n)
+        assert np.array_equal(cabi.to_host(ctx.relinearize(L, cabi.to_device(ct3), d_rlk)), o.relinearize(L, ct3, rlk))
+        if L >= 2:
+            assert np.array_equal(cabi.to_host(ctx.rescale(L, cabi.to_device(ct3))), o.rescale(L, ct3)), "rescale L=%d" % L
+        for e in range(2):
+            assert np.array_equal(cabi.to_host(ctx.galois_permute(e, cabi.to_device(ct))), o.galois(e, ct))
+            want = o.rotate(L, ct, e, glk[e])
+            got = cabi.to_host(ctx.rotate(L, cabi.to_device(ct), e, d_glk[e]))
+            assert np.array_equal(got, want), "rotate L=%d elt=%d" % (L, e)
+        want = o.hoisting(L, ct, [0, 1, 2], glk)
+        got = cabi.to_host(ctx.hoisting(L, cabi.to_device(ct), [0, 1, 2], d_glk))
+        assert np.array_equal(got, want), "hoisting L=%d" % L
+        # decryption of a size-2 and a size-3 ciphertext
+        d_sk = cabi.to_device(sk)
+        assert np.array_equal(cabi.to_host(ctx.decrypt(L, cabi.to_device(ct), d_sk)), o.decrypt(L, ct, sk))
+        assert np.array_equal(cabi.to_host(ctx.decrypt(L, cabi.to_device(ct3), d_sk)), o.decrypt(L, ct3, sk))
+
+
+@pytest.mark.parametrize("n_chunks", [1, 5, 70])
+def test_krum_accumulate(torch_cuda, n_chunks):
+    from lancelot_b200 import cabi
+
+    logn, L = 10, 3
+    o, ctx, mods = make(logn, [60, 40, 40, 60], 1)
+    rng = np.random.default_rng(n_chunks)
+    n = 1 << logn
+    a = rand_rows(rng, row_moduli(mods, 3, L, 0, 2 * n_chunks), n).reshape(n_chunks, 2, L, n)
+    b = rand_rows(rng, row_moduli(mods, 3, L, 0, 2 * n_chunks), n).reshape(n_chunks, 2, L, n)
+    want = np.zeros((3, L, n), dtype=np.uint64)
+    for c in range(n_chunks):
+        want = o.poly_op("add", L, want, o.square(L, o.poly_op("sub", L, b[c], a[c]).reshape(2, L, n)))
+    acc = ctx.empty(3, L, n)
+    ctx.krum_accumulate(L, cabi.to_device(a), cabi.to_device(b), acc, accumulate=False)
+    assert np.array_equal(cabi.to_host(acc), want)
+    # accumulate on top of a previous value
+    ctx.krum_accumulate(L, cabi.to_device(a), cabi.to_device(b), acc, accumulate=True)
+    assert np.array_equal(cabi.to_host(acc), o.poly_op("add", L, want, want))
+
+
+def test_error_reporting_on_gpu(torch_cuda):
+    from lancelot_b200 import cabi
+    from lancelot_b200._lib import InvalidArgument, LancelotError
+
+    o, ctx, mods = make(10, [60, 40, 40, 60], 1, [1])
+    n = 1 << 10
+    ct = ctx.empty(2, 3, n)
+    with pytest.raises(InvalidArgument):
+        ctx.rescale(1, ct)  # no next level
+    with pytest.raises(LancelotError):
+        ctx.galois_permute(5, ct)  # no such Galois key
+    with pytest.raises(InvalidArgument):
+        ctx.ntt_forward(ct, 1, 7, 0)  # more limbs than the context has
