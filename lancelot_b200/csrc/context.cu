@@ -13,6 +13,7 @@ const std::string &last_error() { return g_error; }
 int cuda_fail(cudaError_t e, const char *what)
 {
     g_error = std::string("CUDA error: ") + cudaGetErrorString(e) + " in " + what;
+    (void)cudaGetLastError(); // a rejected launch must not poison the next call's error check
     return LB_ERR_CUDA;
 }
 

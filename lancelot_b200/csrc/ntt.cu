@@ -404,7 +404,8 @@ static int launch(bool forward, const NttK &k, int rows, size_t smem, cudaStream
     auto kern = forward ? ntt_fwd_kernel<LOGC> : ntt_inv_kernel<LOGC>;
     static bool configured[2] = {false, false};
     if (!configured[forward]) {
-        LB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem > 48 * 1024 ? 72 * 1024 : 48 * 1024));
+        // largest request any ring degree makes: 8192 points plus one pad word per 16
+        LB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
         configured[forward] = true;
     }
     cudaLaunchConfig_t cfg = {};
