@@ -86,6 +86,8 @@ LB_API int lb_ntt_inverse(lb_context *ctx, uint64_t *data, int n_groups, int siz
 LB_API int lb_add(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream);
 LB_API int lb_sub(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream);
 LB_API int lb_multiply_poly(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream);
+/* element-wise product of two key-level polynomials [size_QP][N] (compute_secret_key_array, cahel-main/src/secretkey.cu:285-320) */
+LB_API int lb_multiply_poly_key_level(lb_context *ctx, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream);
 LB_API int lb_negate(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, uint64_t *out, void *stream);
 /* ckks_multiply / ckks_square (cahel-main/src/evaluate.cu:447,1433): batch of size-2 ciphertexts -> size-3 */
 LB_API int lb_multiply(lb_context *ctx, int size_l, int batch, const uint64_t *a, const uint64_t *b, uint64_t *out3, void *stream);
@@ -123,6 +125,38 @@ LB_API int lb_krum_accumulate(lb_context *ctx, int size_l, int n_chunks, const u
 /* ---- decryption (cahel-main/src/secretkey.cu:594-654 without the noise-flooding term) --------- */
 
 LB_API int lb_decrypt(lb_context *ctx, int size_l, int n_polys, const uint64_t *ct, const uint64_t *secret_key, uint64_t *pt, void *stream);
+
+/* ---- samplers and keys (cahel-main/src/prng.cu:143-242, secretkey.cu:254-515) -----------------
+ * The reference draws a fresh 64-byte seed from the operating system for every call
+ * (cahel-main/include/prng.cuh:12-23); here the caller supplies the seeds (HOST pointers),
+ * which is what makes results reproducible and comparable bit for bit. */
+
+LB_API int lb_sample_ternary(lb_context *ctx, const uint8_t *seed, int size_l, int size_p, uint64_t *out, void *stream);
+LB_API int lb_sample_error(lb_context *ctx, const uint8_t *seed, int size_l, int size_p, uint64_t *out, void *stream);
+LB_API int lb_sample_uniform(lb_context *ctx, const uint8_t *seed, int size_l, int size_p, uint64_t *out, void *stream);
+/* gen_secretkey (secretkey.cu:254): sk[size_QP][N] = NTT(ternary) */
+LB_API int lb_gen_secret_key(lb_context *ctx, const uint8_t *seed, uint64_t *sk, void *stream);
+/* gen_publickey (secretkey.cu:322,451): pk[2][size_QP][N] = (-(a s + e), a) */
+LB_API int lb_gen_public_key(lb_context *ctx, const uint64_t *sk, const uint8_t *seed_error, const uint8_t *seed_uniform, uint64_t *pk, void *stream);
+/* generate_one_kswitch_key (secretkey.cu:328): out[dnum][2][size_QP][N]; sk_target is s^2 for
+ * a relinearization key, the permuted secret for a Galois key; seeds[dnum][2][64] (error, uniform) */
+LB_API int lb_gen_switch_key(lb_context *ctx, const uint64_t *sk, const uint64_t *sk_target, const uint8_t *seeds, uint64_t *out, void *stream);
+/* encrypt_asymmetric (secretkey.cu:47-249) for a batch: ct[b][2][size_Q][N] = moddown(pk u + e) + (pt[b], 0).
+ * seeds[b][2][64] = (ternary seed, error seed); pt may be NULL (encryption of zero). */
+LB_API int lb_encrypt_asymmetric(lb_context *ctx, const uint64_t *pk, const uint64_t *pt, const uint8_t *seeds, int batch, uint64_t *ct, void *stream);
+
+/* ---- CKKS encoder (cahel-main/src/ckks.cu:104-209,292-465) ---------------------------------- */
+
+/* values: DEVICE array [batch][value_stride] of dtype 0 = double (real), 1 = float (real),
+ * 2 = complex double; the first n_values of each message are encoded into sparse_slots
+ * slots at `scale`; pt[batch][size_l][N] in NTT form.  Values that do not fit the modulus
+ * raise a device flag reported by lb_check_status (the reference throws invalid_argument). */
+LB_API int lb_encode(lb_context *ctx, int size_l, const void *values, int dtype, size_t value_stride, int n_values, int sparse_slots,
+              int batch, double scale, uint64_t *pt, void *stream);
+/* out_complex: DEVICE array of sparse_slots (re, im) pairs */
+LB_API int lb_decode(lb_context *ctx, int size_l, const uint64_t *pt, double scale, int sparse_slots, double *out_complex, void *stream);
+/* Synchronises the stream and reports (then clears) conditions kernels could only flag. */
+LB_API int lb_check_status(lb_context *ctx, void *stream);
 
 #ifdef __cplusplus
 }

@@ -120,6 +120,12 @@ class Context:
         check(lib.lb_multiply_poly(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(b), _p(out), _stream()))
         return out
 
+    def multiply_poly_qp(self, a, b):
+        """element-wise product over the key-level limb list Q || P (used for s^2)"""
+        out = torch.empty_like(a)
+        check(lib.lb_multiply_poly_key_level(self.h, _p(a), _p(b), _p(out), _stream()))
+        return out
+
     def negate(self, size_l, a, out=None):
         out = torch.empty_like(a) if out is None else out
         check(lib.lb_negate(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(out), _stream()))
@@ -201,3 +207,65 @@ class Context:
         pt = self.empty(size_l, self.N)
         check(lib.lb_decrypt(self.h, size_l, n_polys, _p(ct), _p(sk), _p(pt), _stream()))
         return pt
+
+    # -- samplers, keys, encryption (seeds are host bytes; 64 per seed)
+    @staticmethod
+    def _seed(seed, count=1):
+        s = np.ascontiguousarray(seed, dtype=np.uint8).reshape(-1)
+        assert s.size == 64 * count, "need %d seeds of 64 bytes" % count
+        return s, s.ctypes.data_as(C.POINTER(C.c_uint8))
+
+    def sample(self, kind, seed, size_l, size_p):
+        s, sp = self._seed(seed)
+        out = self.empty(size_l + size_p, self.N)
+        fn = {"ternary": lib.lb_sample_ternary, "error": lib.lb_sample_error, "uniform": lib.lb_sample_uniform}[kind]
+        check(fn(self.h, sp, size_l, size_p, _p(out), _stream()))
+        return out
+
+    def gen_secret_key(self, seed):
+        s, sp = self._seed(seed)
+        sk = self.empty(self.size_QP, self.N)
+        check(lib.lb_gen_secret_key(self.h, sp, _p(sk), _stream()))
+        return sk
+
+    def gen_public_key(self, sk, seed_error, seed_uniform):
+        se, pe = self._seed(seed_error)
+        su, pu = self._seed(seed_uniform)
+        pk = self.empty(2, self.size_QP, self.N)
+        check(lib.lb_gen_public_key(self.h, _p(sk), pe, pu, _p(pk), _stream()))
+        return pk
+
+    def gen_switch_key(self, sk, sk_target, seeds):
+        dnum = self.size_Q // self.size_P
+        s, sp = self._seed(seeds, 2 * dnum)
+        out = self.empty(dnum, 2, self.size_QP, self.N)
+        check(lib.lb_gen_switch_key(self.h, _p(sk), _p(sk_target), sp, _p(out), _stream()))
+        return out
+
+    def encrypt_asymmetric(self, pk, pt, seeds, batch=1):
+        s, sp = self._seed(seeds, 2 * batch)
+        ct = self.empty(batch, 2, self.size_Q, self.N) if batch > 1 else self.empty(2, self.size_Q, self.N)
+        check(lib.lb_encrypt_asymmetric(self.h, _p(pk), _p(pt), sp, batch, _p(ct), _stream()))
+        return ct
+
+    # -- encoder
+    def encode(self, size_l, values, scale, sparse_slots=None, batch=1, n_values=None, value_stride=None):
+        """values: CUDA tensor float64 / float32 (real) or complex128, shape [batch, n] or [n]."""
+        dt = {torch.float64: 0, torch.float32: 1, torch.complex128: 2}[values.dtype]
+        assert values.is_cuda and values.is_contiguous()
+        n = values.shape[-1] if n_values is None else n_values
+        stride = values.shape[-1] if value_stride is None else value_stride
+        if sparse_slots is None:
+            sparse_slots = 1 << max(1, int(np.ceil(np.log2(max(n, 2)))))
+        pt = self.empty(batch, size_l, self.N) if batch > 1 else self.empty(size_l, self.N)
+        check(lib.lb_encode(self.h, size_l, C.c_void_p(values.data_ptr()), dt, C.c_size_t(stride), n, sparse_slots, batch,
+                            C.c_double(scale), _p(pt), _stream()))
+        return pt
+
+    def decode(self, size_l, pt, scale, sparse_slots):
+        out = torch.empty(sparse_slots, dtype=torch.complex128, device=pt.device)
+        check(lib.lb_decode(self.h, size_l, _p(pt), C.c_double(scale), sparse_slots, C.c_void_p(out.data_ptr()), _stream()))
+        return out
+
+    def check_status(self):
+        check(lib.lb_check_status(self.h, _stream()))

@@ -180,6 +180,15 @@ int lb_sub(lb_context *h, int size_l, int n, const uint64_t *a, const uint64_t *
 int lb_multiply_poly(lb_context *h, int size_l, int n, const uint64_t *a, const uint64_t *b, uint64_t *out, void *s) { return binary(h, OP_MUL, size_l, n, a, b, out, s); }
 int lb_negate(lb_context *h, int size_l, int n, const uint64_t *a, uint64_t *out, void *s) { return binary(h, OP_NEG, size_l, n, a, nullptr, out, s); }
 
+int lb_multiply_poly_key_level(lb_context *h, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(a && b && out, "operand is null");
+    // at the key level the limb list is Q || P, which is also the table order
+    return poly_binary(C(h), OP_MUL, C(h)->hp.size_QP, C(h)->hp.size_QP, a, b, out, S(stream));
+}
+
 int lb_multiply(lb_context *h, int size_l, int batch, const uint64_t *a, const uint64_t *b, uint64_t *out3, void *stream)
 {
     int rc = bind(h);
@@ -310,6 +319,150 @@ int lb_decrypt(lb_context *h, int size_l, int n_polys, const uint64_t *ct, const
     if ((rc = level_ok(C(h), size_l))) return rc;
     REQUIRE(ct && sk && pt && n_polys >= 1, "operand is null");
     return poly_decrypt(C(h), size_l, n_polys, ct, sk, pt, S(stream));
+}
+
+// ---- samplers, keys, encryption ------------------------------------------------------------
+
+static int stage_seeds(Context *c, const uint8_t *host_seeds, int n_seeds, uint32_t **d_seeds, u64 **scratch, size_t scratch_words,
+                       cudaStream_t stream)
+{
+    // layout of the context scratch: [seeds][scratch_words]
+    const size_t seed_bytes = ((size_t)n_seeds * 64 + 255) / 256 * 256;
+    int rc = c->ensure_workspace(seed_bytes + scratch_words * 8);
+    if (rc) return rc;
+    *d_seeds = reinterpret_cast<uint32_t *>(c->ws);
+    if (scratch) *scratch = reinterpret_cast<u64 *>(reinterpret_cast<uint8_t *>(c->ws) + seed_bytes);
+    LB_CUDA(cudaMemcpyAsync(*d_seeds, host_seeds, (size_t)n_seeds * 64, cudaMemcpyHostToDevice, stream));
+    return LB_OK;
+}
+
+int lb_sample_ternary(lb_context *h, const uint8_t *seed, int size_l, int size_p, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(seed && out, "operand is null");
+    uint32_t *ds;
+    if ((rc = stage_seeds(C(h), seed, 1, &ds, nullptr, 0, S(stream)))) return rc;
+    return sample_small(C(h), 0, ds, 16, 1, size_l, size_p, out, S(stream));
+}
+
+int lb_sample_error(lb_context *h, const uint8_t *seed, int size_l, int size_p, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(seed && out, "operand is null");
+    uint32_t *ds;
+    if ((rc = stage_seeds(C(h), seed, 1, &ds, nullptr, 0, S(stream)))) return rc;
+    return sample_small(C(h), 1, ds, 16, 1, size_l, size_p, out, S(stream));
+}
+
+int lb_sample_uniform(lb_context *h, const uint8_t *seed, int size_l, int size_p, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(seed && out, "operand is null");
+    REQUIRE(C(h)->hp.logN >= 3, "ring degree too small");
+    uint32_t *ds;
+    if ((rc = stage_seeds(C(h), seed, 1, &ds, nullptr, 0, S(stream)))) return rc;
+    return sample_uniform(C(h), ds, 16, 1, size_l, size_p, out, S(stream));
+}
+
+int lb_gen_secret_key(lb_context *h, const uint8_t *seed, uint64_t *sk, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(seed && sk, "operand is null");
+    Context *c = C(h);
+    uint32_t *ds;
+    if ((rc = stage_seeds(c, seed, 1, &ds, nullptr, 0, S(stream)))) return rc;
+    if ((rc = sample_small(c, 0, ds, 16, 1, c->hp.size_Q, c->hp.size_P, sk, S(stream)))) return rc;
+    NttJob j;
+    j.src = sk;
+    j.dst = sk;
+    j.n_groups = 1;
+    j.per_group = c->hp.size_QP;
+    j.size_l = c->hp.size_Q;
+    return ntt_forward(c, j, S(stream));
+}
+
+int lb_gen_public_key(lb_context *h, const uint64_t *sk, const uint8_t *seed_error, const uint8_t *seed_uniform, uint64_t *pk, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(sk && seed_error && seed_uniform && pk, "operand is null");
+    Context *c = C(h);
+    uint8_t both[128];
+    memcpy(both, seed_error, 64);
+    memcpy(both + 64, seed_uniform, 64);
+    uint32_t *ds;
+    u64 *scratch;
+    if ((rc = stage_seeds(c, both, 2, &ds, &scratch, (size_t)c->hp.size_QP << c->hp.logN, S(stream)))) return rc;
+    // the staged copy must not be overwritten by `both` going out of scope: pageable copies complete before return
+    return gen_public_key(c, sk, ds, ds + 16, pk, scratch, S(stream));
+}
+
+int lb_gen_switch_key(lb_context *h, const uint64_t *sk, const uint64_t *sk_target, const uint8_t *seeds, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(sk && sk_target && seeds && out, "operand is null");
+    Context *c = C(h);
+    REQUIRE(c->hp.size_P >= 1 && c->hp.size_Q % c->hp.size_P == 0, "special_modulus_size must divide the number of data primes");
+    const int dnum = c->hp.size_Q / c->hp.size_P;
+    uint32_t *ds;
+    u64 *scratch;
+    if ((rc = stage_seeds(c, seeds, 2 * dnum, &ds, &scratch, (size_t)c->hp.size_QP << c->hp.logN, S(stream)))) return rc;
+    return gen_switch_key(c, sk, sk_target, ds, out, scratch, S(stream));
+}
+
+int lb_encrypt_asymmetric(lb_context *h, const uint64_t *pk, const uint64_t *pt, const uint8_t *seeds, int batch, uint64_t *ct, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(pk && seeds && ct && batch >= 0, "operand is null");
+    if (batch == 0) return LB_OK;
+    return encrypt_asymmetric(C(h), pk, pt, seeds, batch, ct, S(stream));
+}
+
+// ---- encoder ------------------------------------------------------------------------------
+
+int lb_encode(lb_context *h, int size_l, const void *values, int dtype, size_t value_stride, int n_values, int sparse_slots, int batch,
+              double scale, uint64_t *pt, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    if ((rc = level_ok(C(h), size_l))) return rc;
+    REQUIRE((values || n_values == 0) && pt && batch >= 0 && n_values >= 0, "values cannot be null");
+    REQUIRE(dtype >= 0 && dtype <= 2, "unknown value type");
+    return encode(C(h), size_l, values, dtype, (long)value_stride, n_values, sparse_slots, batch, scale, pt, C(h)->d_status, S(stream));
+}
+
+int lb_decode(lb_context *h, int size_l, const uint64_t *pt, double scale, int sparse_slots, double *out_complex, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    if ((rc = level_ok(C(h), size_l))) return rc;
+    REQUIRE(pt && out_complex, "destination cannot be null");
+    return decode(C(h), size_l, pt, scale, sparse_slots, out_complex, S(stream));
+}
+
+int lb_check_status(lb_context *h, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    int flags = 0;
+    LB_CUDA(cudaMemcpyAsync(&flags, C(h)->d_status, sizeof(int), cudaMemcpyDeviceToHost, S(stream)));
+    LB_CUDA(cudaStreamSynchronize(S(stream)));
+    if (flags) {
+        LB_CUDA(cudaMemsetAsync(C(h)->d_status, 0, sizeof(int), S(stream)));
+        if (flags & 1) {
+            set_error("encoded values are too large");
+            return LB_ERR_INVALID_ARG;
+        }
+        set_error("device-side status flag raised");
+        return LB_ERR_LOGIC;
+    }
+    return LB_OK;
 }
 
 } // extern "C"

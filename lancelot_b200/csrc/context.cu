@@ -157,6 +157,13 @@ int context_create(int logN, const std::vector<u64> &moduli, int size_P, const s
         }
         if ((rc = upload(ctx, &ctx->d_rot_group, group.data(), group.size()))) return fail(rc);
     }
+    {
+        e = cudaMalloc((void **)&ctx->d_status, 256);
+        if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMalloc"));
+        ctx->owned.push_back(ctx->d_status);
+        e = cudaMemset(ctx->d_status, 0, 256);
+        if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMemset"));
+    }
     *out = ctx;
     return LB_OK;
 }

@@ -35,6 +35,7 @@ struct Context {
     // encoder tables
     double2 *d_croots = nullptr; // [2N] complex roots of unity
     uint32_t *d_rot_group = nullptr; // [N/4] powers of 5 mod 2N
+    int *d_status = nullptr;         // sticky device-side condition flags (bit 0: encoded values are too large)
     // scratch owned by the context, grown on demand between operations
     void *ws = nullptr;
     size_t ws_bytes = 0;
@@ -80,6 +81,7 @@ struct NttJob {
     const u64 *add = nullptr; // optional addend rows, same shape as dst; only groups < add_groups have one
     long add_group_stride = -1;
     int add_groups = 0;
+    int add_every = 0; // > 0: group g has an addend iff g % add_every == 0, taken from addend group g / add_every
     // Inverse epilogue: closing constants per row replaced by fold[row][4]
     const u64 *fold = nullptr;
 };
@@ -116,5 +118,20 @@ int hoisting(Context *ctx, int size_l, u64 *ct, int n_steps, const int *elt_idx,
 int modup(Context *ctx, int size_l, const u64 *cks, u64 *digits, cudaStream_t stream);
 int inner_product(Context *ctx, int size_l, const u64 *digits, const u64 *cks, const u64 *evk, u64 *cx, cudaStream_t stream);
 int moddown(Context *ctx, int size_l, const u64 *cx, u64 *out, cudaStream_t stream);
+
+// samplers, key generation, encryption (sampler.cu).  d_seeds: device words, 16 per seed.
+int sample_small(Context *ctx, int kind, const uint32_t *d_seeds, int seed_stride, int batch, int size_l, int size_p, u64 *out,
+                 cudaStream_t stream);
+int sample_uniform(Context *ctx, const uint32_t *d_seeds, int seed_stride, int batch, int size_l, int size_p, u64 *out,
+                   cudaStream_t stream);
+int gen_public_key(Context *ctx, const u64 *sk, const uint32_t *d_seed_e, const uint32_t *d_seed_a, u64 *pk, u64 *scratch,
+                   cudaStream_t stream);
+int gen_switch_key(Context *ctx, const u64 *sk, const u64 *skp, const uint32_t *d_seeds, u64 *out, u64 *scratch, cudaStream_t stream);
+size_t encrypt_workspace_bytes(const Context *ctx, int batch);
+// encoder (encoder.cu)
+int encode(Context *ctx, int size_l, const void *values, int dtype, long value_stride, int n_values, int sparse_slots, int batch,
+           double scale, u64 *pt, int *d_status, cudaStream_t stream);
+int decode(Context *ctx, int size_l, const u64 *pt, double scale, int sparse_slots, double *out_complex, cudaStream_t stream);
+int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, const uint8_t *host_seeds, int batch, u64 *ct, cudaStream_t stream);
 
 } // namespace lb

@@ -37,7 +37,7 @@ struct NttK {
     int logN, per_group, size_l, size_Q, tbl_off;
     long src_group_stride, dst_group_stride, aux_group_stride, add_group_stride;
     int src_row_off, skip_lo, skip_hi;
-    int bconv_n, digit_alpha, add_groups;
+    int bconv_n, digit_alpha, add_groups, add_every;
     const u64 *bconv_mat;
     long mat_group_stride, mat_row_stride;
     const u64 *aux, *scal, *scal_s, *add, *fold;
@@ -233,7 +233,9 @@ __global__ void __launch_bounds__(kNttThreads, 3) ntt_fwd_kernel(const NttK a)
     u64 *dst = a.dst + (((size_t)grp * a.dst_group_stride + rr) << logN);
     FwdEpi epi;
     epi.aux = a.aux ? a.aux + (((size_t)grp * a.aux_group_stride + rr) << logN) : nullptr;
-    epi.add = (a.add && grp < a.add_groups) ? a.add + (((size_t)grp * a.add_group_stride + rr) << logN) : nullptr;
+    const bool has_add = a.add && (a.add_every > 0 ? (grp % a.add_every == 0) : (grp < a.add_groups));
+    const int add_grp = a.add_every > 0 ? grp / a.add_every : grp;
+    epi.add = has_add ? a.add + (((size_t)add_grp * a.add_group_stride + rr) << logN) : nullptr;
     epi.scal = a.aux ? a.scal[rr] : 0;
     epi.scal_s = a.aux ? a.scal_s[rr] : 0;
 
@@ -449,6 +451,7 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     k.bconv_n = job.bconv_n;
     k.digit_alpha = job.digit_alpha;
     k.add_groups = job.add_groups;
+    k.add_every = job.add_every;
     k.bconv_mat = job.bconv_mat;
     k.mat_group_stride = job.mat_group_stride;
     k.mat_row_stride = job.mat_row_stride;

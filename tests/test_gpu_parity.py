@@ -201,3 +201,94 @@ def test_error_reporting_on_gpu(torch_cuda):
         ctx.galois_permute(5, ct)  # no such Galois key
     with pytest.raises(InvalidArgument):
         ctx.ntt_forward(ct, 1, 7, 0)  # more limbs than the context has
+
+
+@pytest.mark.parametrize("logn,bits,size_p", [(8, [40, 40, 50], 1), (12, [60, 40, 40, 60], 1), (11, [50, 40, 40, 40, 50, 50], 2)])
+def test_samplers_and_keys(torch_cuda, logn, bits, size_p):
+    from lancelot_b200 import cabi
+
+    o, ctx, mods = make(logn, bits, size_p, [1, 2])
+    rng = np.random.default_rng(17 + logn)
+    size_Q = len(bits) - size_p
+    s = seeds(rng, 1)
+    for kind in ["ternary", "error"]:
+        assert np.array_equal(cabi.to_host(ctx.sample(kind, s, size_Q, size_p)), o.sample_small(kind, s, size_Q, size_p)), kind
+    assert np.array_equal(cabi.to_host(ctx.sample("uniform", s, size_Q, size_p)), o.sample_uniform(s, size_Q, size_p))
+    sk = o.gen_sk(s)
+    d_sk = ctx.gen_secret_key(s)
+    assert np.array_equal(cabi.to_host(d_sk), sk)
+    se, sa = seeds(rng, 1), seeds(rng, 1)
+    pk = o.gen_pk(sk, se, sa)
+    d_pk = ctx.gen_public_key(d_sk, se, sa)
+    assert np.array_equal(cabi.to_host(d_pk), pk)
+    dnum = size_Q // size_p
+    ss = seeds(rng, 2 * dnum)
+    sk2 = o.sk_square(sk)
+    assert np.array_equal(cabi.to_host(ctx.multiply_poly_qp(d_sk, d_sk)), sk2)
+    rlk = o.gen_ksk(sk, sk2, ss)
+    assert np.array_equal(cabi.to_host(ctx.gen_switch_key(d_sk, cabi.to_device(sk2), ss)), rlk)
+    skp = o.galois(1, sk)
+    assert np.array_equal(cabi.to_host(ctx.galois_permute(1, d_sk)), skp)
+    glk = o.gen_ksk(sk, skp, ss)
+    assert np.array_equal(cabi.to_host(ctx.gen_switch_key(d_sk, cabi.to_device(skp), ss)), glk)
+    # batched public-key encryption, with and without a plaintext
+    batch = 3
+    es = seeds(rng, 2 * batch)
+    n = 1 << logn
+    pts = rand_rows(rng, row_moduli(mods, size_Q, size_Q, 0, batch), n).reshape(batch, size_Q, n)
+    got = cabi.to_host(ctx.encrypt_asymmetric(d_pk, cabi.to_device(pts), es, batch)).reshape(batch, 2, size_Q, n)
+    got0 = cabi.to_host(ctx.encrypt_asymmetric(d_pk, None, es, batch)).reshape(batch, 2, size_Q, n)
+    for b in range(batch):
+        su, se_ = es[128 * b:128 * b + 64], es[128 * b + 64:128 * b + 128]
+        assert np.array_equal(got0[b], o.encrypt_zero_asym(pk, su, se_)), "encrypt zero %d" % b
+        assert np.array_equal(got[b], o.encrypt_asym(pk, pts[b], su, se_)), "encrypt %d" % b
+
+
+@pytest.mark.parametrize("logn,slots", [(5, 16), (10, 512), (12, 2048), (13, 4096), (14, 8192), (15, 16384), (16, 32768), (13, 64)])
+def test_encode_decode(torch_cuda, logn, slots):
+    import torch
+    from lancelot_b200 import cabi
+
+    o, ctx, mods = make(logn, [60, 40, 40, 60], 1)
+    rng = np.random.default_rng(logn * 100 + slots)
+    scale = 2.0 ** 40
+    batch = 2
+    vals = rng.uniform(-1, 1, (batch, slots))
+    vals[0, : min(8, slots)] = [0.0, -0.0, 1.0, -1.0, 0.5, -0.5, 1e-13, -1e-13][: min(8, slots)]
+    d = torch.from_numpy(vals).cuda()
+    pt = ctx.encode(3, d, scale, sparse_slots=slots, batch=batch)
+    ctx.check_status()
+    got = cabi.to_host(pt).reshape(batch, 3, 1 << logn)
+    for b in range(batch):
+        want = o.encode(3, vals[b], scale, sparse_slots=slots)
+        assert np.array_equal(got[b], want), "encode message %d" % b
+    # float32 input is widened exactly
+    v32 = vals.astype(np.float32)
+    pt32 = ctx.encode(3, torch.from_numpy(v32).cuda(), scale, sparse_slots=slots, batch=batch)
+    assert np.array_equal(cabi.to_host(pt32).reshape(batch, 3, -1)[1], o.encode(3, v32[1].astype(np.float64), scale, sparse_slots=slots))
+    # complex input and short messages (zero padded)
+    cv = (rng.uniform(-1, 1, slots) + 1j * rng.uniform(-1, 1, slots))[: max(1, slots - 3)]
+    ptc = ctx.encode(3, torch.from_numpy(cv).cuda(), scale, sparse_slots=slots)
+    assert np.array_equal(cabi.to_host(ptc), o.encode(3, cv, scale, sparse_slots=slots))
+    # decode: floating point, tolerance of the reference's own round-trip tests (1e-5, cahel-main/unittest/evaluator.cu)
+    dec = ctx.decode(3, pt[1].contiguous(), scale, slots).cpu().numpy()
+    assert np.abs(dec - vals[1]).max() < 1e-7
+    want = o.decode(3, got[1], scale, slots)
+    assert np.abs(dec - want).max() < 1e-9
+    # two-limb plaintext after a level drop decodes too
+    dec2 = ctx.decode(2, pt[1, :2].contiguous(), scale, slots).cpu().numpy()
+    assert np.abs(dec2 - vals[1]).max() < 1e-7
+
+
+def test_encode_rejects_values_that_do_not_fit(torch_cuda):
+    import torch
+    from lancelot_b200._lib import InvalidArgument
+
+    o, ctx, mods = make(10, [30, 30], 1)
+    big = torch.full((512,), 1e9, dtype=torch.float64, device="cuda")
+    ctx.encode(1, big, 2.0 ** 25, sparse_slots=512)
+    with pytest.raises(InvalidArgument):
+        ctx.check_status()
+    ctx.check_status()  # the flag is cleared once reported
+    with pytest.raises(InvalidArgument):
+        ctx.encode(1, big, 2.0 ** 40, sparse_slots=512)  # scale out of bounds
