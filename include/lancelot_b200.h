@@ -108,6 +108,17 @@ LB_API int lb_keyswitch(lb_context *ctx, int size_l, uint64_t *ct, const uint64_
 LB_API int lb_relinearize(lb_context *ctx, int size_l, uint64_t *ct3, const uint64_t *relin_key, void *stream);
 /* rescale_to_next (cahel-main/src/evaluate.cu:2059,2307; rns.cu:544): in [n_polys][size_l][N] -> out [n_polys][size_l-1][N] */
 LB_API int lb_rescale(lb_context *ctx, int size_l, int n_polys, const uint64_t *in, uint64_t *out, void *stream);
+/* No counterpart in the reference.  Same result as lb_rescale, for callers that must not
+ * allocate device memory while they run (work issued while a CUDA graph is being captured,
+ * serving processes with a fixed memory budget, hosts that own the device allocator):
+ * the scratch lives in a fixed 1.5 MiB array inside the library image instead of the
+ * context's growable workspace, so this call performs no cudaMalloc / cudaFree.
+ * Limits: n_polys * N <= lb_rescale_no_alloc_max_words() (196608), otherwise
+ * LB_ERR_INVALID_ARG.  The first call on a device looks up the array's address; make that
+ * call before any stream capture begins.  All calls on a device share the array, so
+ * calls that overlap on the GPU (different streams) race; calls on one stream do not. */
+LB_API int lb_rescale_no_alloc(lb_context *ctx, int size_l, int n_polys, const uint64_t *in, uint64_t *out, void *stream);
+LB_API size_t lb_rescale_no_alloc_max_words(void);
 /* apply_galois_inplace / rotate_vector for one Galois element that has a key (cahel-main/src/evaluate.cu:2364,2631) */
 LB_API int lb_rotate(lb_context *ctx, int size_l, uint64_t *ct, int elt_index, const uint64_t *galois_key, void *stream);
 /* hoisting_inplace (cahel-main/src/evaluate.cu:2412): ct <- sum over steps of rot(ct, step).

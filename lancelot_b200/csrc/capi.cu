@@ -285,6 +285,16 @@ int lb_rescale(lb_context *h, int size_l, int n_polys, const uint64_t *in, uint6
     return rescale(C(h), size_l, n_polys, in, out, S(stream));
 }
 
+int lb_rescale_no_alloc(lb_context *h, int size_l, int n_polys, const uint64_t *in, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(in && out, "operand is null");
+    return rescale_static(C(h), size_l, n_polys, in, out, S(stream));
+}
+
+size_t lb_rescale_no_alloc_max_words(void) { return rescale_static_max_words(); }
+
 int lb_rotate(lb_context *h, int size_l, uint64_t *ct, int elt, const uint64_t *glk, void *stream)
 {
     int rc = bind(h);

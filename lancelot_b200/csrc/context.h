@@ -112,6 +112,8 @@ int keyswitch(Context *ctx, int size_l, const u64 *cks, const u64 *evk, const u6
 int relinearize(Context *ctx, int size_l, u64 *ct3, const u64 *rlk, cudaStream_t stream);
 int rescale(Context *ctx, int size_l, int n_polys, const u64 *in, u64 *out, cudaStream_t stream);
 int rotate(Context *ctx, int size_l, u64 *ct, int elt_idx, const u64 *glk, cudaStream_t stream);
+int rescale_static(Context *ctx, int size_l, int n_polys, const u64 *in, u64 *out, cudaStream_t stream); // rescale_static.cu
+size_t rescale_static_max_words();
 int hoisting(Context *ctx, int size_l, u64 *ct, int n_steps, const int *elt_idx, const u64 *const *glks,
              cudaStream_t stream);
 // exposed pieces of the key switch for per-stage parity tests
