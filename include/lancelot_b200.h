@@ -108,6 +108,10 @@ LB_API int lb_keyswitch(lb_context *ctx, int size_l, uint64_t *ct, const uint64_
 LB_API int lb_relinearize(lb_context *ctx, int size_l, uint64_t *ct3, const uint64_t *relin_key, void *stream);
 /* rescale_to_next (cahel-main/src/evaluate.cu:2059,2307; rns.cu:544): in [n_polys][size_l][N] -> out [n_polys][size_l-1][N] */
 LB_API int lb_rescale(lb_context *ctx, int size_l, int n_polys, const uint64_t *in, uint64_t *out, void *stream);
+/* rescale of the first polys_per_ct polynomials of `batch` ciphertexts that sit ct_stride words apart
+ * (e.g. the two result polynomials of relinearized size-3 ciphertexts); out is dense [batch][polys_per_ct][size_l-1][N] */
+LB_API int lb_rescale_strided(lb_context *ctx, int size_l, int batch, int polys_per_ct, const uint64_t *in, size_t ct_stride,
+                       uint64_t *out, void *stream);
 /* No counterpart in the reference.  Same result as lb_rescale, for callers that must not
  * allocate device memory while they run (work issued while a CUDA graph is being captured,
  * serving processes with a fixed memory budget, hosts that own the device allocator):
@@ -125,6 +129,15 @@ LB_API int lb_rotate(lb_context *ctx, int size_l, uint64_t *ct, int elt_index, c
  * galois_keys: HOST array of n_steps device pointers, key of elt_indices[i] at [i]. */
 LB_API int lb_hoisting(lb_context *ctx, int size_l, uint64_t *ct, int n_steps, const int *elt_indices,
                 const uint64_t *const *galois_keys, void *stream);
+
+/* Batched forms: `batch` ciphertexts stored back to back ([batch][3][size_l][N] for
+ * relinearize, [batch][2][size_l][N] for rotate / hoisting), all switched with the same key.
+ * The reference has no batch axis (one ciphertext per call, cahel-main/include/evaluate.h);
+ * the Krum driver needs one to keep 190 independent pair results in flight. */
+LB_API int lb_relinearize_batch(lb_context *ctx, int size_l, int batch, uint64_t *ct3, const uint64_t *relin_key, void *stream);
+LB_API int lb_rotate_batch(lb_context *ctx, int size_l, int batch, uint64_t *ct, int elt_index, const uint64_t *galois_key, void *stream);
+LB_API int lb_hoisting_batch(lb_context *ctx, int size_l, int batch, uint64_t *ct, int n_steps, const int *elt_indices,
+                      const uint64_t *const *galois_keys, void *stream);
 
 /* ---- Krum pairwise distance inner loop (lancelot-main-GPU/utils/byzantine_fl.py:201-223) ------- */
 

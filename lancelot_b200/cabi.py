@@ -182,6 +182,11 @@ class Context:
         check(lib.lb_rescale(self.h, size_l, n_polys, _p(ct), _p(out), _stream()))
         return out
 
+    def rescale_strided(self, size_l, ct, batch, polys_per_ct, ct_stride):
+        out = self.empty(batch, polys_per_ct, size_l - 1, self.N)
+        check(lib.lb_rescale_strided(self.h, size_l, batch, polys_per_ct, _p(ct), C.c_size_t(ct_stride), _p(out), _stream()))
+        return out
+
     def rotate(self, size_l, ct, elt_index, glk):
         check(lib.lb_rotate(self.h, size_l, _p(ct), elt_index, _p(glk), _stream()))
         return ct
@@ -191,6 +196,25 @@ class Context:
         idx = (C.c_int * n)(*elt_indices)
         ptrs = (C.c_void_p * n)(*[g.data_ptr() for g in glks])
         check(lib.lb_hoisting(self.h, size_l, _p(ct), n, idx, ptrs, _stream()))
+        return ct
+
+    def relinearize_batch(self, size_l, ct3, rlk):
+        """ct3: [batch][3][size_l][N]; the first two polynomials of each hold the result"""
+        batch = ct3.numel() // (3 * size_l * self.N)
+        check(lib.lb_relinearize_batch(self.h, size_l, batch, _p(ct3), _p(rlk), _stream()))
+        return ct3
+
+    def rotate_batch(self, size_l, ct, elt_index, glk):
+        batch = ct.numel() // (2 * size_l * self.N)
+        check(lib.lb_rotate_batch(self.h, size_l, batch, _p(ct), elt_index, _p(glk), _stream()))
+        return ct
+
+    def hoisting_batch(self, size_l, ct, elt_indices, glks):
+        batch = ct.numel() // (2 * size_l * self.N)
+        n = len(elt_indices)
+        idx = (C.c_int * n)(*elt_indices)
+        ptrs = (C.c_void_p * n)(*[g.data_ptr() for g in glks])
+        check(lib.lb_hoisting_batch(self.h, size_l, batch, _p(ct), n, idx, ptrs, _stream()))
         return ct
 
     def krum_accumulate(self, size_l, a, b, acc, accumulate=False, n_chunks=None, stride_a=None, stride_b=None):

@@ -274,7 +274,16 @@ int lb_relinearize(lb_context *h, int size_l, uint64_t *ct3, const uint64_t *rlk
     int rc = bind(h);
     if (rc) return rc;
     REQUIRE(ct3 && rlk, "operand is null");
-    return relinearize(C(h), size_l, ct3, rlk, S(stream));
+    return relinearize(C(h), size_l, 1, ct3, rlk, S(stream));
+}
+
+int lb_relinearize_batch(lb_context *h, int size_l, int batch, uint64_t *ct3, const uint64_t *rlk, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(ct3 && rlk && batch >= 0, "operand is null");
+    if (batch == 0) return LB_OK;
+    return relinearize(C(h), size_l, batch, ct3, rlk, S(stream));
 }
 
 int lb_rescale(lb_context *h, int size_l, int n_polys, const uint64_t *in, uint64_t *out, void *stream)
@@ -282,7 +291,18 @@ int lb_rescale(lb_context *h, int size_l, int n_polys, const uint64_t *in, uint6
     int rc = bind(h);
     if (rc) return rc;
     REQUIRE(in && out && n_polys >= 1, "operand is null");
-    return rescale(C(h), size_l, n_polys, in, out, S(stream));
+    return rescale(C(h), size_l, n_polys, 1, in, size_l, out, S(stream));
+}
+
+int lb_rescale_strided(lb_context *h, int size_l, int batch, int polys_per_ct, const uint64_t *in, size_t ct_stride, uint64_t *out,
+                       void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(in && out && batch >= 0 && polys_per_ct >= 1, "operand is null");
+    REQUIRE(ct_stride % C(h)->hp.N == 0, "ciphertext stride must be a whole number of limbs");
+    if (batch == 0) return LB_OK;
+    return rescale(C(h), size_l, batch, polys_per_ct, in, (long)(ct_stride / C(h)->hp.N), out, S(stream));
 }
 
 int lb_rescale_no_alloc(lb_context *h, int size_l, int n_polys, const uint64_t *in, uint64_t *out, void *stream)
@@ -300,7 +320,16 @@ int lb_rotate(lb_context *h, int size_l, uint64_t *ct, int elt, const uint64_t *
     int rc = bind(h);
     if (rc) return rc;
     REQUIRE(ct && glk, "operand is null");
-    return rotate(C(h), size_l, ct, elt, glk, S(stream));
+    return rotate(C(h), size_l, 1, ct, elt, glk, S(stream));
+}
+
+int lb_rotate_batch(lb_context *h, int size_l, int batch, uint64_t *ct, int elt, const uint64_t *glk, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(ct && glk && batch >= 0, "operand is null");
+    if (batch == 0) return LB_OK;
+    return rotate(C(h), size_l, batch, ct, elt, glk, S(stream));
 }
 
 int lb_hoisting(lb_context *h, int size_l, uint64_t *ct, int n_steps, const int *elts, const uint64_t *const *keys, void *stream)
@@ -308,7 +337,17 @@ int lb_hoisting(lb_context *h, int size_l, uint64_t *ct, int n_steps, const int 
     int rc = bind(h);
     if (rc) return rc;
     REQUIRE(ct && elts && keys, "operand is null");
-    return hoisting(C(h), size_l, ct, n_steps, elts, keys, S(stream));
+    return hoisting(C(h), size_l, 1, ct, n_steps, elts, keys, S(stream));
+}
+
+int lb_hoisting_batch(lb_context *h, int size_l, int batch, uint64_t *ct, int n_steps, const int *elts, const uint64_t *const *keys,
+                      void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(ct && elts && keys && batch >= 0, "operand is null");
+    if (batch == 0) return LB_OK;
+    return hoisting(C(h), size_l, batch, ct, n_steps, elts, keys, S(stream));
 }
 
 int lb_krum_accumulate(lb_context *h, int size_l, int n_chunks, const uint64_t *a, const uint64_t *b, size_t sa, size_t sb,

@@ -56,33 +56,39 @@ int cuda_fail(cudaError_t e, const char *what);
 // ---- kernels (one launcher per step; all asynchronous on `stream`) ----------------------
 
 struct NttJob {
-    const u64 *src = nullptr; // rows of N residues
+    // Rows are limbs of N residues.  Row r belongs to group g = r / per_group at position
+    // rr = r % per_group; a group is further addressed as (outer, inner) = (g / split, g % split)
+    // so that batches of multi-polynomial ciphertexts map without copies:
+    //   row offset of a group in X = outer * X_outer + inner * X_group_stride      (X = src, dst, aux, add)
+    const u64 *src = nullptr;
     u64 *dst = nullptr;
-    int n_groups = 1;    // number of row groups
-    int per_group = 1;   // limb rows per group
+    int n_groups = 1;
+    int per_group = 1;
+    int split = 1;
     int size_l = 1;      // rows [0,size_l) use table tbl_off + row, the rest size_Q + (row - size_l)
     int tbl_off = 0;
-    long src_group_stride = -1, dst_group_stride = -1; // in rows; -1: per_group
+    long src_group_stride = -1, dst_group_stride = -1; // inner strides in rows; -1: per_group
+    long src_outer = -1, dst_outer = -1;               // outer strides in rows; -1: split * inner stride
     int src_row_off = 0;   // first source row inside a group
     int skip_lo = 0, skip_hi = 0; // rows [skip_lo, skip_hi) of each group are left untouched
     // Forward prologue (fast base conversion fused into the load): the transform input of
-    // row r is  sum_{i < bconv_n} src_row(i)[k] * mat[i]  mod q_r,  where src_row(i) is row
+    // row rr is  sum_{i < bconv_n} src_row(i)[k] * mat[i]  mod q_rr,  where src_row(i) is row
     // src_row_off + i of the group's source block.  mat == nullptr means all-ones with
-    // bconv_n == 1, i.e. "x mod q_r" of a single source row.
+    // bconv_n == 1, i.e. "x mod q_rr" of a single source row.
     int bconv_n = 0;
-    const u64 *bconv_mat = nullptr;     // entries of row r start at (grp * mat_group_stride + r * mat_row_stride)
+    const u64 *bconv_mat = nullptr;     // entries of row rr start at (digit * mat_group_stride + rr * mat_row_stride)
     long mat_group_stride = 0, mat_row_stride = 0;
-    int digit_alpha = 0; // > 0: mod-up mode. Group g converts digit g: source rows [g*alpha, min((g+1)*alpha, size_l)),
-                         // and the digit's own rows are skipped
-    // Forward epilogue: dst = (aux - NTT(x)) * scal[row] (+ add), the closing step of mod-down and rescale
+    int digit_alpha = 0; // > 0: mod-up mode.  inner = digit j of ciphertext `outer`: source rows
+                         // [j*alpha, min((j+1)*alpha, size_l)) of the outer block (the inner stride of
+                         // src is not used), and the digit's own rows are skipped
+    // Forward epilogue: dst = (aux - NTT(x)) * scal[rr] (+ add), the closing step of mod-down and rescale
     const u64 *aux = nullptr;
-    long aux_group_stride = -1;
+    long aux_group_stride = -1, aux_outer = -1;
     const u64 *scal = nullptr, *scal_s = nullptr;
-    const u64 *add = nullptr; // optional addend rows, same shape as dst; only groups < add_groups have one
-    long add_group_stride = -1;
-    int add_groups = 0;
-    int add_every = 0; // > 0: group g has an addend iff g % add_every == 0, taken from addend group g / add_every
-    // Inverse epilogue: closing constants per row replaced by fold[row][4]
+    const u64 *add = nullptr; // optional addend rows; only groups with inner < add_inner have one
+    long add_group_stride = -1, add_outer = -1;
+    int add_inner = 0;
+    // Inverse epilogue: closing constants per row replaced by fold[rr][4]
     const u64 *fold = nullptr;
 };
 
@@ -109,12 +115,12 @@ size_t keyswitch_workspace_bytes(const Context *ctx, int size_l);
 // ct[2][L][N]: out_i = (add_i ? add_i : 0) + moddown(<modup(cks), evk>)_i ; add0/add1 may alias out
 int keyswitch(Context *ctx, int size_l, const u64 *cks, const u64 *evk, const u64 *add0, const u64 *add1, u64 *out,
               cudaStream_t stream);
-int relinearize(Context *ctx, int size_l, u64 *ct3, const u64 *rlk, cudaStream_t stream);
-int rescale(Context *ctx, int size_l, int n_polys, const u64 *in, u64 *out, cudaStream_t stream);
-int rotate(Context *ctx, int size_l, u64 *ct, int elt_idx, const u64 *glk, cudaStream_t stream);
+int relinearize(Context *ctx, int size_l, int batch, u64 *ct3, const u64 *rlk, cudaStream_t stream);
+int rescale(Context *ctx, int size_l, int batch, int polys_per_ct, const u64 *in, long in_outer_rows, u64 *out, cudaStream_t stream);
+int rotate(Context *ctx, int size_l, int batch, u64 *ct, int elt_idx, const u64 *glk, cudaStream_t stream);
 int rescale_static(Context *ctx, int size_l, int n_polys, const u64 *in, u64 *out, cudaStream_t stream); // rescale_static.cu
 size_t rescale_static_max_words();
-int hoisting(Context *ctx, int size_l, u64 *ct, int n_steps, const int *elt_idx, const u64 *const *glks,
+int hoisting(Context *ctx, int size_l, int batch, u64 *ct, int n_steps, const int *elt_idx, const u64 *const *glks,
              cudaStream_t stream);
 // exposed pieces of the key switch for per-stage parity tests
 int modup(Context *ctx, int size_l, const u64 *cks, u64 *digits, cudaStream_t stream);

@@ -19,35 +19,46 @@
 namespace lb {
 
 constexpr int kKsThreads = 256;
-constexpr int kMaxSteps = 16;
+constexpr int kMaxSteps = 32;
 
 struct KsWs {
     u64 *coef, *digits, *cx, *pc, *tmp;
 };
 
-size_t keyswitch_workspace_bytes(const Context *ctx, int L)
+// rows of N words a key switch of `batch` ciphertexts needs:
+// coef[b][L] + digits[b][beta][LP] + cx[b][2][LP] + pc[b][2][P] + tmp[b][3][L]
+static size_t ks_rows(const Context *ctx, int L)
 {
     const HostParams &hp = ctx->hp;
-    const size_t N = hp.N, P = hp.size_P, LP = L + P;
-    const size_t beta = hp.level[L].beta;
-    // coef[L] + digits[beta][LP] + cx[2][LP] + pc[2][P] + tmp[3][L] rows
-    return (L + beta * LP + 2 * LP + 2 * P + 3 * (size_t)L) * N * sizeof(u64);
+    const size_t P = hp.size_P, LP = L + P, beta = hp.level[L].beta;
+    return L + beta * LP + 2 * LP + 2 * P + 3 * (size_t)L;
 }
 
-static int get_ws(Context *ctx, int L, KsWs &w)
+size_t keyswitch_workspace_bytes(const Context *ctx, int L) { return ks_rows(ctx, L) * ctx->hp.N * sizeof(u64); }
+
+static int get_ws(Context *ctx, int L, int batch, KsWs &w)
 {
     const HostParams &hp = ctx->hp;
-    const size_t N = hp.N, P = hp.size_P, LP = L + P;
+    const size_t N = hp.N, P = hp.size_P, LP = L + P, B = batch;
     const size_t beta = hp.level[L].beta;
-    int rc = ctx->ensure_workspace(keyswitch_workspace_bytes(ctx, L));
+    int rc = ctx->ensure_workspace(ks_rows(ctx, L) * N * sizeof(u64) * B);
     if (rc) return rc;
     u64 *p = reinterpret_cast<u64 *>(ctx->ws);
-    w.coef = p; p += L * N;
-    w.digits = p; p += beta * LP * N;
-    w.cx = p; p += 2 * LP * N;
-    w.pc = p; p += 2 * P * N;
+    w.coef = p; p += B * L * N;
+    w.digits = p; p += B * beta * LP * N;
+    w.cx = p; p += B * 2 * LP * N;
+    w.pc = p; p += B * 2 * P * N;
     w.tmp = p;
     return LB_OK;
+}
+
+// ciphertexts per pass so that the scratch stays below ~2 GiB
+static int sub_batch(const Context *ctx, int L, int batch)
+{
+    const size_t per = ks_rows(ctx, L) * ctx->hp.N * sizeof(u64);
+    size_t cap = (size_t(2) << 30) / per;
+    if (cap < 1) cap = 1;
+    return (size_t)batch < cap ? batch : (int)cap;
 }
 
 static int check_level(const Context *ctx, int L)
@@ -63,28 +74,33 @@ static int check_level(const Context *ctx, int L)
 }
 
 // ---- step 1+2: mod-up (cahel-main/src/rns_bconv.cu:668-792) -----------------------------
+// cks: polynomial b at row b * cks_stride
 
-static int modup_into(Context *ctx, int L, const u64 *cks, u64 *coef, u64 *digits, cudaStream_t stream)
+static int modup_into(Context *ctx, int L, int batch, const u64 *cks, long cks_stride, u64 *coef, u64 *digits, cudaStream_t stream)
 {
     const HostParams &hp = ctx->hp;
-    const int P = hp.size_P, LP = L + P, alpha = P;
+    const int P = hp.size_P, LP = L + P, alpha = P, beta = hp.level[L].beta;
     const DevLevel &dl = ctx->d_level[L];
     NttJob inv;
     inv.src = cks;
     inv.dst = coef;
-    inv.n_groups = 1;
+    inv.n_groups = batch;
     inv.per_group = L;
     inv.size_l = L;
+    inv.src_group_stride = cks_stride;
+    inv.dst_group_stride = L;
     inv.fold = alpha > 1 ? dl.fold : nullptr;
     int rc = ntt_inverse(ctx, inv, stream);
     if (rc) return rc;
     NttJob fwd;
     fwd.src = coef;
     fwd.dst = digits;
-    fwd.n_groups = hp.level[L].beta;
+    fwd.n_groups = batch * beta;
     fwd.per_group = LP;
+    fwd.split = beta;
     fwd.size_l = L;
-    fwd.src_group_stride = 0;
+    fwd.src_outer = L;
+    fwd.dst_group_stride = LP;
     fwd.digit_alpha = alpha;
     fwd.bconv_n = alpha;
     fwd.bconv_mat = alpha > 1 ? dl.hat_mod : nullptr;
@@ -103,19 +119,22 @@ struct IpArgs {
 };
 
 __global__ void __launch_bounds__(kKsThreads) inner_product_kernel(const u64 *__restrict__ digits, const u64 *__restrict__ own,
-                                                                   u64 *__restrict__ cx, const ModConst *__restrict__ mc,
-                                                                   const IpArgs args, const int logN, const int L, const int LP,
-                                                                   const int size_Q, const int size_QP, const int alpha,
-                                                                   const int beta)
+                                                                   const long own_stride, u64 *__restrict__ cx,
+                                                                   const ModConst *__restrict__ mc, const IpArgs args, const int logN,
+                                                                   const int L, const int LP, const int size_Q, const int size_QP,
+                                                                   const int alpha, const int beta, const long total)
 {
-    const long total = (long)LP << logN;
+    const long per_ct = (long)LP << logN;
     const long n_mask = (1L << logN) - 1;
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+        const long b = idx / per_ct, i = idx - b * per_ct;
         const int r = (int)(i >> logN);
         const long k = i & n_mask;
         const int tbl = r < L ? r : size_Q + (r - L);
         const ModConst m = mc[tbl];
         const int own_digit = r < L ? r / alpha : -1;
+        const u64 *dig_b = digits + b * beta * per_ct;
+        const u64 *own_b = own + ((b * own_stride) << logN);
         u128d a0 = {0, 0}, a1 = {0, 0};
         u64 r0 = 0, r1 = 0;
         int pending = 0;
@@ -123,7 +142,7 @@ __global__ void __launch_bounds__(kKsThreads) inner_product_kernel(const u64 *__
             const long kk = args.perm[s] ? (long)args.perm[s][k] : k;
             const u64 *key = args.evk[s];
             for (int j = 0; j < beta; ++j) {
-                const u64 d = (j == own_digit) ? own[((long)r << logN) + kk] : digits[(((long)j * LP + r) << logN) + kk];
+                const u64 d = (j == own_digit) ? own_b[((long)r << logN) + kk] : dig_b[(((long)j * LP + r) << logN) + kk];
                 const u64 *kb = key + ((((long)j * 2) * size_QP + tbl) << logN) + k;
                 mac_wide(a0, d, kb[0]);
                 mac_wide(a1, d, kb[(long)size_QP << logN]);
@@ -137,30 +156,35 @@ __global__ void __launch_bounds__(kKsThreads) inner_product_kernel(const u64 *__
         }
         r0 = add_mod(r0, barrett128(a0, m.q, m.r0, m.r1), m.q);
         r1 = add_mod(r1, barrett128(a1, m.q, m.r0, m.r1), m.q);
-        cx[i] = r0;
-        cx[total + i] = r1;
+        cx[2 * b * per_ct + i] = r0;
+        cx[(2 * b + 1) * per_ct + i] = r1;
     }
 }
 
-static int inner_product_steps(Context *ctx, int L, const u64 *digits, const u64 *own, const IpArgs &args, u64 *cx,
-                               cudaStream_t stream)
+static int inner_product_steps(Context *ctx, int L, int batch, const u64 *digits, const u64 *own, long own_stride, const IpArgs &args,
+                               u64 *cx, cudaStream_t stream)
 {
     const HostParams &hp = ctx->hp;
     const int LP = L + hp.size_P;
-    const long total = (long)LP << hp.logN;
+    const long total = ((long)LP << hp.logN) * batch;
     long blocks = (total + kKsThreads - 1) / kKsThreads;
     const long cap = (long)ctx->sm_count * 16;
     if (blocks > cap) blocks = cap;
-    inner_product_kernel<<<(int)blocks, kKsThreads, 0, stream>>>(digits, own, cx, ctx->d_mc, args, hp.logN, L, LP, hp.size_Q,
-                                                                 hp.size_QP, hp.size_P, hp.level[L].beta);
+    inner_product_kernel<<<(int)blocks, kKsThreads, 0, stream>>>(digits, own, own_stride, cx, ctx->d_mc, args, hp.logN, L, LP, hp.size_Q,
+                                                                 hp.size_QP, hp.size_P, hp.level[L].beta, total);
     LB_CUDA(cudaGetLastError());
     return LB_OK;
 }
 
 // ---- step 4+5: mod-down (cahel-main/src/rns_bconv.cu:965-1053, ntt_moddown.cu:244-252) -----
+// cx: [batch][ppc][LP][N]; polynomial (b, p) goes to out + (b * out_outer + p * out_inner) rows
 
-static int moddown_into(Context *ctx, int L, int n_polys, const u64 *cx, u64 *pc, u64 *out, const u64 *add, int add_groups,
-                        cudaStream_t stream)
+struct Placement {
+    long outer, inner; // row strides between ciphertexts and between the polynomials of one
+};
+
+static int moddown_into(Context *ctx, int L, int batch, int ppc, const u64 *cx, u64 *pc, u64 *out, Placement po, const u64 *add,
+                        Placement pa, int add_inner, cudaStream_t stream)
 {
     const HostParams &hp = ctx->hp;
     const int P = hp.size_P, LP = L + P;
@@ -168,7 +192,7 @@ static int moddown_into(Context *ctx, int L, int n_polys, const u64 *cx, u64 *pc
     NttJob inv;
     inv.src = cx;
     inv.dst = pc;
-    inv.n_groups = n_polys;
+    inv.n_groups = batch * ppc;
     inv.per_group = P;
     inv.size_l = 0; // every row is a special limb
     inv.src_group_stride = LP;
@@ -180,11 +204,13 @@ static int moddown_into(Context *ctx, int L, int n_polys, const u64 *cx, u64 *pc
     NttJob fwd;
     fwd.src = pc;
     fwd.dst = out;
-    fwd.n_groups = n_polys;
+    fwd.n_groups = batch * ppc;
     fwd.per_group = L;
+    fwd.split = ppc;
     fwd.size_l = L;
     fwd.src_group_stride = P;
-    fwd.dst_group_stride = L;
+    fwd.dst_group_stride = po.inner;
+    fwd.dst_outer = po.outer;
     fwd.bconv_n = P;
     fwd.bconv_mat = P > 1 ? dl.phat_mod : nullptr;
     fwd.mat_group_stride = 0;
@@ -194,8 +220,9 @@ static int moddown_into(Context *ctx, int L, int n_polys, const u64 *cx, u64 *pc
     fwd.scal = dl.p_inv;
     fwd.scal_s = dl.p_inv_s;
     fwd.add = add;
-    fwd.add_group_stride = L;
-    fwd.add_groups = add ? add_groups : 0;
+    fwd.add_group_stride = pa.inner;
+    fwd.add_outer = pa.outer;
+    fwd.add_inner = add ? add_inner : 0;
     return ntt_forward(ctx, fwd, stream);
 }
 
@@ -206,8 +233,8 @@ int modup(Context *ctx, int L, const u64 *cks, u64 *digits, cudaStream_t stream)
     int rc = check_level(ctx, L);
     if (rc) return rc;
     KsWs w;
-    if ((rc = get_ws(ctx, L, w))) return rc;
-    if ((rc = modup_into(ctx, L, cks, w.coef, digits, stream))) return rc;
+    if ((rc = get_ws(ctx, L, 1, w))) return rc;
+    if ((rc = modup_into(ctx, L, 1, cks, L, w.coef, digits, stream))) return rc;
     // materialise the digit's own limbs for callers that want the reference layout
     const HostParams &hp = ctx->hp;
     const int LP = L + hp.size_P, alpha = hp.size_P;
@@ -227,7 +254,7 @@ int inner_product(Context *ctx, int L, const u64 *digits, const u64 *cks, const 
     args.evk[0] = evk;
     args.perm[0] = nullptr;
     args.n_steps = 1;
-    return inner_product_steps(ctx, L, digits, cks, args, cx, stream);
+    return inner_product_steps(ctx, L, 1, digits, cks, L, args, cx, stream);
 }
 
 int moddown(Context *ctx, int L, const u64 *cx, u64 *out, cudaStream_t stream)
@@ -235,44 +262,61 @@ int moddown(Context *ctx, int L, const u64 *cx, u64 *out, cudaStream_t stream)
     int rc = check_level(ctx, L);
     if (rc) return rc;
     KsWs w;
-    if ((rc = get_ws(ctx, L, w))) return rc;
-    return moddown_into(ctx, L, 1, cx, w.pc, out, nullptr, 0, stream);
+    if ((rc = get_ws(ctx, L, 1, w))) return rc;
+    return moddown_into(ctx, L, 1, 1, cx, w.pc, out, Placement{L, L}, nullptr, Placement{0, 0}, 0, stream);
 }
 
-static int keyswitch_add(Context *ctx, int L, const u64 *cks, const u64 *evk, const u64 *add, int add_groups, u64 *out,
-                         cudaStream_t stream)
+// out(b, p) = (p < add_inner ? add(b, p) : 0) + moddown(<modup(cks_b), evk>)_p for a batch of ciphertexts
+static int keyswitch_batch(Context *ctx, int L, int batch, const u64 *cks, long cks_stride, const u64 *evk, const u64 *add,
+                           Placement pa, int add_inner, u64 *out, Placement po, cudaStream_t stream)
 {
-    int rc = check_level(ctx, L);
-    if (rc) return rc;
-    KsWs w;
-    if ((rc = get_ws(ctx, L, w))) return rc;
-    if ((rc = modup_into(ctx, L, cks, w.coef, w.digits, stream))) return rc;
-    IpArgs args = {};
-    args.evk[0] = evk;
-    args.n_steps = 1;
-    if ((rc = inner_product_steps(ctx, L, w.digits, cks, args, w.cx, stream))) return rc;
-    return moddown_into(ctx, L, 2, w.cx, w.pc, out, add, add_groups, stream);
+    const HostParams &hp = ctx->hp;
+    const int step = sub_batch(ctx, L, batch);
+    for (int b0 = 0; b0 < batch; b0 += step) {
+        const int nb = batch - b0 < step ? batch - b0 : step;
+        KsWs w;
+        int rc = get_ws(ctx, L, nb, w);
+        if (rc) return rc;
+        const u64 *cks_b = cks + ((size_t)b0 * cks_stride << hp.logN);
+        if ((rc = modup_into(ctx, L, nb, cks_b, cks_stride, w.coef, w.digits, stream))) return rc;
+        IpArgs args = {};
+        args.evk[0] = evk;
+        args.n_steps = 1;
+        if ((rc = inner_product_steps(ctx, L, nb, w.digits, cks_b, cks_stride, args, w.cx, stream))) return rc;
+        const u64 *add_b = add ? add + ((size_t)b0 * pa.outer << hp.logN) : nullptr;
+        u64 *out_b = out + ((size_t)b0 * po.outer << hp.logN);
+        if ((rc = moddown_into(ctx, L, nb, 2, w.cx, w.pc, out_b, po, add_b, pa, add_inner, stream))) return rc;
+    }
+    return LB_OK;
 }
 
 int keyswitch(Context *ctx, int L, const u64 *cks, const u64 *evk, const u64 *add0, const u64 *add1, u64 *out, cudaStream_t stream)
 {
+    int rc = check_level(ctx, L);
+    if (rc) return rc;
     const size_t poly = (size_t)L * ctx->hp.N;
     if (add0 && add1 && add1 != add0 + poly) { set_error("addends must be the two polynomials of one ciphertext"); return LB_ERR_INVALID_ARG; }
     if (!add0 && add1) { set_error("an addend for the second polynomial alone is not supported"); return LB_ERR_INVALID_ARG; }
-    return keyswitch_add(ctx, L, cks, evk, add0, add0 ? (add1 ? 2 : 1) : 0, out, stream);
+    return keyswitch_batch(ctx, L, 1, cks, L, evk, add0, Placement{2L * L, L}, add0 ? (add1 ? 2 : 1) : 0, out, Placement{2L * L, L}, stream);
 }
 
-// cahel-main/src/evaluate.cu:2019-2056
-int relinearize(Context *ctx, int L, u64 *ct3, const u64 *rlk, cudaStream_t stream)
+// cahel-main/src/evaluate.cu:2019-2056, for `batch` size-3 ciphertexts stored back to back
+int relinearize(Context *ctx, int L, int batch, u64 *ct3, const u64 *rlk, cudaStream_t stream)
 {
+    int rc = check_level(ctx, L);
+    if (rc) return rc;
     const size_t poly = (size_t)L * ctx->hp.N;
-    return keyswitch_add(ctx, L, ct3 + 2 * poly, rlk, ct3, 2, ct3, stream);
+    const Placement p3{3L * L, L};
+    return keyswitch_batch(ctx, L, batch, ct3 + 2 * poly, 3L * L, rlk, ct3, p3, 2, ct3, p3, stream);
 }
 
-// cahel-main/src/rns.cu:544-570 (floors): two launches for all polynomials
-int rescale(Context *ctx, int L, int n_polys, const u64 *in, u64 *out, cudaStream_t stream)
+// cahel-main/src/rns.cu:544-570 (floors): two launches for all polynomials.
+// Polynomial p of ciphertext b sits at row b * in_outer + p * L of `in`; the output is dense
+// [batch][ppc][L-1][N].
+int rescale(Context *ctx, int L, int batch, int ppc, const u64 *in, long in_outer, u64 *out, cudaStream_t stream)
 {
     if (L < 2 || L > ctx->hp.size_Q) { set_error("cannot rescale: no next level"); return LB_ERR_INVALID_ARG; }
+    const int n_polys = batch * ppc;
     int rc = ctx->ensure_workspace((size_t)n_polys * ctx->hp.N * 8);
     if (rc) return rc;
     u64 *last = reinterpret_cast<u64 *>(ctx->ws);
@@ -281,9 +325,11 @@ int rescale(Context *ctx, int L, int n_polys, const u64 *in, u64 *out, cudaStrea
     inv.dst = last;
     inv.n_groups = n_polys;
     inv.per_group = 1;
+    inv.split = ppc;
     inv.size_l = 1;
     inv.tbl_off = L - 1;
     inv.src_group_stride = L;
+    inv.src_outer = in_outer;
     inv.src_row_off = L - 1;
     inv.dst_group_stride = 1;
     if ((rc = ntt_inverse(ctx, inv, stream))) return rc;
@@ -293,50 +339,69 @@ int rescale(Context *ctx, int L, int n_polys, const u64 *in, u64 *out, cudaStrea
     fwd.dst = out;
     fwd.n_groups = n_polys;
     fwd.per_group = L - 1;
+    fwd.split = ppc;
     fwd.size_l = L - 1;
     fwd.src_group_stride = 1;
     fwd.dst_group_stride = L - 1;
     fwd.bconv_n = 1;
     fwd.aux = in;
     fwd.aux_group_stride = L;
+    fwd.aux_outer = in_outer;
     fwd.scal = dl.qlast_inv;
     fwd.scal_s = dl.qlast_inv_s;
     return ntt_forward(ctx, fwd, stream);
 }
 
-// cahel-main/src/evaluate.cu:2631-2686: permute both polynomials, then switch the permuted c1
-int rotate(Context *ctx, int L, u64 *ct, int elt_idx, const u64 *glk, cudaStream_t stream)
+// cahel-main/src/evaluate.cu:2631-2686 for a batch of size-2 ciphertexts stored back to back:
+// permute both polynomials, then switch the permuted c1
+int rotate(Context *ctx, int L, int batch, u64 *ct, int elt_idx, const u64 *glk, cudaStream_t stream)
 {
     int rc = check_level(ctx, L);
     if (rc) return rc;
-    KsWs w;
-    if ((rc = get_ws(ctx, L, w))) return rc;
-    if ((rc = poly_galois(ctx, elt_idx, 2L * L, ct, w.tmp, stream))) return rc;
-    const size_t poly = (size_t)L * ctx->hp.N;
-    return keyswitch_add(ctx, L, w.tmp + poly, glk, w.tmp, 1, ct, stream);
+    const HostParams &hp = ctx->hp;
+    const int step = sub_batch(ctx, L, batch);
+    const size_t poly = (size_t)L * hp.N;
+    const Placement p2{2L * L, L};
+    for (int b0 = 0; b0 < batch; b0 += step) {
+        const int nb = batch - b0 < step ? batch - b0 : step;
+        KsWs w;
+        if ((rc = get_ws(ctx, L, nb, w))) return rc;
+        u64 *ct_b = ct + 2 * poly * b0;
+        if ((rc = poly_galois(ctx, elt_idx, 2L * L * nb, ct_b, w.tmp, stream))) return rc;
+        if ((rc = modup_into(ctx, L, nb, w.tmp + poly, 2L * L, w.coef, w.digits, stream))) return rc;
+        IpArgs args = {};
+        args.evk[0] = glk;
+        args.n_steps = 1;
+        if ((rc = inner_product_steps(ctx, L, nb, w.digits, w.tmp + poly, 2L * L, args, w.cx, stream))) return rc;
+        if ((rc = moddown_into(ctx, L, nb, 2, w.cx, w.pc, ct_b, p2, w.tmp, p2, 1, stream))) return rc;
+    }
+    return LB_OK;
 }
 
-// sum over steps of the permuted c0 (cahel-main/src/evaluate.cu:2560-2568)
-__global__ void __launch_bounds__(kKsThreads) galois_sum_kernel(const u64 *__restrict__ src, u64 *__restrict__ dst,
+// sum over steps of the permuted c0 (cahel-main/src/evaluate.cu:2560-2568); c0 of ciphertext b at row b * ct_stride
+__global__ void __launch_bounds__(kKsThreads) galois_sum_kernel(const u64 *__restrict__ src, const long ct_stride, u64 *__restrict__ dst,
                                                                 const ModConst *__restrict__ mc, const IpArgs args, const int logN,
-                                                                const long total)
+                                                                const int L, const long total)
 {
     const long n_mask = (1L << logN) - 1;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
         const long row = i >> logN, k = i & n_mask;
-        const u64 q = mc[row].q;
+        const long b = row / L, r = row - b * L;
+        const u64 q = mc[r].q;
+        const u64 *s0 = src + ((b * ct_stride + r) << logN);
         u64 acc = 0;
-        for (int s = 0; s < args.n_steps; ++s) acc = add_mod(acc, src[(row << logN) + args.perm[s][k]], q);
+        for (int s = 0; s < args.n_steps; ++s) acc = add_mod(acc, s0[args.perm[s][k]], q);
         dst[i] = acc;
     }
 }
 
-// cahel-main/src/evaluate.cu:2412-2629: one mod-up, per step a permuted inner product, two mod-downs
-int hoisting(Context *ctx, int L, u64 *ct, int n_steps, const int *elt_idx, const u64 *const *glks, cudaStream_t stream)
+// cahel-main/src/evaluate.cu:2412-2629 for a batch of size-2 ciphertexts stored back to back:
+// one mod-up, per step a permuted inner product, two mod-downs
+int hoisting(Context *ctx, int L, int batch, u64 *ct, int n_steps, const int *elt_idx, const u64 *const *glks, cudaStream_t stream)
 {
     int rc = check_level(ctx, L);
     if (rc) return rc;
-    if (n_steps < 1 || n_steps > kMaxSteps) { set_error("hoisting supports 1 to 16 steps per call"); return LB_ERR_INVALID_ARG; }
+    if (n_steps < 1 || n_steps > kMaxSteps) { set_error("hoisting supports 1 to 32 steps per call"); return LB_ERR_INVALID_ARG; }
     const HostParams &hp = ctx->hp;
     IpArgs args = {};
     args.n_steps = n_steps;
@@ -345,16 +410,24 @@ int hoisting(Context *ctx, int L, u64 *ct, int n_steps, const int *elt_idx, cons
         args.evk[s] = glks[s];
         args.perm[s] = ctx->d_perm + ((size_t)elt_idx[s] << hp.logN);
     }
-    KsWs w;
-    if ((rc = get_ws(ctx, L, w))) return rc;
+    const int step = sub_batch(ctx, L, batch);
     const size_t poly = (size_t)L * hp.N;
-    if ((rc = modup_into(ctx, L, ct + poly, w.coef, w.digits, stream))) return rc;
-    if ((rc = inner_product_steps(ctx, L, w.digits, ct + poly, args, w.cx, stream))) return rc;
-    const long total = (long)L << hp.logN;
-    long blocks = (total + kKsThreads - 1) / kKsThreads;
-    galois_sum_kernel<<<(int)blocks, kKsThreads, 0, stream>>>(ct, w.tmp, ctx->d_mc, args, hp.logN, total);
-    LB_CUDA(cudaGetLastError());
-    return moddown_into(ctx, L, 2, w.cx, w.pc, ct, w.tmp, 1, stream);
+    for (int b0 = 0; b0 < batch; b0 += step) {
+        const int nb = batch - b0 < step ? batch - b0 : step;
+        KsWs w;
+        if ((rc = get_ws(ctx, L, nb, w))) return rc;
+        u64 *ct_b = ct + 2 * poly * b0;
+        if ((rc = modup_into(ctx, L, nb, ct_b + poly, 2L * L, w.coef, w.digits, stream))) return rc;
+        if ((rc = inner_product_steps(ctx, L, nb, w.digits, ct_b + poly, 2L * L, args, w.cx, stream))) return rc;
+        const long total = ((long)L << hp.logN) * nb;
+        long blocks = (total + kKsThreads - 1) / kKsThreads;
+        const long cap = (long)ctx->sm_count * 16;
+        if (blocks > cap) blocks = cap;
+        galois_sum_kernel<<<(int)blocks, kKsThreads, 0, stream>>>(ct_b, 2L * L, w.tmp, ctx->d_mc, args, hp.logN, L, total);
+        LB_CUDA(cudaGetLastError());
+        if ((rc = moddown_into(ctx, L, nb, 2, w.cx, w.pc, ct_b, Placement{2L * L, L}, w.tmp, Placement{L, L}, 1, stream))) return rc;
+    }
+    return LB_OK;
 }
 
 } // namespace lb

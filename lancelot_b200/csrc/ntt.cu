@@ -34,10 +34,11 @@ struct NttK {
     u64 *dst;
     const ulonglong2 *tw;
     const ModConst *mc;
-    int logN, per_group, size_l, size_Q, tbl_off;
+    int logN, per_group, split, size_l, size_Q, tbl_off;
     long src_group_stride, dst_group_stride, aux_group_stride, add_group_stride;
+    long src_outer, dst_outer, aux_outer, add_outer;
     int src_row_off, skip_lo, skip_hi;
-    int bconv_n, digit_alpha, add_groups, add_every;
+    int bconv_n, digit_alpha, add_inner;
     const u64 *bconv_mat;
     long mat_group_stride, mat_row_stride;
     const u64 *aux, *scal, *scal_s, *add, *fold;
@@ -209,14 +210,22 @@ __global__ void __launch_bounds__(kNttThreads, 3) ntt_fwd_kernel(const NttK a)
     const int row = blockIdx.x >> LOGC;
     const int grp = row / a.per_group, rr = row - grp * a.per_group;
     if (rr >= a.skip_lo && rr < a.skip_hi) return; // uniform over the cluster
-    int first_src = a.src_row_off, n_in = a.bconv_n;
+    const int go = grp / a.split, gi = grp - go * a.split;
+    int n_in = a.bconv_n;
+    size_t src_row = (size_t)go * a.src_outer + a.src_row_off;
+    const u64 *mat = a.bconv_mat;
     if (a.digit_alpha > 0) {
-        const int s = grp * a.digit_alpha;
+        const int s = gi * a.digit_alpha;
         const int e = min(s + a.digit_alpha, a.size_l);
         if (rr >= s && rr < e) return; // the digit's own limbs stay in NTT form
-        first_src += s;
+        src_row += s;
         n_in = e - s;
+        if (mat) mat += (size_t)gi * a.mat_group_stride;
+    } else {
+        src_row += (size_t)gi * a.src_group_stride;
     }
+    if (n_in == 0) src_row += rr;
+    if (mat) mat += (size_t)rr * a.mat_row_stride;
     const int tbl = rr < a.size_l ? rr + a.tbl_off : a.size_Q + (rr - a.size_l);
     const ModConst mc = a.mc[tbl];
     const u64 q = mc.q, q2 = q << 1;
@@ -228,14 +237,12 @@ __global__ void __launch_bounds__(kNttThreads, 3) ntt_fwd_kernel(const NttK a)
     in.q = q;
     in.r0 = mc.r0;
     in.r1 = mc.r1;
-    in.src = a.src + (((size_t)grp * a.src_group_stride + first_src + (n_in == 0 ? rr : 0)) << logN);
-    in.mat = a.bconv_mat ? a.bconv_mat + (size_t)grp * a.mat_group_stride + (size_t)rr * a.mat_row_stride : nullptr;
-    u64 *dst = a.dst + (((size_t)grp * a.dst_group_stride + rr) << logN);
+    in.src = a.src + (src_row << logN);
+    in.mat = mat;
+    u64 *dst = a.dst + (((size_t)go * a.dst_outer + (size_t)gi * a.dst_group_stride + rr) << logN);
     FwdEpi epi;
-    epi.aux = a.aux ? a.aux + (((size_t)grp * a.aux_group_stride + rr) << logN) : nullptr;
-    const bool has_add = a.add && (a.add_every > 0 ? (grp % a.add_every == 0) : (grp < a.add_groups));
-    const int add_grp = a.add_every > 0 ? grp / a.add_every : grp;
-    epi.add = has_add ? a.add + (((size_t)add_grp * a.add_group_stride + rr) << logN) : nullptr;
+    epi.aux = a.aux ? a.aux + (((size_t)go * a.aux_outer + (size_t)gi * a.aux_group_stride + rr) << logN) : nullptr;
+    epi.add = (a.add && gi < a.add_inner) ? a.add + (((size_t)go * a.add_outer + (size_t)gi * a.add_group_stride + rr) << logN) : nullptr;
     epi.scal = a.aux ? a.scal[rr] : 0;
     epi.scal_s = a.aux ? a.scal_s[rr] : 0;
 
@@ -323,8 +330,9 @@ __global__ void __launch_bounds__(kNttThreads, 3) ntt_inv_kernel(const NttK a)
     const u64 q = mc.q, q2 = q << 1;
     const int logN = a.logN, logn_loc = logN - LOGC, n_loc = 1 << logn_loc;
     const ulonglong2 *itw = a.tw + ((size_t)tbl << logN);
-    const u64 *src = a.src + (((size_t)grp * a.src_group_stride + rr + a.src_row_off) << logN);
-    u64 *dst = a.dst + (((size_t)grp * a.dst_group_stride + rr) << logN);
+    const int go = grp / a.split, gi = grp - go * a.split;
+    const u64 *src = a.src + (((size_t)go * a.src_outer + (size_t)gi * a.src_group_stride + rr + a.src_row_off) << logN);
+    u64 *dst = a.dst + (((size_t)go * a.dst_outer + (size_t)gi * a.dst_group_stride + rr) << logN);
     u64 cn = mc.ninv, cns = mc.ninvs, cw = mc.iw1n, cws = mc.iw1ns;
     if (a.fold) {
         const u64 *f = a.fold + 4 * rr;
@@ -441,17 +449,21 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     k.size_l = job.size_l;
     k.size_Q = hp.size_Q;
     k.tbl_off = job.tbl_off;
+    k.split = job.split > 0 ? job.split : 1;
     k.src_group_stride = job.src_group_stride >= 0 ? job.src_group_stride : job.per_group;
     k.dst_group_stride = job.dst_group_stride >= 0 ? job.dst_group_stride : job.per_group;
     k.aux_group_stride = job.aux_group_stride >= 0 ? job.aux_group_stride : job.per_group;
     k.add_group_stride = job.add_group_stride >= 0 ? job.add_group_stride : job.per_group;
+    k.src_outer = job.src_outer >= 0 ? job.src_outer : k.split * k.src_group_stride;
+    k.dst_outer = job.dst_outer >= 0 ? job.dst_outer : k.split * k.dst_group_stride;
+    k.aux_outer = job.aux_outer >= 0 ? job.aux_outer : k.split * k.aux_group_stride;
+    k.add_outer = job.add_outer >= 0 ? job.add_outer : k.split * k.add_group_stride;
     k.src_row_off = job.src_row_off;
     k.skip_lo = job.skip_lo;
     k.skip_hi = job.skip_hi;
     k.bconv_n = job.bconv_n;
     k.digit_alpha = job.digit_alpha;
-    k.add_groups = job.add_groups;
-    k.add_every = job.add_every;
+    k.add_inner = job.add_inner;
     k.bconv_mat = job.bconv_mat;
     k.mat_group_stride = job.mat_group_stride;
     k.mat_row_stride = job.mat_row_stride;

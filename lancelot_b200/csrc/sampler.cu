@@ -283,9 +283,11 @@ int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, const uint8_t
     fwd.aux_group_stride = QP;
     fwd.scal = dl.p_inv;
     fwd.scal_s = dl.p_inv_s;
+    fwd.split = 2;
     fwd.add = pt;
-    fwd.add_group_stride = Q;
-    fwd.add_every = pt ? 2 : 0;
+    fwd.add_group_stride = 0;
+    fwd.add_outer = Q;
+    fwd.add_inner = pt ? 1 : 0;
     return ntt_forward(ctx, fwd, stream);
 }
 

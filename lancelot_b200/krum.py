@@ -1,0 +1,376 @@
+"""Encrypted Krum: the pairwise-distance driver of Lancelot on the B200 path.
+
+Two layers:
+
+* ``GPU_init`` ... ``GPU_krum``: the same functions, argument lists and call sequence as
+  ``lancelot-main-GPU/utils/byzantine_fl.py:173-525``, written against
+  ``lancelot_b200.pycahel`` so the reference's driver can be pointed at this module unchanged.
+* ``EncryptedKrum``: the batched driver.  It keeps context and keys across rounds, encodes and
+  encrypts every client ONCE (the reference re-encrypts both clients for every pair,
+  byzantine_fl.py:201-212), runs one fused accumulate kernel per pair, then relinearizes,
+  rescales and rotate-sums all pairs of a rank as one batch, and shards pairs over ranks.
+
+Per pair the arithmetic is the reference's (byzantine_fl.py:221-273):
+    acc = sum over chunks of (ct_j - ct_i)^2            (size 3, scale 2^80, level 1)
+    relinearize, rescale to level 2, scale := 2^40
+    acc += hoisting(acc, [1..15]); then acc += rot(acc, 2^k) for k = 4 .. log2(slots) - 1
+so every slot of the result holds the squared distance.  The reference starts ``acc`` from
+square(Enc(0)) instead of zero, which only adds encryption noise; ``EncryptedKrum`` starts
+from zero, the compatibility layer keeps the reference's start.
+"""
+import math
+import os
+import time
+
+import numpy as np
+import torch
+
+from . import pycahel as cahel
+
+# module constants of the reference driver (byzantine_fl.py:23-34)
+lazy_relin_flag = 1
+Hoisting_flag = 1
+Nslot = 32768
+log_Nslot = 15
+
+
+def set_slots(log_slots):
+    """The reference hard-codes 32768 slots; other ring degrees need these two changed together."""
+    global Nslot, log_Nslot
+    log_Nslot = int(log_slots)
+    Nslot = 1 << log_Nslot
+
+
+# ---------------------------------------------------------------------------------------------
+# compatibility layer: byzantine_fl.py:173-525 against pycahel
+# ---------------------------------------------------------------------------------------------
+
+def GPU_init():
+    """byzantine_fl.py:432-463"""
+    log_n = log_Nslot + 1
+    n = 2 ** log_n
+    modulus_chain = [60, 40, 40, 60]
+    galois_steps = [i for i in range(1, 16) if i < Nslot]
+    galois_steps += [2 ** i for i in range(4, log_n - 1)]
+    scale = 2.0 ** 40
+    params = cahel.params(cahel.scheme_type.ckks)
+    params.set_poly_modulus_degree(n)
+    params.set_coeff_modulus(cahel.coeff_modulus_create(n, modulus_chain))
+    params.set_special_modulus_size(1)
+    params.set_galois_elts(cahel.get_elts_from_steps(galois_steps, n))
+    sec = cahel.sec_level_type.tc128 if n >= 8192 else cahel.sec_level_type.none
+    context = cahel.context(params, True, sec)
+    sk = cahel.secret_key(params)
+    sk.gen_secretkey(context)
+    pk = cahel.public_key(context)
+    sk.gen_publickey(context, pk)
+    rlk = cahel.relin_key(context)
+    sk.gen_relinkey(context, rlk)
+    glk = cahel.galois_key(context)
+    sk.create_galois_keys(context, glk)
+    encoder = cahel.ckks_encoder(context)
+    return context, pk, sk, glk, rlk, encoder, scale
+
+
+def GPU_compute_pair_distance(msg1, msg2, context, pk, sk, glk, rlk, encoder, scale):
+    """byzantine_fl.py:173-323 with lazy relinearization and hoisting (its defaults)"""
+    x0 = [0.0] * Nslot
+    acc = pk.encrypt_asymmetric(context, encoder.encode(context, x0, scale))
+    cahel.square_inplace(context, acc)
+    tmp = cahel.ciphertext(context)
+    for x1, x2 in zip(msg1, msg2):
+        ct1 = pk.encrypt_asymmetric(context, encoder.encode(context, x1, scale))
+        ct2 = pk.encrypt_asymmetric(context, encoder.encode(context, x2, scale))
+        cahel.sub(context, ct2, ct1, tmp)
+        cahel.square_inplace(context, tmp)
+        cahel.add_inplace(context, acc, tmp)
+    cahel.relinearize_inplace(context, acc, rlk)
+    cahel.rescale_to_next_inplace(context, acc)
+    acc.set_scale(scale)
+    first = [s for s in range(1, 16) if s < Nslot]
+    rot = cahel.hoisting(context, acc, glk, first)
+    cahel.add_inplace(context, acc, rot)
+    tmp_rot = cahel.ciphertext(context)
+    for idx in range(4, log_Nslot):
+        cahel.rotate_vector(context, acc, int(2 ** idx), glk, tmp_rot)
+        cahel.add_inplace(context, acc, tmp_rot)
+    return acc
+
+
+def _pad_and_split(vectors):
+    """byzantine_fl.py:478-490: zero-pad to a multiple of the slot count and cut into chunks"""
+    weight_len = len(vectors[0])
+    whole = weight_len if weight_len % Nslot == 0 else (weight_len // Nslot + 1) * Nslot
+    out = []
+    for v in vectors:
+        p = np.pad(np.asarray(v), (0, whole - weight_len), "constant")
+        out.append(np.array_split(p, whole // Nslot))
+    return out
+
+
+def GPU_computing_distance_cipher(context, pk, sk, glk, rlk, encoder, scale, vectors):
+    """byzantine_fl.py:466-514; ``vectors`` are the flattened client updates.  Diagonal included, like the reference."""
+    vectors_final = _pad_and_split(vectors)
+    n = len(vectors_final)
+    distance_matrix = [[None] * n for _ in range(n)]
+    for i in range(n):
+        for j in range(i, n):
+            d = GPU_compute_pair_distance(vectors_final[i], vectors_final[j], context, pk, sk, glk, rlk, encoder, scale)
+            distance_matrix[i][j] = distance_matrix[j][i] = d
+    return distance_matrix, vectors_final
+
+
+def GPU_decrypt_sort_mask(context, pk, sk, encoder, scale, distance_matrix):
+    """byzantine_fl.py:327-369: per client the sum over all pairs, decrypt, slot 0, argsort, one-hot masks"""
+    n = len(distance_matrix)
+    p_distance = []
+    one = pk.encrypt_asymmetric(context, encoder.encode(context, [1.0] * Nslot, scale))
+    for i in range(n):
+        tmp = pk.encrypt_asymmetric(context, encoder.encode(context, [0.0] * Nslot, scale))
+        cahel.mod_switch_to_inplace(context, tmp, 2)
+        for j in range(n):
+            cahel.add_inplace(context, tmp, distance_matrix[i][j])
+        p_distance.append(encoder.decode(context, sk.decrypt(context, tmp))[0])
+    order = np.argsort(p_distance)
+    zero = pk.encrypt_asymmetric(context, encoder.encode(context, [0.0] * Nslot, scale))
+    mask = [[zero for _ in range(n)] for _ in range(n)]
+    for i in range(n):
+        mask[i][order[i]] = one
+    return mask, order[0]
+
+
+def GPU_mul_mask_weight(context, pk, encoder, scale, rlk, vectors_final, mask, sk):
+    """byzantine_fl.py:371-429: sum over clients of weight chunk x mask, size-3 decrypt per chunk"""
+    n_clients, n_chunks = len(vectors_final), len(vectors_final[0])
+    w_new = []
+    tmp = cahel.ciphertext(context)
+    pt_zero = encoder.encode(context, [0.0] * Nslot, scale)
+    for c in range(n_chunks):
+        acc = pk.encrypt_asymmetric(context, pt_zero)
+        cahel.square_inplace(context, acc)
+        for k in range(n_clients):
+            ct2 = pk.encrypt_asymmetric(context, encoder.encode(context, vectors_final[k][c], scale))
+            cahel.multiply(context, ct2, mask[0][k], tmp)
+            cahel.add_inplace(context, acc, tmp)
+        w_new = w_new + encoder.decode(context, sk.decrypt(context, acc))
+    return w_new
+
+
+def GPU_krum(vectors, c=0, args=None):
+    """byzantine_fl.py:517-525 on flattened updates; returns the selected (masked) weights"""
+    context, pk, sk, glk, rlk, encoder, scale = GPU_init()
+    distance_matrix, vectors_final = GPU_computing_distance_cipher(context, pk, sk, glk, rlk, encoder, scale, vectors)
+    mask, chosen = GPU_decrypt_sort_mask(context, pk, sk, encoder, scale, distance_matrix)
+    return GPU_mul_mask_weight(context, pk, encoder, scale, rlk, vectors_final, mask, sk)
+
+
+# ---------------------------------------------------------------------------------------------
+# batched driver
+# ---------------------------------------------------------------------------------------------
+
+def all_pairs(n_clients):
+    return [(i, j) for i in range(n_clients) for j in range(i + 1, n_clients)]
+
+
+def pair_schedule(n_clients, world_size):
+    """Pairs i < j in tile-major order over a g x g grid of client groups, cut into
+    ``world_size`` contiguous, equally long segments: a rank touches few distinct clients
+    (so it encrypts few), and segments differ by at most one pair."""
+    g = max(1, int(math.ceil(math.sqrt(2.0 * world_size))))
+    g = min(g, n_clients)
+    size = int(math.ceil(n_clients / g))
+    group = lambda c: c // size
+    tiles = {}
+    for i, j in all_pairs(n_clients):
+        tiles.setdefault((group(i), group(j)), []).append((i, j))
+    order = []
+    # walk the upper triangle of tiles in a zig-zag so that consecutive tiles share a group
+    for a in range(g):
+        cols = list(range(a, g))
+        if a % 2:
+            cols.reverse()
+        for b in cols:
+            order.extend(tiles.get((a, b), []))
+    total = len(order)
+    out = []
+    for r in range(world_size):
+        lo, hi = (total * r) // world_size, (total * (r + 1)) // world_size
+        out.append(order[lo:hi])
+    return out
+
+
+def clients_of(pairs):
+    return sorted({c for p in pairs for c in p})
+
+
+class EncryptedKrum:
+    """Persistent context + keys, batched encrypt, batched pair scores, plaintext selection.
+
+    log_slots = log2(N/2).  chain {60,40,40 | 60}, scale 2^40 (byzantine_fl.py:432-448)."""
+
+    def __init__(self, log_slots=15, device=None, seed=None, encrypt_batch=64):
+        self.log_slots = log_slots
+        self.slots = 1 << log_slots
+        self.N = 2 * self.slots
+        self.scale = 2.0 ** 40
+        self.encrypt_batch = encrypt_batch
+        self._rng = np.random.default_rng(seed) if seed is not None else None
+        steps = [i for i in range(1, 16) if i < self.slots] + [2 ** i for i in range(4, log_slots)]
+        self.first_steps = [i for i in range(1, 16) if i < self.slots]
+        self.pow_steps = [2 ** i for i in range(4, log_slots)]
+        params = cahel.params(cahel.scheme_type.ckks)
+        params.set_poly_modulus_degree(self.N)
+        params.set_coeff_modulus(cahel.coeff_modulus_create(self.N, [60, 40, 40, 60]))
+        params.set_special_modulus_size(1)
+        params.set_galois_elts(cahel.get_elts_from_steps(steps, self.N))
+        sec = cahel.sec_level_type.tc128 if self.N >= 8192 else cahel.sec_level_type.none
+        self.context = cahel.context(params, True, sec, device=device)
+        self.lb = self.context.lb
+        self.steps = steps
+        prev = cahel._seed_source
+        if self._rng is not None:
+            cahel.set_seed_source(lambda k: self._rng.integers(0, 256, 64 * k, dtype=np.uint8))
+        try:
+            self.sk = cahel.secret_key(params)
+            self.sk.gen_secretkey(self.context)
+            self.pk = cahel.public_key(self.context)
+            self.sk.gen_publickey(self.context, self.pk)
+            self.rlk = cahel.relin_key(self.context)
+            self.sk.gen_relinkey(self.context, self.rlk)
+            self.glk = cahel.galois_key(self.context)
+            self.sk.create_galois_keys(self.context, self.glk)
+        finally:
+            cahel.set_seed_source(prev)
+        self.elt_index = {s: self.context.elt_index(e) for s, e in zip(steps, cahel.get_elts_from_steps(steps, self.N))}
+
+    # -- client side ---------------------------------------------------------------------------
+    def n_chunks(self, dim):
+        return (dim + self.slots - 1) // self.slots
+
+    def client_seeds(self, client, n_chunks, round_seed=0):
+        """Deterministic per-(round, client, chunk) seeds: every rank derives the same ciphertexts."""
+        rng = np.random.default_rng([int(round_seed), int(client), 0x4C42])
+        return rng.integers(0, 256, 128 * n_chunks, dtype=np.uint8)
+
+    def encrypt_client(self, update, client=0, round_seed=0, out=None):
+        """update: 1-D float32/float64 tensor (CUDA or CPU) -> ciphertexts [chunks][2][3][N]."""
+        dev = "cuda:%d" % self.lb.device
+        v = update.to(dev) if isinstance(update, torch.Tensor) else torch.from_numpy(np.asarray(update)).to(dev)
+        if v.dtype not in (torch.float32, torch.float64):
+            v = v.to(torch.float64)
+        dim = v.numel()
+        chunks = self.n_chunks(dim)
+        pad = chunks * self.slots - dim
+        if pad:
+            v = torch.cat([v.reshape(-1), torch.zeros(pad, dtype=v.dtype, device=dev)])
+        v = v.reshape(chunks, self.slots).contiguous()
+        seeds = self.client_seeds(client, chunks, round_seed)
+        cts = self.lb.empty(chunks, 2, 3, self.N) if out is None else out
+        for c0 in range(0, chunks, self.encrypt_batch):
+            nb = min(self.encrypt_batch, chunks - c0)
+            pts = self.lb.encode(3, v[c0:c0 + nb], self.scale, sparse_slots=self.slots, batch=nb)
+            ct = self.lb.encrypt_asymmetric(self.pk.data, pts, seeds[128 * c0:128 * (c0 + nb)], nb)
+            cts[c0:c0 + nb] = ct.reshape(nb, 2, 3, self.N)
+        return cts
+
+    # -- server side ---------------------------------------------------------------------------
+    def pair_scores(self, cts, pairs):
+        """cts: dict client -> [chunks][2][3][N].  Returns [len(pairs)][2][2][N] level-2 score ciphertexts."""
+        lb, N = self.lb, self.N
+        P = len(pairs)
+        if P == 0:
+            return lb.empty(0, 2, 2, N)
+        acc = lb.empty(P, 3, 3, N)
+        for p, (i, j) in enumerate(pairs):
+            lb.krum_accumulate(3, cts[i], cts[j], acc[p], accumulate=False)
+        lb.relinearize_batch(3, acc, self.rlk.data)
+        s = lb.rescale_strided(3, acc, P, 2, 3 * 3 * N)  # [P][2][2][N], scale 2^80 / q_2 ~ 2^40
+        del acc
+        rot = s.clone()
+        idx = [self.elt_index[k] for k in self.first_steps]
+        lb.hoisting_batch(2, rot, idx, [self.glk.keys[i] for i in idx])
+        lb.add(2, s, rot, out=s)
+        for k in self.pow_steps:
+            rot.copy_(s)
+            e = self.elt_index[k]
+            lb.rotate_batch(2, rot, e, self.glk.keys[e])
+            lb.add(2, s, rot, out=s)
+        return s
+
+    def client_sums(self, scores, pairs, n_clients):
+        """sum of the score ciphertexts of every pair a client belongs to: [n_clients][2][2][N]"""
+        lb, N = self.lb, self.N
+        sums = torch.zeros(n_clients, 2, 2, N, dtype=torch.int64, device=scores.device)
+        for p, (i, j) in enumerate(pairs):
+            lb.add(2, sums[i], scores[p], out=sums[i])
+            lb.add(2, sums[j], scores[p], out=sums[j])
+        return sums
+
+    def decrypt_slot0(self, ct_level2):
+        pt = self.lb.decrypt(2, ct_level2.contiguous(), self.sk.data)
+        q2 = self.context.moduli[2]
+        # after rescale the true scale is 2^80 / q_2; the reference overwrites it with 2^40 (byzantine_fl.py:246)
+        out = self.lb.decode(2, pt, self.scale * self.scale / q2, self.slots)
+        return float(out[0].real.item())
+
+    def select(self, sums):
+        """decrypt every client's summed distance (slot 0) and return (distances, argsort)"""
+        d = [self.decrypt_slot0(sums[i]) for i in range(sums.shape[0])]
+        return d, np.argsort(d)
+
+    # -- one round ---------------------------------------------------------------------------------
+    def round(self, updates, rank=0, world_size=1, group=None, round_seed=0, keep=None):
+        """updates: [n_clients][dim] tensor (CUDA, pinned or pageable host).  Every rank runs this; rank 0 returns
+        (distances, order), the others (None, None).  The only collective is the gather of the score ciphertexts."""
+        n_clients = updates.shape[0]
+        schedule = pair_schedule(n_clients, world_size)
+        mine = schedule[rank]
+        cts = {}
+        for c in clients_of(mine):
+            cts[c] = self.encrypt_client(updates[c], client=c, round_seed=round_seed)
+        scores = self.pair_scores(cts, mine)
+        if keep is not None:
+            keep["cts"], keep["scores"], keep["pairs"] = cts, scores, mine
+        del cts
+        if world_size > 1:
+            scores, pairs = gather_scores(scores, schedule, rank, world_size, group)
+        else:
+            pairs = mine
+        if rank != 0:
+            return None, None
+        sums = self.client_sums(scores, pairs, n_clients)
+        return self.select(sums)
+
+
+def gather_scores(local, schedule, rank, world_size, group=None):
+    """Gathers the per-rank score ciphertexts on every rank (torch.distributed all_gather, NCCL over
+    NVLink on GPUs, gloo in the CPU tests) and returns them with the matching global pair list.
+    Segments differ by at most one pair, so shorter ones are padded to the longest."""
+    import torch.distributed as dist
+
+    longest = max(len(s) for s in schedule)
+    shape = (longest,) + tuple(local.shape[1:])
+    send = torch.zeros(shape, dtype=local.dtype, device=local.device)
+    send[: local.shape[0]] = local
+    recv = [torch.empty_like(send) for _ in range(world_size)]
+    dist.all_gather(recv, send, group=group)
+    parts, pairs = [], []
+    for r in range(world_size):
+        k = len(schedule[r])
+        parts.append(recv[r][:k])
+        pairs.extend(schedule[r])
+    return torch.cat(parts, dim=0), pairs
+
+
+def plaintext_krum(updates):
+    """float64 reference of the selection rule as Lancelot applies it (byzantine_fl.py:527-536:
+    sum of squared distances to ALL other clients, argmin)."""
+    x = updates.to(torch.float64)
+    n = x.shape[0]
+    d = torch.zeros(n, dtype=torch.float64)
+    for i in range(n):
+        for j in range(i + 1, n):
+            v = float(((x[i] - x[j]) ** 2).sum().item())
+            d[i] += v
+            d[j] += v
+    return d.tolist(), np.argsort(d.numpy())

@@ -1,0 +1,205 @@
+"""The pyCAHEL mirror used the way the reference's own examples and the Lancelot driver use the
+original: encode -> encrypt -> evaluate -> decrypt -> decode against the plaintext computation
+(tolerance 1e-3 as in cahel-main/examples/example.h:14-19, most checks far tighter), error
+classes, and the batched Krum driver against the step-by-step API."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def env():
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device; there is no CPU fallback")
+    import lancelot_b200.pycahel as cahel
+
+    cahel.set_seed_source(cahel.counter_seed_source(7))
+    n = 1 << 13
+    parms = cahel.params(cahel.scheme_type.ckks)
+    parms.set_poly_modulus_degree(n)
+    parms.set_coeff_modulus(cahel.coeff_modulus_create(n, [60, 40, 40, 60]))
+    parms.set_special_modulus_size(1)
+    steps = [1, 2, 3, 4, 8, -2]
+    parms.set_galois_elts(cahel.get_elts_from_steps(steps, n))
+    ctx = cahel.context(parms, True, cahel.sec_level_type.tc128)
+    sk = cahel.secret_key(parms)
+    sk.gen_secretkey(ctx)
+    pk = cahel.public_key(ctx)
+    sk.gen_publickey(ctx, pk)
+    rlk = cahel.relin_key(ctx)
+    sk.gen_relinkey(ctx, rlk)
+    glk = cahel.galois_key(ctx)
+    sk.create_galois_keys(ctx, glk)
+    enc = cahel.ckks_encoder(ctx)
+    yield dict(cahel=cahel, ctx=ctx, sk=sk, pk=pk, rlk=rlk, glk=glk, enc=enc, n=n, scale=2.0 ** 40)
+    cahel.set_seed_source(None)
+
+
+def _dec(e, ct):
+    return np.array(e["enc"].decode(e["ctx"], e["sk"].decrypt(e["ctx"], ct)))
+
+
+def test_primitive_chain_config(env):
+    """BASELINE configs[0]: encode two 4096-slot vectors, encrypt, multiply, relinearize, rescale, rotate by 1, decrypt."""
+    cahel, ctx = env["cahel"], env["ctx"]
+    rng = np.random.default_rng(2024)
+    x, y = rng.uniform(-1, 1, 4096), rng.uniform(-1, 1, 4096)
+    ct1 = env["pk"].encrypt_asymmetric(ctx, env["enc"].encode(ctx, list(x), env["scale"]))
+    ct2 = env["pk"].encrypt_asymmetric(ctx, env["enc"].encode(ctx, y, env["scale"]))
+    assert np.abs(_dec(env, ct1) - x).max() < 1e-6
+    cahel.multiply_inplace(ctx, ct1, ct2)
+    assert ct1.size == 3
+    assert np.abs(_dec(env, ct1) - x * y).max() < 1e-6  # size-3 decryption uses s^2
+    cahel.relinearize_inplace(ctx, ct1, env["rlk"])
+    cahel.rescale_to_next_inplace(ctx, ct1)
+    assert ct1.chain_index == 2 and abs(np.log2(ct1.scale) - 40) < 1e-3
+    assert np.abs(_dec(env, ct1) - x * y).max() < 1e-5
+    rot = cahel.ciphertext(ctx)
+    cahel.rotate_vector(ctx, ct1, 1, env["glk"], rot)
+    assert np.abs(_dec(env, rot) - np.roll(x * y, -1)).max() < 1e-4
+    # a step without its own key goes through the non-adjacent form (5 = 4 + 1), a negative one rotates right
+    cahel.rotate_vector(ctx, ct1, 5, env["glk"], rot)
+    assert np.abs(_dec(env, rot) - np.roll(x * y, -5)).max() < 1e-4
+    cahel.rotate_vector(ctx, ct1, -2, env["glk"], rot)
+    assert np.abs(_dec(env, rot) - np.roll(x * y, 2)).max() < 1e-4
+    h = cahel.hoisting(ctx, ct1, env["glk"], [1, 2, 3])
+    p = x * y
+    assert np.abs(_dec(env, h) - (np.roll(p, -1) + np.roll(p, -2) + np.roll(p, -3))).max() < 1e-4
+
+
+def test_lancelot_smoke_script_sequence(env):
+    """the operation sequence of lancelot-main-GPU/ckks.py: square, relinearize, rescale, multiply_plain, rescale, add, rotate(-2)"""
+    cahel, ctx = env["cahel"], env["ctx"]
+    x = np.linspace(-1, 1, 4096)
+    ct = env["pk"].encrypt_asymmetric(ctx, env["enc"].encode(ctx, x, env["scale"]))
+    cahel.square_inplace(ctx, ct)
+    cahel.relinearize_inplace(ctx, ct, env["rlk"])
+    cahel.rescale_to_next_inplace(ctx, ct)
+    pt = env["enc"].encode_to(ctx, [0.5] * 4096, 2, env["scale"])
+    cahel.multiply_plain_inplace(ctx, ct, pt)
+    cahel.rescale_to_next_inplace(ctx, ct)
+    assert ct.chain_index == 3
+    got = _dec(env, ct)
+    assert np.abs(got - 0.5 * x * x).max() < 1e-4
+    other = ct.copy()
+    cahel.add_inplace(ctx, ct, other)
+    cahel.rotate_vector_inplace(ctx, ct, -2, env["glk"])
+    assert np.abs(_dec(env, ct) - np.roll(x * x, 2)).max() < 1e-3
+
+
+def test_add_sub_negate_plain_and_errors(env):
+    cahel, ctx = env["cahel"], env["ctx"]
+    rng = np.random.default_rng(5)
+    x, y = rng.uniform(-1, 1, 4096), rng.uniform(-1, 1, 4096)
+    pt_x = env["enc"].encode(ctx, x, env["scale"])
+    ct1 = env["pk"].encrypt_asymmetric(ctx, pt_x)
+    ct2 = env["sk"].encrypt_symmetric(ctx, env["enc"].encode(ctx, y, env["scale"]), False)
+    out = cahel.ciphertext(ctx)
+    cahel.sub(ctx, ct2, ct1, out)  # out = ct2 - ct1, as the Krum loop uses it
+    assert np.abs(_dec(env, out) - (y - x)).max() < 1e-6
+    cahel.add(ctx, ct1, ct2, out)
+    assert np.abs(_dec(env, out) - (x + y)).max() < 1e-6
+    cahel.negate(ctx, ct1, out)
+    assert np.abs(_dec(env, out) + x).max() < 1e-6
+    cahel.add_plain(ctx, ct2, pt_x, out)
+    assert np.abs(_dec(env, out) - (x + y)).max() < 1e-6
+    cahel.sub_plain(ctx, ct2, pt_x, out)
+    assert np.abs(_dec(env, out) - (y - x)).max() < 1e-6
+    many = cahel.ciphertext(ctx)
+    cahel.add_many(ctx, [ct1, ct2, ct1], many)
+    assert np.abs(_dec(env, many) - (2 * x + y)).max() < 1e-6
+    # a size-3 plus a size-2 ciphertext keeps three polynomials
+    sq = ct1.copy()
+    cahel.square_inplace(ctx, sq)
+    with pytest.raises(ValueError):
+        cahel.add_inplace(ctx, sq, ct2)  # scale mismatch 2^80 vs 2^40
+    low = ct1.copy()
+    cahel.mod_switch_to_inplace(ctx, low, 2)
+    assert np.abs(_dec(env, low) - x).max() < 1e-6
+    with pytest.raises(ValueError):
+        cahel.add_inplace(ctx, low, ct1)  # level mismatch
+    with pytest.raises(ValueError):
+        cahel.relinearize_inplace(ctx, ct1, env["rlk"])  # size must be 3
+    with pytest.raises(ValueError):
+        cahel.mod_switch_to_inplace(ctx, low, 1)  # cannot go back up
+    with pytest.raises(ValueError):
+        env["enc"].encode(ctx, [1.0] * 5000, env["scale"])  # more values than slots
+    with pytest.raises((RuntimeError, ValueError)):
+        cahel.rotate_vector(ctx, ct1, 4095, env["glk"], out)  # no key and no decomposition into available steps
+    with pytest.raises(ValueError):
+        cahel.params(cahel.scheme_type.bfv) and cahel.context(cahel.params(cahel.scheme_type.bfv))
+
+
+def test_batched_krum_driver_equals_stepwise_api_and_plaintext():
+    """EncryptedKrum (fused accumulate, batched relinearize / rescale / rotations) against the same
+    ciphertexts pushed through the one-call-per-operation API of the reference driver: bit-exact;
+    and against float64 plaintext Krum: relative error of the distances below 1e-6."""
+    import torch
+
+    import lancelot_b200.pycahel as cahel
+    from lancelot_b200 import cabi, krum
+
+    torch.manual_seed(3)
+    log_slots = 10
+    ek = krum.EncryptedKrum(log_slots=log_slots, seed=11)
+    n_clients, dim = 5, 3 * 1024 - 100
+    upd = torch.randn(n_clients, dim, dtype=torch.float32) * 0.5
+    upd[1] += 2.0
+    keep = {}
+    d, order = ek.round(upd.cuda(), keep=keep)
+    want_d, want_order = krum.plaintext_krum(upd)
+    rel = max(abs(a - b) / b for a, b in zip(d, want_d))
+    assert rel < 1e-6, rel
+    assert list(order) == list(want_order) and order[-1] == 1
+    # step-by-step API on the very same ciphertexts for one pair
+    ctx = ek.context
+    i, j = keep["pairs"][2]
+    acc = None
+    for c in range(keep["cts"][i].shape[0]):
+        a, b = cahel.ciphertext(ctx), cahel.ciphertext(ctx)
+        for obj, src in ((a, keep["cts"][i][c]), (b, keep["cts"][j][c])):
+            obj.data, obj.size, obj.chain_index, obj.scale = src.clone(), 2, 1, ek.scale
+        tmp = cahel.ciphertext(ctx)
+        cahel.sub(ctx, b, a, tmp)
+        cahel.square_inplace(ctx, tmp)
+        if acc is None:
+            acc = tmp
+        else:
+            cahel.add_inplace(ctx, acc, tmp)
+    cahel.relinearize_inplace(ctx, acc, ek.rlk)
+    cahel.rescale_to_next_inplace(ctx, acc)
+    acc.set_scale(ek.scale)
+    rot = cahel.hoisting(ctx, acc, ek.glk, ek.first_steps)
+    cahel.add_inplace(ctx, acc, rot)
+    tmp_rot = cahel.ciphertext(ctx)
+    for k in ek.pow_steps:
+        cahel.rotate_vector(ctx, acc, k, ek.glk, tmp_rot)
+        cahel.add_inplace(ctx, acc, tmp_rot)
+    assert torch.equal(acc.data.reshape(-1), keep["scores"][2].reshape(-1))
+
+
+def test_reference_driver_flow_small():
+    """GPU_init .. GPU_krum with the reference's call sequence (diagonal pairs, re-encryption per pair, masks)"""
+    import torch
+
+    from lancelot_b200 import krum
+
+    krum.set_slots(9)
+    try:
+        rng = np.random.default_rng(8)
+        vecs = [rng.normal(0, 0.1, 700).astype(np.float32) for _ in range(3)]
+        vecs[2] = vecs[2] + 1.0
+        context, pk, sk, glk, rlk, encoder, scale = krum.GPU_init()
+        dm, vf = krum.GPU_computing_distance_cipher(context, pk, sk, glk, rlk, encoder, scale, vecs)
+        mask, chosen = krum.GPU_decrypt_sort_mask(context, pk, sk, encoder, scale, dm)
+        d01 = float(((vecs[0].astype(np.float64) - vecs[1]) ** 2).sum())
+        got = encoder.decode(context, sk.decrypt(context, dm[0][1]))[0]
+        assert abs(got - d01) / d01 < 1e-5
+        assert chosen in (0, 1)
+        w = krum.GPU_mul_mask_weight(context, pk, encoder, scale, rlk, vf, mask, sk)
+        assert np.abs(np.array(w[:700]) - vecs[chosen]).max() < 1e-4
+    finally:
+        krum.set_slots(15)

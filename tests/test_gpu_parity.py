@@ -292,3 +292,33 @@ def test_encode_rejects_values_that_do_not_fit(torch_cuda):
     ctx.check_status()  # the flag is cleared once reported
     with pytest.raises(InvalidArgument):
         ctx.encode(1, big, 2.0 ** 40, sparse_slots=512)  # scale out of bounds
+
+
+@pytest.mark.parametrize("logn,bits,size_p,L", [(10, [60, 40, 40, 60], 1, 2), (11, [50, 40, 40, 40, 40, 40, 50, 50], 2, 5)])
+def test_batched_keyswitch_matches_per_ciphertext(torch_cuda, logn, bits, size_p, L):
+    from lancelot_b200 import cabi
+
+    steps = [1, 2, 3]
+    o, ctx, mods = make(logn, bits, size_p, steps)
+    rng = np.random.default_rng(500 + logn)
+    n = 1 << logn
+    size_Q = len(bits) - size_p
+    sk, rlk, glk = _keys(o, rng, len(steps))
+    d_rlk = cabi.to_device(rlk)
+    d_glk = [cabi.to_device(g) for g in glk]
+    batch = 5
+    ct3 = rand_rows(rng, row_moduli(mods, size_Q, L, 0, 3 * batch), n).reshape(batch, 3, L, n)
+    got = cabi.to_host(ctx.relinearize_batch(L, cabi.to_device(ct3), d_rlk)).reshape(batch, 3, L, n)
+    for b in range(batch):
+        assert np.array_equal(got[b, :2], o.relinearize(L, ct3[b], rlk)), "relinearize %d" % b
+    ct = rand_rows(rng, row_moduli(mods, size_Q, L, 0, 2 * batch), n).reshape(batch, 2, L, n)
+    got = cabi.to_host(ctx.rotate_batch(L, cabi.to_device(ct), 1, d_glk[1])).reshape(batch, 2, L, n)
+    for b in range(batch):
+        assert np.array_equal(got[b], o.rotate(L, ct[b], 1, glk[1])), "rotate %d" % b
+    got = cabi.to_host(ctx.hoisting_batch(L, cabi.to_device(ct), [0, 1, 2], d_glk)).reshape(batch, 2, L, n)
+    for b in range(batch):
+        assert np.array_equal(got[b], o.hoisting(L, ct[b], [0, 1, 2], glk)), "hoisting %d" % b
+    # rescale already takes any number of polynomials
+    got = cabi.to_host(ctx.rescale(L, cabi.to_device(ct))).reshape(batch, 2, L - 1, n)
+    for b in range(batch):
+        assert np.array_equal(got[b], o.rescale(L, ct[b]))

@@ -1,0 +1,67 @@
+"""Host-side logic of the Krum driver: pair scheduling and the world_size-2 gather (gloo, CPU)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+
+def test_pair_schedule_covers_every_pair_once_and_balances():
+    from lancelot_b200.krum import all_pairs, clients_of, pair_schedule
+
+    for n in (2, 4, 10, 20, 33):
+        for world in (1, 2, 4, 8):
+            sched = pair_schedule(n, world)
+            assert len(sched) == world
+            flat = [p for s in sched for p in s]
+            assert sorted(flat) == all_pairs(n)
+            sizes = [len(s) for s in sched]
+            assert max(sizes) - min(sizes) <= 1
+    # the tiling keeps the number of clients a rank must encrypt well below "all of them"
+    sched = pair_schedule(20, 8)
+    assert max(len(clients_of(s)) for s in sched) <= 15
+
+
+def test_plaintext_krum_rule():
+    from lancelot_b200.krum import plaintext_krum
+
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(6, 50, generator=g) * 0.01
+    x[4] += 1.0  # an outlier has the largest summed distance
+    d, order = plaintext_krum(x)
+    assert order[-1] == 4 and len(d) == 6
+    i, j = 1, 3
+    xd = x.double()
+    assert abs(sum(float(((xd[i] - xd[k]) ** 2).sum()) for k in range(6) if k != i) - d[i]) < 1e-9
+
+
+def _gather_worker(rank, world, port, ret):
+    import torch.distributed as dist
+
+    from lancelot_b200.krum import gather_scores, pair_schedule
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        n_clients = 5  # 10 pairs over 2 ranks; with 3 ranks segments would be uneven
+        sched = pair_schedule(n_clients, world)
+        mine = sched[rank]
+        # a fake "score ciphertext" whose words encode the pair it belongs to
+        local = torch.stack([torch.full((2, 2, 8), 100 * i + j, dtype=torch.int64) for i, j in mine])
+        scores, pairs = gather_scores(local, sched, rank, world)
+        ok = len(pairs) == 10 and all(int(scores[k, 0, 0, 0]) == 100 * i + j for k, (i, j) in enumerate(pairs))
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_gather_scores_world_size_n_gloo(world):
+    import torch.multiprocessing as mp
+
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 29500 + (os.getpid() % 500) + world
+    mp.spawn(_gather_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert all(ret.get(r) for r in range(world)), dict(ret)
