@@ -44,6 +44,8 @@ extern "C" {
 typedef struct lb_context lb_context;
 
 LB_API const char *lb_last_error(void);
+/* number of kernels this library has launched in this process (benchmark bookkeeping) */
+LB_API unsigned long long lb_launch_count(void);
 
 /* ---- host-only parameter helpers (no GPU needed) ---------------------------------------- */
 

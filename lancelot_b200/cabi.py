@@ -266,9 +266,12 @@ class Context:
         check(lib.lb_gen_switch_key(self.h, _p(sk), _p(sk_target), sp, _p(out), _stream()))
         return out
 
-    def encrypt_asymmetric(self, pk, pt, seeds, batch=1):
+    def encrypt_asymmetric(self, pk, pt, seeds, batch=1, out=None):
         s, sp = self._seed(seeds, 2 * batch)
-        ct = self.empty(batch, 2, self.size_Q, self.N) if batch > 1 else self.empty(2, self.size_Q, self.N)
+        if out is not None:
+            ct = out
+        else:
+            ct = self.empty(batch, 2, self.size_Q, self.N) if batch > 1 else self.empty(2, self.size_Q, self.N)
         check(lib.lb_encrypt_asymmetric(self.h, _p(pk), _p(pt), sp, batch, _p(ct), _stream()))
         return ct
 

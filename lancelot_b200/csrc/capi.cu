@@ -49,6 +49,8 @@ extern "C" {
 
 const char *lb_last_error(void) { return last_error().c_str(); }
 
+unsigned long long lb_launch_count(void) { return launch_count(); }
+
 int lb_coeff_modulus_create(uint64_t n, const int *bit_sizes, int count, uint64_t *out)
 {
     REQUIRE(bit_sizes && out && count >= 1 && count <= 64, "bit_sizes is invalid");

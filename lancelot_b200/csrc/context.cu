@@ -8,6 +8,10 @@ namespace lb {
 static thread_local std::string g_error;
 
 void set_error(const std::string &msg) { g_error = msg; }
+
+static unsigned long long g_launches = 0;
+void count_launch() { ++g_launches; }
+unsigned long long launch_count() { return g_launches; }
 const std::string &last_error() { return g_error; }
 
 int cuda_fail(cudaError_t e, const char *what)

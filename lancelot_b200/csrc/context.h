@@ -45,6 +45,8 @@ struct Context {
 };
 
 void set_error(const std::string &msg);
+void count_launch();            // every kernel launch of this library is counted (lb_launch_count)
+unsigned long long launch_count();
 int cuda_fail(cudaError_t e, const char *what);
 
 #define LB_CUDA(call)                                         \

@@ -272,6 +272,7 @@ static int launch_encode(const EncK &k, int batch, size_t smem, cudaStream_t str
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    count_launch();
     LB_CUDA(cudaLaunchKernelEx(&cfg, kern, k));
     return LB_OK;
 }
@@ -491,13 +492,16 @@ int decode(Context *ctx, int size_l, const u64 *pt, double scale, int sparse_slo
         cc.Qhalf[i] = (Q[i] >> 1) | (i + 1 < W ? Q[i + 1] << 63 : 0);
     }
     const unsigned n = (unsigned)sparse_slots;
+    count_launch();
     compose_kernel<<<(2 * n + 255) / 256, 256, 0, stream>>>(buf, coef, ctx->d_mc, cc, hp.logN, logn, size_l, 1.0 / scale);
     LB_CUDA(cudaGetLastError());
     for (int iter = 0; iter < logn; ++iter) {
         const int u = logn - iter - 1;
+        count_launch();
         fft_stage_kernel<<<(n / 2 + 255) / 256, 256, 0, stream>>>(buf, ctx->d_croots, ctx->d_rot_group, hp.logN, logn, u);
     }
     LB_CUDA(cudaGetLastError());
+    count_launch();
     bitrev_out_kernel<<<(n + 255) / 256, 256, 0, stream>>>(reinterpret_cast<cplx *>(out_complex), buf, logn);
     LB_CUDA(cudaGetLastError());
     return LB_OK;

@@ -170,6 +170,7 @@ static int inner_product_steps(Context *ctx, int L, int batch, const u64 *digits
     long blocks = (total + kKsThreads - 1) / kKsThreads;
     const long cap = (long)ctx->sm_count * 16;
     if (blocks > cap) blocks = cap;
+    count_launch();
     inner_product_kernel<<<(int)blocks, kKsThreads, 0, stream>>>(digits, own, own_stride, cx, ctx->d_mc, args, hp.logN, L, LP, hp.size_Q,
                                                                  hp.size_QP, hp.size_P, hp.level[L].beta, total);
     LB_CUDA(cudaGetLastError());
@@ -423,6 +424,7 @@ int hoisting(Context *ctx, int L, int batch, u64 *ct, int n_steps, const int *el
         long blocks = (total + kKsThreads - 1) / kKsThreads;
         const long cap = (long)ctx->sm_count * 16;
         if (blocks > cap) blocks = cap;
+        count_launch();
         galois_sum_kernel<<<(int)blocks, kKsThreads, 0, stream>>>(ct_b, 2L * L, w.tmp, ctx->d_mc, args, hp.logN, L, total);
         LB_CUDA(cudaGetLastError());
         if ((rc = moddown_into(ctx, L, nb, 2, w.cx, w.pc, ct_b, Placement{2L * L, L}, w.tmp, Placement{L, L}, 1, stream))) return rc;

@@ -430,6 +430,7 @@ static int launch(bool forward, const NttK &k, int rows, size_t smem, cudaStream
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    count_launch();
     LB_CUDA(cudaLaunchKernelEx(&cfg, kern, k));
     return LB_OK;
 }

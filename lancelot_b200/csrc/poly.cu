@@ -56,6 +56,7 @@ int poly_binary(Context *ctx, int op, int size_l, long rows, const u64 *a, const
     const int grid = grid_for(ctx, total, kPolyThreads);
     const ulonglong2 *pa = reinterpret_cast<const ulonglong2 *>(a), *pb = reinterpret_cast<const ulonglong2 *>(b);
     ulonglong2 *po = reinterpret_cast<ulonglong2 *>(out);
+    count_launch();
     switch (op) {
     case OP_ADD: binary_kernel<OP_ADD><<<grid, kPolyThreads, 0, stream>>>(pa, pb, po, ctx->d_mc, size_l, log_half_n, total); break;
     case OP_SUB: binary_kernel<OP_SUB><<<grid, kPolyThreads, 0, stream>>>(pa, pb, po, ctx->d_mc, size_l, log_half_n, total); break;
@@ -106,6 +107,7 @@ int poly_tensor(Context *ctx, int size_l, int batch, const u64 *a, const u64 *b,
     const int log_half_n = ctx->hp.logN - 1;
     const long per_ct = (long)size_l << log_half_n;
     const long total = per_ct * batch;
+    count_launch();
     tensor_kernel<<<grid_for(ctx, total, kPolyThreads), kPolyThreads, 0, stream>>>(
         reinterpret_cast<const ulonglong2 *>(a), reinterpret_cast<const ulonglong2 *>(b), reinterpret_cast<ulonglong2 *>(out),
         ctx->d_mc, size_l, log_half_n, per_ct, total);
@@ -132,6 +134,7 @@ int poly_galois(Context *ctx, int elt_idx, long rows, const u64 *src, u64 *dst, 
         return LB_ERR_LOGIC;
     }
     const long total = rows << ctx->hp.logN;
+    count_launch();
     galois_kernel<<<grid_for(ctx, total, kPolyThreads), kPolyThreads, 0, stream>>>(
         src, dst, ctx->d_perm + ((size_t)elt_idx << ctx->hp.logN), ctx->hp.logN, total);
     LB_CUDA(cudaGetLastError());
@@ -196,6 +199,7 @@ int krum_accumulate(Context *ctx, int size_l, int n_chunks, const u64 *a, const 
     const int log_half_n = ctx->hp.logN - 1;
     const long per_poly = (long)size_l << log_half_n;
     long blocks = (per_poly + kPolyThreads - 1) / kPolyThreads;
+    count_launch();
     krum_accumulate_kernel<<<(int)blocks, kPolyThreads, 0, stream>>>(
         reinterpret_cast<const ulonglong2 *>(a), reinterpret_cast<const ulonglong2 *>(b), reinterpret_cast<ulonglong2 *>(acc),
         ctx->d_mc, log_half_n, per_poly, chunk_stride_a / 2, chunk_stride_b / 2, n_chunks, accumulate);
@@ -233,6 +237,7 @@ __global__ void __launch_bounds__(kPolyThreads) decrypt_kernel(const u64 *__rest
 int poly_decrypt(Context *ctx, int size_l, int n_polys, const u64 *ct, const u64 *sk, u64 *pt, cudaStream_t stream)
 {
     const long per_poly = (long)size_l << ctx->hp.logN;
+    count_launch();
     decrypt_kernel<<<grid_for(ctx, per_poly, kPolyThreads), kPolyThreads, 0, stream>>>(ct, sk, pt, ctx->d_mc, ctx->hp.logN, n_polys,
                                                                                        per_poly);
     LB_CUDA(cudaGetLastError());

@@ -114,6 +114,7 @@ int sample_small(Context *ctx, int kind, const uint32_t *d_seeds, int seed_strid
 {
     const long total = (long)batch << ctx->hp.logN;
     if (total == 0) return LB_OK;
+    count_launch();
     sample_small_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(out, d_seeds, seed_stride, ctx->d_mc, kind, ctx->hp.logN, size_l, size_p,
                                                                           ctx->hp.size_Q, total);
     LB_CUDA(cudaGetLastError());
@@ -124,6 +125,7 @@ int sample_uniform(Context *ctx, const uint32_t *d_seeds, int seed_stride, int b
 {
     const long total = ((long)batch * (size_l + size_p) << ctx->hp.logN) >> 3;
     if (total == 0) return LB_OK;
+    count_launch();
     sample_uniform_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(out, d_seeds, seed_stride, ctx->d_mc, ctx->hp.logN, size_l, size_p,
                                                                             ctx->hp.size_Q, total);
     LB_CUDA(cudaGetLastError());
@@ -177,6 +179,7 @@ int gen_public_key(Context *ctx, const u64 *sk, const uint32_t *d_seed_e, const 
     j.size_l = hp.size_Q;
     if ((rc = ntt_forward(ctx, j, stream))) return rc;
     if ((rc = sample_uniform(ctx, d_seed_a, 16, 1, hp.size_Q, hp.size_P, pk + poly, stream))) return rc;
+    count_launch();
     pk_combine_kernel<<<grid_for(ctx, poly), kSampThreads, 0, stream>>>(pk, pk + poly, sk, scratch, ctx->d_mc, hp.logN, poly);
     LB_CUDA(cudaGetLastError());
     return LB_OK;
@@ -192,6 +195,7 @@ int gen_switch_key(Context *ctx, const u64 *sk, const u64 *skp, const uint32_t *
         if (rc) return rc;
     }
     const long total = (long)hp.size_Q << hp.logN;
+    count_launch();
     ksk_add_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(out, skp, ctx->d_p_mod_q, ctx->d_p_mod_q_s, ctx->d_mc, hp.logN,
                                                                      hp.size_P, 2 * poly, total);
     LB_CUDA(cudaGetLastError());
@@ -253,6 +257,7 @@ int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, const uint8_t
     j.size_l = Q;
     if ((rc = ntt_forward(ctx, j, stream))) return rc;
     const long total = batch * poly;
+    count_launch();
     encrypt_combine_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(cx, pk, u, e, ctx->d_mc, hp.logN, poly, total);
     LB_CUDA(cudaGetLastError());
     // moddown of 2*batch polynomials from QP to Q

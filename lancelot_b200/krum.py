@@ -269,8 +269,7 @@ class EncryptedKrum:
         for c0 in range(0, chunks, self.encrypt_batch):
             nb = min(self.encrypt_batch, chunks - c0)
             pts = self.lb.encode(3, v[c0:c0 + nb], self.scale, sparse_slots=self.slots, batch=nb)
-            ct = self.lb.encrypt_asymmetric(self.pk.data, pts, seeds[128 * c0:128 * (c0 + nb)], nb)
-            cts[c0:c0 + nb] = ct.reshape(nb, 2, 3, self.N)
+            self.lb.encrypt_asymmetric(self.pk.data, pts, seeds[128 * c0:128 * (c0 + nb)], nb, out=cts[c0:c0 + nb])
         return cts
 
     # -- server side ---------------------------------------------------------------------------
