@@ -245,6 +245,10 @@ def run_gpu(args, wl):
     with ClockSampler(local) as clocks:
         ms, _ = timed(wl.step_gpu, args.steps)
     ok = wl.check_gpu()
+    if hasattr(wl, "profile_phases"):  # one extra, untimed pass with per-phase synchronisation for the breakdown
+        wl.profile_phases = True
+        wl.step_gpu()
+        wl.profile_phases = False
     for _ in range(2):
         wl.step_e2e()
     ms_e2e, io = timed(wl.step_e2e, args.steps)
@@ -276,6 +280,10 @@ def run_gpu(args, wl):
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "traffic": getattr(wl, "ncu_traffic_bytes", None), "kernel": kname, "peak_kind": "of " + peak_kind},
                 "cpu_baseline": cpu, "clocks": clocks.summary(), "parity_check": ok}
+        if getattr(wl, "breakdown", None):
+            line["breakdown"] = wl.breakdown
+        if hasattr(wl, "rel_err"):
+            line["max_rel_err_vs_float64_plaintext"] = wl.rel_err
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

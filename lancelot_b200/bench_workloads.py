@@ -39,6 +39,7 @@ class KrumWorkload:
         self.chunks = (self.dim + self.slots - 1) // self.slots
         self.launches_per_step = 0
         self.breakdown = {}
+        self.profile_phases = False
 
     def config(self):
         return {"workload": "%s encrypted Krum distance round: %d clients x %d float32, N=2^%d, %d ciphertexts per client, "
@@ -90,11 +91,14 @@ class KrumWorkload:
         ek = krum.EncryptedKrum(log_slots=self.log_slots, device=self.device, seed=1)
         self.torch.cuda.synchronize()
         t1 = time.perf_counter()
-        d, order = ek.round(updates, rank=self.rank, world_size=self.world)
+        timing = {} if self.profile_phases else None
+        d, order = ek.round(updates, rank=self.rank, world_size=self.world, timing=timing)
         self.torch.cuda.synchronize()
         t2 = time.perf_counter()
         self.launches_per_step = _launches() - l0
-        self.breakdown = {"init_s": t1 - t0, "round_s": t2 - t1}
+        if timing:
+            self.breakdown = {"init_s": t1 - t0, "round_s": t2 - t1}
+            self.breakdown.update({k: v for k, v in timing.items() if k != "start"})
         self.result = (d, order)
         del ek
 

@@ -21,7 +21,27 @@ typedef unsigned __int128 u128;
 #endif
 
 // ---- host-only helpers (precompute) ---------------------------------------------------
+#if defined(__x86_64__) && !defined(__CUDA_ARCH__)
+// 128-by-64 division in one instruction; valid whenever the high half is below q
+inline u64 h_div128(u64 hi, u64 lo, u64 q, u64 *rem)
+{
+    u64 quo, r;
+    __asm__("divq %4" : "=a"(quo), "=d"(r) : "a"(lo), "d"(hi), "r"(q) : "cc");
+    *rem = r;
+    return quo;
+}
+inline u64 h_mulmod(u64 a, u64 b, u64 q)
+{
+    if (a >= q) a %= q;
+    if (b >= q) b %= q;
+    const u128 p = (u128)a * b;
+    u64 r;
+    h_div128((u64)(p >> 64), (u64)p, q, &r);
+    return r;
+}
+#else
 inline u64 h_mulmod(u64 a, u64 b, u64 q) { return (u64)((u128)a * b % q); }
+#endif
 inline u64 h_powmod(u64 b, u64 e, u64 q)
 {
     u64 r = 1 % q;
@@ -33,7 +53,16 @@ inline u64 h_powmod(u64 b, u64 e, u64 q)
     return r;
 }
 inline u64 h_invmod(u64 a, u64 q) { return h_powmod(a % q, q - 2, q); } // q prime
+#if defined(__x86_64__) && !defined(__CUDA_ARCH__)
+inline u64 h_shoup(u64 w, u64 q)
+{
+    if (w >= q) return (u64)(((u128)w << 64) / q);
+    u64 r;
+    return h_div128(w, 0, q, &r);
+}
+#else
 inline u64 h_shoup(u64 w, u64 q) { return (u64)(((u128)w << 64) / q); }
+#endif
 
 #if defined(__CUDACC__)
 // ---- device arithmetic ----------------------------------------------------------------

@@ -80,10 +80,13 @@ u64 minimal_primitive_root(u64 degree, u64 q)
 
 uint32_t bit_reverse(uint32_t x, int bits)
 {
-    uint32_t r = 0;
-    for (int i = 0; i < bits; ++i)
-        if (x >> i & 1u) r |= 1u << (bits - 1 - i);
-    return r;
+    if (bits <= 0) return 0;
+    x = ((x >> 1) & 0x55555555u) | ((x & 0x55555555u) << 1);
+    x = ((x >> 2) & 0x33333333u) | ((x & 0x33333333u) << 2);
+    x = ((x >> 4) & 0x0F0F0F0Fu) | ((x & 0x0F0F0F0Fu) << 4);
+    x = ((x >> 8) & 0x00FF00FFu) | ((x & 0x00FF00FFu) << 8);
+    x = (x >> 16) | (x << 16);
+    return x >> (32 - bits);
 }
 
 uint32_t galois_elt_from_step(int step, u64 N)

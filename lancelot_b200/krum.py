@@ -273,7 +273,7 @@ class EncryptedKrum:
         return cts
 
     # -- server side ---------------------------------------------------------------------------
-    def pair_scores(self, cts, pairs):
+    def pair_scores(self, cts, pairs, mark=lambda name: None):
         """cts: dict client -> [chunks][2][3][N].  Returns [len(pairs)][2][2][N] level-2 score ciphertexts."""
         lb, N = self.lb, self.N
         P = len(pairs)
@@ -282,9 +282,11 @@ class EncryptedKrum:
         acc = lb.empty(P, 3, 3, N)
         for p, (i, j) in enumerate(pairs):
             lb.krum_accumulate(3, cts[i], cts[j], acc[p], accumulate=False)
+        mark("pair_accumulate_s")
         lb.relinearize_batch(3, acc, self.rlk.data)
         s = lb.rescale_strided(3, acc, P, 2, 3 * 3 * N)  # [P][2][2][N], scale 2^80 / q_2 ~ 2^40
         del acc
+        mark("relin_rescale_s")
         rot = s.clone()
         idx = [self.elt_index[k] for k in self.first_steps]
         lb.hoisting_batch(2, rot, idx, [self.glk.keys[i] for i in idx])
@@ -294,6 +296,7 @@ class EncryptedKrum:
             e = self.elt_index[k]
             lb.rotate_batch(2, rot, e, self.glk.keys[e])
             lb.add(2, s, rot, out=s)
+        mark("rotate_sum_s")
         return s
 
     def client_sums(self, scores, pairs, n_clients):
@@ -318,16 +321,28 @@ class EncryptedKrum:
         return d, np.argsort(d)
 
     # -- one round ---------------------------------------------------------------------------------
-    def round(self, updates, rank=0, world_size=1, group=None, round_seed=0, keep=None):
+    def round(self, updates, rank=0, world_size=1, group=None, round_seed=0, keep=None, timing=None):
         """updates: [n_clients][dim] tensor (CUDA, pinned or pageable host).  Every rank runs this; rank 0 returns
-        (distances, order), the others (None, None).  The only collective is the gather of the score ciphertexts."""
+        (distances, order), the others (None, None).  The only collective is the gather of the score ciphertexts.
+        timing: optional dict; when given, the phases are separated by device synchronisations and timed."""
+        def mark(name, t=[None]):
+            if timing is None:
+                return
+            torch.cuda.synchronize()
+            now = time.perf_counter()
+            if t[0] is not None:
+                timing[name] = timing.get(name, 0.0) + now - t[0]
+            t[0] = now
+
+        mark("start")
         n_clients = updates.shape[0]
         schedule = pair_schedule(n_clients, world_size)
         mine = schedule[rank]
         cts = {}
         for c in clients_of(mine):
             cts[c] = self.encrypt_client(updates[c], client=c, round_seed=round_seed)
-        scores = self.pair_scores(cts, mine)
+        mark("encode_encrypt_s")
+        scores = self.pair_scores(cts, mine, mark)
         if keep is not None:
             keep["cts"], keep["scores"], keep["pairs"] = cts, scores, mine
         del cts
@@ -335,10 +350,13 @@ class EncryptedKrum:
             scores, pairs = gather_scores(scores, schedule, rank, world_size, group)
         else:
             pairs = mine
+        mark("gather_s")
         if rank != 0:
             return None, None
         sums = self.client_sums(scores, pairs, n_clients)
-        return self.select(sums)
+        out = self.select(sums)
+        mark("sum_decrypt_s")
+        return out
 
 
 def gather_scores(local, schedule, rank, world_size, group=None):
