@@ -179,6 +179,11 @@ LB_API int lb_encrypt_asymmetric(lb_context *ctx, const uint64_t *pk, const uint
  * raise a device flag reported by lb_check_status (the reference throws invalid_argument). */
 LB_API int lb_encode(lb_context *ctx, int size_l, const void *values, int dtype, size_t value_stride, int n_values, int sparse_slots,
               int batch, double scale, uint64_t *pt, void *stream);
+/* lb_encode followed by lb_encrypt_asymmetric for a batch, bit-identical to the two calls, with
+ * the plaintext kept in coefficient form and folded into the encryption's mod-down transform
+ * (three transforms and one round trip through HBM fewer per ciphertext): ct[batch][2][size_Q][N] */
+LB_API int lb_encode_encrypt(lb_context *ctx, const uint64_t *pk, const void *values, int dtype, size_t value_stride, int n_values,
+                      int sparse_slots, int batch, double scale, const uint8_t *seeds, uint64_t *ct, void *stream);
 /* out_complex: DEVICE array of sparse_slots (re, im) pairs */
 LB_API int lb_decode(lb_context *ctx, int size_l, const uint64_t *pt, double scale, int sparse_slots, double *out_complex, void *stream);
 /* Synchronises the stream and reports (then clears) conditions kernels could only flag. */

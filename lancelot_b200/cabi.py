@@ -289,6 +289,16 @@ class Context:
                             C.c_double(scale), _p(pt), _stream()))
         return pt
 
+    def encode_encrypt(self, pk, values, scale, seeds, sparse_slots, batch=1, out=None):
+        """fused encode + public-key encryption of a batch of messages [batch][n]"""
+        dt = {torch.float64: 0, torch.float32: 1, torch.complex128: 2}[values.dtype]
+        assert values.is_cuda and values.is_contiguous()
+        s, sp = self._seed(seeds, 2 * batch)
+        ct = out if out is not None else self.empty(batch, 2, self.size_Q, self.N)
+        check(lib.lb_encode_encrypt(self.h, _p(pk), C.c_void_p(values.data_ptr()), dt, C.c_size_t(values.shape[-1]), values.shape[-1],
+                                    sparse_slots, batch, C.c_double(scale), sp, _p(ct), _stream()))
+        return ct
+
     def decode(self, size_l, pt, scale, sparse_slots):
         out = torch.empty(sparse_slots, dtype=torch.complex128, device=pt.device)
         check(lib.lb_decode(self.h, size_l, _p(pt), C.c_double(scale), sparse_slots, C.c_void_p(out.data_ptr()), _stream()))

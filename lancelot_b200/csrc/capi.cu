@@ -472,7 +472,26 @@ int lb_encrypt_asymmetric(lb_context *h, const uint64_t *pk, const uint64_t *pt,
     if (rc) return rc;
     REQUIRE(pk && seeds && ct && batch >= 0, "operand is null");
     if (batch == 0) return LB_OK;
-    return encrypt_asymmetric(C(h), pk, pt, seeds, batch, ct, S(stream));
+    return encrypt_asymmetric(C(h), pk, pt, 0, seeds, batch, ct, S(stream));
+}
+
+int lb_encode_encrypt(lb_context *h, const uint64_t *pk, const void *values, int dtype, size_t value_stride, int n_values,
+                      int sparse_slots, int batch, double scale, const uint8_t *seeds, uint64_t *ct, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(pk && seeds && ct && batch >= 0 && (values || n_values == 0), "operand is null");
+    REQUIRE(dtype >= 0 && dtype <= 2, "unknown value type");
+    if (batch == 0) return LB_OK;
+    Context *c = C(h);
+    const int Q = c->hp.size_Q;
+    // coefficient-form plaintexts live behind the encryption scratch
+    const size_t enc_bytes = (encrypt_workspace_bytes(c, batch) + 255) / 256 * 256;
+    const size_t pt_bytes = ((size_t)batch * Q << c->hp.logN) * 8;
+    if ((rc = c->ensure_workspace(enc_bytes + pt_bytes))) return rc;
+    u64 *pt = reinterpret_cast<u64 *>(reinterpret_cast<uint8_t *>(c->ws) + enc_bytes);
+    if ((rc = encode(c, Q, values, dtype, (long)value_stride, n_values, sparse_slots, batch, scale, pt, c->d_status, 1, S(stream)))) return rc;
+    return encrypt_asymmetric(c, pk, pt, 1, seeds, batch, ct, S(stream));
 }
 
 // ---- encoder ------------------------------------------------------------------------------
@@ -485,7 +504,7 @@ int lb_encode(lb_context *h, int size_l, const void *values, int dtype, size_t v
     if ((rc = level_ok(C(h), size_l))) return rc;
     REQUIRE((values || n_values == 0) && pt && batch >= 0 && n_values >= 0, "values cannot be null");
     REQUIRE(dtype >= 0 && dtype <= 2, "unknown value type");
-    return encode(C(h), size_l, values, dtype, (long)value_stride, n_values, sparse_slots, batch, scale, pt, C(h)->d_status, S(stream));
+    return encode(C(h), size_l, values, dtype, (long)value_stride, n_values, sparse_slots, batch, scale, pt, C(h)->d_status, 0, S(stream));
 }
 
 int lb_decode(lb_context *h, int size_l, const uint64_t *pt, double scale, int sparse_slots, double *out_complex, void *stream)

@@ -83,6 +83,11 @@ struct NttJob {
     int digit_alpha = 0; // > 0: mod-up mode.  inner = digit j of ciphertext `outer`: source rows
                          // [j*alpha, min((j+1)*alpha, size_l)) of the outer block (the inner stride of
                          // src is not used), and the digit's own rows are skipped
+    // Forward prologue, second part: x <- x - presub[k] * presub_scal[rr] for groups with inner < presub_inner;
+    // presub rows are [outer][per_group][N] in coefficient form (a plaintext folded into the mod-down of an encryption)
+    const u64 *presub = nullptr, *presub_scal = nullptr, *presub_scal_s = nullptr;
+    long presub_outer = -1;
+    int presub_inner = 0;
     // Forward epilogue: dst = (aux - NTT(x)) * scal[rr] (+ add), the closing step of mod-down and rescale
     const u64 *aux = nullptr;
     long aux_group_stride = -1, aux_outer = -1;
@@ -140,8 +145,9 @@ int gen_switch_key(Context *ctx, const u64 *sk, const u64 *skp, const uint32_t *
 size_t encrypt_workspace_bytes(const Context *ctx, int batch);
 // encoder (encoder.cu)
 int encode(Context *ctx, int size_l, const void *values, int dtype, long value_stride, int n_values, int sparse_slots, int batch,
-           double scale, u64 *pt, int *d_status, cudaStream_t stream);
+           double scale, u64 *pt, int *d_status, int skip_ntt, cudaStream_t stream);
 int decode(Context *ctx, int size_l, const u64 *pt, double scale, int sparse_slots, double *out_complex, cudaStream_t stream);
-int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, const uint8_t *host_seeds, int batch, u64 *ct, cudaStream_t stream);
+int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, int pt_is_coeff, const uint8_t *host_seeds, int batch, u64 *ct,
+                       cudaStream_t stream);
 
 } // namespace lb

@@ -279,7 +279,7 @@ static int launch_encode(const EncK &k, int batch, size_t smem, cudaStream_t str
 
 // values -> plaintexts [batch][size_l][N] in NTT form
 int encode(Context *ctx, int size_l, const void *values, int dtype, long value_stride, int n_values, int sparse_slots, int batch,
-           double scale, u64 *pt, int *d_status, cudaStream_t stream)
+           double scale, u64 *pt, int *d_status, int skip_ntt, cudaStream_t stream)
 {
     const HostParams &hp = ctx->hp;
     int logn = 0;
@@ -332,6 +332,7 @@ int encode(Context *ctx, int size_l, const void *values, int dtype, long value_s
     default: set_error("slot count above 32768 is not supported"); return LB_ERR_INVALID_ARG;
     }
     if (rc) return rc;
+    if (skip_ntt) return LB_OK; // coefficient form, for an encryption that folds the plaintext in
     NttJob j;
     j.src = pt;
     j.dst = pt;

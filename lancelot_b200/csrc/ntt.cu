@@ -42,6 +42,9 @@ struct NttK {
     const u64 *bconv_mat;
     long mat_group_stride, mat_row_stride;
     const u64 *aux, *scal, *scal_s, *add, *fold;
+    const u64 *presub, *presub_scal, *presub_scal_s;
+    long presub_outer;
+    int presub_inner;
     int npass;
     unsigned char S[8];
 };
@@ -49,9 +52,13 @@ struct NttK {
 // one spare word per 16 keeps the stride-8 and stride-1 passes off the same banks
 LB_D int sidx(int i) { return i + (i >> 4); }
 
+// LAZY: the prime is below 2^58, so x may grow by 2q per stage over all seventeen possible
+// stages (bound 35q < 2^64) and the per-butterfly conditional subtraction is dropped; the
+// closing pass reduces once.
+template <bool LAZY>
 LB_D void fwd_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
 {
-    x = csub(x, q2);
+    if (!LAZY) x = csub(x, q2);
     const u64 t = shoup_lazy(y, w.x, w.y, q);
     y = x + q2 - t;
     x = x + t;
@@ -66,7 +73,7 @@ LB_D void inv_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
 }
 
 // S consecutive forward stages on 2^S register values; stage u uses twiddle (t0 << u) + block
-template <int S>
+template <int S, bool LAZY>
 LB_D void fwd_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ tw, const unsigned t0, const u64 q, const u64 q2)
 {
 #pragma unroll
@@ -76,7 +83,7 @@ LB_D void fwd_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ tw, const un
         for (int b = 0; b < (1 << u); ++b) {
             const ulonglong2 w = __ldg(tw + ((t0 << u) + b));
 #pragma unroll
-            for (int i = 0; i < half; ++i) fwd_bf(v[b * 2 * half + i], v[b * 2 * half + i + half], w, q, q2);
+            for (int i = 0; i < half; ++i) fwd_bf<LAZY>(v[b * 2 * half + i], v[b * 2 * half + i + half], w, q, q2);
         }
     }
 }
@@ -139,19 +146,27 @@ LB_D void store_contig(const u64 (&v)[R], u64 *p)
 struct FwdIn {
     const u64 *src;
     const u64 *mat;
+    const u64 *sub; // optional: the loaded value becomes value - sub[k] * sub_w (plaintext folded into a mod-down)
     int n, logN;
-    u64 q, r0, r1;
+    u64 q, r0, r1, sub_w, sub_ws;
 };
 
 LB_D u64 load_in(const FwdIn &in, const int idx)
 {
-    if (in.n == 0) return in.src[idx];
-    if (in.mat == nullptr) return barrett64(in.src[idx], in.q, in.r1);
-    u128d acc;
-    acc.lo = 0;
-    acc.hi = 0;
-    for (int i = 0; i < in.n; ++i) mac_wide(acc, in.src[((size_t)i << in.logN) + idx], __ldg(in.mat + i));
-    return barrett128(acc, in.q, in.r0, in.r1);
+    u64 v;
+    if (in.n == 0) {
+        v = in.src[idx];
+    } else if (in.mat == nullptr) {
+        v = barrett64(in.src[idx], in.q, in.r1);
+    } else {
+        u128d acc;
+        acc.lo = 0;
+        acc.hi = 0;
+        for (int i = 0; i < in.n; ++i) mac_wide(acc, in.src[((size_t)i << in.logN) + idx], __ldg(in.mat + i));
+        v = barrett128(acc, in.q, in.r0, in.r1);
+    }
+    if (in.sub) v = sub_mod(v, shoup_mul(in.sub[idx], in.sub_w, in.sub_ws, in.q), in.q);
+    return v;
 }
 
 struct FwdEpi {
@@ -160,7 +175,7 @@ struct FwdEpi {
     u64 scal, scal_s;
 };
 
-template <int S>
+template <int S, bool LAZY>
 LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, const int logn_loc, const int logt,
                    const unsigned cc, const ulonglong2 *tw, const u64 q, const u64 q2, const FwdEpi &epi)
 {
@@ -179,10 +194,15 @@ LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, 
 #pragma unroll
             for (int i = 0; i < R; ++i) v[i] = sm[sidx(base + (i << logst))];
         }
-        fwd_core<S>(v, tw, (cc << logm0) + hi, q, q2);
+        fwd_core<S, LAZY>(v, tw, (cc << logm0) + hi, q, q2);
         if (gdst) { // closing pass: logst == 0, the 2^S results are contiguous
+            if (LAZY) {
 #pragma unroll
-            for (int i = 0; i < R; ++i) v[i] = csub(csub(v[i], q2), q);
+                for (int i = 0; i < R; ++i) v[i] = barrett64(v[i], q, in.r1);
+            } else {
+#pragma unroll
+                for (int i = 0; i < R; ++i) v[i] = csub(csub(v[i], q2), q);
+            }
             if (epi.aux) {
                 u64 t[R];
                 load_contig<R>(t, epi.aux + base);
@@ -239,6 +259,10 @@ __global__ void __launch_bounds__(kNttThreads, 3) ntt_fwd_kernel(const NttK a)
     in.r1 = mc.r1;
     in.src = a.src + (src_row << logN);
     in.mat = mat;
+    in.sub = (a.presub && gi < a.presub_inner) ? a.presub + (((size_t)go * a.presub_outer + rr) << logN) : nullptr;
+    in.sub_w = in.sub ? a.presub_scal[rr] : 0;
+    in.sub_ws = in.sub ? a.presub_scal_s[rr] : 0;
+    const bool lazy = (q >> 58) == 0;
     u64 *dst = a.dst + (((size_t)go * a.dst_outer + (size_t)gi * a.dst_group_stride + rr) << logN);
     FwdEpi epi;
     epi.aux = a.aux ? a.aux + (((size_t)go * a.aux_outer + (size_t)gi * a.aux_group_stride + rr) << logN) : nullptr;
@@ -260,7 +284,8 @@ __global__ void __launch_bounds__(kNttThreads, 3) ntt_fwd_kernel(const NttK a)
             u64 v[C];
 #pragma unroll
             for (int k = 0; k < C; ++k) v[k] = load_in(in, j + k * n_loc);
-            fwd_core<LOGC>(v, tw, 1u, q, q2);
+            if (lazy) fwd_core<LOGC, true>(v, tw, 1u, q, q2);
+            else fwd_core<LOGC, false>(v, tw, 1u, q, q2);
 #pragma unroll
             for (int k = 0; k < C; ++k) remote[k][sidx(j)] = v[k];
         }
@@ -276,9 +301,15 @@ __global__ void __launch_bounds__(kNttThreads, 3) ntt_fwd_kernel(const NttK a)
         const int S = a.S[p];
         const bool from_global = (LOGC == 0 && p == 0);
         u64 *gdst = (p == a.npass - 1) ? dst + (size_t)c * n_loc : nullptr;
-        if (S == 3) fwd_pass<3>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
-        else if (S == 2) fwd_pass<2>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
-        else fwd_pass<1>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+        if (lazy) {
+            if (S == 3) fwd_pass<3, true>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+            else if (S == 2) fwd_pass<2, true>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+            else fwd_pass<1, true>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+        } else {
+            if (S == 3) fwd_pass<3, false>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+            else if (S == 2) fwd_pass<2, false>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+            else fwd_pass<1, false>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+        }
         logt -= S;
         if (p + 1 < a.npass) __syncthreads();
     }
@@ -473,6 +504,11 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     k.scal_s = job.scal_s;
     k.add = job.add;
     k.fold = job.fold;
+    k.presub = job.presub;
+    k.presub_scal = job.presub_scal;
+    k.presub_scal_s = job.presub_scal_s;
+    k.presub_outer = job.presub_outer >= 0 ? job.presub_outer : job.per_group;
+    k.presub_inner = job.presub ? job.presub_inner : 0;
     const int logc = hp.logN > kMaxLocalLog ? hp.logN - kMaxLocalLog : 0;
     const int logn_loc = hp.logN - logc;
     k.npass = plan_passes(logn_loc, forward, k.S);

@@ -143,25 +143,32 @@ int poly_galois(Context *ctx, int elt_idx, long rows, const u64 *src, u64 *dst, 
 
 // ---- Krum inner loop: acc += sum_c (b_c - a_c)^2 as a size-3 ciphertext ---------------------
 
-// One thread owns two coefficients of one limb and walks all chunks with 128-bit lazy
-// accumulators (products of residues below 2^61 leave room for 64 terms between reductions).
-__global__ void __launch_bounds__(kPolyThreads) krum_accumulate_kernel(const ulonglong2 *__restrict__ a, const ulonglong2 *__restrict__ b,
-                                                                       ulonglong2 *__restrict__ acc, const ModConst *__restrict__ mc,
+constexpr int kKrumThreads = 128;
+
+// One thread owns two coefficients of one limb and walks a slice of the chunks with 128-bit
+// lazy accumulators (products of residues below 2^61 leave room for 64 terms between
+// reductions).  The chunk axis is cut into gridDim.y slices so that a pair keeps every SM
+// busy even though one polynomial only has L * N / 2 vector elements; slices > 1 write
+// partial sums that krum_reduce_kernel adds.
+__global__ void __launch_bounds__(kKrumThreads) krum_accumulate_kernel(const ulonglong2 *__restrict__ a, const ulonglong2 *__restrict__ b,
+                                                                       ulonglong2 *__restrict__ out, const ModConst *__restrict__ mc,
                                                                        const int log_half_n, const long per_poly,
                                                                        const long stride_a, const long stride_b,
                                                                        const int n_chunks, const int accumulate)
 {
-    // per_poly = size_l * N / 2 vector elements; strides in vector elements between chunks
+    const int slices = gridDim.y, slice = blockIdx.y;
+    const int c_lo = (int)(((long)n_chunks * slice) / slices), c_hi = (int)(((long)n_chunks * (slice + 1)) / slices);
+    ulonglong2 *dst = out + (long)slice * 3 * per_poly;
     for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < per_poly; e += (long)gridDim.x * blockDim.x) {
         const ModConst m = mc[(int)(e >> log_half_n)];
         u64 r0x = 0, r0y = 0, r1x = 0, r1y = 0, r2x = 0, r2y = 0;
-        for (int c0 = 0; c0 < n_chunks; c0 += 64) {
-            const int c1 = min(c0 + 64, n_chunks);
+        for (int c0 = c_lo; c0 < c_hi; c0 += 64) {
+            const int c1 = min(c0 + 64, c_hi);
             u128d s0x = {0, 0}, s0y = {0, 0}, s1x = {0, 0}, s1y = {0, 0}, s2x = {0, 0}, s2y = {0, 0};
-#pragma unroll 2
+#pragma unroll 4
             for (int c = c0; c < c1; ++c) {
-                const ulonglong2 a0 = a[c * stride_a + e], a1 = a[c * stride_a + per_poly + e];
-                const ulonglong2 b0 = b[c * stride_b + e], b1 = b[c * stride_b + per_poly + e];
+                const ulonglong2 a0 = __ldcs(a + c * stride_a + e), a1 = __ldcs(a + c * stride_a + per_poly + e);
+                const ulonglong2 b0 = __ldcs(b + c * stride_b + e), b1 = __ldcs(b + c * stride_b + per_poly + e);
                 const u64 x0 = sub_mod(b0.x, a0.x, m.q), y0 = sub_mod(b0.y, a0.y, m.q);
                 const u64 x1 = sub_mod(b1.x, a1.x, m.q), y1 = sub_mod(b1.y, a1.y, m.q);
                 mac_wide(s0x, x0, x0);
@@ -181,15 +188,33 @@ __global__ void __launch_bounds__(kPolyThreads) krum_accumulate_kernel(const ulo
         // middle term is 2 x0 x1
         r1x = add_mod(r1x, r1x, m.q);
         r1y = add_mod(r1y, r1y, m.q);
-        if (accumulate) {
-            const ulonglong2 o0 = acc[e], o1 = acc[per_poly + e], o2 = acc[2 * per_poly + e];
+        if (accumulate && slices == 1) {
+            const ulonglong2 o0 = dst[e], o1 = dst[per_poly + e], o2 = dst[2 * per_poly + e];
             r0x = add_mod(r0x, o0.x, m.q); r0y = add_mod(r0y, o0.y, m.q);
             r1x = add_mod(r1x, o1.x, m.q); r1y = add_mod(r1y, o1.y, m.q);
             r2x = add_mod(r2x, o2.x, m.q); r2y = add_mod(r2y, o2.y, m.q);
         }
-        acc[e] = make_ulonglong2(r0x, r0y);
-        acc[per_poly + e] = make_ulonglong2(r1x, r1y);
-        acc[2 * per_poly + e] = make_ulonglong2(r2x, r2y);
+        dst[e] = make_ulonglong2(r0x, r0y);
+        dst[per_poly + e] = make_ulonglong2(r1x, r1y);
+        dst[2 * per_poly + e] = make_ulonglong2(r2x, r2y);
+    }
+}
+
+// acc (+)= sum over slices of partial[slice]; total = 3 * per_poly vector elements
+__global__ void __launch_bounds__(kPolyThreads) krum_reduce_kernel(const ulonglong2 *__restrict__ partial, ulonglong2 *__restrict__ acc,
+                                                                   const ModConst *__restrict__ mc, const int log_half_n,
+                                                                   const int size_l, const long total, const int slices,
+                                                                   const int accumulate)
+{
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const u64 q = mc[(int)((i >> log_half_n) % size_l)].q;
+        ulonglong2 r = accumulate ? acc[i] : make_ulonglong2(0, 0);
+        for (int s = 0; s < slices; ++s) {
+            const ulonglong2 p = partial[(long)s * total + i];
+            r.x = add_mod(r.x, p.x, q);
+            r.y = add_mod(r.y, p.y, q);
+        }
+        acc[i] = r;
     }
 }
 
@@ -198,12 +223,30 @@ int krum_accumulate(Context *ctx, int size_l, int n_chunks, const u64 *a, const 
 {
     const int log_half_n = ctx->hp.logN - 1;
     const long per_poly = (long)size_l << log_half_n;
-    long blocks = (per_poly + kPolyThreads - 1) / kPolyThreads;
+    const long blocks = (per_poly + kKrumThreads - 1) / kKrumThreads;
+    // enough slices for about eight resident blocks per SM, at least four chunks per slice
+    long slices = ((long)ctx->sm_count * 8 + blocks - 1) / blocks;
+    if (slices > n_chunks / 4) slices = n_chunks / 4;
+    if (slices > 32) slices = 32;
+    if (slices < 1) slices = 1;
+    ulonglong2 *dst = reinterpret_cast<ulonglong2 *>(acc);
+    if (slices > 1) {
+        int rc = ctx->ensure_workspace((size_t)slices * 3 * per_poly * sizeof(ulonglong2));
+        if (rc) return rc;
+        dst = reinterpret_cast<ulonglong2 *>(ctx->ws);
+    }
     count_launch();
-    krum_accumulate_kernel<<<(int)blocks, kPolyThreads, 0, stream>>>(
-        reinterpret_cast<const ulonglong2 *>(a), reinterpret_cast<const ulonglong2 *>(b), reinterpret_cast<ulonglong2 *>(acc),
-        ctx->d_mc, log_half_n, per_poly, chunk_stride_a / 2, chunk_stride_b / 2, n_chunks, accumulate);
+    krum_accumulate_kernel<<<dim3((unsigned)blocks, (unsigned)slices), kKrumThreads, 0, stream>>>(
+        reinterpret_cast<const ulonglong2 *>(a), reinterpret_cast<const ulonglong2 *>(b), dst, ctx->d_mc, log_half_n, per_poly,
+        chunk_stride_a / 2, chunk_stride_b / 2, n_chunks, accumulate);
     LB_CUDA(cudaGetLastError());
+    if (slices > 1) {
+        const long total = 3 * per_poly;
+        count_launch();
+        krum_reduce_kernel<<<grid_for(ctx, total, kPolyThreads), kPolyThreads, 0, stream>>>(
+            dst, reinterpret_cast<ulonglong2 *>(acc), ctx->d_mc, log_half_n, size_l, total, (int)slices, accumulate);
+        LB_CUDA(cudaGetLastError());
+    }
     return LB_OK;
 }
 

@@ -232,7 +232,10 @@ size_t encrypt_workspace_bytes(const Context *ctx, int batch)
 }
 
 // ct[b][2][Q][N] = moddown(pk u + e) (+ pt[b] on the first polynomial)
-int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, const uint8_t *host_seeds, int batch, u64 *ct, cudaStream_t stream)
+// pt_is_coeff: the plaintext rows are in coefficient form and are folded into the mod-down
+// transform ((cx - NTT(delta - P m)) P^-1 equals (cx - NTT(delta)) P^-1 + NTT(m) word for word)
+int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, int pt_is_coeff, const uint8_t *host_seeds, int batch, u64 *ct,
+                       cudaStream_t stream)
 {
     const HostParams &hp = ctx->hp;
     if (hp.size_P < 1) { set_error("public-key encryption needs a special prime"); return LB_ERR_INVALID_ARG; }
@@ -289,10 +292,18 @@ int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, const uint8_t
     fwd.scal = dl.p_inv;
     fwd.scal_s = dl.p_inv_s;
     fwd.split = 2;
-    fwd.add = pt;
-    fwd.add_group_stride = 0;
-    fwd.add_outer = Q;
-    fwd.add_inner = pt ? 1 : 0;
+    if (pt && pt_is_coeff) {
+        fwd.presub = pt;
+        fwd.presub_outer = Q;
+        fwd.presub_inner = 1;
+        fwd.presub_scal = ctx->d_p_mod_q;
+        fwd.presub_scal_s = ctx->d_p_mod_q_s;
+    } else {
+        fwd.add = pt;
+        fwd.add_group_stride = 0;
+        fwd.add_outer = Q;
+        fwd.add_inner = pt ? 1 : 0;
+    }
     return ntt_forward(ctx, fwd, stream);
 }
 

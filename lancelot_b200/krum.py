@@ -268,8 +268,31 @@ class EncryptedKrum:
         cts = self.lb.empty(chunks, 2, 3, self.N) if out is None else out
         for c0 in range(0, chunks, self.encrypt_batch):
             nb = min(self.encrypt_batch, chunks - c0)
-            pts = self.lb.encode(3, v[c0:c0 + nb], self.scale, sparse_slots=self.slots, batch=nb)
-            self.lb.encrypt_asymmetric(self.pk.data, pts, seeds[128 * c0:128 * (c0 + nb)], nb, out=cts[c0:c0 + nb])
+            self.lb.encode_encrypt(self.pk.data, v[c0:c0 + nb], self.scale, seeds[128 * c0:128 * (c0 + nb)], self.slots, nb,
+                                   out=cts[c0:c0 + nb])
+        return cts
+
+    def encrypt_and_share(self, updates, rank, world_size, group, round_seed, needed, mark=lambda name: None):
+        """Client c is encrypted by rank c % world_size; one all_gather per slice of world_size clients
+        hands every rank every ciphertext.  Only the clients in ``needed`` are kept."""
+        import torch.distributed as dist
+
+        n_clients, dim = updates.shape[0], updates.shape[1]
+        chunks = self.n_chunks(dim)
+        mine_buf = self.lb.empty(chunks, 2, 3, self.N)
+        cts = {}
+        for base in range(0, n_clients, world_size):
+            c = base + rank
+            if c < n_clients:
+                self.encrypt_client(updates[c], client=c, round_seed=round_seed, out=mine_buf)
+            mark("encode_encrypt_s")
+            recv = self.lb.empty(world_size, chunks, 2, 3, self.N)
+            dist.all_gather_into_tensor(recv.view(-1), mine_buf.view(-1), group=group)
+            for r in range(world_size):
+                if base + r < n_clients and (base + r) in needed:
+                    cts[base + r] = recv[r]
+            del recv
+            mark("ciphertext_allgather_s")
         return cts
 
     # -- server side ---------------------------------------------------------------------------
@@ -321,9 +344,13 @@ class EncryptedKrum:
         return d, np.argsort(d)
 
     # -- one round ---------------------------------------------------------------------------------
-    def round(self, updates, rank=0, world_size=1, group=None, round_seed=0, keep=None, timing=None):
+    def round(self, updates, rank=0, world_size=1, group=None, round_seed=0, keep=None, timing=None, exchange="allgather"):
         """updates: [n_clients][dim] tensor (CUDA, pinned or pageable host).  Every rank runs this; rank 0 returns
-        (distances, order), the others (None, None).  The only collective is the gather of the score ciphertexts.
+        (distances, order), the others (None, None).
+        exchange (only with several ranks): "allgather": every client is encrypted once, by rank
+        client % world_size, and the ciphertexts are all-gathered (NCCL over NVLink) so that encryption
+        scales with the ranks too; "reencrypt": every rank re-derives the ciphertexts of the clients its
+        pairs touch from the shared seeds, and the score gather is the only collective.
         timing: optional dict; when given, the phases are separated by device synchronisations and timed."""
         def mark(name, t=[None]):
             if timing is None:
@@ -339,9 +366,12 @@ class EncryptedKrum:
         schedule = pair_schedule(n_clients, world_size)
         mine = schedule[rank]
         cts = {}
-        for c in clients_of(mine):
-            cts[c] = self.encrypt_client(updates[c], client=c, round_seed=round_seed)
-        mark("encode_encrypt_s")
+        if world_size > 1 and exchange == "allgather":
+            cts = self.encrypt_and_share(updates, rank, world_size, group, round_seed, needed=set(clients_of(mine)), mark=mark)
+        else:
+            for c in clients_of(mine):
+                cts[c] = self.encrypt_client(updates[c], client=c, round_seed=round_seed)
+            mark("encode_encrypt_s")
         scores = self.pair_scores(cts, mine, mark)
         if keep is not None:
             keep["cts"], keep["scores"], keep["pairs"] = cts, scores, mine

@@ -322,3 +322,23 @@ def test_batched_keyswitch_matches_per_ciphertext(torch_cuda, logn, bits, size_p
     got = cabi.to_host(ctx.rescale(L, cabi.to_device(ct))).reshape(batch, 2, L - 1, n)
     for b in range(batch):
         assert np.array_equal(got[b], o.rescale(L, ct[b]))
+
+
+@pytest.mark.parametrize("logn,slots", [(12, 2048), (15, 16384), (13, 256)])
+def test_fused_encode_encrypt_equals_two_calls(torch_cuda, logn, slots):
+    import torch
+    from lancelot_b200 import cabi
+
+    o, ctx, mods = make(logn, [60, 40, 40, 60], 1)
+    rng = np.random.default_rng(31 + logn)
+    batch = 3
+    vals = torch.from_numpy(rng.normal(0, 0.01, (batch, slots)).astype(np.float32)).cuda()
+    s = seeds(rng, 1)
+    sk = ctx.gen_secret_key(s)
+    pk = ctx.gen_public_key(sk, seeds(rng, 1), seeds(rng, 1))
+    es = seeds(rng, 2 * batch)
+    scale = 2.0 ** 40
+    pts = ctx.encode(3, vals, scale, sparse_slots=slots, batch=batch)
+    two = cabi.to_host(ctx.encrypt_asymmetric(pk, pts, es, batch))
+    one = cabi.to_host(ctx.encode_encrypt(pk, vals, scale, es, slots, batch))
+    assert np.array_equal(one.reshape(-1), two.reshape(-1))
