@@ -26,8 +26,19 @@ namespace cg = cooperative_groups;
 
 namespace lb {
 
-constexpr int kNttThreads = 256;
-constexpr int kMaxLocalLog = 13; // 8192 points (64 KiB + padding) per CTA
+// Tunables (overridable at build time for sweeps): threads per CTA, CTAs per SM the register
+// allocation aims at, and log2 of the points one CTA keeps in shared memory.
+#ifndef LB_NTT_THREADS
+#define LB_NTT_THREADS 256
+#endif
+#ifndef LB_NTT_MINBLOCKS
+#define LB_NTT_MINBLOCKS 3
+#endif
+#ifndef LB_NTT_LOCAL_LOG
+#define LB_NTT_LOCAL_LOG 13
+#endif
+constexpr int kNttThreads = LB_NTT_THREADS;
+constexpr int kMaxLocalLog = LB_NTT_LOCAL_LOG; // 13: 8192 points (64 KiB + padding) per CTA
 
 struct NttK {
     const u64 *src;
@@ -223,7 +234,7 @@ LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, 
 }
 
 template <int LOGC>
-__global__ void __launch_bounds__(kNttThreads, 3) ntt_fwd_kernel(const NttK a)
+__global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(const NttK a)
 {
     extern __shared__ __align__(16) u64 sm[];
     constexpr int C = 1 << LOGC;
@@ -349,7 +360,7 @@ LB_D void inv_pass(u64 *sm, const u64 *gsrc, u64 *gdst, const int logn_loc, cons
 }
 
 template <int LOGC>
-__global__ void __launch_bounds__(kNttThreads, 3) ntt_inv_kernel(const NttK a)
+__global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_inv_kernel(const NttK a)
 {
     extern __shared__ __align__(16) u64 sm[];
     constexpr int C = 1 << LOGC;
@@ -447,6 +458,7 @@ static int launch(bool forward, const NttK &k, int rows, size_t smem, cudaStream
     if (!configured[forward]) {
         // largest request any ring degree makes: 8192 points plus one pad word per 16
         LB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
+        if (LOGC > 3) LB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
         configured[forward] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -519,6 +531,7 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     case 1: return launch<1>(forward, k, rows, smem, stream);
     case 2: return launch<2>(forward, k, rows, smem, stream);
     case 3: return launch<3>(forward, k, rows, smem, stream);
+    case 4: return launch<4>(forward, k, rows, smem, stream);
     default: set_error("poly_modulus_degree above 65536 is not supported"); return LB_ERR_INVALID_ARG;
     }
 }
