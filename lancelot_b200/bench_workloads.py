@@ -260,8 +260,21 @@ class HmultWorkload:
         resc = 2 * (L + L - 1) * n * 8
         return self.batch * (tensor + ks + resc)
 
+    def time_dominant_kernel(self, timed):
+        """the forward transform over as many limbs as one step's mod-up digits (beta x (L+P) per ciphertext),
+        the kernel with the largest share of a key switch"""
+        rows = self.batch * 3 * (self.L + self.P)
+        buf = self.torch.randint(0, 1 << 49, (rows, self.N), dtype=self.torch.int64, device=self.a.device)
+        groups = rows // (self.L + self.P)
+        fn = lambda: self.ctx.ntt_forward(buf, groups, self.L, self.P)
+        for _ in range(3):
+            fn()
+        ms, _ = timed(fn, 10)
+        self._kernel_bytes = 16 * self.N * rows
+        return ms / 10, "ntt_fwd_kernel<3>"
+
     def roofline_kernel_bytes(self):
-        return self.algorithmic_bytes_per_step()
+        return self._kernel_bytes
 
     def cpu_sample(self, threads):
         from oracle import binding

@@ -203,3 +203,14 @@ def test_reference_driver_flow_small():
         assert np.abs(np.array(w[:700]) - vecs[chosen]).max() < 1e-4
     finally:
         krum.set_slots(15)
+
+
+def test_cpp_class_layer_program():
+    """include/cahel_b200.hpp used like the reference's C++ examples use cahel.h (tests/cpp_api_check.cu)"""
+    import os
+    import subprocess
+
+    exe = os.path.join(os.path.dirname(os.path.abspath(__file__)), "cpp_api_check")
+    assert os.path.exists(exe), "run __graft_entry__.build() first"
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
