@@ -72,6 +72,9 @@ LB_API void lb_context_destroy(lb_context *ctx);
 LB_API int lb_context_get_modulus(const lb_context *ctx, int index, uint64_t *out);
 LB_API int lb_context_get_root(const lb_context *ctx, int index, uint64_t *out);
 LB_API int lb_context_get_galois_table(const lb_context *ctx, int elt_index, uint32_t *out_host_table);
+/* The context owns one scratch block that grows on demand (device synchronisation + cudaMalloc when it
+ * does).  Reserving the largest size up front keeps every later call allocation-free. */
+LB_API int lb_context_reserve_workspace(lb_context *ctx, size_t bytes);
 /* bytes of context-owned scratch a key switch at this level uses */
 LB_API size_t lb_keyswitch_workspace_bytes(const lb_context *ctx, int size_l);
 

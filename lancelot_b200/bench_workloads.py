@@ -101,6 +101,9 @@ class KrumWorkload:
             self.breakdown.update({k: v for k, v in timing.items() if k != "start"})
         self.result = (d, order)
         del ek
+        if timing:
+            self.torch.cuda.synchronize()
+            self.breakdown["teardown_s"] = time.perf_counter() - t2
 
     def step_gpu(self):
         self._round(self.updates)

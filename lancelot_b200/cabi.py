@@ -81,6 +81,9 @@ class Context:
         except Exception:
             pass
 
+    def reserve_workspace(self, nbytes):
+        check(lib.lb_context_reserve_workspace(self.h, C.c_size_t(int(nbytes))))
+
     def beta(self, size_l):
         return (size_l + self.size_P - 1) // self.size_P
 

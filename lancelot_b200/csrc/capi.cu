@@ -134,6 +134,13 @@ int lb_context_get_galois_table(const lb_context *h, int e, uint32_t *out)
     return LB_OK;
 }
 
+int lb_context_reserve_workspace(lb_context *h, size_t bytes)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    return C(h)->ensure_workspace(bytes);
+}
+
 size_t lb_keyswitch_workspace_bytes(const lb_context *h, int size_l)
 {
     const Context *c = C(h);

@@ -208,7 +208,7 @@ class EncryptedKrum:
 
     log_slots = log2(N/2).  chain {60,40,40 | 60}, scale 2^40 (byzantine_fl.py:432-448)."""
 
-    def __init__(self, log_slots=15, device=None, seed=None, encrypt_batch=64):
+    def __init__(self, log_slots=15, device=None, seed=None, encrypt_batch=64, workspace_bytes=5 << 29):
         self.log_slots = log_slots
         self.slots = 1 << log_slots
         self.N = 2 * self.slots
@@ -226,6 +226,7 @@ class EncryptedKrum:
         sec = cahel.sec_level_type.tc128 if self.N >= 8192 else cahel.sec_level_type.none
         self.context = cahel.context(params, True, sec, device=device)
         self.lb = self.context.lb
+        self.lb.reserve_workspace(workspace_bytes)
         self.steps = steps
         prev = cahel._seed_source
         if self._rng is not None:
