@@ -151,9 +151,18 @@ LB_API int lb_hoisting_batch(lb_context *ctx, int size_l, int batch, uint64_t *c
 LB_API int lb_krum_accumulate(lb_context *ctx, int size_l, int n_chunks, const uint64_t *a, const uint64_t *b,
                        size_t chunk_stride_a, size_t chunk_stride_b, uint64_t *acc, int accumulate, void *stream);
 
+/* Mask multiplication of the aggregation phase (lancelot-main-GPU/utils/byzantine_fl.py:371-429):
+ * out[c][3][size_l][N] = sum over clients k of ct_k[c] (x) mask_k (ckks_multiply + add_inplace per client
+ * in the reference).  client_cts: HOST array of n_clients device pointers, chunk c of client k at
+ * client_cts[k] + c * chunk_stride words; masks: [n_clients][2][size_l][N]. */
+LB_API int lb_mask_accumulate(lb_context *ctx, int size_l, int n_clients, int n_chunks, const uint64_t *const *client_cts,
+                       size_t chunk_stride, const uint64_t *masks, uint64_t *out, void *stream);
+
 /* ---- decryption (cahel-main/src/secretkey.cu:594-654 without the noise-flooding term) --------- */
 
 LB_API int lb_decrypt(lb_context *ctx, int size_l, int n_polys, const uint64_t *ct, const uint64_t *secret_key, uint64_t *pt, void *stream);
+/* `batch` ciphertexts of n_polys polynomials each, stored back to back -> pt[batch][size_l][N] */
+LB_API int lb_decrypt_batch(lb_context *ctx, int size_l, int n_polys, int batch, const uint64_t *ct, const uint64_t *secret_key, uint64_t *pt, void *stream);
 
 /* ---- samplers and keys (cahel-main/src/prng.cu:143-242, secretkey.cu:254-515) -----------------
  * The reference draws a fresh 64-byte seed from the operating system for every call
@@ -189,6 +198,8 @@ LB_API int lb_encode_encrypt(lb_context *ctx, const uint64_t *pk, const void *va
                       int sparse_slots, int batch, double scale, const uint8_t *seeds, uint64_t *ct, void *stream);
 /* out_complex: DEVICE array of sparse_slots (re, im) pairs */
 LB_API int lb_decode(lb_context *ctx, int size_l, const uint64_t *pt, double scale, int sparse_slots, double *out_complex, void *stream);
+/* pt[batch][size_l][N] -> out_complex[batch][sparse_slots] (re, im) pairs */
+LB_API int lb_decode_batch(lb_context *ctx, int size_l, int batch, const uint64_t *pt, double scale, int sparse_slots, double *out_complex, void *stream);
 /* Synchronises the stream and reports (then clears) conditions kernels could only flag. */
 LB_API int lb_check_status(lb_context *ctx, void *stream);
 

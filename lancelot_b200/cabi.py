@@ -307,5 +307,23 @@ class Context:
         check(lib.lb_decode(self.h, size_l, _p(pt), C.c_double(scale), sparse_slots, C.c_void_p(out.data_ptr()), _stream()))
         return out
 
+    def decode_batch(self, size_l, pts, scale, sparse_slots, batch):
+        out = torch.empty(batch, sparse_slots, dtype=torch.complex128, device=pts.device)
+        check(lib.lb_decode_batch(self.h, size_l, batch, _p(pts), C.c_double(scale), sparse_slots, C.c_void_p(out.data_ptr()), _stream()))
+        return out
+
+    def decrypt_batch(self, size_l, cts, sk, n_polys, batch):
+        pt = self.empty(batch, size_l, self.N)
+        check(lib.lb_decrypt_batch(self.h, size_l, n_polys, batch, _p(cts), _p(sk), _p(pt), _stream()))
+        return pt
+
+    def mask_accumulate(self, size_l, client_cts, masks, n_chunks):
+        """client_cts: list of [chunks][2][size_l][N] tensors; masks [n_clients][2][size_l][N] -> [chunks][3][size_l][N]"""
+        n = len(client_cts)
+        ptrs = (C.c_void_p * n)(*[t.data_ptr() for t in client_cts])
+        out = self.empty(n_chunks, 3, size_l, self.N)
+        check(lib.lb_mask_accumulate(self.h, size_l, n, n_chunks, ptrs, C.c_size_t(2 * size_l * self.N), _p(masks), _p(out), _stream()))
+        return out
+
     def check_status(self):
         check(lib.lb_check_status(self.h, _stream()))

@@ -376,7 +376,28 @@ int lb_decrypt(lb_context *h, int size_l, int n_polys, const uint64_t *ct, const
     if (rc) return rc;
     if ((rc = level_ok(C(h), size_l))) return rc;
     REQUIRE(ct && sk && pt && n_polys >= 1, "operand is null");
-    return poly_decrypt(C(h), size_l, n_polys, ct, sk, pt, S(stream));
+    return poly_decrypt(C(h), size_l, n_polys, 1, ct, sk, pt, S(stream));
+}
+
+int lb_decrypt_batch(lb_context *h, int size_l, int n_polys, int batch, const uint64_t *ct, const uint64_t *sk, uint64_t *pt, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    if ((rc = level_ok(C(h), size_l))) return rc;
+    REQUIRE(ct && sk && pt && n_polys >= 1 && batch >= 0, "operand is null");
+    if (batch == 0) return LB_OK;
+    return poly_decrypt(C(h), size_l, n_polys, batch, ct, sk, pt, S(stream));
+}
+
+int lb_mask_accumulate(lb_context *h, int size_l, int n_clients, int n_chunks, const uint64_t *const *client_cts, size_t chunk_stride,
+                       const uint64_t *masks, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    if ((rc = level_ok(C(h), size_l))) return rc;
+    REQUIRE(client_cts && masks && out && n_chunks >= 0, "operand is null");
+    REQUIRE(chunk_stride % 2 == 0, "chunk stride must be even");
+    return mask_accumulate(C(h), size_l, n_clients, n_chunks, client_cts, (long)chunk_stride, masks, out, S(stream));
 }
 
 // ---- samplers, keys, encryption ------------------------------------------------------------
@@ -520,7 +541,17 @@ int lb_decode(lb_context *h, int size_l, const uint64_t *pt, double scale, int s
     if (rc) return rc;
     if ((rc = level_ok(C(h), size_l))) return rc;
     REQUIRE(pt && out_complex, "destination cannot be null");
-    return decode(C(h), size_l, pt, scale, sparse_slots, out_complex, S(stream));
+    return decode(C(h), size_l, 1, pt, scale, sparse_slots, out_complex, S(stream));
+}
+
+int lb_decode_batch(lb_context *h, int size_l, int batch, const uint64_t *pt, double scale, int sparse_slots, double *out_complex, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    if ((rc = level_ok(C(h), size_l))) return rc;
+    REQUIRE(pt && out_complex && batch >= 0, "destination cannot be null");
+    if (batch == 0) return LB_OK;
+    return decode(C(h), size_l, batch, pt, scale, sparse_slots, out_complex, S(stream));
 }
 
 int lb_check_status(lb_context *h, void *stream)

@@ -115,7 +115,10 @@ int krum_accumulate(Context *ctx, int size_l, int n_chunks, const u64 *a, const 
 // drop the last limb of each polynomial: in [polys][L][N] -> out [polys][L-1][N]
 int poly_drop_last(Context *ctx, int size_l, int n_polys, const u64 *in, u64 *out, cudaStream_t stream);
 // pt = c0 + c1 s + c2 s^2 ...
-int poly_decrypt(Context *ctx, int size_l, int n_polys, const u64 *ct, const u64 *sk, u64 *pt, cudaStream_t stream);
+int poly_decrypt(Context *ctx, int size_l, int n_polys, int batch, const u64 *ct, const u64 *sk, u64 *pt, cudaStream_t stream);
+// out[c][3][L][N] = sum over clients k of ct_k[c] (x) mask_k; client_cts: host array of device pointers
+int mask_accumulate(Context *ctx, int size_l, int n_clients, int n_chunks, const u64 *const *client_cts, long chunk_stride,
+                    const u64 *masks, u64 *out, cudaStream_t stream);
 
 // key switching (keyswitch.cu); all buffers in NTT form, evk [dnum][2][size_QP][N]
 size_t keyswitch_workspace_bytes(const Context *ctx, int size_l);
@@ -146,7 +149,7 @@ size_t encrypt_workspace_bytes(const Context *ctx, int batch);
 // encoder (encoder.cu)
 int encode(Context *ctx, int size_l, const void *values, int dtype, long value_stride, int n_values, int sparse_slots, int batch,
            double scale, u64 *pt, int *d_status, int skip_ntt, cudaStream_t stream);
-int decode(Context *ctx, int size_l, const u64 *pt, double scale, int sparse_slots, double *out_complex, cudaStream_t stream);
+int decode(Context *ctx, int size_l, int batch, const u64 *pt, double scale, int sparse_slots, double *out_complex, cudaStream_t stream);
 int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, int pt_is_coeff, const uint8_t *host_seeds, int batch, u64 *ct,
                        cudaStream_t stream);
 

@@ -363,6 +363,8 @@ __global__ void __launch_bounds__(256) compose_kernel(cplx *__restrict__ out, co
     const unsigned n = 1u << logn;
     const int ratio_log = (logN - 1) - logn;
     const int W = size_l + 1;
+    coef += ((size_t)blockIdx.y * size_l) << logN;
+    out += (size_t)blockIdx.y * n;
     for (unsigned id = blockIdx.x * blockDim.x + threadIdx.x; id < 2 * n; id += gridDim.x * blockDim.x) {
         u64 v[kMaxComposeLimbs];
         for (int r = 0; r < size_l; ++r) {
@@ -418,6 +420,7 @@ __global__ void __launch_bounds__(256) fft_stage_kernel(cplx *__restrict__ a, co
     const unsigned half = 1u << (logn - 1);
     const int logRatio = logN + 1 - logn - 2;
     const unsigned M = 2u << logN;
+    a += (size_t)blockIdx.y << logn;
     for (unsigned tid = blockIdx.x * blockDim.x + threadIdx.x; tid < half; tid += gridDim.x * blockDim.x) {
         const unsigned pairs = 1u << u;
         const unsigned k = tid >> u, j = tid & (pairs - 1), g = 2 * k * pairs + j;
@@ -436,17 +439,19 @@ __global__ void __launch_bounds__(256) fft_stage_kernel(cplx *__restrict__ a, co
 __global__ void __launch_bounds__(256) bitrev_out_kernel(cplx *__restrict__ out, const cplx *__restrict__ in, const int logn)
 {
     const unsigned n = 1u << logn;
+    out += (size_t)blockIdx.y << logn;
+    in += (size_t)blockIdx.y << logn;
     for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
         out[__brev(i) >> (32 - logn)] = in[i];
 }
 
-size_t decode_workspace_bytes(const Context *ctx, int size_l)
+size_t decode_workspace_bytes(const Context *ctx, int size_l, int batch)
 {
-    return (((size_t)size_l << ctx->hp.logN) + ctx->hp.N) * 8 + 256;
+    return (((size_t)size_l << ctx->hp.logN) + ctx->hp.N) * 8 * batch + 256;
 }
 
 // plaintext [size_l][N] (NTT form) -> sparse_slots complex doubles on the device
-int decode(Context *ctx, int size_l, const u64 *pt, double scale, int sparse_slots, double *out_complex, cudaStream_t stream)
+int decode(Context *ctx, int size_l, int batch, const u64 *pt, double scale, int sparse_slots, double *out_complex, cudaStream_t stream)
 {
     const HostParams &hp = ctx->hp;
     if (size_l > kMaxComposeLimbs) { set_error("decode supports at most 8 limbs"); return LB_ERR_INVALID_ARG; }
@@ -457,14 +462,14 @@ int decode(Context *ctx, int size_l, const u64 *pt, double scale, int sparse_slo
         return LB_ERR_INVALID_ARG;
     }
     if (scale <= 0) { set_error("scale out of bounds"); return LB_ERR_INVALID_ARG; }
-    int rc = ctx->ensure_workspace(decode_workspace_bytes(ctx, size_l));
+    int rc = ctx->ensure_workspace(decode_workspace_bytes(ctx, size_l, batch));
     if (rc) return rc;
     u64 *coef = reinterpret_cast<u64 *>(ctx->ws);
-    cplx *buf = reinterpret_cast<cplx *>(coef + ((size_t)size_l << hp.logN));
+    cplx *buf = reinterpret_cast<cplx *>(coef + (((size_t)size_l * batch) << hp.logN));
     NttJob inv;
     inv.src = pt;
     inv.dst = coef;
-    inv.n_groups = 1;
+    inv.n_groups = batch;
     inv.per_group = size_l;
     inv.size_l = size_l;
     if ((rc = ntt_inverse(ctx, inv, stream))) return rc;
@@ -494,16 +499,16 @@ int decode(Context *ctx, int size_l, const u64 *pt, double scale, int sparse_slo
     }
     const unsigned n = (unsigned)sparse_slots;
     count_launch();
-    compose_kernel<<<(2 * n + 255) / 256, 256, 0, stream>>>(buf, coef, ctx->d_mc, cc, hp.logN, logn, size_l, 1.0 / scale);
+    compose_kernel<<<dim3((2 * n + 255) / 256, batch), 256, 0, stream>>>(buf, coef, ctx->d_mc, cc, hp.logN, logn, size_l, 1.0 / scale);
     LB_CUDA(cudaGetLastError());
     for (int iter = 0; iter < logn; ++iter) {
         const int u = logn - iter - 1;
         count_launch();
-        fft_stage_kernel<<<(n / 2 + 255) / 256, 256, 0, stream>>>(buf, ctx->d_croots, ctx->d_rot_group, hp.logN, logn, u);
+        fft_stage_kernel<<<dim3((n / 2 + 255) / 256, batch), 256, 0, stream>>>(buf, ctx->d_croots, ctx->d_rot_group, hp.logN, logn, u);
     }
     LB_CUDA(cudaGetLastError());
     count_launch();
-    bitrev_out_kernel<<<(n + 255) / 256, 256, 0, stream>>>(reinterpret_cast<cplx *>(out_complex), buf, logn);
+    bitrev_out_kernel<<<dim3((n + 255) / 256, batch), 256, 0, stream>>>(reinterpret_cast<cplx *>(out_complex), buf, logn);
     LB_CUDA(cudaGetLastError());
     return LB_OK;
 }

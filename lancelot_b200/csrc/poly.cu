@@ -250,6 +250,77 @@ int krum_accumulate(Context *ctx, int size_l, int n_chunks, const u64 *a, const 
     return LB_OK;
 }
 
+// ---- mask multiplication: out[c] = sum_k ct_k[c] (x) mask_k as size-3 ciphertexts -------------
+// (lancelot-main-GPU/utils/byzantine_fl.py:401-409: per chunk, multiply every client's ciphertext
+// with that client's mask ciphertext and add the products)
+
+constexpr int kMaxMaskClients = 64;
+
+struct MaskArgs {
+    const ulonglong2 *ct[kMaxMaskClients]; // client k, chunk c at ct[k] + c * chunk_stride
+    int n_clients;
+};
+
+__global__ void __launch_bounds__(kKrumThreads) mask_accumulate_kernel(const MaskArgs args, const ulonglong2 *__restrict__ masks,
+                                                                       ulonglong2 *__restrict__ out, const ModConst *__restrict__ mc,
+                                                                       const int log_half_n, const long per_poly,
+                                                                       const long chunk_stride)
+{
+    const long c = blockIdx.y;
+    ulonglong2 *dst = out + c * 3 * per_poly;
+    for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < per_poly; e += (long)gridDim.x * blockDim.x) {
+        const ModConst m = mc[(int)(e >> log_half_n)];
+        u64 r0x = 0, r0y = 0, r1x = 0, r1y = 0, r2x = 0, r2y = 0;
+        for (int k0 = 0; k0 < args.n_clients; k0 += 32) {
+            const int k1 = min(k0 + 32, args.n_clients);
+            u128d s0x = {0, 0}, s0y = {0, 0}, s1x = {0, 0}, s1y = {0, 0}, s2x = {0, 0}, s2y = {0, 0};
+#pragma unroll 2
+            for (int k = k0; k < k1; ++k) {
+                const ulonglong2 *a = args.ct[k] + c * chunk_stride;
+                const ulonglong2 *b = masks + (long)k * 2 * per_poly;
+                const ulonglong2 a0 = __ldcs(a + e), a1 = __ldcs(a + per_poly + e);
+                const ulonglong2 b0 = b[e], b1 = b[per_poly + e];
+                mac_wide(s0x, a0.x, b0.x);
+                mac_wide(s0y, a0.y, b0.y);
+                mac_wide(s1x, a0.x, b1.x);
+                mac_wide(s1x, a1.x, b0.x);
+                mac_wide(s1y, a0.y, b1.y);
+                mac_wide(s1y, a1.y, b0.y);
+                mac_wide(s2x, a1.x, b1.x);
+                mac_wide(s2y, a1.y, b1.y);
+            }
+            r0x = add_mod(r0x, barrett128(s0x, m.q, m.r0, m.r1), m.q);
+            r0y = add_mod(r0y, barrett128(s0y, m.q, m.r0, m.r1), m.q);
+            r1x = add_mod(r1x, barrett128(s1x, m.q, m.r0, m.r1), m.q);
+            r1y = add_mod(r1y, barrett128(s1y, m.q, m.r0, m.r1), m.q);
+            r2x = add_mod(r2x, barrett128(s2x, m.q, m.r0, m.r1), m.q);
+            r2y = add_mod(r2y, barrett128(s2y, m.q, m.r0, m.r1), m.q);
+        }
+        dst[e] = make_ulonglong2(r0x, r0y);
+        dst[per_poly + e] = make_ulonglong2(r1x, r1y);
+        dst[2 * per_poly + e] = make_ulonglong2(r2x, r2y);
+    }
+}
+
+int mask_accumulate(Context *ctx, int size_l, int n_clients, int n_chunks, const u64 *const *client_cts, long chunk_stride,
+                    const u64 *masks, u64 *out, cudaStream_t stream)
+{
+    if (n_clients < 1 || n_clients > kMaxMaskClients) { set_error("mask multiplication supports 1 to 64 clients per call"); return LB_ERR_INVALID_ARG; }
+    if (n_chunks <= 0) return LB_OK;
+    MaskArgs args;
+    args.n_clients = n_clients;
+    for (int k = 0; k < n_clients; ++k) args.ct[k] = reinterpret_cast<const ulonglong2 *>(client_cts[k]);
+    const int log_half_n = ctx->hp.logN - 1;
+    const long per_poly = (long)size_l << log_half_n;
+    long blocks = (per_poly + kKrumThreads - 1) / kKrumThreads;
+    count_launch();
+    mask_accumulate_kernel<<<dim3((unsigned)blocks, (unsigned)n_chunks), kKrumThreads, 0, stream>>>(
+        args, reinterpret_cast<const ulonglong2 *>(masks), reinterpret_cast<ulonglong2 *>(out), ctx->d_mc, log_half_n, per_poly,
+        chunk_stride / 2);
+    LB_CUDA(cudaGetLastError());
+    return LB_OK;
+}
+
 // ---- level drop and decryption ---------------------------------------------------------
 
 int poly_drop_last(Context *ctx, int size_l, int n_polys, const u64 *in, u64 *out, cudaStream_t stream)
@@ -263,26 +334,29 @@ int poly_drop_last(Context *ctx, int size_l, int n_polys, const u64 *in, u64 *ou
 // cahel-main/src/secretkey.cu:594-631 without the noise-flooding term
 __global__ void __launch_bounds__(kPolyThreads) decrypt_kernel(const u64 *__restrict__ ct, const u64 *__restrict__ sk,
                                                                u64 *__restrict__ pt, const ModConst *__restrict__ mc,
-                                                               const int logN, const int n_polys, const long per_poly)
+                                                               const int logN, const int n_polys, const long per_poly, const long total)
 {
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < per_poly; i += (long)gridDim.x * blockDim.x) {
+    for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+        const long b = idx / per_poly, i = idx - b * per_poly;
         const ModConst m = mc[(int)(i >> logN)];
+        const u64 *c = ct + b * n_polys * per_poly;
         const u64 s = sk[i];
-        u64 sp = s, r = ct[i];
+        u64 sp = s, r = c[i];
         for (int p = 1; p < n_polys; ++p) {
-            r = add_mod(r, mul_mod(ct[p * per_poly + i], sp, m.q, m.r0, m.r1), m.q);
+            r = add_mod(r, mul_mod(c[p * per_poly + i], sp, m.q, m.r0, m.r1), m.q);
             sp = mul_mod(sp, s, m.q, m.r0, m.r1);
         }
-        pt[i] = r;
+        pt[idx] = r;
     }
 }
 
-int poly_decrypt(Context *ctx, int size_l, int n_polys, const u64 *ct, const u64 *sk, u64 *pt, cudaStream_t stream)
+int poly_decrypt(Context *ctx, int size_l, int n_polys, int batch, const u64 *ct, const u64 *sk, u64 *pt, cudaStream_t stream)
 {
     const long per_poly = (long)size_l << ctx->hp.logN;
+    const long total = per_poly * batch;
     count_launch();
-    decrypt_kernel<<<grid_for(ctx, per_poly, kPolyThreads), kPolyThreads, 0, stream>>>(ct, sk, pt, ctx->d_mc, ctx->hp.logN, n_polys,
-                                                                                       per_poly);
+    decrypt_kernel<<<grid_for(ctx, total, kPolyThreads), kPolyThreads, 0, stream>>>(ct, sk, pt, ctx->d_mc, ctx->hp.logN, n_polys,
+                                                                                    per_poly, total);
     LB_CUDA(cudaGetLastError());
     return LB_OK;
 }

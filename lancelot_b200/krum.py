@@ -344,6 +344,31 @@ class EncryptedKrum:
         d = [self.decrypt_slot0(sums[i]) for i in range(sums.shape[0])]
         return d, np.argsort(d)
 
+    # -- aggregation phase (byzantine_fl.py:371-429, and the trimmed-mean variant) ---------------------------
+    def encrypt_constant(self, value):
+        """one ciphertext whose slots all hold ``value`` (the reference's Enc(1) / Enc(0) masks)"""
+        dev = "cuda:%d" % self.lb.device
+        v = torch.full((1, self.slots), float(value), dtype=torch.float64, device=dev)
+        seeds = cahel._seeds(2)
+        return self.lb.encode_encrypt(self.pk.data, v, self.scale, seeds, self.slots, 1).reshape(2, 3, self.N)
+
+    def aggregate(self, cts, selected, dim):
+        """cts: dict client -> [chunks][2][3][N] for ALL clients 0..n-1.  Multiplies every client's ciphertexts
+        with its mask ciphertext (Enc(1/k) for the k selected clients, Enc(0) for the rest), adds the products,
+        decrypts the size-3 results and decodes them: the plaintext average of the selected updates.
+        With one selected client this is GPU_mul_mask_weight; with several it is an encrypted trimmed mean."""
+        lb, N = self.lb, self.N
+        n_clients = len(cts)
+        chunks = cts[0].shape[0]
+        one = self.encrypt_constant(1.0 / len(selected))
+        zero = self.encrypt_constant(0.0)
+        masks = torch.stack([one if k in set(int(x) for x in selected) else zero for k in range(n_clients)]).contiguous()
+        acc = lb.mask_accumulate(3, [cts[k] for k in range(n_clients)], masks, chunks)
+        pts = lb.decrypt_batch(3, acc, self.sk.data, 3, chunks)
+        del acc
+        vals = lb.decode_batch(3, pts, self.scale * self.scale, self.slots, chunks)
+        return vals.real.reshape(-1)[:dim]
+
     # -- one round ---------------------------------------------------------------------------------
     def round(self, updates, rank=0, world_size=1, group=None, round_seed=0, keep=None, timing=None, exchange="allgather"):
         """updates: [n_clients][dim] tensor (CUDA, pinned or pageable host).  Every rank runs this; rank 0 returns

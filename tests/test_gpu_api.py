@@ -214,3 +214,37 @@ def test_cpp_class_layer_program():
     assert os.path.exists(exe), "run __graft_entry__.build() first"
     r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout + r.stderr
+
+
+def test_mask_multiplication_selects_and_averages():
+    """aggregation phase: one-hot mask returns the chosen client's update, a k-hot mask with 1/k their mean"""
+    import torch
+
+    from lancelot_b200 import cabi, krum
+
+    torch.manual_seed(5)
+    ek = krum.EncryptedKrum(log_slots=10, seed=3)
+    n_clients, dim = 4, 2 * 1024 + 77
+    upd = (torch.randn(n_clients, dim, dtype=torch.float32) * 0.3).cuda()
+    cts = {c: ek.encrypt_client(upd[c], client=c) for c in range(n_clients)}
+    got = ek.aggregate(cts, [2], dim)
+    assert float((got - upd[2].double()).abs().max()) < 1e-6
+    got = ek.aggregate(cts, [0, 3], dim)
+    assert float((got - (upd[0].double() + upd[3].double()) / 2).abs().max()) < 1e-6
+    # the fused accumulation equals multiply + add_inplace per client of the stepwise API, bit for bit
+    import lancelot_b200.pycahel as cahel
+    ctx = ek.context
+    one, zero = ek.encrypt_constant(1.0), ek.encrypt_constant(0.0)
+    masks = torch.stack([zero, one, zero, zero]).contiguous()
+    fused = ek.lb.mask_accumulate(3, [cts[k] for k in range(n_clients)], masks, cts[0].shape[0])
+    acc = None
+    for k in range(n_clients):
+        a, m, t = cahel.ciphertext(ctx), cahel.ciphertext(ctx), cahel.ciphertext(ctx)
+        a.data, a.size, a.chain_index, a.scale = cts[k][1].clone(), 2, 1, ek.scale
+        m.data, m.size, m.chain_index, m.scale = masks[k].clone(), 2, 1, ek.scale
+        cahel.multiply(ctx, a, m, t)
+        if acc is None:
+            acc = t
+        else:
+            cahel.add_inplace(ctx, acc, t)
+    assert torch.equal(acc.data.reshape(-1), fused[1].reshape(-1))
