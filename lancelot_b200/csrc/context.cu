@@ -21,9 +21,28 @@ int cuda_fail(cudaError_t e, const char *what)
     return LB_ERR_CUDA;
 }
 
+// One scratch block per device survives its context: a caller that builds a fresh context
+// every round (as the reference's Krum driver does) then pays for cudaMalloc / cudaFree of
+// gigabytes only once per process.
+constexpr int kMaxCachedDevices = 64;
+static void *g_ws_cache[kMaxCachedDevices];
+static size_t g_ws_cache_bytes[kMaxCachedDevices];
+
 int Context::ensure_workspace(size_t bytes)
 {
     if (bytes <= ws_bytes) return LB_OK;
+    if (device >= 0 && device < kMaxCachedDevices && g_ws_cache[device] && g_ws_cache_bytes[device] >= bytes) {
+        // work queued on the previous block (if any) must finish before it is dropped
+        if (ws) {
+            LB_CUDA(cudaDeviceSynchronize());
+            LB_CUDA(cudaFree(ws));
+        }
+        ws = g_ws_cache[device];
+        ws_bytes = g_ws_cache_bytes[device];
+        g_ws_cache[device] = nullptr;
+        g_ws_cache_bytes[device] = 0;
+        return LB_OK;
+    }
     // the old block may still be in use by work queued earlier
     LB_CUDA(cudaDeviceSynchronize());
     if (ws) LB_CUDA(cudaFree(ws));
@@ -178,7 +197,16 @@ void context_destroy(Context *ctx)
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
     for (void *p : ctx->owned) cudaFree(p);
-    if (ctx->ws) cudaFree(ctx->ws);
+    if (ctx->ws) {
+        const int d = ctx->device;
+        if (d >= 0 && d < kMaxCachedDevices && ctx->ws_bytes > g_ws_cache_bytes[d]) {
+            if (g_ws_cache[d]) cudaFree(g_ws_cache[d]);
+            g_ws_cache[d] = ctx->ws;
+            g_ws_cache_bytes[d] = ctx->ws_bytes;
+        } else {
+            cudaFree(ctx->ws);
+        }
+    }
     delete ctx;
 }
 

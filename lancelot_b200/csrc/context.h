@@ -88,6 +88,10 @@ struct NttJob {
     const u64 *presub = nullptr, *presub_scal = nullptr, *presub_scal_s = nullptr;
     long presub_outer = -1;
     int presub_inner = 0;
+    // Encryption only (one special prime): esmall[outer][N] is the small error polynomial as signed bytes;
+    // the single source row is (INTT(pk u) on p); the load forms ((x + e) mod p) mod q_rr - e
+    const signed char *esmall = nullptr;
+    u64 esmall_p = 0;
     // Forward epilogue: dst = (aux - NTT(x)) * scal[rr] (+ add), the closing step of mod-down and rescale
     const u64 *aux = nullptr;
     long aux_group_stride = -1, aux_outer = -1;

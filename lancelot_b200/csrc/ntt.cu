@@ -37,6 +37,9 @@ namespace lb {
 #ifndef LB_NTT_LOCAL_LOG
 #define LB_NTT_LOCAL_LOG 13
 #endif
+#ifndef LB_NTT_MAX_RADIX_LOG
+#define LB_NTT_MAX_RADIX_LOG 3 // stages per register pass: 3 = radix 8, 4 = radix 16
+#endif
 constexpr int kNttThreads = LB_NTT_THREADS;
 constexpr int kMaxLocalLog = LB_NTT_LOCAL_LOG; // 13: 8192 points (64 KiB + padding) per CTA
 
@@ -54,6 +57,8 @@ struct NttK {
     long mat_group_stride, mat_row_stride;
     const u64 *aux, *scal, *scal_s, *add, *fold;
     const u64 *presub, *presub_scal, *presub_scal_s;
+    const signed char *esmall;
+    u64 esmall_p;
     long presub_outer;
     int presub_inner;
     int npass;
@@ -158,8 +163,9 @@ struct FwdIn {
     const u64 *src;
     const u64 *mat;
     const u64 *sub; // optional: the loaded value becomes value - sub[k] * sub_w (plaintext folded into a mod-down)
+    const signed char *es; // optional small error polynomial e of an encryption (see the encrypt path)
     int n, logN;
-    u64 q, r0, r1, sub_w, sub_ws;
+    u64 q, r0, r1, sub_w, sub_ws, es_p;
 };
 
 LB_D u64 load_in(const FwdIn &in, const int idx)
@@ -168,7 +174,18 @@ LB_D u64 load_in(const FwdIn &in, const int idx)
     if (in.n == 0) {
         v = in.src[idx];
     } else if (in.mat == nullptr) {
-        v = barrett64(in.src[idx], in.q, in.r1);
+        u64 x = in.src[idx];
+        if (in.es) {
+            // x is INTT(pk u) on the special prime p: add e mod p first (INTT is linear, so this is the
+            // special limb of pk u + e), convert, then take e off again on this prime, because the
+            // caller's aux rows hold pk u without e:  (pk u + e) - NTT(delta) = pk u - NTT(delta - e)
+            const int ev = in.es[idx];
+            x = add_mod(x, ev < 0 ? in.es_p - (u64)(-ev) : (u64)ev, in.es_p);
+            v = barrett64(x, in.q, in.r1);
+            v = sub_mod(v, ev < 0 ? in.q - (u64)(-ev) : (u64)ev, in.q);
+        } else {
+            v = barrett64(x, in.q, in.r1);
+        }
     } else {
         u128d acc;
         acc.lo = 0;
@@ -273,6 +290,8 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(
     in.sub = (a.presub && gi < a.presub_inner) ? a.presub + (((size_t)go * a.presub_outer + rr) << logN) : nullptr;
     in.sub_w = in.sub ? a.presub_scal[rr] : 0;
     in.sub_ws = in.sub ? a.presub_scal_s[rr] : 0;
+    in.es = a.esmall ? a.esmall + ((size_t)go << logN) : nullptr;
+    in.es_p = a.esmall_p;
     const bool lazy = (q >> 58) == 0;
     u64 *dst = a.dst + (((size_t)go * a.dst_outer + (size_t)gi * a.dst_group_stride + rr) << logN);
     FwdEpi epi;
@@ -313,11 +332,13 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(
         const bool from_global = (LOGC == 0 && p == 0);
         u64 *gdst = (p == a.npass - 1) ? dst + (size_t)c * n_loc : nullptr;
         if (lazy) {
-            if (S == 3) fwd_pass<3, true>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+            if (LB_NTT_MAX_RADIX_LOG >= 4 && S == 4) fwd_pass<LB_NTT_MAX_RADIX_LOG >= 4 ? 4 : 3, true>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+            else if (S == 3) fwd_pass<3, true>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
             else if (S == 2) fwd_pass<2, true>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
             else fwd_pass<1, true>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
         } else {
-            if (S == 3) fwd_pass<3, false>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+            if (LB_NTT_MAX_RADIX_LOG >= 4 && S == 4) fwd_pass<LB_NTT_MAX_RADIX_LOG >= 4 ? 4 : 3, false>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+            else if (S == 3) fwd_pass<3, false>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
             else if (S == 2) fwd_pass<2, false>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
             else fwd_pass<1, false>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
         }
@@ -394,11 +415,13 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_inv_kernel(
         u64 *gdst = closing ? dst : nullptr;
         if (p > 0) __syncthreads();
         if (closing) {
-            if (S == 3) inv_pass<3, true>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
+            if (LB_NTT_MAX_RADIX_LOG >= 4 && S == 4) inv_pass<LB_NTT_MAX_RADIX_LOG >= 4 ? 4 : 3, true>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
+            else if (S == 3) inv_pass<3, true>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
             else if (S == 2) inv_pass<2, true>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
             else inv_pass<1, true>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
         } else {
-            if (S == 3) inv_pass<3, false>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
+            if (LB_NTT_MAX_RADIX_LOG >= 4 && S == 4) inv_pass<LB_NTT_MAX_RADIX_LOG >= 4 ? 4 : 3, false>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
+            else if (S == 3) inv_pass<3, false>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
             else if (S == 2) inv_pass<2, false>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
             else inv_pass<1, false>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
         }
@@ -428,17 +451,19 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_inv_kernel(
 
 static int plan_passes(int logn_loc, bool forward, unsigned char *S)
 {
-    // Radix-8 wherever possible; the pass that touches global memory with contiguous
-    // per-thread data (forward: last, inverse: first) is kept at radix 8 when it fits.
+    // As few register passes as the radix allows; the pass that touches global memory with
+    // contiguous per-thread data (forward: last, inverse: first) takes the largest radix.
+    const int R = LB_NTT_MAX_RADIX_LOG;
     int n = 0, rem = logn_loc;
-    int edge = rem >= 3 ? 3 : rem;
+    int edge = rem >= R ? R : rem;
     rem -= edge;
     unsigned char mid[8];
     int nm = 0;
-    while (rem > 0) {
-        if (rem == 4) { mid[nm++] = 2; mid[nm++] = 2; rem = 0; }
-        else if (rem >= 3) { mid[nm++] = 3; rem -= 3; }
-        else { mid[nm++] = (unsigned char)rem; rem = 0; }
+    const int count = (rem + R - 1) / R; // number of middle passes
+    for (int i = 0; i < count; ++i) {
+        const int s = (rem + (count - i) - 1) / (count - i); // spread the stages evenly
+        mid[nm++] = (unsigned char)s;
+        rem -= s;
     }
     if (forward) {
         for (int i = 0; i < nm; ++i) S[n++] = mid[i];
@@ -517,6 +542,8 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     k.add = job.add;
     k.fold = job.fold;
     k.presub = job.presub;
+    k.esmall = job.esmall;
+    k.esmall_p = job.esmall_p;
     k.presub_scal = job.presub_scal;
     k.presub_scal_s = job.presub_scal_s;
     k.presub_outer = job.presub_outer >= 0 ? job.presub_outer : job.per_group;

@@ -103,6 +103,20 @@ __global__ void __launch_bounds__(kSampThreads) sample_uniform_kernel(u64 *__res
     }
 }
 
+// the same small polynomial as one signed byte per coefficient (|value| <= 21)
+__global__ void __launch_bounds__(kSampThreads) sample_small_i8_kernel(signed char *__restrict__ out, const uint32_t *__restrict__ seeds,
+                                                                       const int seed_stride, const int kind, const int logN,
+                                                                       const long total)
+{
+    const long n_mask = (1L << logN) - 1;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long b = i >> logN, k = i & n_mask;
+        uint32_t x[16];
+        prng_block(seeds + seed_stride * b, (u64)k, x);
+        out[i] = (signed char)small_value(kind, x[0], x[1]);
+    }
+}
+
 static inline int grid_for(const Context *ctx, long items)
 {
     long need = (items + kSampThreads - 1) / kSampThreads;
@@ -204,6 +218,20 @@ int gen_switch_key(Context *ctx, const u64 *sk, const u64 *skp, const uint32_t *
 
 // ---- public-key encryption (cahel-main/src/secretkey.cu:47-170) -----------------------------
 
+// cx[b][p][QP][N] = pk[p] * u[b]   (the error term joins inside the mod-down transform)
+__global__ void __launch_bounds__(kSampThreads) encrypt_product_kernel(u64 *__restrict__ cx, const u64 *__restrict__ pk,
+                                                                       const u64 *__restrict__ u, const ModConst *__restrict__ mc,
+                                                                       const int logN, const long poly, const long total)
+{
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long b = i / poly, k = i - b * poly;
+        const ModConst m = mc[(int)(k >> logN)];
+        const u64 uu = u[i];
+#pragma unroll
+        for (int p = 0; p < 2; ++p) cx[(2 * b + p) * poly + k] = mul_mod(uu, pk[p * poly + k], m.q, m.r0, m.r1);
+    }
+}
+
 // cx[b][p][QP][N] = pk[p] * u[b] + e[b]   (u and e already in NTT form; e0 == e1)
 __global__ void __launch_bounds__(kSampThreads) encrypt_combine_kernel(u64 *__restrict__ cx, const u64 *__restrict__ pk,
                                                                        const u64 *__restrict__ u, const u64 *__restrict__ e,
@@ -251,18 +279,37 @@ int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, int pt_is_coe
     // seeds arrive as [batch][2][64 bytes]: (ternary seed, error seed) per ciphertext
     LB_CUDA(cudaMemcpyAsync(seeds, host_seeds, (size_t)batch * 128, cudaMemcpyHostToDevice, stream));
     if ((rc = sample_small(ctx, 0, seeds, 32, batch, Q, P, u, stream))) return rc;
-    if ((rc = sample_small(ctx, 1, seeds + 16, 32, batch, Q, P, e, stream))) return rc;
-    NttJob j;
-    j.src = u;
-    j.dst = u;
-    j.n_groups = 2 * batch; // u and e are adjacent
-    j.per_group = QP;
-    j.size_l = Q;
-    if ((rc = ntt_forward(ctx, j, stream))) return rc;
+    const bool fold_e = (P == 1); // one special prime: the error never needs its own transforms
     const long total = batch * poly;
-    count_launch();
-    encrypt_combine_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(cx, pk, u, e, ctx->d_mc, hp.logN, poly, total);
-    LB_CUDA(cudaGetLastError());
+    if (fold_e) {
+        const long n_small = (long)batch << hp.logN;
+        count_launch();
+        sample_small_i8_kernel<<<grid_for(ctx, n_small), kSampThreads, 0, stream>>>(reinterpret_cast<signed char *>(e), seeds + 16, 32, 1,
+                                                                                   hp.logN, n_small);
+        LB_CUDA(cudaGetLastError());
+        NttJob j;
+        j.src = u;
+        j.dst = u;
+        j.n_groups = batch;
+        j.per_group = QP;
+        j.size_l = Q;
+        if ((rc = ntt_forward(ctx, j, stream))) return rc;
+        count_launch();
+        encrypt_product_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(cx, pk, u, ctx->d_mc, hp.logN, poly, total);
+        LB_CUDA(cudaGetLastError());
+    } else {
+        if ((rc = sample_small(ctx, 1, seeds + 16, 32, batch, Q, P, e, stream))) return rc;
+        NttJob j;
+        j.src = u;
+        j.dst = u;
+        j.n_groups = 2 * batch; // u and e are adjacent
+        j.per_group = QP;
+        j.size_l = Q;
+        if ((rc = ntt_forward(ctx, j, stream))) return rc;
+        count_launch();
+        encrypt_combine_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(cx, pk, u, e, ctx->d_mc, hp.logN, poly, total);
+        LB_CUDA(cudaGetLastError());
+    }
     // moddown of 2*batch polynomials from QP to Q
     const DevLevel &dl = ctx->d_level[Q];
     NttJob inv;
@@ -292,6 +339,10 @@ int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, int pt_is_coe
     fwd.scal = dl.p_inv;
     fwd.scal_s = dl.p_inv_s;
     fwd.split = 2;
+    if (fold_e) {
+        fwd.esmall = reinterpret_cast<const signed char *>(e);
+        fwd.esmall_p = hp.q[Q];
+    }
     if (pt && pt_is_coeff) {
         fwd.presub = pt;
         fwd.presub_outer = Q;
