@@ -37,26 +37,59 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs.  Uses NVML in-process
+    (a query costs microseconds); falls back to the nvidia-smi command line when the module is missing."""
 
-    def __init__(self, index=0):
-        self.index = index
-        self.rows = []
+    def __init__(self, index=0, period=0.25):
+        self.index, self.period = index, period
+        self.sm, self.sm_max, self.reasons = [], None, set()
         self._stop = threading.Event()
         self._t = None
 
-    def _run(self):
+    def _run_nvml(self):
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+        self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+        names = {"hw_slowdown": getattr(pynvml, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(pynvml, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(pynvml, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(pynvml, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            self.sm.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+            try:
+                mask = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+            except Exception:
+                mask = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+            for nm, bit in names.items():
+                if mask & bit:
+                    self.reasons.add(nm)
+            self._stop.wait(self.period)
+
+    def _run_smi(self):
         q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits"],
                                      capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([x.strip() for x in out.split(",")])
+                r = [x.strip() for x in out.split(",")]
+                if r and r[0].isdigit():
+                    self.sm.append(int(r[0]))
+                    self.sm_max = int(r[1])
+                    for i, nm in enumerate(names):
+                        if len(r) > 2 + i and r[2 + i].lower().startswith("active"):
+                            self.reasons.add(nm)
             except Exception:
                 pass
-            self._stop.wait(0.2)
+            self._stop.wait(1.0)
+
+    def _run(self):
+        try:
+            self._run_nvml()
+        except Exception:
+            self._run_smi()
 
     def __enter__(self):
         self._t = threading.Thread(target=self._run, daemon=True)
@@ -68,11 +101,8 @@ class ClockSampler:
         self._t.join(timeout=6)
 
     def summary(self):
-        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
-        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [nm for i, nm in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+        sm = sorted(self.sm)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons),
                 "samples": len(sm)}
 
 
@@ -138,6 +168,14 @@ class NttWorkload:
     def roofline_kernel_bytes(self):
         # one launch transforms the whole batch once
         return 16 * self.N * self.limbs * self.batch
+
+    def int_roof(self):
+        """integer-pipe ceiling of the transform: the register-only butterfly rate converted to transform traffic"""
+        rate = self.ctx.butterfly_rate(lazy=True)  # the 50-bit primes of this workload take the lazy butterfly
+        per_limb = (self.N // 2) * self.logn
+        gbs = rate / per_limb * 16 * self.N / 1e9
+        step_s = self.algorithmic_bytes_per_step() / 1e9
+        return {"butterflies_per_s": rate, "equivalent_transform_gbs": gbs, "note": "min(HBM, INT) roof for the NTT is this figure"}
 
     def cpu_sample(self, threads):
         """forward + inverse of one polynomial (24 limbs) on the CPU checker"""
@@ -280,6 +318,8 @@ def run_gpu(args, wl):
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "traffic": getattr(wl, "ncu_traffic_bytes", None), "kernel": kname, "peak_kind": "of " + peak_kind},
                 "cpu_baseline": cpu, "clocks": clocks.summary(), "parity_check": ok}
+        if hasattr(wl, "int_roof"):
+            line["int_roof"] = wl.int_roof()
         if getattr(wl, "breakdown", None):
             line["breakdown"] = wl.breakdown
         if hasattr(wl, "rel_err"):

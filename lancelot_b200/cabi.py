@@ -100,6 +100,11 @@ class Context:
         check(lib.lb_context_get_galois_table(self.h, i, out.ctypes.data_as(C.POINTER(C.c_uint32))))
         return out
 
+    def butterfly_rate(self, lazy=False):
+        out = C.c_double()
+        check(lib.lb_probe_butterfly_rate(self.h, int(lazy), C.byref(out)))
+        return float(out.value)
+
     # -- transforms
     def ntt_forward(self, data, n_groups, size_l, size_p):
         check(lib.lb_ntt_forward(self.h, _p(data), n_groups, size_l, size_p, _stream()))

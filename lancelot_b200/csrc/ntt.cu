@@ -563,6 +563,69 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     }
 }
 
+// ---- integer-pipe ceiling probe ---------------------------------------------------------------
+// The same forward butterfly as the transform kernels, on registers only (no shared or global
+// memory traffic inside the loop), at the transform kernels' occupancy.  Its rate is the ceiling
+// the 64-bit Shoup arithmetic sets for any NTT schedule on this GPU; one limb of N points needs
+// (N/2) log2 N butterflies for 16 N bytes of traffic.
+template <bool LAZY>
+__global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) butterfly_probe_kernel(u64 *out, const u64 q, const u64 w0, const u64 ws0,
+                                                                                       const int iters)
+{
+    u64 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (u64)threadIdx.x * 8 + i + blockIdx.x;
+    const u64 q2 = q << 1;
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int s = 0; s < 3; ++s) {
+            const int half = 4 >> s;
+#pragma unroll
+            for (int b = 0; b < (1 << s); ++b) {
+                const ulonglong2 w = make_ulonglong2(w0 + threadIdx.x + b, ws0 + threadIdx.x + s);
+#pragma unroll
+                for (int i = 0; i < half; ++i) fwd_bf<LAZY>(v[b * 2 * half + i], v[b * 2 * half + i + half], w, q, q2);
+            }
+        }
+        if (LAZY) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] &= 0x03FFFFFFFFFFFFFFull; // keep the lazy range bounded, as the closing reduction does
+        }
+    }
+    u64 acc = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc ^= v[i];
+    out[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = acc;
+}
+
+int probe_butterfly_rate(Context *ctx, int lazy, double *butterflies_per_second)
+{
+    const int blocks = ctx->sm_count * LB_NTT_MINBLOCKS, iters = 2000;
+    int rc = ctx->ensure_workspace((size_t)blocks * kNttThreads * sizeof(u64));
+    if (rc) return rc;
+    u64 *out = reinterpret_cast<u64 *>(ctx->ws);
+    const u64 q = ctx->hp.q[0], w = q / 3, ws = h_shoup(w, q);
+    cudaEvent_t e0, e1;
+    LB_CUDA(cudaEventCreate(&e0));
+    LB_CUDA(cudaEventCreate(&e1));
+    float best = 1e30f;
+    for (int rep = 0; rep < 4; ++rep) {
+        LB_CUDA(cudaEventRecord(e0, 0));
+        count_launch();
+        if (lazy) butterfly_probe_kernel<true><<<blocks, kNttThreads>>>(out, q, w, ws, iters);
+        else butterfly_probe_kernel<false><<<blocks, kNttThreads>>>(out, q, w, ws, iters);
+        LB_CUDA(cudaEventRecord(e1, 0));
+        LB_CUDA(cudaEventSynchronize(e1));
+        float ms = 0;
+        LB_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        if (rep > 0 && ms < best) best = ms;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *butterflies_per_second = (double)blocks * kNttThreads * iters * 12.0 / (best * 1e-3);
+    return LB_OK;
+}
+
 int ntt_forward(Context *ctx, const NttJob &job, cudaStream_t stream) { return run(ctx, job, true, stream); }
 int ntt_inverse(Context *ctx, const NttJob &job, cudaStream_t stream) { return run(ctx, job, false, stream); }
 
