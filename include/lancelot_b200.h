@@ -83,10 +83,13 @@ LB_API size_t lb_keyswitch_workspace_bytes(const lb_context *ctx, int size_l);
 /* data: n_groups x (size_l + size_p) limbs; inside a group the first size_l limbs use data
  * primes 0..size_l-1 and the next size_p the special primes.  In place. */
 LB_API int lb_ntt_forward(lb_context *ctx, uint64_t *data, int n_groups, int size_l, int size_p, void *stream);
-/* Measures the register-only rate of the transform's 64-bit Shoup butterfly on this GPU (butterflies per second,
- * synchronous, a few milliseconds): the integer-pipe ceiling of any NTT schedule; lazy selects the variant used
- * for primes below 2^58.  One limb needs (N/2) log2 N butterflies for its 16 N bytes. */
-LB_API int lb_probe_butterfly_rate(lb_context *ctx, int lazy, double *butterflies_per_second);
+/* Measures the register-only rate of one of the transform's butterfly variants on this GPU (butterflies per
+ * second, synchronous, a few milliseconds): the arithmetic ceiling of any NTT schedule for primes of that size.
+ * variant: 0 integer Shoup product with conditional subtraction (primes of 58 bits and more), 1 the same without
+ * it (below 2^58), 2 / 3 quotient estimated on the FP64 pipe with / without conditional subtraction (primes below
+ * 2^50 / 2^46), -1 the variant the context's first prime takes.  One limb needs (N/2) log2 N butterflies for
+ * its 16 N bytes. */
+LB_API int lb_probe_butterfly_rate(lb_context *ctx, int variant, double *butterflies_per_second);
 LB_API int lb_ntt_inverse(lb_context *ctx, uint64_t *data, int n_groups, int size_l, int size_p, void *stream);
 
 /* ---- element-wise evaluator ops (cahel-main/src/evaluate.cu:15,42,199; polymath.cu:16-227) ---- */

@@ -100,9 +100,10 @@ class Context:
         check(lib.lb_context_get_galois_table(self.h, i, out.ctypes.data_as(C.POINTER(C.c_uint32))))
         return out
 
-    def butterfly_rate(self, lazy=False):
+    def butterfly_rate(self, variant=-1):
+        """register-only butterfly rate; variant 0..3 (integer strict / lazy, FP64-assisted strict / lazy), -1: the first prime's"""
         out = C.c_double()
-        check(lib.lb_probe_butterfly_rate(self.h, int(lazy), C.byref(out)))
+        check(lib.lb_probe_butterfly_rate(self.h, int(variant), C.byref(out)))
         return float(out.value)
 
     # -- transforms

@@ -165,12 +165,12 @@ static int ntt_rows(lb_context *h, uint64_t *data, int n_groups, int size_l, int
     return fwd ? ntt_forward(c, job, S(stream)) : ntt_inverse(c, job, S(stream));
 }
 
-int lb_probe_butterfly_rate(lb_context *h, int lazy, double *butterflies_per_second)
+int lb_probe_butterfly_rate(lb_context *h, int mode, double *butterflies_per_second)
 {
     int rc = bind(h);
     if (rc) return rc;
     REQUIRE(butterflies_per_second, "destination cannot be null");
-    return probe_butterfly_rate(C(h), lazy, butterflies_per_second);
+    return probe_butterfly_rate(C(h), mode, butterflies_per_second);
 }
 
 int lb_ntt_forward(lb_context *h, uint64_t *data, int n_groups, int size_l, int size_p, void *stream)

@@ -105,7 +105,7 @@ struct NttJob {
 
 int ntt_forward(Context *ctx, const NttJob &job, cudaStream_t stream);
 int ntt_inverse(Context *ctx, const NttJob &job, cudaStream_t stream);
-int probe_butterfly_rate(Context *ctx, int lazy, double *butterflies_per_second);
+int probe_butterfly_rate(Context *ctx, int mode, double *butterflies_per_second);
 
 // element-wise kernels (poly.cu).  Rows are limbs of N residues; row r uses prime r % size_l.
 enum PolyOp { OP_ADD = 0, OP_SUB = 1, OP_MUL = 2, OP_NEG = 3 };

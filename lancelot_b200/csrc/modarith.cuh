@@ -64,8 +64,39 @@ inline u64 h_shoup(u64 w, u64 q)
 inline u64 h_shoup(u64 w, u64 q) { return (u64)(((u128)w << 64) / q); }
 #endif
 
+// ---- quotient estimate on the FP64 pipe ---------------------------------------------------
+// For primes below 2^50 the transform kernels estimate the quotient floor(x w / q) with one
+// double-precision fused multiply-add instead of a 64 x 64 -> 128 bit integer product: the
+// integer multiplier then only has to produce the two low products x w and Q q.  The twiddle
+// tables of such primes carry the double w / q in place of the Shoup quotient.
+constexpr u64 kFpPrimeLimit = u64(1) << 50; // operands stay below 4q <= 2^52, the exact-integer range of the trick
+constexpr u64 kFpLazyLimit = u64(1) << 46;  // 35 q < 2^52: no conditional subtraction for seventeen stages
+
+inline u64 h_fp_quot(u64 w, u64 q)
+{
+    const double d = (double)w / (double)q; // both exact in double, so the quotient is correctly rounded
+    u64 bits;
+    static_assert(sizeof(bits) == sizeof(d), "double is 64 bits");
+    __builtin_memcpy(&bits, &d, sizeof(bits));
+    return bits;
+}
+// the second word of a twiddle-table entry for prime q
+inline u64 h_twiddle_quot(u64 w, u64 q) { return q < kFpPrimeLimit ? h_fp_quot(w, q) : h_shoup(w, q); }
+
 #if defined(__CUDACC__)
 // ---- device arithmetic ----------------------------------------------------------------
+
+// x * w - Q * q with Q within one of x w / q, as a two's-complement value in (-q, q).
+// Needs x < 2^52, w < q < 2^50 and wq = bits of the double nearest to w / q.  Error budget:
+// x is exact in double; the rounding of w / q moves the product by less than 2^52 * 2^-53 =
+// 0.5; the fused multiply-add into 2^52 rounds once to an integer, another 0.5 at most.
+LB_D u64 fp_mul_signed(u64 x, u64 w, u64 wq, u64 q)
+{
+    const double xd = __longlong_as_double((long long)(x | 0x4330000000000000ull)) - 4503599627370496.0;
+    const double u = __fma_rn(xd, __longlong_as_double((long long)wq), 4503599627370496.0);
+    const u64 Q = (u64)__double_as_longlong(u) & 0x000FFFFFFFFFFFFFull;
+    return x * w - Q * q;
+}
 
 // x * w mod q in [0, 2q) for any 64-bit x, given ws = floor(w 2^64 / q), w < q.
 LB_D u64 shoup_lazy(u64 x, u64 w, u64 ws, u64 q)

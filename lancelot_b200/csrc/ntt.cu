@@ -40,6 +40,14 @@ namespace lb {
 #ifndef LB_NTT_MAX_RADIX_LOG
 #define LB_NTT_MAX_RADIX_LOG 3 // stages per register pass: 3 = radix 8, 4 = radix 16
 #endif
+#ifndef LB_NTT_WARP_LOCAL
+#define LB_NTT_WARP_LOCAL 1 // 0: every register pass is shared out over the whole CTA
+#endif
+#ifndef LB_NTT_GROUP_UNROLL
+#define LB_NTT_GROUP_UNROLL 1 // register groups of one pass a thread keeps in flight
+#endif
+#define LB_PRAGMA_(x) _Pragma(#x)
+#define LB_UNROLL(n) LB_PRAGMA_(unroll n)
 constexpr int kNttThreads = LB_NTT_THREADS;
 constexpr int kMaxLocalLog = LB_NTT_LOCAL_LOG; // 13: 8192 points (64 KiB + padding) per CTA
 
@@ -62,34 +70,58 @@ struct NttK {
     long presub_outer;
     int presub_inner;
     int npass;
+    int nwide; // passes whose butterflies cross warp chunks (forward: the first nwide, inverse: the last nwide)
+    int wlog;  // log2 of the contiguous chunk one warp owns in the other passes
     unsigned char S[8];
 };
 
 // one spare word per 16 keeps the stride-8 and stride-1 passes off the same banks
 LB_D int sidx(int i) { return i + (i >> 4); }
 
-// LAZY: the prime is below 2^58, so x may grow by 2q per stage over all seventeen possible
-// stages (bound 35q < 2^64) and the per-butterfly conditional subtraction is dropped; the
-// closing pass reduces once.
-template <bool LAZY>
-LB_D void fwd_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
+// Butterfly variants, chosen per prime:
+//   integer, strict: Shoup product on the integer multiplier, values kept in [0, 4q);
+//   integer, lazy:   the prime is below 2^58, so x may grow by 2q per stage over all seventeen
+//                    possible stages (bound 35q < 2^64) and the per-butterfly conditional
+//                    subtraction is dropped; the closing pass reduces once;
+//   FP64, strict / lazy: primes below 2^50 / 2^46, quotient estimated on the FP64 pipe
+//                    (fp_mul_signed), which takes the 64 x 64 -> 128 bit product off the
+//                    integer multiplier, the pipe that bounds these kernels.
+// Every variant leaves the same canonical residues in memory.
+enum { kIntStrict = 0, kIntLazy = 1, kFpStrict = 2, kFpLazy = 3 };
+
+LB_D int butterfly_mode(const u64 q)
 {
-    if (!LAZY) x = csub(x, q2);
-    const u64 t = shoup_lazy(y, w.x, w.y, q);
-    y = x + q2 - t;
-    x = x + t;
+    if (q < kFpLazyLimit) return kFpLazy;
+    if (q < kFpPrimeLimit) return kFpStrict;
+    return (q >> 58) == 0 ? kIntLazy : kIntStrict;
 }
 
+template <int MODE>
+LB_D void fwd_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
+{
+    if (MODE == kIntStrict || MODE == kFpStrict) x = csub(x, q2);
+    if (MODE == kFpStrict || MODE == kFpLazy) {
+        const u64 r = fp_mul_signed(y, w.x, w.y, q), xq = x + q; // r in (-q, q)
+        y = xq - r;
+        x = xq + r;
+    } else {
+        const u64 t = shoup_lazy(y, w.x, w.y, q);
+        y = x + q2 - t;
+        x = x + t;
+    }
+}
+
+template <bool FP>
 LB_D void inv_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
 {
     const u64 s = csub(x + y, q2);
-    const u64 d = x + q2 - y;
+    const u64 d = x + q2 - y; // below 4q
     x = s;
-    y = shoup_lazy(d, w.x, w.y, q);
+    y = FP ? fp_mul_signed(d, w.x, w.y, q) + q : shoup_lazy(d, w.x, w.y, q);
 }
 
 // S consecutive forward stages on 2^S register values; stage u uses twiddle (t0 << u) + block
-template <int S, bool LAZY>
+template <int S, int MODE>
 LB_D void fwd_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ tw, const unsigned t0, const u64 q, const u64 q2)
 {
 #pragma unroll
@@ -99,14 +131,14 @@ LB_D void fwd_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ tw, const un
         for (int b = 0; b < (1 << u); ++b) {
             const ulonglong2 w = __ldg(tw + ((t0 << u) + b));
 #pragma unroll
-            for (int i = 0; i < half; ++i) fwd_bf<LAZY>(v[b * 2 * half + i], v[b * 2 * half + i + half], w, q, q2);
+            for (int i = 0; i < half; ++i) fwd_bf<MODE>(v[b * 2 * half + i], v[b * 2 * half + i + half], w, q, q2);
         }
     }
 }
 
 // S consecutive inverse stages; stage u pairs distance 2^u and uses twiddle (tb >> u) + block.
 // CLOSE: the last of them is the transform's last stage and carries the N^-1 scaling.
-template <int S, bool CLOSE>
+template <int S, bool CLOSE, bool FP>
 LB_D void inv_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ itw, const unsigned tb, const u64 q, const u64 q2,
                    const u64 cn, const u64 cns, const u64 cw, const u64 cws)
 {
@@ -126,7 +158,7 @@ LB_D void inv_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ itw, const u
             } else {
                 const ulonglong2 w = __ldg(itw + ((tb >> u) + b));
 #pragma unroll
-                for (int i = 0; i < dist; ++i) inv_bf(v[b * 2 * dist + i], v[b * 2 * dist + i + dist], w, q, q2);
+                for (int i = 0; i < dist; ++i) inv_bf<FP>(v[b * 2 * dist + i], v[b * 2 * dist + i + dist], w, q, q2);
             }
         }
     }
@@ -203,15 +235,40 @@ struct FwdEpi {
     u64 scal, scal_s;
 };
 
-template <int S, bool LAZY>
+// Work split of one register pass.  A pass whose largest butterfly span exceeds a warp's chunk
+// is shared out over the whole CTA; in every other pass a warp keeps to the groups of its own
+// contiguous 2^wlog-point chunk, so that consecutive such passes only need a warp-level barrier.
+struct PassSplit {
+    int first, end, step;
+};
+
+template <int S>
+LB_D PassSplit pass_split(const int logn_loc, const int wlog)
+{
+    PassSplit ps;
+    if (wlog < 0) {
+        ps.first = threadIdx.x;
+        ps.end = 1 << (logn_loc - S);
+        ps.step = kNttThreads;
+    } else {
+        const int gpw = 1 << (wlog - S), warp = threadIdx.x >> 5;
+        ps.first = warp * gpw + (threadIdx.x & 31);
+        ps.end = (warp + 1) * gpw;
+        ps.step = 32;
+    }
+    return ps;
+}
+
+template <int S, int MODE>
 LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, const int logn_loc, const int logt,
-                   const unsigned cc, const ulonglong2 *tw, const u64 q, const u64 q2, const FwdEpi &epi)
+                   const unsigned cc, const ulonglong2 *tw, const u64 q, const u64 q2, const FwdEpi &epi, const int wlog)
 {
     constexpr int R = 1 << S;
     const int logst = logt - (S - 1);
-    const int groups = 1 << (logn_loc - S);
     const int logm0 = logn_loc - 1 - logt;
-    for (int g = threadIdx.x; g < groups; g += kNttThreads) {
+    const PassSplit ps = pass_split<S>(logn_loc, wlog);
+    LB_UNROLL(LB_NTT_GROUP_UNROLL)
+    for (int g = ps.first; g < ps.end; g += ps.step) {
         const int lo = g & ((1 << logst) - 1), hi = g >> logst;
         const int base = (hi << (logt + 1)) + lo;
         u64 v[R];
@@ -222,9 +279,9 @@ LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, 
 #pragma unroll
             for (int i = 0; i < R; ++i) v[i] = sm[sidx(base + (i << logst))];
         }
-        fwd_core<S, LAZY>(v, tw, (cc << logm0) + hi, q, q2);
+        fwd_core<S, MODE>(v, tw, (cc << logm0) + hi, q, q2);
         if (gdst) { // closing pass: logst == 0, the 2^S results are contiguous
-            if (LAZY) {
+            if (MODE == kIntLazy || MODE == kFpLazy) {
 #pragma unroll
                 for (int i = 0; i < R; ++i) v[i] = barrett64(v[i], q, in.r1);
             } else {
@@ -250,14 +307,33 @@ LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, 
     }
 }
 
-template <int LOGC>
-__global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(const NttK a)
+template <int MODE>
+LB_D void fwd_pass_any(const int S, u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, const int logn_loc, const int logt,
+                       const unsigned cc, const ulonglong2 *tw, const u64 q, const u64 q2, const FwdEpi &epi, const int wlog)
 {
-    extern __shared__ __align__(16) u64 sm[];
-    constexpr int C = 1 << LOGC;
-    const int row = blockIdx.x >> LOGC;
+    constexpr int RMAX = LB_NTT_MAX_RADIX_LOG >= 4 ? 4 : 3;
+    if (RMAX == 4 && S == 4) fwd_pass<RMAX, MODE>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog);
+    else if (S == 3) fwd_pass<3, MODE>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog);
+    else if (S == 2) fwd_pass<2, MODE>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog);
+    else fwd_pass<1, MODE>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog);
+}
+
+// Everything a forward CTA derives from its row index: where the limb comes from, which prime
+// and tables it uses, and what the closing pass does with the result.
+struct FwdRow {
+    FwdIn in;
+    FwdEpi epi;
+    u64 *dst;
+    const ulonglong2 *tw;
+    u64 q;
+    int mode;
+};
+
+// false: this row has nothing to transform (uniform over the cluster that owns the row)
+LB_D bool fwd_row_setup(const NttK &a, const int row, FwdRow &r)
+{
     const int grp = row / a.per_group, rr = row - grp * a.per_group;
-    if (rr >= a.skip_lo && rr < a.skip_hi) return; // uniform over the cluster
+    if (rr >= a.skip_lo && rr < a.skip_hi) return false;
     const int go = grp / a.split, gi = grp - go * a.split;
     int n_in = a.bconv_n;
     size_t src_row = (size_t)go * a.src_outer + a.src_row_off;
@@ -265,7 +341,7 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(
     if (a.digit_alpha > 0) {
         const int s = gi * a.digit_alpha;
         const int e = min(s + a.digit_alpha, a.size_l);
-        if (rr >= s && rr < e) return; // the digit's own limbs stay in NTT form
+        if (rr >= s && rr < e) return false; // the digit's own limbs stay in NTT form
         src_row += s;
         n_in = e - s;
         if (mat) mat += (size_t)gi * a.mat_group_stride;
@@ -276,13 +352,13 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(
     if (mat) mat += (size_t)rr * a.mat_row_stride;
     const int tbl = rr < a.size_l ? rr + a.tbl_off : a.size_Q + (rr - a.size_l);
     const ModConst mc = a.mc[tbl];
-    const u64 q = mc.q, q2 = q << 1;
-    const int logN = a.logN, logn_loc = logN - LOGC, n_loc = 1 << logn_loc;
-    const ulonglong2 *tw = a.tw + ((size_t)tbl << logN);
-    FwdIn in;
+    const int logN = a.logN;
+    r.q = mc.q;
+    r.tw = a.tw + ((size_t)tbl << logN);
+    FwdIn &in = r.in;
     in.n = n_in;
     in.logN = logN;
-    in.q = q;
+    in.q = mc.q;
     in.r0 = mc.r0;
     in.r1 = mc.r1;
     in.src = a.src + (src_row << logN);
@@ -292,34 +368,61 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(
     in.sub_ws = in.sub ? a.presub_scal_s[rr] : 0;
     in.es = a.esmall ? a.esmall + ((size_t)go << logN) : nullptr;
     in.es_p = a.esmall_p;
-    const bool lazy = (q >> 58) == 0;
-    u64 *dst = a.dst + (((size_t)go * a.dst_outer + (size_t)gi * a.dst_group_stride + rr) << logN);
-    FwdEpi epi;
+    r.mode = butterfly_mode(mc.q);
+    r.dst = a.dst + (((size_t)go * a.dst_outer + (size_t)gi * a.dst_group_stride + rr) << logN);
+    FwdEpi &epi = r.epi;
     epi.aux = a.aux ? a.aux + (((size_t)go * a.aux_outer + (size_t)gi * a.aux_group_stride + rr) << logN) : nullptr;
     epi.add = (a.add && gi < a.add_inner) ? a.add + (((size_t)go * a.add_outer + (size_t)gi * a.add_group_stride + rr) << logN) : nullptr;
     epi.scal = a.aux ? a.scal[rr] : 0;
     epi.scal_s = a.aux ? a.scal_s[rr] : 0;
+    return true;
+}
+
+template <int LOGC>
+__global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(const NttK a)
+{
+    extern __shared__ __align__(16) u64 sm[];
+    constexpr int C = 1 << LOGC;
+    FwdRow fr;
+    if (!fwd_row_setup(a, blockIdx.x >> LOGC, fr)) return;
+    const FwdIn &in = fr.in;
+    FwdEpi &epi = fr.epi;
+    u64 *dst = fr.dst;
+    const ulonglong2 *tw = fr.tw;
+    const u64 q = fr.q, q2 = q << 1;
+    const int mode = fr.mode;
+    const int logn_loc = a.logN - LOGC, n_loc = 1 << logn_loc;
 
     unsigned c = 0;
     if constexpr (LOGC > 0) {
         cg::cluster_group cluster = cg::this_cluster();
         c = cluster.block_rank();
-        cluster.sync(); // every CTA of the cluster is running before its shared memory is written
+        // Every CTA of the cluster must be running before its shared memory is written; the
+        // first loads and butterflies do not touch it, so only the first scatter waits.
+        cluster.barrier_arrive();
         u64 *remote[C];
 #pragma unroll
         for (int k = 0; k < C; ++k) remote[k] = cluster.map_shared_rank(sm, k);
         const int share = n_loc >> LOGC;
-        for (int jj = threadIdx.x; jj < share; jj += kNttThreads) {
+        auto column = [&](const int jj, const bool first) {
             const int j = c * share + jj;
             u64 v[C];
 #pragma unroll
             for (int k = 0; k < C; ++k) v[k] = load_in(in, j + k * n_loc);
-            if (lazy) fwd_core<LOGC, true>(v, tw, 1u, q, q2);
-            else fwd_core<LOGC, false>(v, tw, 1u, q, q2);
+            switch (mode) {
+            case kFpLazy: fwd_core<LOGC, kFpLazy>(v, tw, 1u, q, q2); break;
+            case kFpStrict: fwd_core<LOGC, kFpStrict>(v, tw, 1u, q, q2); break;
+            case kIntLazy: fwd_core<LOGC, kIntLazy>(v, tw, 1u, q, q2); break;
+            default: fwd_core<LOGC, kIntStrict>(v, tw, 1u, q, q2); break;
+            }
+            if (first) cluster.barrier_wait();
 #pragma unroll
             for (int k = 0; k < C; ++k) remote[k][sidx(j)] = v[k];
-        }
-        cluster.sync();
+        };
+        if ((int)threadIdx.x < share) column(threadIdx.x, true);
+        else cluster.barrier_wait();
+        for (int jj = threadIdx.x + kNttThreads; jj < share; jj += kNttThreads) column(jj, false);
+        cluster.sync(); // all scatters into this CTA have landed; from here on it only touches its own memory
         const size_t off = (size_t)c * n_loc;
         if (epi.aux) epi.aux += off;
         if (epi.add) epi.add += off;
@@ -331,35 +434,34 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(
         const int S = a.S[p];
         const bool from_global = (LOGC == 0 && p == 0);
         u64 *gdst = (p == a.npass - 1) ? dst + (size_t)c * n_loc : nullptr;
-        if (lazy) {
-            if (LB_NTT_MAX_RADIX_LOG >= 4 && S == 4) fwd_pass<LB_NTT_MAX_RADIX_LOG >= 4 ? 4 : 3, true>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
-            else if (S == 3) fwd_pass<3, true>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
-            else if (S == 2) fwd_pass<2, true>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
-            else fwd_pass<1, true>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
-        } else {
-            if (LB_NTT_MAX_RADIX_LOG >= 4 && S == 4) fwd_pass<LB_NTT_MAX_RADIX_LOG >= 4 ? 4 : 3, false>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
-            else if (S == 3) fwd_pass<3, false>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
-            else if (S == 2) fwd_pass<2, false>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
-            else fwd_pass<1, false>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi);
+        const int wlog = p < a.nwide ? -1 : a.wlog;
+        switch (mode) {
+        case kFpLazy: fwd_pass_any<kFpLazy>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
+        case kFpStrict: fwd_pass_any<kFpStrict>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
+        case kIntLazy: fwd_pass_any<kIntLazy>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
+        default: fwd_pass_any<kIntStrict>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
         }
         logt -= S;
-        if (p + 1 < a.npass) __syncthreads();
+        if (p + 1 < a.npass) {
+            if (wlog < 0) __syncthreads();
+            else __syncwarp();
+        }
     }
-    if constexpr (LOGC > 0) cg::this_cluster().sync(); // nobody leaves while a peer may still write here
 }
 
 // ---- inverse --------------------------------------------------------------------------
 
-template <int S, bool CLOSE>
+template <int S, bool CLOSE, bool FP>
 LB_D void inv_pass(u64 *sm, const u64 *gsrc, u64 *gdst, const int logn_loc, const int logt, const unsigned cc,
                    const ulonglong2 *itw, const u64 q, const u64 q2, const u64 cn, const u64 cns, const u64 cw,
-                   const u64 cws)
+                   const u64 cws, const int wlog)
 {
     constexpr int R = 1 << S;
     const int logst = logt;
-    const int groups = 1 << (logn_loc - S);
     const int logm0 = logn_loc - 1 - logt;
-    for (int g = threadIdx.x; g < groups; g += kNttThreads) {
+    const PassSplit ps = pass_split<S>(logn_loc, wlog);
+    LB_UNROLL(LB_NTT_GROUP_UNROLL)
+    for (int g = ps.first; g < ps.end; g += ps.step) {
         const int lo = g & ((1 << logst) - 1), hi = g >> logst;
         const int base = (hi << (logst + S)) + lo;
         u64 v[R];
@@ -369,7 +471,7 @@ LB_D void inv_pass(u64 *sm, const u64 *gsrc, u64 *gdst, const int logn_loc, cons
 #pragma unroll
             for (int i = 0; i < R; ++i) v[i] = sm[sidx(base + (i << logst))];
         }
-        inv_core<S, CLOSE>(v, itw, (cc << logm0) + (hi << (S - 1)), q, q2, cn, cns, cw, cws);
+        inv_core<S, CLOSE, FP>(v, itw, (cc << logm0) + (hi << (S - 1)), q, q2, cn, cns, cw, cws);
         if (gdst) {
 #pragma unroll
             for (int i = 0; i < R; ++i) gdst[base + (i << logst)] = v[i];
@@ -378,6 +480,18 @@ LB_D void inv_pass(u64 *sm, const u64 *gsrc, u64 *gdst, const int logn_loc, cons
             for (int i = 0; i < R; ++i) sm[sidx(base + (i << logst))] = v[i];
         }
     }
+}
+
+template <bool CLOSE, bool FP>
+LB_D void inv_pass_any(const int S, u64 *sm, const u64 *gsrc, u64 *gdst, const int logn_loc, const int logt, const unsigned cc,
+                       const ulonglong2 *itw, const u64 q, const u64 q2, const u64 cn, const u64 cns, const u64 cw, const u64 cws,
+                       const int wlog)
+{
+    constexpr int RMAX = LB_NTT_MAX_RADIX_LOG >= 4 ? 4 : 3;
+    if (RMAX == 4 && S == 4) inv_pass<RMAX, CLOSE, FP>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
+    else if (S == 3) inv_pass<3, CLOSE, FP>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
+    else if (S == 2) inv_pass<2, CLOSE, FP>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
+    else inv_pass<1, CLOSE, FP>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
 }
 
 template <int LOGC>
@@ -402,34 +516,32 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_inv_kernel(
         cn = f[0]; cns = f[1]; cw = f[2]; cws = f[3];
     }
     unsigned c = 0;
-    if constexpr (LOGC > 0) {
-        c = cg::this_cluster().block_rank();
-        cg::this_cluster().sync();
-    }
+    if constexpr (LOGC > 0) c = cg::this_cluster().block_rank();
     const unsigned cc = C + c;
+    const bool fp = q < kFpPrimeLimit;
     int logt = 0;
     for (int p = 0; p < a.npass; ++p) {
         const int S = a.S[p];
         const u64 *gsrc = (p == 0) ? src + (size_t)c * n_loc : nullptr;
         const bool closing = (LOGC == 0 && p == a.npass - 1);
         u64 *gdst = closing ? dst : nullptr;
-        if (p > 0) __syncthreads();
-        if (closing) {
-            if (LB_NTT_MAX_RADIX_LOG >= 4 && S == 4) inv_pass<LB_NTT_MAX_RADIX_LOG >= 4 ? 4 : 3, true>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
-            else if (S == 3) inv_pass<3, true>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
-            else if (S == 2) inv_pass<2, true>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
-            else inv_pass<1, true>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
+        const int wlog = p >= a.npass - a.nwide ? -1 : a.wlog;
+        if (p > 0) {
+            if (wlog < 0) __syncthreads();
+            else __syncwarp();
+        }
+        if (fp) {
+            if (closing) inv_pass_any<true, true>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
+            else inv_pass_any<false, true>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
         } else {
-            if (LB_NTT_MAX_RADIX_LOG >= 4 && S == 4) inv_pass<LB_NTT_MAX_RADIX_LOG >= 4 ? 4 : 3, false>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
-            else if (S == 3) inv_pass<3, false>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
-            else if (S == 2) inv_pass<2, false>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
-            else inv_pass<1, false>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws);
+            if (closing) inv_pass_any<true, false>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
+            else inv_pass_any<false, false>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
         }
         logt += S;
     }
     if constexpr (LOGC > 0) {
         cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync(); // all local transforms of the cluster are in shared memory
+        cluster.sync(); // all local transforms of the cluster are in shared memory (and every peer is running)
         const u64 *remote[C];
 #pragma unroll
         for (int k = 0; k < C; ++k) remote[k] = cluster.map_shared_rank(sm, k);
@@ -439,7 +551,8 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_inv_kernel(
             u64 v[C];
 #pragma unroll
             for (int k = 0; k < C; ++k) v[k] = remote[k][sidx(j)];
-            inv_core<LOGC, true>(v, itw, C / 2, q, q2, cn, cns, cw, cws);
+            if (fp) inv_core<LOGC, true, true>(v, itw, C / 2, q, q2, cn, cns, cw, cws);
+            else inv_core<LOGC, true, false>(v, itw, C / 2, q, q2, cn, cns, cw, cws);
 #pragma unroll
             for (int k = 0; k < C; ++k) dst[j + k * n_loc] = v[k];
         }
@@ -447,44 +560,338 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_inv_kernel(
     }
 }
 
+// ---- fixed schedule for rings of 8192 points and more ---------------------------------------------
+// Every production ring degree leaves 8192 points per CTA, so the local transform is always the
+// same thirteen stages.  With the stage numbers known at compile time the index arithmetic of a
+// register group collapses to one shared-memory address plus immediate offsets, and the split
+//   first pass : log2(C) + 1 stages on strided global loads (the cluster stages and the first
+//                local one), scattered through distributed shared memory,
+//   pass A     : local stages with spans 2048, 1024, 512 (CTA-wide),
+//   passes B-D : spans 256..1 inside each warp's 1024-point chunk (warp barriers only),
+// makes every register pass a radix-8 one: five passes instead of six.  The inverse mirrors it.
+#if LB_NTT_THREADS == 256 && LB_NTT_LOCAL_LOG == 13
+#define LB_NTT_HAS_FIXED 1
+constexpr int kHalfLoc = 4096;                                // points per half of a CTA's part
+constexpr int kHalfLocPad = kHalfLoc + (kHalfLoc >> 4);        // the same distance in padded shared memory
+
+// offset of element i of a register group in padded shared memory; the group's elements are
+// 2^LOGST apart and its base has zero bits where the element index goes
+template <int LOGST>
+LB_D constexpr int pad_off(const int i)
+{
+    return LOGST >= 4 ? (i << LOGST) + (i << (LOGST - 4)) : LOGST == 3 ? 8 * i + (i >> 1) : i;
+}
+
+LB_D uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+LB_D uint32_t map_to_cta(const uint32_t addr, const unsigned rank)
+{
+    uint32_t r;
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+LB_D void st_cluster(const uint32_t addr, const u64 v) { asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory"); }
+LB_D u64 ld_cluster(const uint32_t addr)
+{
+    u64 v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+// group index of iteration `it` (0..3): shared out over the CTA, or inside the warp's own chunk
+template <bool WIDE>
+LB_D int fixed_group(const int it)
+{
+    return WIDE ? (int)threadIdx.x + 256 * it : (int)((threadIdx.x >> 5) << 7) + (int)(threadIdx.x & 31) + 32 * it;
+}
+
+template <int LOGC, int MODE>
+LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulonglong2 *tw, const u64 q, const u64 q2)
+{
+    constexpr int F = LOGC + 1, R0 = 1 << F, COLS = kHalfLoc >> LOGC;
+    const uint32_t sbase = smem_addr(sm);
+    for (int col = threadIdx.x; col < COLS; col += 256) {
+        const int j = c * COLS + col;
+        u64 v[R0];
+#pragma unroll
+        for (int k = 0; k < R0; ++k) v[k] = load_in(in, j + k * kHalfLoc);
+        fwd_core<F, MODE>(v, tw, 1u, q, q2);
+        const int s0 = sidx(j);
+        if constexpr (LOGC == 0) {
+            sm[s0] = v[0];
+            sm[s0 + kHalfLocPad] = v[1];
+        } else {
+            // every CTA of the cluster must be running before its shared memory is written
+            if (col == (int)threadIdx.x) cg::this_cluster().barrier_wait();
+#pragma unroll
+            for (int r = 0; r < (1 << LOGC); ++r) {
+                const uint32_t ra = map_to_cta(sbase + 8u * s0, r);
+                st_cluster(ra, v[2 * r]);
+                st_cluster(ra + 8u * kHalfLocPad, v[2 * r + 1]);
+            }
+        }
+    }
+}
+
+// three forward stages starting at span 2^LOGT
+template <int LOGT, int MODE>
+LB_D void fwd_pass_fixed(u64 *sm, u64 *gdst, const unsigned cc, const ulonglong2 *tw, const u64 q, const u64 q2, const u64 r1,
+                         const FwdEpi &epi)
+{
+    constexpr int LOGST = LOGT - 2;
+    constexpr bool WIDE = LOGT + 1 > 10, CLOSING = LOGST == 0;
+    LB_UNROLL(LB_NTT_GROUP_UNROLL)
+    for (int it = 0; it < 4; ++it) {
+        const int g = fixed_group<WIDE>(it);
+        const int lo = g & ((1 << LOGST) - 1), hi = g >> LOGST;
+        const int base = (hi << (LOGT + 1)) + lo;
+        u64 *p = sm + sidx(base);
+        u64 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = p[pad_off<LOGST>(i)];
+        fwd_core<3, MODE>(v, tw, (cc << (12 - LOGT)) + hi, q, q2);
+        if constexpr (CLOSING) {
+            if (MODE == kIntLazy || MODE == kFpLazy) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = barrett64(v[i], q, r1);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = csub(csub(v[i], q2), q);
+            }
+            if (epi.aux) {
+                u64 t[8];
+                load_contig<8>(t, epi.aux + base);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = shoup_mul(sub_mod(t[i], v[i], q), epi.scal, epi.scal_s, q);
+                if (epi.add) {
+                    load_contig<8>(t, epi.add + base);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] = add_mod(v[i], t[i], q);
+                }
+            }
+            store_contig<8>(v, gdst + base);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) p[pad_off<LOGST>(i)] = v[i];
+        }
+    }
+}
+
+template <int LOGC, int MODE>
+LB_D void fwd_body_fixed(u64 *sm, const FwdRow &fr, const unsigned c)
+{
+    const u64 q = fr.q, q2 = q << 1;
+    const unsigned cc = (1u << LOGC) + c;
+    fwd_first_fixed<LOGC, MODE>(sm, fr.in, c, fr.tw, q, q2);
+    if constexpr (LOGC > 0) cg::this_cluster().sync(); // all scatters into this CTA have landed
+    else __syncthreads();
+    fwd_pass_fixed<11, MODE>(sm, nullptr, cc, fr.tw, q, q2, fr.in.r1, fr.epi);
+    __syncthreads();
+    fwd_pass_fixed<8, MODE>(sm, nullptr, cc, fr.tw, q, q2, fr.in.r1, fr.epi);
+    __syncwarp();
+    fwd_pass_fixed<5, MODE>(sm, nullptr, cc, fr.tw, q, q2, fr.in.r1, fr.epi);
+    __syncwarp();
+    fwd_pass_fixed<2, MODE>(sm, fr.dst + (size_t)c * (2 * kHalfLoc), cc, fr.tw, q, q2, fr.in.r1, fr.epi);
+}
+
+template <int LOGC>
+__global__ void __launch_bounds__(256, LB_NTT_MINBLOCKS) ntt_fwd_fixed_kernel(const NttK a)
+{
+    extern __shared__ __align__(16) u64 sm[];
+    FwdRow fr;
+    if (!fwd_row_setup(a, blockIdx.x >> LOGC, fr)) return;
+    unsigned c = 0;
+    if constexpr (LOGC > 0) {
+        c = cg::this_cluster().block_rank();
+        cg::this_cluster().barrier_arrive();
+        const size_t off = (size_t)c * (2 * kHalfLoc);
+        if (fr.epi.aux) fr.epi.aux += off;
+        if (fr.epi.add) fr.epi.add += off;
+    }
+    switch (fr.mode) {
+    case kFpLazy: fwd_body_fixed<LOGC, kFpLazy>(sm, fr, c); break;
+    case kFpStrict: fwd_body_fixed<LOGC, kFpStrict>(sm, fr, c); break;
+    case kIntLazy: fwd_body_fixed<LOGC, kIntLazy>(sm, fr, c); break;
+    default: fwd_body_fixed<LOGC, kIntStrict>(sm, fr, c); break;
+    }
+}
+
+// three inverse stages starting at distance 2^LOGT
+template <int LOGT, bool FP>
+LB_D void inv_pass_fixed(u64 *sm, const u64 *gsrc, const unsigned cc, const ulonglong2 *itw, const u64 q, const u64 q2)
+{
+    constexpr bool WIDE = LOGT + 3 > 10, OPENING = LOGT == 0;
+    LB_UNROLL(LB_NTT_GROUP_UNROLL)
+    for (int it = 0; it < 4; ++it) {
+        const int g = fixed_group<WIDE>(it);
+        const int lo = g & ((1 << LOGT) - 1), hi = g >> LOGT;
+        const int base = (hi << (LOGT + 3)) + lo;
+        u64 *p = sm + sidx(base);
+        u64 v[8];
+        if constexpr (OPENING) {
+            load_contig<8>(v, gsrc + base);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = p[pad_off<LOGT>(i)];
+        }
+        inv_core<3, false, FP>(v, itw, (cc << (12 - LOGT)) + (hi << 2), q, q2, 0, 0, 0, 0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) p[pad_off<LOGT>(i)] = v[i];
+    }
+}
+
+template <int LOGC, bool FP>
+LB_D void inv_last_fixed(u64 *sm, u64 *dst, const unsigned c, const ulonglong2 *itw, const u64 q, const u64 q2, const u64 cn,
+                         const u64 cns, const u64 cw, const u64 cws)
+{
+    constexpr int F = LOGC + 1, R0 = 1 << F, COLS = kHalfLoc >> LOGC;
+    const uint32_t sbase = smem_addr(sm);
+    for (int col = threadIdx.x; col < COLS; col += 256) {
+        const int j = c * COLS + col;
+        const int s0 = sidx(j);
+        u64 v[R0];
+        if constexpr (LOGC == 0) {
+            v[0] = sm[s0];
+            v[1] = sm[s0 + kHalfLocPad];
+        } else {
+#pragma unroll
+            for (int r = 0; r < (1 << LOGC); ++r) {
+                const uint32_t ra = map_to_cta(sbase + 8u * s0, r);
+                v[2 * r] = ld_cluster(ra);
+                v[2 * r + 1] = ld_cluster(ra + 8u * kHalfLocPad);
+            }
+        }
+        inv_core<F, true, FP>(v, itw, 1u << LOGC, q, q2, cn, cns, cw, cws);
+#pragma unroll
+        for (int k = 0; k < R0; ++k) dst[j + k * kHalfLoc] = v[k];
+    }
+}
+
+template <int LOGC, bool FP>
+LB_D void inv_body_fixed(u64 *sm, const u64 *src, u64 *dst, const unsigned c, const ulonglong2 *itw, const u64 q, const u64 cn,
+                         const u64 cns, const u64 cw, const u64 cws)
+{
+    const u64 q2 = q << 1;
+    const unsigned cc = (1u << LOGC) + c;
+    inv_pass_fixed<0, FP>(sm, src + (size_t)c * (2 * kHalfLoc), cc, itw, q, q2);
+    __syncwarp();
+    inv_pass_fixed<3, FP>(sm, nullptr, cc, itw, q, q2);
+    __syncwarp();
+    inv_pass_fixed<6, FP>(sm, nullptr, cc, itw, q, q2);
+    __syncthreads();
+    inv_pass_fixed<9, FP>(sm, nullptr, cc, itw, q, q2);
+    if constexpr (LOGC > 0) cg::this_cluster().sync(); // every local transform of the cluster is in shared memory
+    else __syncthreads();
+    inv_last_fixed<LOGC, FP>(sm, dst, c, itw, q, q2, cn, cns, cw, cws);
+    if constexpr (LOGC > 0) cg::this_cluster().sync(); // shared memory stays alive until every peer has read it
+}
+
+template <int LOGC>
+__global__ void __launch_bounds__(256, LB_NTT_MINBLOCKS) ntt_inv_fixed_kernel(const NttK a)
+{
+    extern __shared__ __align__(16) u64 sm[];
+    const int row = blockIdx.x >> LOGC;
+    const int grp = row / a.per_group, rr = row - grp * a.per_group;
+    if (rr >= a.skip_lo && rr < a.skip_hi) return;
+    const int tbl = rr < a.size_l ? rr + a.tbl_off : a.size_Q + (rr - a.size_l);
+    const ModConst mc = a.mc[tbl];
+    const int logN = a.logN;
+    const ulonglong2 *itw = a.tw + ((size_t)tbl << logN);
+    const int go = grp / a.split, gi = grp - go * a.split;
+    const u64 *src = a.src + (((size_t)go * a.src_outer + (size_t)gi * a.src_group_stride + rr + a.src_row_off) << logN);
+    u64 *dst = a.dst + (((size_t)go * a.dst_outer + (size_t)gi * a.dst_group_stride + rr) << logN);
+    u64 cn = mc.ninv, cns = mc.ninvs, cw = mc.iw1n, cws = mc.iw1ns;
+    if (a.fold) {
+        const u64 *f = a.fold + 4 * rr;
+        cn = f[0]; cns = f[1]; cw = f[2]; cws = f[3];
+    }
+    unsigned c = 0;
+    if constexpr (LOGC > 0) c = cg::this_cluster().block_rank();
+    if (mc.q < kFpPrimeLimit) inv_body_fixed<LOGC, true>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
+    else inv_body_fixed<LOGC, false>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
+}
+#else
+#define LB_NTT_HAS_FIXED 0
+#endif
+
 // ---- launchers ------------------------------------------------------------------------
 
-static int plan_passes(int logn_loc, bool forward, unsigned char *S)
+// Splits `stages` into as few register passes of at most R stages as possible, evenly.
+static int split_even(int stages, int R, unsigned char *out)
 {
-    // As few register passes as the radix allows; the pass that touches global memory with
-    // contiguous per-thread data (forward: last, inverse: first) takes the largest radix.
-    const int R = LB_NTT_MAX_RADIX_LOG;
-    int n = 0, rem = logn_loc;
-    int edge = rem >= R ? R : rem;
-    rem -= edge;
-    unsigned char mid[8];
-    int nm = 0;
-    const int count = (rem + R - 1) / R; // number of middle passes
+    const int count = (stages + R - 1) / R;
+    int n = 0;
     for (int i = 0; i < count; ++i) {
-        const int s = (rem + (count - i) - 1) / (count - i); // spread the stages evenly
-        mid[nm++] = (unsigned char)s;
-        rem -= s;
-    }
-    if (forward) {
-        for (int i = 0; i < nm; ++i) S[n++] = mid[i];
-        S[n++] = (unsigned char)edge;
-    } else {
-        S[n++] = (unsigned char)edge;
-        for (int i = nm - 1; i >= 0; --i) S[n++] = mid[i];
+        const int s = (stages + (count - i) - 1) / (count - i);
+        out[n++] = (unsigned char)s;
+        stages -= s;
     }
     return n;
 }
 
+struct PassPlan {
+    int npass, nwide, wlog;
+    unsigned char S[8];
+};
+
+static PassPlan plan_passes(int logn_loc, bool forward)
+{
+    // The log2(warps) stages whose butterflies span more than one warp's chunk run as
+    // CTA-wide passes; the rest stay inside a warp's contiguous chunk.  Of those, the pass
+    // that touches global memory with contiguous per-thread data (forward: last, inverse:
+    // first) takes the largest radix.  Short transforms keep every pass CTA-wide.
+    const int R = LB_NTT_MAX_RADIX_LOG;
+    int lw = 0;
+    while ((32 << lw) < kNttThreads) ++lw;
+    PassPlan pl;
+    unsigned char wide[8], mid[8];
+    int nw = 0, local = logn_loc;
+    pl.wlog = -1;
+    if (LB_NTT_WARP_LOCAL && logn_loc - lw >= 8) {
+        local = logn_loc - lw;
+        pl.wlog = local;
+        nw = split_even(lw, R, wide);
+    }
+    const int edge = local >= R ? R : local;
+    const int nm = split_even(local - edge, R, mid);
+    int n = 0;
+    if (forward) {
+        for (int i = 0; i < nw; ++i) pl.S[n++] = wide[i];
+        for (int i = 0; i < nm; ++i) pl.S[n++] = mid[i];
+        pl.S[n++] = (unsigned char)edge;
+    } else {
+        pl.S[n++] = (unsigned char)edge;
+        for (int i = nm - 1; i >= 0; --i) pl.S[n++] = mid[i];
+        for (int i = nw - 1; i >= 0; --i) pl.S[n++] = wide[i];
+    }
+    pl.npass = n;
+    pl.nwide = nw;
+    if (pl.wlog < 0) pl.nwide = n; // every pass CTA-wide
+    return pl;
+}
+
+#ifndef LB_NTT_FIXED
+#define LB_NTT_FIXED 1 // 0: rings of 8192 points and more also take the general kernels
+#endif
+
 template <int LOGC>
-static int launch(bool forward, const NttK &k, int rows, size_t smem, cudaStream_t stream)
+static int launch(bool forward, bool fixed, const NttK &k, int rows, size_t smem, cudaStream_t stream)
 {
     auto kern = forward ? ntt_fwd_kernel<LOGC> : ntt_inv_kernel<LOGC>;
-    static bool configured[2] = {false, false};
-    if (!configured[forward]) {
+#if LB_NTT_HAS_FIXED
+    if constexpr (LOGC <= 3) {
+        if (fixed) kern = forward ? ntt_fwd_fixed_kernel<LOGC> : ntt_inv_fixed_kernel<LOGC>;
+    }
+#endif
+    // function attributes belong to the device the kernel image is loaded on
+    static bool configured[64][2][2] = {};
+    int dev = 0;
+    LB_CUDA(cudaGetDevice(&dev));
+    bool &done = configured[dev & 63][forward][fixed];
+    if (!done) {
         // largest request any ring degree makes: 8192 points plus one pad word per 16
         LB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
         if (LOGC > 3) LB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-        configured[forward] = true;
+        done = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)rows << LOGC);
@@ -550,25 +957,30 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     k.presub_inner = job.presub ? job.presub_inner : 0;
     const int logc = hp.logN > kMaxLocalLog ? hp.logN - kMaxLocalLog : 0;
     const int logn_loc = hp.logN - logc;
-    k.npass = plan_passes(logn_loc, forward, k.S);
+    const PassPlan pl = plan_passes(logn_loc, forward);
+    k.npass = pl.npass;
+    k.nwide = pl.nwide;
+    k.wlog = pl.wlog;
+    for (int i = 0; i < pl.npass; ++i) k.S[i] = pl.S[i];
     const size_t n_loc = size_t(1) << logn_loc;
     const size_t smem = (n_loc + (n_loc >> 4) + 2) * sizeof(u64);
+    const bool fixed = LB_NTT_FIXED && LB_NTT_HAS_FIXED && logn_loc == 13;
     switch (logc) {
-    case 0: return launch<0>(forward, k, rows, smem, stream);
-    case 1: return launch<1>(forward, k, rows, smem, stream);
-    case 2: return launch<2>(forward, k, rows, smem, stream);
-    case 3: return launch<3>(forward, k, rows, smem, stream);
-    case 4: return launch<4>(forward, k, rows, smem, stream);
+    case 0: return launch<0>(forward, fixed, k, rows, smem, stream);
+    case 1: return launch<1>(forward, fixed, k, rows, smem, stream);
+    case 2: return launch<2>(forward, fixed, k, rows, smem, stream);
+    case 3: return launch<3>(forward, fixed, k, rows, smem, stream);
+    case 4: return launch<4>(forward, fixed, k, rows, smem, stream);
     default: set_error("poly_modulus_degree above 65536 is not supported"); return LB_ERR_INVALID_ARG;
     }
 }
 
-// ---- integer-pipe ceiling probe ---------------------------------------------------------------
+// ---- arithmetic ceiling probe -------------------------------------------------------------------
 // The same forward butterfly as the transform kernels, on registers only (no shared or global
 // memory traffic inside the loop), at the transform kernels' occupancy.  Its rate is the ceiling
-// the 64-bit Shoup arithmetic sets for any NTT schedule on this GPU; one limb of N points needs
-// (N/2) log2 N butterflies for 16 N bytes of traffic.
-template <bool LAZY>
+// the modular arithmetic of that butterfly variant sets for any NTT schedule on this GPU; one
+// limb of N points needs (N/2) log2 N butterflies for 16 N bytes of traffic.
+template <int MODE>
 __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) butterfly_probe_kernel(u64 *out, const u64 q, const u64 w0, const u64 ws0,
                                                                                        const int iters)
 {
@@ -584,12 +996,17 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) butterfly_probe
             for (int b = 0; b < (1 << s); ++b) {
                 const ulonglong2 w = make_ulonglong2(w0 + threadIdx.x + b, ws0 + threadIdx.x + s);
 #pragma unroll
-                for (int i = 0; i < half; ++i) fwd_bf<LAZY>(v[b * 2 * half + i], v[b * 2 * half + i + half], w, q, q2);
+                for (int i = 0; i < half; ++i) fwd_bf<MODE>(v[b * 2 * half + i], v[b * 2 * half + i + half], w, q, q2);
             }
         }
-        if (LAZY) {
+        // keep the lazy ranges bounded, as the closing reduction does
+        if (MODE == kIntLazy) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] &= 0x03FFFFFFFFFFFFFFull; // keep the lazy range bounded, as the closing reduction does
+            for (int i = 0; i < 8; ++i) v[i] &= 0x03FFFFFFFFFFFFFFull;
+        }
+        if (MODE == kFpLazy) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] &= 0x0003FFFFFFFFFFFFull;
         }
     }
     u64 acc = 0;
@@ -598,13 +1015,25 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) butterfly_probe
     out[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = acc;
 }
 
-int probe_butterfly_rate(Context *ctx, int lazy, double *butterflies_per_second)
+// mode: 0 integer strict, 1 integer lazy, 2 FP64-assisted strict, 3 FP64-assisted lazy,
+// -1 the variant the context's first prime takes.
+int probe_butterfly_rate(Context *ctx, int mode, double *butterflies_per_second)
 {
+    if (mode < 0) {
+        const u64 q0 = ctx->hp.q[0];
+        mode = q0 < kFpLazyLimit ? kFpLazy : q0 < kFpPrimeLimit ? kFpStrict : (q0 >> 58) == 0 ? kIntLazy : kIntStrict;
+    }
+    if (mode > kFpLazy) {
+        set_error("butterfly variant must be 0..3 or -1");
+        return LB_ERR_INVALID_ARG;
+    }
     const int blocks = ctx->sm_count * LB_NTT_MINBLOCKS, iters = 2000;
     int rc = ctx->ensure_workspace((size_t)blocks * kNttThreads * sizeof(u64));
     if (rc) return rc;
     u64 *out = reinterpret_cast<u64 *>(ctx->ws);
-    const u64 q = ctx->hp.q[0], w = q / 3, ws = h_shoup(w, q);
+    // any odd modulus of the variant's size gives the variant's instruction stream
+    static const u64 size_of_mode[4] = {(u64(1) << 60) - 93, (u64(1) << 50) - 27, (u64(1) << 49) - 69, (u64(1) << 40) - 87};
+    const u64 q = size_of_mode[mode], w = q / 3, ws = mode >= kFpStrict ? h_fp_quot(w, q) : h_shoup(w, q);
     cudaEvent_t e0, e1;
     LB_CUDA(cudaEventCreate(&e0));
     LB_CUDA(cudaEventCreate(&e1));
@@ -612,8 +1041,12 @@ int probe_butterfly_rate(Context *ctx, int lazy, double *butterflies_per_second)
     for (int rep = 0; rep < 4; ++rep) {
         LB_CUDA(cudaEventRecord(e0, 0));
         count_launch();
-        if (lazy) butterfly_probe_kernel<true><<<blocks, kNttThreads>>>(out, q, w, ws, iters);
-        else butterfly_probe_kernel<false><<<blocks, kNttThreads>>>(out, q, w, ws, iters);
+        switch (mode) {
+        case kIntStrict: butterfly_probe_kernel<kIntStrict><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
+        case kIntLazy: butterfly_probe_kernel<kIntLazy><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
+        case kFpStrict: butterfly_probe_kernel<kFpStrict><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
+        default: butterfly_probe_kernel<kFpLazy><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
+        }
         LB_CUDA(cudaEventRecord(e1, 0));
         LB_CUDA(cudaEventSynchronize(e1));
         float ms = 0;

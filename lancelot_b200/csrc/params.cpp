@@ -154,9 +154,9 @@ bool HostParams::init(int logN_, const std::vector<u64> &moduli, int size_P_, co
         for (u64 i = 0; i < N; ++i) {
             const uint32_t r = bit_reverse((uint32_t)i, logN);
             t[2 * r] = pw;
-            t[2 * r + 1] = h_shoup(pw, p);
+            t[2 * r + 1] = h_twiddle_quot(pw, p);
             it[2 * r] = ipw;
-            it[2 * r + 1] = h_shoup(ipw, p);
+            it[2 * r + 1] = h_twiddle_quot(ipw, p);
             pw = h_mulmod(pw, psi[m], p);
             ipw = h_mulmod(ipw, ipsi, p);
         }

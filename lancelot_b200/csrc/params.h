@@ -50,7 +50,7 @@ struct HostParams {
     int size_QP = 0, size_Q = 0, size_P = 0;
     std::vector<u64> q, psi;
     std::vector<ModConst> mc;             // [size_QP]
-    std::vector<u64> tw, itw;             // [size_QP][N][2]  (value, Shoup quotient), index m + k
+    std::vector<u64> tw, itw;             // [size_QP][N][2]  (value, Shoup quotient or, below 2^50, the double value / q), index m + k
     std::vector<uint32_t> galois_elts;    // as given by the caller
     std::vector<uint32_t> perm;           // [n_elts][N]
     std::vector<LevelConst> level;        // index = size_l (1..size_Q); [0] unused

@@ -68,6 +68,27 @@ def test_ntt_edge_values(torch_cuda):
     assert np.array_equal(cabi.to_host(d), data)
 
 
+@pytest.mark.parametrize("logn", [11, 13, 16])
+def test_ntt_every_butterfly_variant(torch_cuda, logn):
+    """primes on both sides of the size limits that select the butterfly variant (2^58, 2^50, 2^46),
+    on random residues and on the extremes 0 and q-1"""
+    from lancelot_b200 import cabi
+
+    bits = [60, 59, 58, 57, 51, 50, 49, 47, 46, 45, 40, 30]
+    o, ctx, mods = make(logn, bits, 0)
+    n, L = 1 << logn, len(bits)
+    rng = np.random.default_rng(100 + logn)
+    rand = rand_rows(rng, row_moduli(mods, L, L, 0, 1), n)
+    top = np.stack([np.full(n, q - 1, np.uint64) for q in mods])
+    data = np.concatenate([rand, top, np.zeros_like(top)])
+    d = cabi.to_device(data)
+    ctx.ntt_forward(d, 3, L, 0)
+    want = o.ntt_rows(data, 3, L, 0)
+    assert np.array_equal(cabi.to_host(d), want)
+    ctx.ntt_inverse(d, 3, L, 0)
+    assert np.array_equal(cabi.to_host(d), data)
+
+
 def test_ntt_special_limbs_only_and_empty(torch_cuda):
     from lancelot_b200 import cabi
 
