@@ -158,6 +158,14 @@ LB_API int lb_hoisting_batch(lb_context *ctx, int size_l, int batch, uint64_t *c
 LB_API int lb_krum_accumulate(lb_context *ctx, int size_l, int n_chunks, const uint64_t *a, const uint64_t *b,
                        size_t chunk_stride_a, size_t chunk_stride_b, uint64_t *acc, int accumulate, void *stream);
 
+/* The same sums for several client pairs from one pass over their ciphertexts.  a / b / out are HOST
+ * arrays of device pointers; every client's chunk c sits chunk_stride words after chunk c - 1.
+ * n_b == 0: triangle, all pairs inside the 2..4 clients of a, in the order (0,1),(0,2),..,(1,2),..;
+ * n_b > 0: rectangle, 1..2 clients of a against 1..4 clients of b, pair a_i, b_j at index i * n_b + j.
+ * out[p][3][size_l][N] = sum over chunks of square(second - first) for pair p (overwritten). */
+LB_API int lb_krum_accumulate_tile(lb_context *ctx, int size_l, int n_chunks, int n_a, const uint64_t *const *a, int n_b,
+                            const uint64_t *const *b, size_t chunk_stride, uint64_t *const *out, void *stream);
+
 /* Mask multiplication of the aggregation phase (lancelot-main-GPU/utils/byzantine_fl.py:371-429):
  * out[c][3][size_l][N] = sum over clients k of ct_k[c] (x) mask_k (ckks_multiply + add_inplace per client
  * in the reference).  client_cts: HOST array of n_clients device pointers, chunk c of client k at

@@ -72,7 +72,6 @@ class KrumWorkload:
         self.updates = self.make_updates(dev)
         self.host = torch.empty(self.updates.shape, dtype=torch.float32).pin_memory()
         self.host.copy_(self.updates)
-        self.staging = torch.empty_like(self.updates)
         self.result = None
         # float64 plaintext Krum on the device, for the parity check
         n = self.n_clients
@@ -109,8 +108,8 @@ class KrumWorkload:
         self._round(self.updates)
 
     def step_e2e(self):
-        self.staging.copy_(self.host, non_blocking=True)
-        self._round(self.staging)
+        # the round takes the pinned host tensor itself: it copies one client ahead of the encryption
+        self._round(self.host)
         out_bytes = 8 * self.n_clients * 2
         return self.host.numel() * 4, out_bytes
 

@@ -235,6 +235,19 @@ class Context:
                                      _p(acc), int(accumulate), _stream()))
         return acc
 
+    def krum_accumulate_tile(self, size_l, a, b, outs, n_chunks=None):
+        """a, b: lists of client tensors [chunks][2][size_l][N] (b empty: all pairs inside a); outs: one
+        [3][size_l][N] tensor per pair, triangle order (0,1),(0,2),..,(1,2),.. or rectangle order i * len(b) + j"""
+        ct_words = 2 * size_l * self.N
+        n_chunks = a[0].numel() // ct_words if n_chunks is None else n_chunks
+        pa = (C.c_void_p * len(a))(*[t.data_ptr() for t in a])
+        pb = (C.c_void_p * max(1, len(b)))(*[t.data_ptr() for t in b])
+        po = (C.c_void_p * len(outs))(*[t.data_ptr() for t in outs])
+        n_pairs = len(a) * len(b) if b else len(a) * (len(a) - 1) // 2
+        assert len(outs) == n_pairs, "one output per pair"
+        check(lib.lb_krum_accumulate_tile(self.h, size_l, n_chunks, len(a), pa, len(b), pb, C.c_size_t(ct_words), po, _stream()))
+        return outs
+
     def decrypt(self, size_l, ct, sk):
         n_polys = ct.numel() // (size_l * self.N)
         pt = self.empty(size_l, self.N)

@@ -378,6 +378,21 @@ int lb_krum_accumulate(lb_context *h, int size_l, int n_chunks, const uint64_t *
     return krum_accumulate(C(h), size_l, n_chunks, a, b, (long)sa, (long)sb, acc, accumulate, S(stream));
 }
 
+int lb_krum_accumulate_tile(lb_context *h, int size_l, int n_chunks, int n_a, const uint64_t *const *a, int n_b,
+                            const uint64_t *const *b, size_t chunk_stride, uint64_t *const *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    if ((rc = level_ok(C(h), size_l))) return rc;
+    REQUIRE(a && out && (b || n_b == 0) && n_chunks >= 0, "operand is null");
+    REQUIRE(n_a >= 1 && n_a <= 4 && n_b >= 0 && n_b <= 4, "tile shape is out of range");
+    for (int i = 0; i < n_a; ++i) REQUIRE(a[i], "operand is null");
+    for (int i = 0; i < n_b; ++i) REQUIRE(b[i], "operand is null");
+    const int n_pairs = n_b ? n_a * n_b : n_a * (n_a - 1) / 2;
+    for (int i = 0; i < n_pairs && i < 8; ++i) REQUIRE(out[i], "operand is null");
+    return krum_accumulate_tile(C(h), size_l, n_chunks, n_a, a, n_b, b, (long)chunk_stride, out, S(stream));
+}
+
 int lb_decrypt(lb_context *h, int size_l, int n_polys, const uint64_t *ct, const uint64_t *sk, uint64_t *pt, void *stream)
 {
     int rc = bind(h);

@@ -117,6 +117,8 @@ int poly_galois(Context *ctx, int elt_idx, long rows, const u64 *src, u64 *dst, 
 // acc[3][L][N] (+)= sum_c square(b_c - a_c) over n_chunks ciphertext pairs [2][L][N]
 int krum_accumulate(Context *ctx, int size_l, int n_chunks, const u64 *a, const u64 *b, long chunk_stride_a,
                     long chunk_stride_b, u64 *acc, int accumulate, cudaStream_t stream);
+int krum_accumulate_tile(Context *ctx, int size_l, int n_chunks, int n_a, const u64 *const *a, int n_b, const u64 *const *b,
+                         long chunk_stride, u64 *const *out, cudaStream_t stream);
 // drop the last limb of each polynomial: in [polys][L][N] -> out [polys][L-1][N]
 int poly_drop_last(Context *ctx, int size_l, int n_polys, const u64 *in, u64 *out, cudaStream_t stream);
 // pt = c0 + c1 s + c2 s^2 ...

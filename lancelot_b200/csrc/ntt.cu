@@ -604,7 +604,9 @@ LB_D int fixed_group(const int it)
     return WIDE ? (int)threadIdx.x + 256 * it : (int)((threadIdx.x >> 5) << 7) + (int)(threadIdx.x & 31) + 32 * it;
 }
 
-template <int LOGC, int MODE>
+// PLAIN: the input is the limb itself, so none of the fused input conversions is compiled in
+// (sixteen inlined copies of them make the instruction stream of this pass miss the cache).
+template <int LOGC, int MODE, bool PLAIN>
 LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulonglong2 *tw, const u64 q, const u64 q2)
 {
     constexpr int F = LOGC + 1, R0 = 1 << F, COLS = kHalfLoc >> LOGC;
@@ -613,7 +615,7 @@ LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulon
         const int j = c * COLS + col;
         u64 v[R0];
 #pragma unroll
-        for (int k = 0; k < R0; ++k) v[k] = load_in(in, j + k * kHalfLoc);
+        for (int k = 0; k < R0; ++k) v[k] = PLAIN ? in.src[j + k * kHalfLoc] : load_in(in, j + k * kHalfLoc);
         fwd_core<F, MODE>(v, tw, 1u, q, q2);
         const int s0 = sidx(j);
         if constexpr (LOGC == 0) {
@@ -676,12 +678,12 @@ LB_D void fwd_pass_fixed(u64 *sm, u64 *gdst, const unsigned cc, const ulonglong2
     }
 }
 
-template <int LOGC, int MODE>
+template <int LOGC, int MODE, bool PLAIN>
 LB_D void fwd_body_fixed(u64 *sm, const FwdRow &fr, const unsigned c)
 {
     const u64 q = fr.q, q2 = q << 1;
     const unsigned cc = (1u << LOGC) + c;
-    fwd_first_fixed<LOGC, MODE>(sm, fr.in, c, fr.tw, q, q2);
+    fwd_first_fixed<LOGC, MODE, PLAIN>(sm, fr.in, c, fr.tw, q, q2);
     if constexpr (LOGC > 0) cg::this_cluster().sync(); // all scatters into this CTA have landed
     else __syncthreads();
     fwd_pass_fixed<11, MODE>(sm, nullptr, cc, fr.tw, q, q2, fr.in.r1, fr.epi);
@@ -693,7 +695,7 @@ LB_D void fwd_body_fixed(u64 *sm, const FwdRow &fr, const unsigned c)
     fwd_pass_fixed<2, MODE>(sm, fr.dst + (size_t)c * (2 * kHalfLoc), cc, fr.tw, q, q2, fr.in.r1, fr.epi);
 }
 
-template <int LOGC>
+template <int LOGC, bool PLAIN>
 __global__ void __launch_bounds__(256, LB_NTT_MINBLOCKS) ntt_fwd_fixed_kernel(const NttK a)
 {
     extern __shared__ __align__(16) u64 sm[];
@@ -708,10 +710,10 @@ __global__ void __launch_bounds__(256, LB_NTT_MINBLOCKS) ntt_fwd_fixed_kernel(co
         if (fr.epi.add) fr.epi.add += off;
     }
     switch (fr.mode) {
-    case kFpLazy: fwd_body_fixed<LOGC, kFpLazy>(sm, fr, c); break;
-    case kFpStrict: fwd_body_fixed<LOGC, kFpStrict>(sm, fr, c); break;
-    case kIntLazy: fwd_body_fixed<LOGC, kIntLazy>(sm, fr, c); break;
-    default: fwd_body_fixed<LOGC, kIntStrict>(sm, fr, c); break;
+    case kFpLazy: fwd_body_fixed<LOGC, kFpLazy, PLAIN>(sm, fr, c); break;
+    case kFpStrict: fwd_body_fixed<LOGC, kFpStrict, PLAIN>(sm, fr, c); break;
+    case kIntLazy: fwd_body_fixed<LOGC, kIntLazy, PLAIN>(sm, fr, c); break;
+    default: fwd_body_fixed<LOGC, kIntStrict, PLAIN>(sm, fr, c); break;
     }
 }
 
@@ -877,16 +879,21 @@ template <int LOGC>
 static int launch(bool forward, bool fixed, const NttK &k, int rows, size_t smem, cudaStream_t stream)
 {
     auto kern = forward ? ntt_fwd_kernel<LOGC> : ntt_inv_kernel<LOGC>;
+    int which = 0;
 #if LB_NTT_HAS_FIXED
     if constexpr (LOGC <= 3) {
-        if (fixed) kern = forward ? ntt_fwd_fixed_kernel<LOGC> : ntt_inv_fixed_kernel<LOGC>;
+        if (fixed) {
+            const bool plain = k.bconv_n == 0 && k.digit_alpha == 0 && !k.presub && !k.esmall;
+            kern = !forward ? ntt_inv_fixed_kernel<LOGC> : plain ? ntt_fwd_fixed_kernel<LOGC, true> : ntt_fwd_fixed_kernel<LOGC, false>;
+            which = plain ? 2 : 1;
+        }
     }
 #endif
     // function attributes belong to the device the kernel image is loaded on
-    static bool configured[64][2][2] = {};
+    static bool configured[64][2][3] = {};
     int dev = 0;
     LB_CUDA(cudaGetDevice(&dev));
-    bool &done = configured[dev & 63][forward][fixed];
+    bool &done = configured[dev & 63][forward][which];
     if (!done) {
         // largest request any ring degree makes: 8192 points plus one pad word per 16
         LB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));

@@ -250,6 +250,112 @@ int krum_accumulate(Context *ctx, int size_l, int n_chunks, const u64 *a, const 
     return LB_OK;
 }
 
+// ---- tiled Krum inner loop ------------------------------------------------------------------------
+// A round needs the sum for every pair of clients, so the one-pair kernel reads each client once
+// per partner.  A tile keeps the current chunk of up to six clients in registers and produces up
+// to eight pair sums from it: a triangle (all pairs inside one set of NA clients, NB == 0) or a
+// rectangle (every client of set A against every client of set B).  Pair p of a triangle is
+// (0,1),(0,2),..,(1,2),..; of a rectangle a * NB + b.  HBM reads per pair drop from two clients to
+// (NA + NB) / (NA * NB), 0.75 for the 2 x 4 rectangle.
+
+constexpr int kTileThreads = 128;
+constexpr int kTileMaxIn = 6, kTileMaxPairs = 8;
+
+struct KrumTileArgs {
+    const u64 *in[kTileMaxIn];
+    u64 *out[kTileMaxPairs];
+};
+
+template <int NA, int NB>
+__global__ void __launch_bounds__(kTileThreads, 3) krum_tile_kernel(const KrumTileArgs args, const ModConst *__restrict__ mc, const int logn,
+                                                                    const long per_poly, const long chunk_stride, const int n_chunks)
+{
+    constexpr int NI = NA + NB, NP = NB ? NA * NB : NA * (NA - 1) / 2;
+    for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < per_poly; e += (long)gridDim.x * blockDim.x) {
+        const ModConst m = mc[(int)(e >> logn)];
+        // 128-bit running sums; every 64 chunks they are reduced in place, which leaves room for
+        // 63 more products of residues below 2^61
+        u128d s0[NP], s1[NP], s2[NP];
+#pragma unroll
+        for (int p = 0; p < NP; ++p) s0[p] = s1[p] = s2[p] = u128d{0, 0};
+        for (int c0 = 0; c0 < n_chunks; c0 += 63) {
+            const int c1 = min(c0 + 63, n_chunks);
+            for (int c = c0; c < c1; ++c) {
+                u64 v0[NI], v1[NI];
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    const u64 *base = args.in[i] + c * chunk_stride + e;
+                    v0[i] = __ldcs(base);
+                    v1[i] = __ldcs(base + per_poly);
+                }
+                int p = 0;
+#pragma unroll
+                for (int i = 0; i < NA; ++i) {
+#pragma unroll
+                    for (int j = NB ? NA : i + 1; j < NI; ++j, ++p) {
+                        const u64 x0 = sub_mod(v0[j], v0[i], m.q), x1 = sub_mod(v1[j], v1[i], m.q);
+                        mac_wide(s0[p], x0, x0);
+                        mac_wide(s1[p], x0, x1);
+                        mac_wide(s2[p], x1, x1);
+                    }
+                }
+            }
+#pragma unroll
+            for (int p = 0; p < NP; ++p) {
+                s0[p] = u128d{barrett128(s0[p], m.q, m.r0, m.r1), 0};
+                s1[p] = u128d{barrett128(s1[p], m.q, m.r0, m.r1), 0};
+                s2[p] = u128d{barrett128(s2[p], m.q, m.r0, m.r1), 0};
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < NP; ++p) {
+            u64 *dst = args.out[p];
+            dst[e] = s0[p].lo;
+            dst[per_poly + e] = add_mod(s1[p].lo, s1[p].lo, m.q); // middle term is 2 x0 x1
+            dst[2 * per_poly + e] = s2[p].lo;
+        }
+    }
+}
+
+template <int NA, int NB>
+static void launch_tile(Context *ctx, const KrumTileArgs &args, int size_l, int n_chunks, long chunk_stride, cudaStream_t stream)
+{
+    const long per_poly = (long)size_l << ctx->hp.logN;
+    const long blocks = (per_poly + kTileThreads - 1) / kTileThreads;
+    count_launch();
+    krum_tile_kernel<NA, NB><<<(unsigned)blocks, kTileThreads, 0, stream>>>(args, ctx->d_mc, ctx->hp.logN, per_poly, chunk_stride, n_chunks);
+}
+
+int krum_accumulate_tile(Context *ctx, int size_l, int n_chunks, int n_a, const u64 *const *a, int n_b, const u64 *const *b,
+                         long chunk_stride, u64 *const *out, cudaStream_t stream)
+{
+    const int n_pairs = n_b ? n_a * n_b : n_a * (n_a - 1) / 2;
+    const bool ok = n_b == 0 ? (n_a >= 2 && n_a <= 4) : (n_a >= 1 && n_a <= 2 && n_b >= 1 && n_b <= 4);
+    if (!ok) {
+        set_error("a Krum tile is a triangle of 2..4 clients or a rectangle of 1..2 by 1..4 clients");
+        return LB_ERR_INVALID_ARG;
+    }
+    KrumTileArgs args = {};
+    for (int i = 0; i < n_a; ++i) args.in[i] = a[i];
+    for (int i = 0; i < n_b; ++i) args.in[n_a + i] = b[i];
+    for (int p = 0; p < n_pairs; ++p) args.out[p] = out[p];
+    switch (n_a * 8 + n_b) {
+    case 2 * 8 + 0: launch_tile<2, 0>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 3 * 8 + 0: launch_tile<3, 0>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 4 * 8 + 0: launch_tile<4, 0>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 1 * 8 + 1: launch_tile<1, 1>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 1 * 8 + 2: launch_tile<1, 2>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 1 * 8 + 3: launch_tile<1, 3>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 1 * 8 + 4: launch_tile<1, 4>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 2 * 8 + 1: launch_tile<2, 1>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 2 * 8 + 2: launch_tile<2, 2>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 2 * 8 + 3: launch_tile<2, 3>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    default: launch_tile<2, 4>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    }
+    LB_CUDA(cudaGetLastError());
+    return LB_OK;
+}
+
 // ---- mask multiplication: out[c] = sum_k ct_k[c] (x) mask_k as size-3 ciphertexts -------------
 // (lancelot-main-GPU/utils/byzantine_fl.py:401-409: per chunk, multiply every client's ciphertext
 // with that client's mask ciphertext and add the products)

@@ -199,6 +199,45 @@ def pair_schedule(n_clients, world_size):
     return out
 
 
+def pair_tiles(pairs, width=4):
+    """Covers a list of pairs i < j with the tiles lb_krum_accumulate_tile computes in one pass:
+    ("tri", clients, []) for all pairs inside a set of 2..width clients, ("rect", rows, cols) for
+    1..2 clients against 1..width clients.  Clients are blocked by index in groups of ``width``;
+    any pair list is covered, full blocks by the shapes that read least."""
+    blocks = {}
+    for i, j in pairs:
+        blocks.setdefault((i // width, j // width), []).append((i, j))
+    tiles = []
+    for (ga, gb), ps in sorted(blocks.items()):
+        if ga == gb:
+            cl = sorted({c for p in ps for c in p})
+            if len(ps) == len(cl) * (len(cl) - 1) // 2:
+                tiles.append(("tri", cl, []))
+                continue
+        rows = {}
+        for i, j in ps:
+            rows.setdefault(i, []).append(j)
+        keys = sorted(rows)
+        k = 0
+        while k < len(keys):
+            cols = sorted(rows[keys[k]])
+            if k + 1 < len(keys) and sorted(rows[keys[k + 1]]) == cols:
+                tiles.append(("rect", [keys[k], keys[k + 1]], cols))
+                k += 2
+            else:
+                tiles.append(("rect", [keys[k]], cols))
+                k += 1
+    return tiles
+
+
+def tile_pairs(tile):
+    """the pairs of one tile in the order the kernel writes them"""
+    kind, rows, cols = tile
+    if kind == "tri":
+        return [(rows[a], rows[b]) for a in range(len(rows)) for b in range(a + 1, len(rows))]
+    return [(i, j) for i in rows for j in cols]
+
+
 def clients_of(pairs):
     return sorted({c for p in pairs for c in p})
 
@@ -273,6 +312,40 @@ class EncryptedKrum:
                                    out=cts[c0:c0 + nb])
         return cts
 
+    def staged(self, updates, clients):
+        """Yields (client, update on the device) for the given clients.  Updates that live in host
+        memory are copied on a side stream one client ahead of the encryption that consumes them (two
+        device buffers), so a pinned host tensor streams in behind the encode + encrypt kernels."""
+        if updates.is_cuda:
+            for c in clients:
+                yield c, updates[c]
+            return
+        dev = torch.device("cuda", self.lb.device)
+        main = torch.cuda.current_stream(dev)
+        if getattr(self, "_copy_stream", None) is None:
+            self._copy_stream = torch.cuda.Stream(dev)
+        copy = self._copy_stream
+        bufs = [torch.empty(updates.shape[1], dtype=updates.dtype, device=dev) for _ in range(2)]
+        ready = [torch.cuda.Event() for _ in range(2)]
+        free = [torch.cuda.Event() for _ in range(2)]
+        for e in free:
+            e.record(main)
+
+        def start(k):
+            with torch.cuda.stream(copy):
+                copy.wait_event(free[k % 2])
+                bufs[k % 2].copy_(updates[clients[k]], non_blocking=True)
+                ready[k % 2].record(copy)
+
+        if clients:
+            start(0)
+        for k, c in enumerate(clients):
+            if k + 1 < len(clients):
+                start(k + 1)
+            main.wait_event(ready[k % 2])
+            yield c, bufs[k % 2]
+            free[k % 2].record(main)
+
     def encrypt_and_share(self, updates, rank, world_size, group, round_seed, needed, mark=lambda name: None):
         """Client c is encrypted by rank c % world_size; one all_gather per slice of world_size clients
         hands every rank every ciphertext.  Only the clients in ``needed`` are kept."""
@@ -282,10 +355,12 @@ class EncryptedKrum:
         chunks = self.n_chunks(dim)
         mine_buf = self.lb.empty(chunks, 2, 3, self.N)
         cts = {}
+        feed = self.staged(updates, list(range(rank, n_clients, world_size)))
         for base in range(0, n_clients, world_size):
             c = base + rank
             if c < n_clients:
-                self.encrypt_client(updates[c], client=c, round_seed=round_seed, out=mine_buf)
+                _, upd = next(feed)
+                self.encrypt_client(upd, client=c, round_seed=round_seed, out=mine_buf)
             mark("encode_encrypt_s")
             recv = self.lb.empty(world_size, chunks, 2, 3, self.N)
             dist.all_gather_into_tensor(recv.view(-1), mine_buf.view(-1), group=group)
@@ -304,8 +379,10 @@ class EncryptedKrum:
         if P == 0:
             return lb.empty(0, 2, 2, N)
         acc = lb.empty(P, 3, 3, N)
-        for p, (i, j) in enumerate(pairs):
-            lb.krum_accumulate(3, cts[i], cts[j], acc[p], accumulate=False)
+        slot = {pair: p for p, pair in enumerate(pairs)}
+        for tile in pair_tiles(pairs):
+            outs = [acc[slot[pair]] for pair in tile_pairs(tile)]
+            lb.krum_accumulate_tile(3, [cts[i] for i in tile[1]], [cts[j] for j in tile[2]], outs)
         mark("pair_accumulate_s")
         lb.relinearize_batch(3, acc, self.rlk.data)
         s = lb.rescale_strided(3, acc, P, 2, 3 * 3 * N)  # [P][2][2][N], scale 2^80 / q_2 ~ 2^40
@@ -395,8 +472,8 @@ class EncryptedKrum:
         if world_size > 1 and exchange == "allgather":
             cts = self.encrypt_and_share(updates, rank, world_size, group, round_seed, needed=set(clients_of(mine)), mark=mark)
         else:
-            for c in clients_of(mine):
-                cts[c] = self.encrypt_client(updates[c], client=c, round_seed=round_seed)
+            for c, upd in self.staged(updates, clients_of(mine)):
+                cts[c] = self.encrypt_client(upd, client=c, round_seed=round_seed)
             mark("encode_encrypt_s")
         scores = self.pair_scores(cts, mine, mark)
         if keep is not None:

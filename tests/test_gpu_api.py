@@ -181,6 +181,24 @@ def test_batched_krum_driver_equals_stepwise_api_and_plaintext():
     assert torch.equal(acc.data.reshape(-1), keep["scores"][2].reshape(-1))
 
 
+def test_round_from_pinned_host_updates_equals_device_updates():
+    """updates left in (pinned) host memory are streamed in one client ahead of the encryption; the
+    ciphertexts and the distances are the same as from a device tensor"""
+    import torch
+
+    from lancelot_b200 import krum
+
+    torch.manual_seed(5)
+    ek = krum.EncryptedKrum(log_slots=10, seed=3)
+    upd = (torch.randn(6, 2 * 1024 + 17, dtype=torch.float32) * 0.3).pin_memory()
+    k_dev, k_host = {}, {}
+    d_dev, o_dev = ek.round(upd.cuda(), keep=k_dev)
+    d_host, o_host = ek.round(upd, keep=k_host)
+    assert d_dev == d_host and list(o_dev) == list(o_host)
+    for c in k_dev["cts"]:
+        assert torch.equal(k_dev["cts"][c], k_host["cts"][c])
+
+
 def test_reference_driver_flow_small():
     """GPU_init .. GPU_krum with the reference's call sequence (diagonal pairs, re-encryption per pair, masks)"""
     import torch

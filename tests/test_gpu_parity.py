@@ -209,6 +209,43 @@ def test_krum_accumulate(torch_cuda, n_chunks):
     assert np.array_equal(cabi.to_host(acc), o.poly_op("add", L, want, want))
 
 
+@pytest.mark.parametrize("n_a,n_b,n_chunks", [(2, 0, 3), (3, 0, 1), (4, 0, 70), (1, 1, 5), (1, 4, 2), (2, 1, 130), (2, 3, 4), (2, 4, 66)])
+def test_krum_accumulate_tile(torch_cuda, n_a, n_b, n_chunks):
+    """every pair sum of a tile equals the per-chunk sub / square / add sequence of the oracle"""
+    from lancelot_b200 import cabi
+
+    logn, L = 10, 3
+    o, ctx, mods = make(logn, [60, 40, 40, 60], 1)
+    rng = np.random.default_rng(1000 * n_a + 100 * n_b + n_chunks)
+    n = 1 << logn
+    host = [rand_rows(rng, row_moduli(mods, 3, L, 0, 2 * n_chunks), n).reshape(n_chunks, 2, L, n) for _ in range(n_a + n_b)]
+    dev = [cabi.to_device(h) for h in host]
+    if n_b:
+        pairs = [(i, n_a + j) for i in range(n_a) for j in range(n_b)]
+    else:
+        pairs = [(i, j) for i in range(n_a) for j in range(i + 1, n_a)]
+    outs = [ctx.empty(3, L, n) for _ in pairs]
+    ctx.krum_accumulate_tile(L, dev[:n_a], dev[n_a:], outs)
+    for (i, j), got in zip(pairs, outs):
+        want = np.zeros((3, L, n), dtype=np.uint64)
+        for c in range(n_chunks):
+            want = o.poly_op("add", L, want, o.square(L, o.poly_op("sub", L, host[j][c], host[i][c]).reshape(2, L, n)))
+        assert np.array_equal(cabi.to_host(got), want)
+
+
+def test_krum_tile_shape_errors(torch_cuda):
+    from lancelot_b200 import cabi
+    from lancelot_b200._lib import InvalidArgument
+
+    o, ctx, mods = make(10, [60, 40, 40, 60], 1)
+    t = [ctx.empty(1, 2, 3, 1 << 10) for _ in range(5)]
+    outs = [ctx.empty(3, 3, 1 << 10) for _ in range(10)]
+    with pytest.raises(InvalidArgument):
+        ctx.krum_accumulate_tile(3, t[:5], [], outs[:10])  # triangle of five
+    with pytest.raises(InvalidArgument):
+        ctx.krum_accumulate_tile(3, t[:3], t[3:5], outs[:6])  # three rows
+
+
 def test_error_reporting_on_gpu(torch_cuda):
     from lancelot_b200 import cabi
     from lancelot_b200._lib import InvalidArgument, LancelotError

@@ -22,6 +22,28 @@ def test_pair_schedule_covers_every_pair_once_and_balances():
     assert max(len(clients_of(s)) for s in sched) <= 15
 
 
+def test_pair_tiles_cover_every_pair_once_with_valid_shapes():
+    from lancelot_b200.krum import all_pairs, pair_schedule, pair_tiles, tile_pairs
+
+    reads = 0
+    for n in (2, 3, 5, 10, 20, 33):
+        for world in (1, 2, 3, 8):
+            for part in pair_schedule(n, world):
+                tiles = pair_tiles(part)
+                covered = [p for t in tiles for p in tile_pairs(t)]
+                assert sorted(covered) == sorted(part) and len(covered) == len(set(covered))
+                for kind, rows, cols in tiles:
+                    if kind == "tri":
+                        assert 2 <= len(rows) <= 4 and not cols
+                    else:
+                        assert 1 <= len(rows) <= 2 and 1 <= len(cols) <= 4
+                        assert all(i < j for i in rows for j in cols)
+                if n == 20 and world == 1:
+                    reads = sum(len(r) + len(c) for _, r, c in tiles)
+    # 20 clients on one rank: 140 client reads instead of 2 x 190
+    assert reads == 140 and len(all_pairs(20)) == 190
+
+
 def test_plaintext_krum_rule():
     from lancelot_b200.krum import plaintext_krum
 
