@@ -295,7 +295,7 @@ def run_gpu(args, wl):
         wl.profile_phases = True
         wl.step_gpu()
         wl.profile_phases = False
-    for _ in range(2):
+    for _ in range(max(args.warmup, 3)):
         wl.step_e2e()
     ms_e2e, io = timed(wl.step_e2e, args.steps)
 

@@ -2,6 +2,7 @@
 
 #include <cmath>
 #include <cstring>
+#include <mutex>
 
 namespace lb {
 
@@ -96,10 +97,47 @@ static void complex_root(size_t index, size_t M, double &re, double &im)
     }
 }
 
+// Destroyed contexts are parked with their device tables instead of being freed: the tables
+// depend only on (device, ring degree, primes, Galois elements), and a caller that builds a
+// fresh context for every round (as the reference's Krum driver does) otherwise repeats the
+// host precompute, some fifty allocations and their uploads each time.
+constexpr size_t kMaxParked = 4;
+static std::mutex g_parked_mu;
+static std::vector<Context *> g_parked;
+
+static void release_tables(Context *ctx)
+{
+    for (void *p : ctx->owned) cudaFree(p);
+    delete ctx;
+}
+
+static Context *take_parked(int logN, const std::vector<u64> &moduli, int size_P, const std::vector<uint32_t> &elts, int device)
+{
+    std::lock_guard<std::mutex> lock(g_parked_mu);
+    for (size_t i = 0; i < g_parked.size(); ++i) {
+        Context *c = g_parked[i];
+        if (c->device == device && c->hp.logN == logN && c->hp.size_P == size_P && c->hp.q == moduli && c->hp.galois_elts == elts) {
+            g_parked.erase(g_parked.begin() + i);
+            return c;
+        }
+    }
+    return nullptr;
+}
+
 int context_create(int logN, const std::vector<u64> &moduli, int size_P, const std::vector<uint32_t> &elts, int device,
                    Context **out)
 {
     *out = nullptr;
+    if (Context *parked = take_parked(logN, moduli, size_P, elts, device)) {
+        cudaError_t pe = cudaSetDevice(device);
+        if (pe == cudaSuccess) pe = cudaMemset(parked->d_status, 0, 256);
+        if (pe != cudaSuccess) {
+            release_tables(parked);
+            return cuda_fail(pe, "reviving a parked context");
+        }
+        *out = parked;
+        return LB_OK;
+    }
     Context *ctx = new Context();
     if (!ctx->hp.init(logN, moduli, size_P, elts)) {
         set_error(ctx->hp.error);
@@ -196,7 +234,6 @@ void context_destroy(Context *ctx)
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
-    for (void *p : ctx->owned) cudaFree(p);
     if (ctx->ws) {
         const int d = ctx->device;
         if (d >= 0 && d < kMaxCachedDevices && ctx->ws_bytes > g_ws_cache_bytes[d]) {
@@ -206,8 +243,23 @@ void context_destroy(Context *ctx)
         } else {
             cudaFree(ctx->ws);
         }
+        ctx->ws = nullptr;
+        ctx->ws_bytes = 0;
     }
-    delete ctx;
+    Context *evicted = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_parked_mu);
+        g_parked.push_back(ctx);
+        if (g_parked.size() > kMaxParked) {
+            evicted = g_parked.front();
+            g_parked.erase(g_parked.begin());
+        }
+    }
+    if (evicted) {
+        cudaSetDevice(evicted->device);
+        release_tables(evicted);
+        cudaSetDevice(ctx->device);
+    }
 }
 
 } // namespace lb

@@ -242,6 +242,17 @@ def clients_of(pairs):
     return sorted({c for p in pairs for c in p})
 
 
+_COPY_STREAMS = {}
+
+
+def _copy_stream(dev):
+    """One side stream per device for the whole process: a stream taken fresh from the pool is created
+    on first use, and creating a stream while kernels are running can stall for a long time."""
+    if dev.index not in _COPY_STREAMS:
+        _COPY_STREAMS[dev.index] = torch.cuda.Stream(dev)
+    return _COPY_STREAMS[dev.index]
+
+
 class EncryptedKrum:
     """Persistent context + keys, batched encrypt, batched pair scores, plaintext selection.
 
@@ -322,9 +333,7 @@ class EncryptedKrum:
             return
         dev = torch.device("cuda", self.lb.device)
         main = torch.cuda.current_stream(dev)
-        if getattr(self, "_copy_stream", None) is None:
-            self._copy_stream = torch.cuda.Stream(dev)
-        copy = self._copy_stream
+        copy = _copy_stream(dev)
         bufs = [torch.empty(updates.shape[1], dtype=updates.dtype, device=dev) for _ in range(2)]
         ready = [torch.cuda.Event() for _ in range(2)]
         free = [torch.cuda.Event() for _ in range(2)]
