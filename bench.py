@@ -328,6 +328,13 @@ def run_gpu(args, wl):
                 "cpu_baseline": cpu, "clocks": clocks.summary(), "parity_check": ok}
         if hasattr(wl, "int_roof"):
             line["int_roof"] = wl.int_roof()
+        if hasattr(wl, "int_roof_gbs"):
+            line["roofline"]["arithmetic_roof_gbs"] = wl.int_roof_gbs
+            line["roofline"]["frac_of_arithmetic_roof"] = achieved / wl.int_roof_gbs
+        if hasattr(wl, "pair_kernel"):
+            wl.pair_kernel["peak"] = peak
+            wl.pair_kernel["frac"] = wl.pair_kernel["achieved"] / peak
+            line["roofline_pair_kernel"] = wl.pair_kernel
         if getattr(wl, "breakdown", None):
             line["breakdown"] = wl.breakdown
         if hasattr(wl, "rel_err"):

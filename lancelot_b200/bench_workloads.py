@@ -130,29 +130,49 @@ class KrumWorkload:
 
     # -- dominant kernel -------------------------------------------------------------------------------
     def time_dominant_kernel(self, timed):
-        """the pair accumulation kernel alone on two resident clients (inputs 2 x chunks x ct > L2)"""
+        """The forward transform takes the largest share of a round (see the launch shares under profiles/):
+        timed alone on 64 key-level polynomials of this chain ({60,40,40|60}: 256 limbs, 128 MiB > L2).
+        The pair accumulation tile (2 x 4 clients, the round's second kernel) is timed too and reported
+        as ``roofline_pair_kernel``."""
         from . import krum
         torch = self.torch
         ek = krum.EncryptedKrum(log_slots=self.log_slots, device=self.device, seed=1)
-        a = ek.encrypt_client(self.updates[0], client=0)
-        b = ek.encrypt_client(self.updates[1], client=1)
-        acc = ek.lb.empty(3, 3, ek.N)
-        fn = lambda: ek.lb.krum_accumulate(3, a, b, acc, accumulate=False)
+        lb, N = ek.lb, ek.N
+        polys = 64
+        g = torch.Generator(device="cuda:%d" % self.device)
+        g.manual_seed(7)
+        data = torch.randint(0, 1 << 39, (polys, 4, N), dtype=torch.int64, device="cuda:%d" % self.device, generator=g)
+        fn = lambda: lb.ntt_forward(data, polys, 3, 1)
         for _ in range(3):
             fn()
         ms, _ = timed(fn, 10)
-        self._kernel_bytes = 2 * a.numel() * 8 + acc.numel() * 8
-        del a, b
-        return ms / 10, "krum_accumulate_kernel"
+        self._kernel_bytes = 16 * N * 4 * polys
+        per_limb = (N // 2) * (self.log_slots + 1)
+        # half of the limbs take the integer butterfly (60-bit primes), half the FP64-assisted lazy one (40-bit)
+        roofs = [lb.butterfly_rate(v) / per_limb * 16 * N / 1e9 for v in (0, 3)]
+        self.int_roof_gbs = 2.0 / (1.0 / roofs[0] + 1.0 / roofs[1])
+        del data
+        # pair tile: two clients against four
+        cl = [ek.encrypt_client(self.updates[i], client=i) for i in range(6)]
+        outs = [lb.empty(3, 3, N) for _ in range(8)]
+        tile = lambda: lb.krum_accumulate_tile(3, cl[:2], cl[2:], outs)
+        for _ in range(2):
+            tile()
+        tms, _ = timed(tile, 5)
+        tile_bytes = 6 * cl[0].numel() * 8 + 8 * outs[0].numel() * 8
+        self.pair_kernel = {"kernel": "krum_tile_kernel<2,4>", "bound": "hbm", "achieved": tile_bytes / (tms / 5 * 1e-3) / 1e9, "unit": "GB/s",
+                            "bytes_per_launch": tile_bytes, "pairs_per_launch": 8}
+        del cl, outs
+        return ms / 10, "ntt_fwd_fixed_kernel<3> (plain input)"
 
     def roofline_kernel_bytes(self):
         return self._kernel_bytes
 
     @property
     def ncu_traffic_bytes(self):
-        # one captured pair launch of the 10-client size moved 327.1 MB of DRAM traffic for
-        # 330.3 MB of algorithmic bytes; every byte is read once, so the ratio carries over
-        return int(self._kernel_bytes * 327.1 / 330.3)
+        # one captured launch of this kernel moved 404.1 MB of DRAM traffic for 402.7 MB of algorithmic
+        # bytes (16 polynomials x 24 limbs); traffic grows with the limb count, so the ratio carries over
+        return int(self._kernel_bytes * 404.1 / 402.7)
 
     # -- CPU baseline -----------------------------------------------------------------------------------
     def cpu_sample(self, threads):
@@ -279,7 +299,7 @@ class HmultWorkload:
             fn()
         ms, _ = timed(fn, 10)
         self._kernel_bytes = 16 * self.N * rows
-        return ms / 10, "ntt_fwd_kernel<3>"
+        return ms / 10, "ntt_fwd_fixed_kernel<3> (plain input)"
 
     def roofline_kernel_bytes(self):
         return self._kernel_bytes

@@ -136,11 +136,13 @@ LB_D u128d mul_wide(u64 a, u64 b)
     return r;
 }
 
+// acc += a * b; the 128-bit integer type lets the compiler share partial products between the
+// two halves and keep the additions on the carry chain
 LB_D void mac_wide(u128d &acc, u64 a, u64 b)
 {
-    u64 lo = a * b, hi = __umul64hi(a, b);
-    acc.lo += lo;
-    acc.hi += hi + (acc.lo < lo);
+    const u128 s = ((u128)acc.hi << 64 | acc.lo) + (u128)a * b;
+    acc.lo = (u64)s;
+    acc.hi = (u64)(s >> 64);
 }
 
 // (hi:lo) mod q with the two-word ratio floor(2^128 / q) = (r1:r0); exact for q < 2^62.

@@ -273,8 +273,8 @@ __global__ void __launch_bounds__(kTileThreads, 3) krum_tile_kernel(const KrumTi
     constexpr int NI = NA + NB, NP = NB ? NA * NB : NA * (NA - 1) / 2;
     for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < per_poly; e += (long)gridDim.x * blockDim.x) {
         const ModConst m = mc[(int)(e >> logn)];
-        // 128-bit running sums; every 64 chunks they are reduced in place, which leaves room for
-        // 63 more products of residues below 2^61
+        // 128-bit running sums; every 63 chunks they are reduced in place, which leaves room for
+        // 63 more products of differences below 2^61
         u128d s0[NP], s1[NP], s2[NP];
 #pragma unroll
         for (int p = 0; p < NP; ++p) s0[p] = s1[p] = s2[p] = u128d{0, 0};
@@ -293,7 +293,8 @@ __global__ void __launch_bounds__(kTileThreads, 3) krum_tile_kernel(const KrumTi
                 for (int i = 0; i < NA; ++i) {
 #pragma unroll
                     for (int j = NB ? NA : i + 1; j < NI; ++j, ++p) {
-                        const u64 x0 = sub_mod(v0[j], v0[i], m.q), x1 = sub_mod(v1[j], v1[i], m.q);
+                        // differences left in (0, 2q): 63 products below 2^122 and a residue fit 128 bits
+                        const u64 x0 = v0[j] + m.q - v0[i], x1 = v1[j] + m.q - v1[i];
                         mac_wide(s0[p], x0, x0);
                         mac_wide(s1[p], x0, x1);
                         mac_wide(s2[p], x1, x1);
