@@ -725,12 +725,11 @@ def hoisting_inplace(ctx, ct, glk, steps):
         raise RuntimeError("Galois key not present in hoisting")
     L = ctx.size_l(ct.chain_index)
     data = ct.data.contiguous()
-    # the C ABI takes up to 16 steps per call; longer lists are summed in groups (each group
-    # performs its own mod-up, the sum is the same ciphertext)
-    out = None
-    for s in range(0, len(idx), 16):
-        part = ctx.lb.hoisting(L, data.clone(), idx[s:s + 16], [glk.keys[i] for i in idx[s:s + 16]])
-        out = part if out is None else ctx.lb.add(L, out, part)
+    # one mod-up and one mod-down for the whole list, as in the reference; the C ABI takes up to 32 steps
+    # (the Krum driver uses 15), and splitting a longer list would round in a different place
+    if len(idx) > 32:
+        raise ValueError("hoisting takes at most 32 rotation steps per call")
+    out = ctx.lb.hoisting(L, data.clone(), idx, [glk.keys[i] for i in idx])
     ct.data = out
 
 
