@@ -13,8 +13,11 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <array>
 #include <functional>
+#include <istream>
 #include <memory>
+#include <ostream>
 #include <random>
 #include <stdexcept>
 #include <vector>
@@ -165,6 +168,112 @@ private:
 
 } // namespace cahel_b200
 
+// ---- byte streams in the reference's own format ----------------------------------------------
+namespace cahel {
+using parms_id_type = std::array<std::uint64_t, 4>;
+}
+
+namespace cahel_b200 {
+
+// BLAKE2b (RFC 7693), unkeyed, 32-byte digest: the hash behind the reference's parms_id
+// (cahel-main/include/util/hash.h:22-38)
+inline cahel::parms_id_type blake2b_256(const std::uint8_t *in, std::size_t len)
+{
+    static const std::uint64_t iv[8] = {0x6a09e667f3bcc908ULL, 0xbb67ae8584caa73bULL, 0x3c6ef372fe94f82bULL, 0xa54ff53a5f1d36f1ULL,
+                                        0x510e527fade682d1ULL, 0x9b05688c2b3e6c1fULL, 0x1f83d9abfb41bd6bULL, 0x5be0cd19137e2179ULL};
+    static const std::uint8_t sigma[12][16] = {
+        {0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15}, {14, 10, 4, 8, 9, 15, 13, 6, 1, 12, 0, 2, 11, 7, 5, 3},
+        {11, 8, 12, 0, 5, 2, 15, 13, 10, 14, 3, 6, 7, 1, 9, 4}, {7, 9, 3, 1, 13, 12, 11, 14, 2, 6, 5, 10, 4, 0, 15, 8},
+        {9, 0, 5, 7, 2, 4, 10, 15, 14, 1, 11, 12, 6, 8, 3, 13}, {2, 12, 6, 10, 0, 11, 8, 3, 4, 13, 7, 5, 15, 14, 1, 9},
+        {12, 5, 1, 15, 14, 13, 4, 10, 0, 7, 6, 3, 9, 2, 8, 11}, {13, 11, 7, 14, 12, 1, 3, 9, 5, 0, 15, 4, 8, 6, 2, 10},
+        {6, 15, 14, 9, 11, 3, 0, 8, 12, 2, 13, 7, 1, 4, 10, 5}, {10, 2, 8, 4, 7, 6, 1, 5, 15, 11, 9, 14, 3, 12, 13, 0},
+        {0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15}, {14, 10, 4, 8, 9, 15, 13, 6, 1, 12, 0, 2, 11, 7, 5, 3}};
+    auto rotr = [](std::uint64_t x, int n) { return (x >> n) | (x << (64 - n)); };
+    std::uint64_t h[8];
+    for (int i = 0; i < 8; ++i) h[i] = iv[i];
+    h[0] ^= 0x01010000ULL ^ 32; // digest length 32, no key, fanout = depth = 1
+    auto compress = [&](const std::uint8_t *block, std::uint64_t t, bool last) {
+        std::uint64_t m[16], v[16];
+        for (int i = 0; i < 16; ++i) {
+            m[i] = 0;
+            for (int b = 7; b >= 0; --b) m[i] = (m[i] << 8) | block[8 * i + b];
+        }
+        for (int i = 0; i < 8; ++i) {
+            v[i] = h[i];
+            v[i + 8] = iv[i];
+        }
+        v[12] ^= t;
+        if (last) v[14] = ~v[14];
+        auto g = [&](int a, int b, int c, int d, std::uint64_t x, std::uint64_t y) {
+            v[a] = v[a] + v[b] + x; v[d] = rotr(v[d] ^ v[a], 32);
+            v[c] = v[c] + v[d];     v[b] = rotr(v[b] ^ v[c], 24);
+            v[a] = v[a] + v[b] + y; v[d] = rotr(v[d] ^ v[a], 16);
+            v[c] = v[c] + v[d];     v[b] = rotr(v[b] ^ v[c], 63);
+        };
+        for (int r = 0; r < 12; ++r) {
+            const std::uint8_t *s = sigma[r];
+            g(0, 4, 8, 12, m[s[0]], m[s[1]]);   g(1, 5, 9, 13, m[s[2]], m[s[3]]);
+            g(2, 6, 10, 14, m[s[4]], m[s[5]]);  g(3, 7, 11, 15, m[s[6]], m[s[7]]);
+            g(0, 5, 10, 15, m[s[8]], m[s[9]]);  g(1, 6, 11, 12, m[s[10]], m[s[11]]);
+            g(2, 7, 8, 13, m[s[12]], m[s[13]]); g(3, 4, 9, 14, m[s[14]], m[s[15]]);
+        }
+        for (int i = 0; i < 8; ++i) h[i] ^= v[i] ^ v[i + 8];
+    };
+    std::uint8_t block[128];
+    std::size_t off = 0;
+    while (len - off > 128) {
+        compress(in + off, off + 128, false);
+        off += 128;
+    }
+    std::memset(block, 0, sizeof(block));
+    std::memcpy(block, in + off, len - off);
+    compress(block, len, true);
+    return {h[0], h[1], h[2], h[3]};
+}
+
+// parms_id of a chain level (cahel-main/include/util/encryptionparams.h:337-381): scheme, N, number of
+// special primes, every prime of the key level, the primes in use at the level, and a zero plain modulus
+inline cahel::parms_id_type parms_id_of(std::size_t n, const std::vector<std::uint64_t> &moduli, std::size_t size_p, std::size_t size_l_or_all)
+{
+    std::vector<std::uint64_t> w = {3 /* scheme_type::ckks */, (std::uint64_t)n, (std::uint64_t)size_p};
+    w.insert(w.end(), moduli.begin(), moduli.end());
+    w.insert(w.end(), moduli.begin(), moduli.begin() + size_l_or_all);
+    w.push_back(0);
+    return blake2b_256(reinterpret_cast<const std::uint8_t *>(w.data()), w.size() * 8); // little-endian host, as the reference assumes
+}
+
+template <class T>
+inline void put(std::ostream &s, const T &v) { s.write(reinterpret_cast<const char *>(&v), sizeof(T)); }
+template <class T>
+inline T get(std::istream &s)
+{
+    T v{};
+    s.read(reinterpret_cast<char *>(&v), sizeof(T));
+    if (!s) throw std::runtime_error("I/O error");
+    return v;
+}
+
+inline void put_words(std::ostream &s, const std::uint64_t *dev, std::size_t n)
+{
+    std::vector<std::uint64_t> h(n);
+    if (n) cuda_check(cudaMemcpy(h.data(), dev, n * 8, cudaMemcpyDeviceToHost));
+    put<std::uint64_t>(s, n);
+    s.write(reinterpret_cast<const char *>(h.data()), (std::streamsize)(n * 8));
+    if (!s) throw std::runtime_error("I/O error");
+}
+
+inline void get_words(std::istream &s, DeviceWords &dst, std::size_t expect)
+{
+    if (get<std::uint64_t>(s) != expect) throw std::invalid_argument("stream does not match the context");
+    std::vector<std::uint64_t> h(expect);
+    s.read(reinterpret_cast<char *>(h.data()), (std::streamsize)(expect * 8));
+    if (!s) throw std::runtime_error("I/O error");
+    dst.resize(expect);
+    if (expect) cuda_check(cudaMemcpy(dst.get(), h.data(), expect * 8, cudaMemcpyHostToDevice));
+}
+
+} // namespace cahel_b200
+
 // ---- context and containers -------------------------------------------------------------------
 
 // cahel-main/include/gpucontext.h:15-136.  chain index 0 = key level, 1 = first data level,
@@ -220,6 +329,10 @@ struct CAHELGPUContext {
             if (galois_elts_[i] == elt) return (int)i;
         return -1;
     }
+    cahel::parms_id_type parms_id(std::size_t chain_index) const
+    {
+        return cahel_b200::parms_id_of(poly_degree_, moduli_, size_P_, chain_index == 0 ? size_QP_ : (std::size_t)size_l(chain_index));
+    }
 };
 
 // cahel-main/include/plaintext.h:11
@@ -236,6 +349,30 @@ struct CAHELGPUPlaintext {
     double &scale() { return scale_; }
     double scale() const { return scale_; }
     bool is_ntt_form() const { return is_ntt_form_; }
+    // cahel-main/include/plaintext.h:109-213, byte for byte.  The reference's save() takes no context
+    // because its containers keep the parms_id; these look it up in the context.
+    void save(const CAHELGPUContext &context, std::ostream &stream) const
+    {
+        const std::size_t limbs = (std::size_t)context.size_l(chain_index_), n = context.poly_degree_;
+        cahel_b200::put(stream, context.parms_id(chain_index_));
+        cahel_b200::put<std::uint64_t>(stream, limbs);
+        cahel_b200::put<std::uint64_t>(stream, chain_index_);
+        cahel_b200::put<std::uint64_t>(stream, n);
+        cahel_b200::put(stream, scale_);
+        cahel_b200::put_words(stream, data_.get(), limbs * n);
+    }
+    void load(const CAHELGPUContext &context, std::istream &stream)
+    {
+        const auto id = cahel_b200::get<cahel::parms_id_type>(stream);
+        const auto limbs = cahel_b200::get<std::uint64_t>(stream), chain = cahel_b200::get<std::uint64_t>(stream),
+                   n = cahel_b200::get<std::uint64_t>(stream);
+        const double scale = cahel_b200::get<double>(stream);
+        if (n != context.poly_degree_ || chain > context.max_chain() || limbs != (std::uint64_t)context.size_l(chain) ||
+            id != context.parms_id(chain))
+            throw std::invalid_argument("plaintext data is invalid");
+        cahel_b200::get_words(stream, data_, limbs * n);
+        chain_index_ = chain; coeff_modulus_size_ = limbs; poly_modulus_degree_ = n; scale_ = scale; is_ntt_form_ = true;
+    }
 };
 
 // cahel-main/include/ciphertext.h:7
@@ -263,12 +400,78 @@ struct CAHELGPUCiphertext {
         poly_modulus_degree_ = context.poly_degree_;
         data_.resize(size_ * coeff_modulus_size_ * poly_modulus_degree_);
     }
+    // cahel-main/include/ciphertext.h:174-292, byte for byte (the trailing 64-byte seed block is zero,
+    // as the reference leaves it); see CAHELGPUPlaintext::save for the context argument
+    void save(const CAHELGPUContext &context, std::ostream &stream) const
+    {
+        const std::size_t limbs = (std::size_t)context.size_l(chain_index_), n = context.poly_degree_;
+        cahel_b200::put(stream, context.parms_id(chain_index_));
+        cahel_b200::put(stream, is_ntt_form_);
+        cahel_b200::put<std::uint64_t>(stream, chain_index_);
+        cahel_b200::put<std::uint64_t>(stream, size_);
+        cahel_b200::put<std::uint64_t>(stream, n);
+        cahel_b200::put<std::uint64_t>(stream, limbs);
+        cahel_b200::put(stream, scale_);
+        cahel_b200::put_words(stream, data_.get(), size_ * limbs * n);
+        const char seed[64] = {0};
+        stream.write(seed, sizeof(seed));
+        if (!stream) throw std::runtime_error("I/O error");
+    }
+    void load(const CAHELGPUContext &context, std::istream &stream)
+    {
+        const auto id = cahel_b200::get<cahel::parms_id_type>(stream);
+        const bool ntt = cahel_b200::get<bool>(stream);
+        const auto chain = cahel_b200::get<std::uint64_t>(stream), size = cahel_b200::get<std::uint64_t>(stream),
+                   n = cahel_b200::get<std::uint64_t>(stream), limbs = cahel_b200::get<std::uint64_t>(stream);
+        const double scale = cahel_b200::get<double>(stream);
+        if (n != context.poly_degree_ || chain > context.max_chain() || limbs != (std::uint64_t)context.size_l(chain) || size < 2 ||
+            id != context.parms_id(chain))
+            throw std::invalid_argument("ciphertext data is invalid");
+        cahel_b200::get_words(stream, data_, size * limbs * n);
+        char seed[64];
+        stream.read(seed, sizeof(seed));
+        if (!stream) throw std::runtime_error("I/O error");
+        size_ = size; chain_index_ = chain; coeff_modulus_size_ = limbs; poly_modulus_degree_ = n; scale_ = scale; is_ntt_form_ = ntt;
+    }
 };
 
 struct CAHELGPUPublicKey {
     cahel_b200::DeviceWords pk_;
     CAHELGPUPublicKey() = default;
     explicit CAHELGPUPublicKey(const CAHELGPUContext &) {}
+    // cahel-main/include/secretkey.h:54-60: the pair as a size-2 ciphertext over all primes; the reference
+    // writes the key level's parms_id with chain index 1 and scale 1
+    void save(const CAHELGPUContext &context, std::ostream &stream) const
+    {
+        if (!pk_.size()) throw std::logic_error("public key has not been generated");
+        const std::size_t n = context.poly_degree_;
+        cahel_b200::put(stream, context.parms_id(0));
+        cahel_b200::put(stream, true);
+        cahel_b200::put<std::uint64_t>(stream, 1);
+        cahel_b200::put<std::uint64_t>(stream, 2);
+        cahel_b200::put<std::uint64_t>(stream, n);
+        cahel_b200::put<std::uint64_t>(stream, context.size_QP_);
+        cahel_b200::put(stream, 1.0);
+        cahel_b200::put_words(stream, pk_.get(), 2 * context.size_QP_ * n);
+        const char seed[64] = {0};
+        stream.write(seed, sizeof(seed));
+        if (!stream) throw std::runtime_error("I/O error");
+    }
+    void load(const CAHELGPUContext &context, std::istream &stream)
+    {
+        const auto id = cahel_b200::get<cahel::parms_id_type>(stream);
+        (void)cahel_b200::get<bool>(stream);
+        (void)cahel_b200::get<std::uint64_t>(stream);
+        const auto size = cahel_b200::get<std::uint64_t>(stream), n = cahel_b200::get<std::uint64_t>(stream),
+                   limbs = cahel_b200::get<std::uint64_t>(stream);
+        (void)cahel_b200::get<double>(stream);
+        if (n != context.poly_degree_ || limbs != context.size_QP_ || size != 2 || id != context.parms_id(0))
+            throw std::invalid_argument("public key data is invalid");
+        cahel_b200::get_words(stream, pk_, 2 * limbs * n);
+        char seed[64];
+        stream.read(seed, sizeof(seed));
+        if (!stream) throw std::runtime_error("I/O error");
+    }
     // cahel-main/src/secretkey.cu:179-249; only plaintexts of the first data level, like the reference
     void encrypt_asymmetric(const CAHELGPUContext &context, const CAHELGPUPlaintext &plain, CAHELGPUCiphertext &cipher,
                             bool save_seed = false) const

@@ -16,7 +16,10 @@ Differences from the reference that a caller can see:
   Python-list round trip;
 * decryption adds no noise-flooding term (the reference's needs OpenFHE,
   cahel-main/src/secretkey.cu:632-649);
-* BFV/BGV entry points raise ``ValueError("unsupported scheme")``.
+* BFV/BGV entry points raise ``ValueError("unsupported scheme")``;
+* ``save`` / ``load`` of plaintexts, ciphertexts and public keys exist here although the pybind module
+  does not export them: they write and read the byte streams of the reference's C++ classes
+  (``lancelot_b200.wire``), and take the context as their first argument.
 """
 import enum
 import math
@@ -25,7 +28,7 @@ import os
 import numpy as np
 import torch
 
-from . import cabi
+from . import cabi, wire
 from ._lib import InvalidArgument, LancelotError
 
 # ---- enums (binding.cu:9-29, export_values) -------------------------------------------------
@@ -196,6 +199,19 @@ class context:
 # ---- containers --------------------------------------------------------------------------------
 
 
+def _to_device(ctx, words):
+    return torch.from_numpy(np.ascontiguousarray(words).view(np.int64)).to("cuda:%d" % ctx.lb.device)
+
+
+def _stream_bytes(stream, unpack):
+    """reads one object from a binary stream that may hold several, leaving the stream after it"""
+    start = stream.tell()
+    blob = stream.read()
+    out = unpack(blob)
+    stream.seek(start + out["consumed"])
+    return out
+
+
 class plaintext:
     """CAHELGPUPlaintext: [limb][N] residues in NTT form, a chain index and a scale."""
 
@@ -204,6 +220,22 @@ class plaintext:
         self.chain_index = 0
         self.scale = 1.0
         self.is_ntt_form = True
+
+    def save(self, ctx, stream):
+        """cahel-main/include/plaintext.h:109-146, byte for byte (the reference method takes no context; this
+        container does not keep one, so it is passed in)"""
+        limbs = ctx.size_l(self.chain_index)
+        pid = wire.parms_id(ctx.N, ctx.moduli, ctx.size_P, self.chain_index)
+        stream.write(wire.pack_plaintext(pid, self.chain_index, ctx.N, limbs, self.scale, self.data.cpu().numpy()))
+
+    def load(self, ctx, stream):
+        """cahel-main/include/plaintext.h:148-213"""
+        f = _stream_bytes(stream, wire.unpack_plaintext)
+        if f["poly_modulus_degree"] != ctx.N or f["parms_id"] != wire.parms_id(ctx.N, ctx.moduli, ctx.size_P, f["chain_index"]) \
+                or f["coeff_modulus_size"] != ctx.size_l(f["chain_index"]):
+            raise ValueError("plaintext data is invalid")
+        self.data = _to_device(ctx, f["data"])
+        self.chain_index, self.scale, self.is_ntt_form = int(f["chain_index"]), float(f["scale"]), True
 
 
 class ciphertext:
@@ -228,10 +260,40 @@ class ciphertext:
         c._assign(self)
         return c
 
+    def save(self, ctx, stream):
+        """cahel-main/include/ciphertext.h:174-223, byte for byte (seed block zeroed, as the reference leaves it)"""
+        limbs = ctx.size_l(self.chain_index)
+        pid = wire.parms_id(ctx.N, ctx.moduli, ctx.size_P, self.chain_index)
+        stream.write(wire.pack_ciphertext(pid, self.chain_index, self.size, ctx.N, limbs, self.scale, self.data.cpu().numpy(),
+                                          is_ntt_form=self.is_ntt_form))
+
+    def load(self, ctx, stream):
+        """cahel-main/include/ciphertext.h:225-292"""
+        f = _stream_bytes(stream, wire.unpack_ciphertext)
+        if f["poly_modulus_degree"] != ctx.N or f["parms_id"] != wire.parms_id(ctx.N, ctx.moduli, ctx.size_P, f["chain_index"]) \
+                or f["coeff_modulus_size"] != ctx.size_l(f["chain_index"]) or f["size"] < 2:
+            raise ValueError("ciphertext data is invalid")
+        self.data = _to_device(ctx, f["data"])
+        self.size, self.chain_index, self.scale, self.is_ntt_form = int(f["size"]), int(f["chain_index"]), float(f["scale"]), f["is_ntt_form"]
+
 
 class public_key:
     def __init__(self, ctx):
         self.data = None
+
+    def save(self, ctx, stream):
+        """cahel-main/include/secretkey.h:54-56: the key pair as a size-2 ciphertext over all primes"""
+        if self.data is None:
+            raise RuntimeError("public key has not been generated")
+        stream.write(wire.pack_public_key(ctx.N, ctx.moduli, ctx.size_P, self.data.cpu().numpy()))
+
+    def load(self, ctx, stream):
+        """cahel-main/include/secretkey.h:58-60"""
+        f = _stream_bytes(stream, wire.unpack_ciphertext)
+        if f["poly_modulus_degree"] != ctx.N or f["parms_id"] != wire.parms_id(ctx.N, ctx.moduli, ctx.size_P, 0) \
+                or f["coeff_modulus_size"] != ctx.size_QP or f["size"] != 2:
+            raise ValueError("public key data is invalid")
+        self.data = _to_device(ctx, f["data"])
 
     def encrypt_asymmetric(self, ctx, plain, save_seed=False):
         """cahel-main/src/secretkey.cu:179-249: encrypt at the key level, divide by P, add the plaintext.

@@ -151,6 +151,22 @@ static void record_seeds(const std::string &name, size_t from)
     g_json << "]}";
 }
 
+// the byte stream of an object's own save(): digest of everything, and for ciphertexts also of
+// everything before the trailing 64-byte seed buffer (whose content the library never defines
+// for ciphertexts it did not seed-compress) plus that tail itself
+template <class T>
+static void record_stream(const std::string &name, T &obj, bool has_seed_tail)
+{
+    std::ostringstream os(std::ios::binary);
+    obj.save(os);
+    const std::string b = os.str();
+    record_host(name, b.data(), b.size());
+    if (has_seed_tail && b.size() >= 64) {
+        record_host(name + "_body", b.data(), b.size() - 64);
+        record_host(name + "_tail", b.data() + b.size() - 64, 64);
+    }
+}
+
 // message slot i = (i * 2654435761 mod 2^32) / 2^31 - 1, exactly representable
 static std::vector<double> message(size_t n, uint32_t salt)
 {
@@ -227,6 +243,9 @@ static void run_case(const std::string &name, size_t n, const std::vector<int> &
     record_seeds("seed_enc", mark);
     record_dev("ct1", ct1.data(), 2 * size_Q * n);
     record_dev("ct2", ct2.data(), 2 * size_Q * n);
+    record_stream("stream_pt1", pt1, false);
+    record_stream("stream_ct1", ct1, true);
+    record_stream("stream_pk", pk, true);
 
     CAHELGPUCiphertext diff(context), prod(context);
     sub(context, ct2, ct1, diff);
@@ -243,6 +262,7 @@ static void run_case(const std::string &name, size_t n, const std::vector<int> &
     const size_t L2 = size_Q - 1;
     record_dev("rescale", prod.data(), 2 * L2 * n);
     prod.set_scale(scale);
+    record_stream("stream_rescaled", prod, true);
 
     CAHELGPUCiphertext rot(context);
     rotate_vector(context, prod, steps[0], glk, rot);

@@ -3,6 +3,10 @@
 // multiply, relinearize, rescale, rotate, hoisting, decrypt, decode; results must match the
 // plaintext computation within 1e-3 (cahel-main/examples/example.h:14-19).  Exit code 0 = pass.
 #include <cstdio>
+#include <cstdlib>
+#include <fstream>
+#include <sstream>
+#include <string>
 
 #include "cahel_b200.hpp"
 
@@ -15,8 +19,31 @@ static double max_err(const std::vector<double> &got, const std::vector<double> 
     return e;
 }
 
-int main()
+// host-only mode: cpp_api_check --parms-id N size_P chain_index q0 q1 ...  prints the 32 digest bytes in hex
+static int print_parms_id(int argc, char **argv)
 {
+    if (argc < 6) return 2;
+    const size_t n = std::strtoull(argv[2], nullptr, 10), size_p = std::strtoull(argv[3], nullptr, 10), chain = std::strtoull(argv[4], nullptr, 10);
+    std::vector<uint64_t> moduli;
+    for (int i = 5; i < argc; ++i) moduli.push_back(std::strtoull(argv[i], nullptr, 10));
+    const size_t size_q = moduli.size() - size_p;
+    const auto id = cahel_b200::parms_id_of(n, moduli, size_p, chain == 0 ? moduli.size() : size_q - (chain - 1));
+    const unsigned char *b = reinterpret_cast<const unsigned char *>(id.data());
+    for (int i = 0; i < 32; ++i) printf("%02x", b[i]);
+    printf("\n");
+    return 0;
+}
+
+static std::vector<uint64_t> words_of(const uint64_t *dev, size_t n)
+{
+    std::vector<uint64_t> h(n);
+    cudaMemcpy(h.data(), dev, n * 8, cudaMemcpyDeviceToHost);
+    return h;
+}
+
+int main(int argc, char **argv)
+{
+    if (argc > 1 && std::string(argv[1]) == "--parms-id") return print_parms_id(argc, argv);
     try {
         const size_t n = 8192, slots = n / 2;
         EncryptionParameters parms(scheme_type::ckks);
@@ -65,8 +92,38 @@ int main()
         } catch (const std::invalid_argument &) {
             threw = true;
         }
-        printf("multiply %.3g rotate %.3g hoisting %.3g refused %d\n", e1, e2, e3, (int)threw);
-        return (e1 < 1e-3 && e2 < 1e-3 && e3 < 1e-3 && threw) ? 0 : 1;
+        // streams in the reference's layout: several objects in one stream, loaded back word for word
+        std::stringstream wire(std::ios::in | std::ios::out | std::ios::binary);
+        px.save(context, wire);
+        cx.save(context, wire);
+        pk.save(context, wire);
+        CAHELGPUPlaintext px2;
+        CAHELGPUCiphertext cx2;
+        CAHELGPUPublicKey pk2;
+        px2.load(context, wire);
+        cx2.load(context, wire);
+        pk2.load(context, wire);
+        const size_t limbs2 = (size_t)context.size_l(cx.chain_index());
+        bool same = words_of(px2.data(), 3 * n) == words_of(px.data(), 3 * n) &&
+                    words_of(cx2.data(), 2 * limbs2 * n) == words_of(cx.data(), 2 * limbs2 * n) &&
+                    words_of(pk2.pk_.get(), 2 * 4 * n) == words_of(pk.pk_.get(), 2 * 4 * n) && cx2.chain_index() == cx.chain_index() &&
+                    cx2.size() == 2 && cx2.scale() == cx.scale() && px2.scale() == px.scale();
+        bool refused_stream = false;
+        try {
+            std::stringstream bad(wire.str().substr(1), std::ios::in | std::ios::binary); // shifted: parms_id cannot match
+            CAHELGPUPlaintext p3;
+            p3.load(context, bad);
+        } catch (const std::invalid_argument &) {
+            refused_stream = true;
+        }
+        if (const char *path = std::getenv("CPP_API_CHECK_STREAM")) {
+            std::ofstream f(path, std::ios::binary);
+            const std::string b = wire.str();
+            f.write(b.data(), (std::streamsize)b.size());
+        }
+        printf("multiply %.3g rotate %.3g hoisting %.3g refused %d streams %d bad-stream-refused %d\n", e1, e2, e3, (int)threw, (int)same,
+               (int)refused_stream);
+        return (e1 < 1e-3 && e2 < 1e-3 && e3 < 1e-3 && threw && same && refused_stream) ? 0 : 1;
     } catch (const std::exception &e) {
         printf("exception: %s\n", e.what());
         return 2;

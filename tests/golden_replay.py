@@ -49,9 +49,10 @@ def check(fix, name, arr, report):
     return ok
 
 
-def replay(case, fix, ops):
+def replay(case, fix, ops, keep=None):
     """ops: an object with the oracle's method names (the oracle itself, or an adapter that
-    runs the CUDA library).  Returns the list of (stage, ok)."""
+    runs the CUDA library).  Returns the list of (stage, ok); ``keep`` (a dict) receives the
+    public key, first plaintext, first ciphertext and the rescaled product."""
     cfg = CASES[case]
     report = []
     size_QP = fix["moduli"]["bytes"] // 8
@@ -97,6 +98,8 @@ def replay(case, fix, ops):
     check(fix, "relin", rel, report)
     res = ops.rescale(L, rel)
     check(fix, "rescale", res, report)
+    if keep is not None:
+        keep.update(pk=pk, pt1=pt1, ct1=ct1, rescaled=res, size_QP=size_QP, size_Q=size_Q, n=n)
     L2 = L - 1
     check(fix, "rotate", ops.rotate(L2, res, 0, glk[0]), report)
     hoist = ops.hoisting(L2, res, list(range(n_elts)), glk)

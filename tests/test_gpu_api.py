@@ -199,6 +199,42 @@ def test_round_from_pinned_host_updates_equals_device_updates():
         assert torch.equal(k_dev["cts"][c], k_host["cts"][c])
 
 
+def test_save_load_streams_round_trip_on_the_device(env):
+    """objects written with the reference's stream layout come back identical, several per stream"""
+    import io
+
+    import torch
+
+    import lancelot_b200.pycahel as cahel
+
+    ctx, sk, pk, rlk, enc, scale = env["ctx"], env["sk"], env["pk"], env["rlk"], env["enc"], env["scale"]
+    pt = enc.encode(ctx, [0.5, -0.25, 3.0], scale)
+    ct = pk.encrypt_asymmetric(ctx, pt)
+    cahel.square_inplace(ctx, ct)
+    buf = io.BytesIO()
+    pt.save(ctx, buf)
+    ct.save(ctx, buf)
+    pk.save(ctx, buf)
+    buf.seek(0)
+    pt2, ct2, pk2 = cahel.plaintext(), cahel.ciphertext(), cahel.public_key(ctx)
+    pt2.load(ctx, buf)
+    ct2.load(ctx, buf)
+    pk2.load(ctx, buf)
+    assert buf.read() == b""
+    assert torch.equal(pt2.data.reshape(-1), pt.data.reshape(-1)) and pt2.chain_index == pt.chain_index and pt2.scale == pt.scale
+    assert torch.equal(ct2.data.reshape(-1), ct.data.reshape(-1)) and (ct2.size, ct2.chain_index, ct2.scale) == (3, ct.chain_index, ct.scale)
+    assert torch.equal(pk2.data.reshape(-1), pk.data.reshape(-1))
+    # a loaded ciphertext keeps working
+    cahel.relinearize_inplace(ctx, ct2, rlk)
+    cahel.rescale_to_next_inplace(ctx, ct2)
+    out = enc.decode(ctx, sk.decrypt(ctx, ct2))
+    assert abs(out[0] - 0.25) < 1e-6 and abs(out[2] - 9.0) < 1e-5
+    # a stream of another parameter set is refused
+    other = io.BytesIO(buf.getvalue()[:32][::-1] + buf.getvalue()[32:])
+    with pytest.raises(ValueError):
+        cahel.plaintext().load(ctx, other)
+
+
 def test_reference_driver_flow_small():
     """GPU_init .. GPU_krum with the reference's call sequence (diagonal pairs, re-encryption per pair, masks)"""
     import torch
@@ -228,10 +264,28 @@ def test_cpp_class_layer_program():
     import os
     import subprocess
 
+    import tempfile
+
+    from lancelot_b200 import cabi, wire
+
     exe = os.path.join(os.path.dirname(os.path.abspath(__file__)), "cpp_api_check")
     assert os.path.exists(exe), "run __graft_entry__.build() first"
-    r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
-    assert r.returncode == 0, r.stdout + r.stderr
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "objects.bin")
+        r = subprocess.run([exe], capture_output=True, text=True, timeout=120, env=dict(os.environ, CPP_API_CHECK_STREAM=path))
+        assert r.returncode == 0, r.stdout + r.stderr
+        blob = open(path, "rb").read()
+    # the stream the C++ classes wrote (plaintext, rescaled ciphertext, public key) parses with the Python reader
+    n = 8192
+    mods = cabi.coeff_modulus_create(n, [60, 40, 40, 60])
+    pt = wire.unpack_plaintext(blob)
+    assert pt["parms_id"] == wire.parms_id(n, mods, 1, 1) and pt["coeff_modulus_size"] == 3 and pt["chain_index"] == 1
+    ct = wire.unpack_ciphertext(blob[pt["consumed"]:])
+    assert ct["parms_id"] == wire.parms_id(n, mods, 1, 2) and (ct["size"], ct["coeff_modulus_size"], ct["chain_index"]) == (2, 2, 2)
+    pk = wire.unpack_ciphertext(blob[pt["consumed"] + ct["consumed"]:])
+    assert pk["parms_id"] == wire.parms_id(n, mods, 1, 0) and (pk["size"], pk["coeff_modulus_size"], pk["chain_index"]) == (2, 4, 1)
+    assert pt["consumed"] + ct["consumed"] + pk["consumed"] == len(blob)
+    assert all(int(x) < m for x, m in zip(ct["data"][0].max(axis=1), mods[:2]))
 
 
 def test_mask_multiplication_selects_and_averages():
