@@ -362,22 +362,35 @@ class EncryptedKrum:
 
         n_clients, dim = updates.shape[0], updates.shape[1]
         chunks = self.n_chunks(dim)
-        mine_buf = self.lb.empty(chunks, 2, 3, self.N)
+        # two send buffers: the gather of one slice runs (on NCCL's stream) while the next slice is encrypted
+        mine = [self.lb.empty(chunks, 2, 3, self.N) for _ in range(2)]
         cts = {}
         feed = self.staged(updates, list(range(rank, n_clients, world_size)))
-        for base in range(0, n_clients, world_size):
-            c = base + rank
-            if c < n_clients:
-                _, upd = next(feed)
-                self.encrypt_client(upd, client=c, round_seed=round_seed, out=mine_buf)
-            mark("encode_encrypt_s")
-            recv = self.lb.empty(world_size, chunks, 2, 3, self.N)
-            dist.all_gather_into_tensor(recv.view(-1), mine_buf.view(-1), group=group)
+        pending = None
+
+        def collect(p):
+            work, recv, base = p
+            work.wait()
             for r in range(world_size):
                 if base + r < n_clients and (base + r) in needed:
                     cts[base + r] = recv[r]
-            del recv
+
+        for k, base in enumerate(range(0, n_clients, world_size)):
+            buf = mine[k % 2]
+            c = base + rank
+            if c < n_clients:
+                _, upd = next(feed)
+                self.encrypt_client(upd, client=c, round_seed=round_seed, out=buf)
+            mark("encode_encrypt_s")
+            recv = self.lb.empty(world_size, chunks, 2, 3, self.N)
+            work = dist.all_gather_into_tensor(recv.view(-1), buf.view(-1), group=group, async_op=True)
+            if pending is not None:
+                collect(pending)
+            pending = (work, recv, base)
             mark("ciphertext_allgather_s")
+        if pending is not None:
+            collect(pending)
+        mark("ciphertext_allgather_s")
         return cts
 
     # -- server side ---------------------------------------------------------------------------
