@@ -604,8 +604,9 @@ LB_D int fixed_group(const int it)
     return WIDE ? (int)threadIdx.x + 256 * it : (int)((threadIdx.x >> 5) << 7) + (int)(threadIdx.x & 31) + 32 * it;
 }
 
-// PLAIN: the input is the limb itself, so none of the fused input conversions is compiled in
-// (sixteen inlined copies of them make the instruction stream of this pass miss the cache).
+// PLAIN: the input is the limb itself and the output is stored as it is, so none of the fused
+// conversions is compiled in (sixteen inlined copies of the input ones make the instruction stream
+// of this pass miss the cache).
 template <int LOGC, int MODE, bool PLAIN>
 LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulonglong2 *tw, const u64 q, const u64 q2)
 {
@@ -614,8 +615,42 @@ LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulon
     for (int col = threadIdx.x; col < COLS; col += 256) {
         const int j = c * COLS + col;
         u64 v[R0];
+        if (PLAIN) {
 #pragma unroll
-        for (int k = 0; k < R0; ++k) v[k] = PLAIN ? in.src[j + k * kHalfLoc] : load_in(in, j + k * kHalfLoc);
+            for (int k = 0; k < R0; ++k) v[k] = in.src[j + k * kHalfLoc];
+        } else if (in.n == 1 && in.mat == nullptr) {
+            // One source row reduced into this prime (every conversion of a chain with one special
+            // prime).  The branches on the optional parts stay outside the loops so that all loads
+            // of a part are in flight together; inside load_in each element would wait for its own.
+#pragma unroll
+            for (int k = 0; k < R0; ++k) v[k] = in.src[j + k * kHalfLoc];
+            if (in.es) {
+                int ev[R0];
+#pragma unroll
+                for (int k = 0; k < R0; ++k) ev[k] = in.es[j + k * kHalfLoc];
+#pragma unroll
+                for (int k = 0; k < R0; ++k) {
+                    const u64 x = add_mod(v[k], ev[k] < 0 ? in.es_p - (u64)(-ev[k]) : (u64)ev[k], in.es_p);
+                    v[k] = sub_mod(barrett64(x, q, in.r1), ev[k] < 0 ? q - (u64)(-ev[k]) : (u64)ev[k], q);
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < R0; ++k) v[k] = barrett64(v[k], q, in.r1);
+            }
+            if (in.sub) {
+#pragma unroll
+                for (int h = 0; h < R0; h += 8) {
+                    u64 t[R0 < 8 ? R0 : 8];
+#pragma unroll
+                    for (int k = 0; k < (R0 < 8 ? R0 : 8); ++k) t[k] = in.sub[j + (h + k) * kHalfLoc];
+#pragma unroll
+                    for (int k = 0; k < (R0 < 8 ? R0 : 8); ++k) v[h + k] = sub_mod(v[h + k], shoup_mul(t[k], in.sub_w, in.sub_ws, q), q);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < R0; ++k) v[k] = load_in(in, j + k * kHalfLoc);
+        }
         fwd_core<F, MODE>(v, tw, 1u, q, q2);
         const int s0 = sidx(j);
         if constexpr (LOGC == 0) {
@@ -635,7 +670,7 @@ LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulon
 }
 
 // three forward stages starting at span 2^LOGT
-template <int LOGT, int MODE>
+template <int LOGT, int MODE, bool PLAIN = false>
 LB_D void fwd_pass_fixed(u64 *sm, u64 *gdst, const unsigned cc, const ulonglong2 *tw, const u64 q, const u64 q2, const u64 r1,
                          const FwdEpi &epi)
 {
@@ -648,6 +683,8 @@ LB_D void fwd_pass_fixed(u64 *sm, u64 *gdst, const unsigned cc, const ulonglong2
         const int base = (hi << (LOGT + 1)) + lo;
         u64 *p = sm + sidx(base);
         u64 v[8];
+        u64 t[8];
+        if (CLOSING && !PLAIN && epi.aux) load_contig<8>(t, epi.aux + base); // in flight during the butterflies
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = p[pad_off<LOGST>(i)];
         fwd_core<3, MODE>(v, tw, (cc << (12 - LOGT)) + hi, q, q2);
@@ -659,9 +696,7 @@ LB_D void fwd_pass_fixed(u64 *sm, u64 *gdst, const unsigned cc, const ulonglong2
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] = csub(csub(v[i], q2), q);
             }
-            if (epi.aux) {
-                u64 t[8];
-                load_contig<8>(t, epi.aux + base);
+            if (!PLAIN && epi.aux) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] = shoup_mul(sub_mod(t[i], v[i], q), epi.scal, epi.scal_s, q);
                 if (epi.add) {
@@ -692,7 +727,7 @@ LB_D void fwd_body_fixed(u64 *sm, const FwdRow &fr, const unsigned c)
     __syncwarp();
     fwd_pass_fixed<5, MODE>(sm, nullptr, cc, fr.tw, q, q2, fr.in.r1, fr.epi);
     __syncwarp();
-    fwd_pass_fixed<2, MODE>(sm, fr.dst + (size_t)c * (2 * kHalfLoc), cc, fr.tw, q, q2, fr.in.r1, fr.epi);
+    fwd_pass_fixed<2, MODE, PLAIN>(sm, fr.dst + (size_t)c * (2 * kHalfLoc), cc, fr.tw, q, q2, fr.in.r1, fr.epi);
 }
 
 template <int LOGC, bool PLAIN>
@@ -883,7 +918,7 @@ static int launch(bool forward, bool fixed, const NttK &k, int rows, size_t smem
 #if LB_NTT_HAS_FIXED
     if constexpr (LOGC <= 3) {
         if (fixed) {
-            const bool plain = k.bconv_n == 0 && k.digit_alpha == 0 && !k.presub && !k.esmall;
+            const bool plain = k.bconv_n == 0 && k.digit_alpha == 0 && !k.presub && !k.esmall && !k.aux;
             kern = !forward ? ntt_inv_fixed_kernel<LOGC> : plain ? ntt_fwd_fixed_kernel<LOGC, true> : ntt_fwd_fixed_kernel<LOGC, false>;
             which = plain ? 2 : 1;
         }
