@@ -647,6 +647,24 @@ LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulon
                     for (int k = 0; k < (R0 < 8 ? R0 : 8); ++k) v[h + k] = sub_mod(v[h + k], shoup_mul(t[k], in.sub_w, in.sub_ws, q), q);
                 }
             }
+        } else if (in.mat != nullptr && in.sub == nullptr) {
+            // base conversion of several source rows: four outputs share one walk over the rows, so four
+            // loads are in flight per row instead of one
+            constexpr int G = R0 < 4 ? R0 : 4;
+#pragma unroll
+            for (int h = 0; h < R0; h += G) {
+                u128d acc[G];
+#pragma unroll
+                for (int k = 0; k < G; ++k) acc[k] = u128d{0, 0};
+                for (int i = 0; i < in.n; ++i) {
+                    const u64 m = __ldg(in.mat + i);
+                    const u64 *row = in.src + ((size_t)i << in.logN) + j;
+#pragma unroll
+                    for (int k = 0; k < G; ++k) mac_wide(acc[k], row[(h + k) * kHalfLoc], m);
+                }
+#pragma unroll
+                for (int k = 0; k < G; ++k) v[h + k] = barrett128(acc[k], q, in.r0, in.r1);
+            }
         } else {
 #pragma unroll
             for (int k = 0; k < R0; ++k) v[k] = load_in(in, j + k * kHalfLoc);
