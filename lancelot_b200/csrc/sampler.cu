@@ -219,16 +219,18 @@ int gen_switch_key(Context *ctx, const u64 *sk, const u64 *skp, const uint32_t *
 // ---- public-key encryption (cahel-main/src/secretkey.cu:47-170) -----------------------------
 
 // cx[b][p][QP][N] = pk[p] * u[b]   (the error term joins inside the mod-down transform)
-__global__ void __launch_bounds__(kSampThreads) encrypt_product_kernel(u64 *__restrict__ cx, const u64 *__restrict__ pk,
-                                                                       const u64 *__restrict__ u, const ModConst *__restrict__ mc,
-                                                                       const int logN, const long poly, const long total)
+// two coefficients per thread through 16-byte accesses; blockIdx.y is the ciphertext
+__global__ void __launch_bounds__(kSampThreads) encrypt_product_kernel(ulonglong2 *__restrict__ cx, const ulonglong2 *__restrict__ pk,
+                                                                       const ulonglong2 *__restrict__ u, const ModConst *__restrict__ mc,
+                                                                       const int log_half_n, const long half_poly, const int batch)
 {
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-        const long b = i / poly, k = i - b * poly;
-        const ModConst m = mc[(int)(k >> logN)];
-        const u64 uu = u[i];
-#pragma unroll
-        for (int p = 0; p < 2; ++p) cx[(2 * b + p) * poly + k] = mul_mod(uu, pk[p * poly + k], m.q, m.r0, m.r1);
+    for (long b = blockIdx.y; b < batch; b += gridDim.y) {
+        for (long k = (long)blockIdx.x * blockDim.x + threadIdx.x; k < half_poly; k += (long)gridDim.x * blockDim.x) {
+            const ModConst m = mc[(int)(k >> log_half_n)];
+            const ulonglong2 uu = u[b * half_poly + k], p0 = pk[k], p1 = pk[half_poly + k];
+            cx[2 * b * half_poly + k] = make_ulonglong2(mul_mod(uu.x, p0.x, m.q, m.r0, m.r1), mul_mod(uu.y, p0.y, m.q, m.r0, m.r1));
+            cx[(2 * b + 1) * half_poly + k] = make_ulonglong2(mul_mod(uu.x, p1.x, m.q, m.r0, m.r1), mul_mod(uu.y, p1.y, m.q, m.r0, m.r1));
+        }
     }
 }
 
@@ -295,7 +297,11 @@ int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, int pt_is_coe
         j.size_l = Q;
         if ((rc = ntt_forward(ctx, j, stream))) return rc;
         count_launch();
-        encrypt_product_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(cx, pk, u, ctx->d_mc, hp.logN, poly, total);
+        const long half_poly = poly / 2;
+        const unsigned gx = (unsigned)((half_poly + kSampThreads - 1) / kSampThreads);
+        encrypt_product_kernel<<<dim3(gx, (unsigned)(batch < 65535 ? batch : 65535)), kSampThreads, 0, stream>>>(
+            reinterpret_cast<ulonglong2 *>(cx), reinterpret_cast<const ulonglong2 *>(pk), reinterpret_cast<const ulonglong2 *>(u), ctx->d_mc,
+            hp.logN - 1, half_poly, batch);
         LB_CUDA(cudaGetLastError());
     } else {
         if ((rc = sample_small(ctx, 1, seeds + 16, 32, batch, Q, P, e, stream))) return rc;
