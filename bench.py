@@ -243,7 +243,7 @@ def run_reference(args, wl):
     else:
         value = sum(vals) / len(vals)
     line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": None, "higher_is_better": wl.higher_is_better, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+            "ms_per_step": None, "higher_is_better": wl.higher_is_better, "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None, "dtype": wl.dtype,
             "data": "synthetic", "config": wl.config(), "impl": "reference",
             "cpu_baseline": {"value": value, "unit": wl.unit, "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}

@@ -271,6 +271,8 @@ __global__ void __launch_bounds__(kTileThreads, 3) krum_tile_kernel(const KrumTi
                                                                     const long per_poly, const long chunk_stride, const int n_chunks)
 {
     constexpr int NI = NA + NB, NP = NB ? NA * NB : NA * (NA - 1) / 2;
+    // chunks a thread keeps in flight: as many as the accumulators of the shape leave registers for
+    constexpr int kTileUnroll = NP <= 4 ? 3 : NP <= 6 ? 2 : 1;
     for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < per_poly; e += (long)gridDim.x * blockDim.x) {
         const ModConst m = mc[(int)(e >> logn)];
         // 128-bit running sums; every 63 chunks they are reduced in place, which leaves room for
@@ -280,6 +282,7 @@ __global__ void __launch_bounds__(kTileThreads, 3) krum_tile_kernel(const KrumTi
         for (int p = 0; p < NP; ++p) s0[p] = s1[p] = s2[p] = u128d{0, 0};
         for (int c0 = 0; c0 < n_chunks; c0 += 63) {
             const int c1 = min(c0 + 63, n_chunks);
+#pragma unroll(kTileUnroll)
             for (int c = c0; c < c1; ++c) {
                 u64 v0[NI], v1[NI];
 #pragma unroll
