@@ -35,6 +35,10 @@ struct Context {
     // encoder tables
     double2 *d_croots = nullptr; // [2N] complex roots of unity
     uint32_t *d_rot_group = nullptr; // [N/4] powers of 5 mod 2N
+    // inverse-FFT twiddles of the encoder in the order its stages use them, for ifft_tw_logn = log2(slots):
+    // entry (n - (n >> u)) + k is the twiddle of butterfly group k at stage u (built on first use)
+    double2 *d_ifft_tw = nullptr;
+    int ifft_tw_logn = 0;
     int *d_status = nullptr;         // sticky device-side condition flags (bit 0: encoded values are too large)
     // scratch owned by the context, grown on demand between operations
     void *ws = nullptr;

@@ -44,6 +44,7 @@ struct EncK {
     u64 *pt;            // [batch][size_l][N]
     const double2 *roots;
     const uint32_t *group;
+    const double2 *tw; // stage-ordered copy of the twiddles (see Context::d_ifft_tw), or nullptr
     const ModConst *mc;
     int logN, logn, size_l;
     double fix;
@@ -71,6 +72,11 @@ LB_D cplx load_value(const EncK &a, const long msg, const unsigned idx)
 // twiddle of butterfly group k at stage u (pairs = 2^u): fft.cu:216-222
 LB_D cplx ifft_twiddle(const EncK &a, const unsigned k, const int u)
 {
+    if (a.tw) { // one load instead of two dependent ones
+        const unsigned n = 1u << a.logn;
+        const double2 w = __ldg(a.tw + (n - (n >> u)) + k);
+        return {w.x, w.y};
+    }
     const int logRatio = a.logN + 1 - a.logn - 2;
     const unsigned M = 2u << a.logN;
     const unsigned rev = a.logn > 1 ? (__brev(k << u) >> (33 - a.logn)) : 0u;
@@ -123,8 +129,25 @@ LB_D void ifft_pass(cplx *sm, const EncK &a, const long msg, const bool first, c
         cplx v[R];
         if (first) { // logt == 0: the bit-reversal placement is folded into the load
             const unsigned gbase = (c << logn_loc) + base;
+            // the type switch sits outside the element loop so that the R loads are in flight together
+            unsigned idx[R];
 #pragma unroll
-            for (int i = 0; i < R; ++i) v[i] = load_value(a, msg, __brev(gbase + i) >> (32 - a.logn));
+            for (int i = 0; i < R; ++i) idx[i] = __brev(gbase + i) >> (32 - a.logn);
+            if (a.dtype == 1) {
+                const float *f = reinterpret_cast<const float *>(a.values) + msg * a.value_stride;
+                float t[R];
+#pragma unroll
+                for (int i = 0; i < R; ++i) t[i] = idx[i] < (unsigned)a.n_values ? f[idx[i]] : 0.0f;
+#pragma unroll
+                for (int i = 0; i < R; ++i) v[i] = {(double)t[i], 0.0};
+            } else if (a.dtype == 0) {
+                const double *f = reinterpret_cast<const double *>(a.values) + msg * a.value_stride;
+#pragma unroll
+                for (int i = 0; i < R; ++i) v[i] = {idx[i] < (unsigned)a.n_values ? f[idx[i]] : 0.0, 0.0};
+            } else {
+#pragma unroll
+                for (int i = 0; i < R; ++i) v[i] = load_value(a, msg, idx[i]);
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < R; ++i) v[i] = sm[fidx(base + (i << logt))];
@@ -164,6 +187,21 @@ LB_D void ifft_pass(cplx *sm, const EncK &a, const long msg, const bool first, c
 #pragma unroll
             for (int i = 0; i < R; ++i) sm[fidx(base + (i << logt))] = v[i];
         }
+    }
+}
+
+// fills the stage-ordered twiddle table from the root table: the same values, found once
+__global__ void ifft_twiddle_table_kernel(EncK a, double2 *out)
+{
+    const unsigned n = 1u << a.logn;
+    a.tw = nullptr;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i + 1 < n; i += gridDim.x * blockDim.x) {
+        // stage u holds the entries [n - (n >> u), n - (n >> (u + 1)))
+        int u = 0;
+        while (i >= n - (n >> (u + 1))) ++u;
+        const unsigned k = i - (n - (n >> u));
+        const cplx w = ifft_twiddle(a, k, u);
+        out[i] = make_double2(w.x, w.y);
     }
 }
 
@@ -311,9 +349,21 @@ int encode(Context *ctx, int size_l, const void *values, int dtype, long value_s
     k.pt = pt;
     k.roots = ctx->d_croots;
     k.group = ctx->d_rot_group;
+    k.tw = nullptr;
     k.mc = ctx->d_mc;
     k.logN = hp.logN;
     k.logn = logn;
+    if (ctx->ifft_tw_logn != logn) {
+        double2 *tbl = nullptr;
+        LB_CUDA(cudaMalloc((void **)&tbl, sizeof(double2) << logn));
+        ctx->owned.push_back(tbl);
+        count_launch();
+        ifft_twiddle_table_kernel<<<(unsigned)(((1u << logn) + 255) / 256), 256, 0, stream>>>(k, tbl);
+        LB_CUDA(cudaGetLastError());
+        ctx->d_ifft_tw = tbl;
+        ctx->ifft_tw_logn = logn;
+    }
+    k.tw = ctx->d_ifft_tw;
     k.size_l = size_l;
     k.fix = scale / (double)sparse_slots;
     k.too_large = ldexp(1.0, total_bits - 2);
