@@ -118,46 +118,82 @@ struct IpArgs {
     int n_steps;
 };
 
+// grid: x over the coefficients of a limb (two per thread without a gather, one with), y = limb of
+// QlP, z = ciphertext; no index division, 16-byte accesses on the streaming path
+template <bool GATHER>
 __global__ void __launch_bounds__(kKsThreads) inner_product_kernel(const u64 *__restrict__ digits, const u64 *__restrict__ own,
                                                                    const long own_stride, u64 *__restrict__ cx,
                                                                    const ModConst *__restrict__ mc, const IpArgs args, const int logN,
                                                                    const int L, const int LP, const int size_Q, const int size_QP,
-                                                                   const int alpha, const int beta, const long total)
+                                                                   const int alpha, const int beta, const int batch)
 {
+    constexpr int V = GATHER ? 1 : 2;
     const long per_ct = (long)LP << logN;
-    const long n_mask = (1L << logN) - 1;
-    for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
-        const long b = idx / per_ct, i = idx - b * per_ct;
-        const int r = (int)(i >> logN);
-        const long k = i & n_mask;
-        const int tbl = r < L ? r : size_Q + (r - L);
-        const ModConst m = mc[tbl];
-        const int own_digit = r < L ? r / alpha : -1;
+    const int r = blockIdx.y;
+    const int tbl = r < L ? r : size_Q + (r - L);
+    const ModConst m = mc[tbl];
+    const int own_digit = r < L ? r / alpha : -1;
+    const long n = 1L << logN;
+    for (long b = blockIdx.z; b < batch; b += gridDim.z) {
         const u64 *dig_b = digits + b * beta * per_ct;
         const u64 *own_b = own + ((b * own_stride) << logN);
-        u128d a0 = {0, 0}, a1 = {0, 0};
-        u64 r0 = 0, r1 = 0;
-        int pending = 0;
-        for (int s = 0; s < args.n_steps; ++s) {
-            const long kk = args.perm[s] ? (long)args.perm[s][k] : k;
-            const u64 *key = args.evk[s];
-            for (int j = 0; j < beta; ++j) {
-                const u64 d = (j == own_digit) ? own_b[((long)r << logN) + kk] : dig_b[(((long)j * LP + r) << logN) + kk];
-                const u64 *kb = key + ((((long)j * 2) * size_QP + tbl) << logN) + k;
-                mac_wide(a0, d, kb[0]);
-                mac_wide(a1, d, kb[(long)size_QP << logN]);
-                if (++pending == 32) {
-                    r0 = add_mod(r0, barrett128(a0, m.q, m.r0, m.r1), m.q);
-                    r1 = add_mod(r1, barrett128(a1, m.q, m.r0, m.r1), m.q);
-                    a0.lo = a0.hi = a1.lo = a1.hi = 0;
-                    pending = 0;
+        for (long k = ((long)blockIdx.x * blockDim.x + threadIdx.x) * V; k < n; k += (long)gridDim.x * blockDim.x * V) {
+            u128d a0[V], a1[V];
+            u64 r0[V], r1[V];
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                a0[v] = a1[v] = u128d{0, 0};
+                r0[v] = r1[v] = 0;
+            }
+            int pending = 0;
+            for (int s = 0; s < args.n_steps; ++s) {
+                const u64 *key = args.evk[s];
+                for (int j = 0; j < beta; ++j) {
+                    const u64 *src = (j == own_digit) ? own_b + ((long)r << logN) : dig_b + (((long)j * LP + r) << logN);
+                    const u64 *kb = key + ((((long)j * 2) * size_QP + tbl) << logN) + k;
+                    u64 d[V], k0[V], k1[V];
+                    if (GATHER) {
+                        d[0] = src[args.perm[s] ? (long)args.perm[s][k] : k];
+                        k0[0] = kb[0];
+                        k1[0] = kb[(long)size_QP << logN];
+                    } else {
+                        const ulonglong2 dv = *reinterpret_cast<const ulonglong2 *>(src + k);
+                        const ulonglong2 kv0 = *reinterpret_cast<const ulonglong2 *>(kb);
+                        const ulonglong2 kv1 = *reinterpret_cast<const ulonglong2 *>(kb + ((long)size_QP << logN));
+                        d[0] = dv.x; d[V - 1] = dv.y;
+                        k0[0] = kv0.x; k0[V - 1] = kv0.y;
+                        k1[0] = kv1.x; k1[V - 1] = kv1.y;
+                    }
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        mac_wide(a0[v], d[v], k0[v]);
+                        mac_wide(a1[v], d[v], k1[v]);
+                    }
+                    if (++pending == 32) {
+#pragma unroll
+                        for (int v = 0; v < V; ++v) {
+                            r0[v] = add_mod(r0[v], barrett128(a0[v], m.q, m.r0, m.r1), m.q);
+                            r1[v] = add_mod(r1[v], barrett128(a1[v], m.q, m.r0, m.r1), m.q);
+                            a0[v] = a1[v] = u128d{0, 0};
+                        }
+                        pending = 0;
+                    }
                 }
             }
+            u64 *o0 = cx + 2 * b * per_ct + ((long)r << logN) + k, *o1 = o0 + per_ct;
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                r0[v] = add_mod(r0[v], barrett128(a0[v], m.q, m.r0, m.r1), m.q);
+                r1[v] = add_mod(r1[v], barrett128(a1[v], m.q, m.r0, m.r1), m.q);
+            }
+            if (GATHER) {
+                o0[0] = r0[0];
+                o1[0] = r1[0];
+            } else {
+                *reinterpret_cast<ulonglong2 *>(o0) = make_ulonglong2(r0[0], r0[V - 1]);
+                *reinterpret_cast<ulonglong2 *>(o1) = make_ulonglong2(r1[0], r1[V - 1]);
+            }
         }
-        r0 = add_mod(r0, barrett128(a0, m.q, m.r0, m.r1), m.q);
-        r1 = add_mod(r1, barrett128(a1, m.q, m.r0, m.r1), m.q);
-        cx[2 * b * per_ct + i] = r0;
-        cx[(2 * b + 1) * per_ct + i] = r1;
     }
 }
 
@@ -166,13 +202,19 @@ static int inner_product_steps(Context *ctx, int L, int batch, const u64 *digits
 {
     const HostParams &hp = ctx->hp;
     const int LP = L + hp.size_P;
-    const long total = ((long)LP << hp.logN) * batch;
-    long blocks = (total + kKsThreads - 1) / kKsThreads;
-    const long cap = (long)ctx->sm_count * 16;
-    if (blocks > cap) blocks = cap;
+    bool gather = false;
+    for (int s = 0; s < args.n_steps; ++s) gather = gather || args.perm[s] != nullptr;
+    const long per_thread = gather ? 1 : 2;
+    long gx = ((long)hp.N / per_thread + kKsThreads - 1) / kKsThreads;
+    if (gx < 1) gx = 1;
+    const dim3 grid((unsigned)gx, (unsigned)LP, (unsigned)(batch < 65535 ? batch : 65535));
     count_launch();
-    inner_product_kernel<<<(int)blocks, kKsThreads, 0, stream>>>(digits, own, own_stride, cx, ctx->d_mc, args, hp.logN, L, LP, hp.size_Q,
-                                                                 hp.size_QP, hp.size_P, hp.level[L].beta, total);
+    if (gather)
+        inner_product_kernel<true><<<grid, kKsThreads, 0, stream>>>(digits, own, own_stride, cx, ctx->d_mc, args, hp.logN, L, LP, hp.size_Q,
+                                                                   hp.size_QP, hp.size_P, hp.level[L].beta, batch);
+    else
+        inner_product_kernel<false><<<grid, kKsThreads, 0, stream>>>(digits, own, own_stride, cx, ctx->d_mc, args, hp.logN, L, LP, hp.size_Q,
+                                                                    hp.size_QP, hp.size_P, hp.level[L].beta, batch);
     LB_CUDA(cudaGetLastError());
     return LB_OK;
 }
