@@ -5,6 +5,7 @@ Each class follows the small protocol bench.py drives: setup_gpu / step_gpu / st
 check_gpu / cpu_sample, plus the bookkeeping the JSON line needs.  Inputs are seeded synthetic
 tensors with the shapes and value distributions BASELINE.json names (no dataset exists here)."""
 import ctypes as C
+import os
 import time
 
 import numpy as np
@@ -40,6 +41,8 @@ class KrumWorkload:
         self.launches_per_step = 0
         self.breakdown = {}
         self.profile_phases = False
+        # how ciphertexts reach the ranks that need them when several GPUs share a round (EncryptedKrum.round)
+        self.exchange = os.environ.get("LANCELOT_KRUM_EXCHANGE", "p2p")
 
     def config(self):
         return {"workload": "%s encrypted Krum distance round: %d clients x %d float32, N=2^%d, %d ciphertexts per client, "
@@ -91,7 +94,7 @@ class KrumWorkload:
         self.torch.cuda.synchronize()
         t1 = time.perf_counter()
         timing = {} if self.profile_phases else None
-        d, order = ek.round(updates, rank=self.rank, world_size=self.world, timing=timing)
+        d, order = ek.round(updates, rank=self.rank, world_size=self.world, timing=timing, exchange=self.exchange)
         self.torch.cuda.synchronize()
         t2 = time.perf_counter()
         self.launches_per_step = _launches() - l0

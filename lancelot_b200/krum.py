@@ -172,13 +172,9 @@ def all_pairs(n_clients):
     return [(i, j) for i in range(n_clients) for j in range(i + 1, n_clients)]
 
 
-def pair_schedule(n_clients, world_size):
-    """Pairs i < j in tile-major order over a g x g grid of client groups, cut into
-    ``world_size`` contiguous, equally long segments: a rank touches few distinct clients
-    (so it encrypts few), and segments differ by at most one pair."""
-    g = max(1, int(math.ceil(math.sqrt(2.0 * world_size))))
-    g = min(g, n_clients)
+def _schedule_for_grid(n_clients, world_size, g):
     size = int(math.ceil(n_clients / g))
+    g = int(math.ceil(n_clients / size))
     group = lambda c: c // size
     tiles = {}
     for i, j in all_pairs(n_clients):
@@ -192,11 +188,22 @@ def pair_schedule(n_clients, world_size):
         for b in cols:
             order.extend(tiles.get((a, b), []))
     total = len(order)
-    out = []
-    for r in range(world_size):
-        lo, hi = (total * r) // world_size, (total * (r + 1)) // world_size
-        out.append(order[lo:hi])
-    return out
+    return [order[(total * r) // world_size:(total * (r + 1)) // world_size] for r in range(world_size)]
+
+
+def pair_schedule(n_clients, world_size):
+    """Pairs i < j in tile-major order over a g x g grid of client groups, cut into
+    ``world_size`` contiguous, equally long segments: a rank touches few distinct clients
+    (so it encrypts or receives few), and segments differ by at most one pair.  The grid size
+    is the one whose busiest rank touches the fewest clients (then the fewest in total)."""
+    best = None
+    for g in range(1, n_clients + 1):
+        sched = _schedule_for_grid(n_clients, world_size, g)
+        touched = [len(clients_of(seg)) for seg in sched]
+        key = (max(touched) if touched else 0, sum(touched), g)
+        if best is None or key < best[0]:
+            best = (key, sched)
+    return best[1]
 
 
 def pair_tiles(pairs, width=4):
@@ -240,6 +247,52 @@ def tile_pairs(tile):
 
 def clients_of(pairs):
     return sorted({c for p in pairs for c in p})
+
+
+def share_slices(world_size, rank, n_clients, needed_by, produce, alloc, group=None, mark=lambda name: None):
+    """Point-to-point exchange of per-client tensors.  Client c is produced by rank c % world_size
+    (``produce(c)`` returns its tensor) and sent only to the ranks that list it in ``needed_by[rank]``;
+    every rank must call this with the same ``needed_by``.  Clients are handled in slices of world_size
+    (one per rank); the transfers of a slice are posted as one batch of isend / irecv and waited for
+    after the next slice has been produced, so they overlap with that work.  ``alloc()`` returns an
+    empty tensor of a client's shape.  Returns {client: tensor} for the clients this rank needs."""
+    import torch.distributed as dist
+
+    out = {}
+    pending = None
+
+    def finish(p):
+        reqs, keep_alive = p
+        for r in reqs:
+            r.wait()
+        del keep_alive
+
+    for base in range(0, n_clients, world_size):
+        c = base + rank
+        mine = produce(c) if c < n_clients else None
+        mark("encode_encrypt_s")
+        ops, hold = [], [mine]
+        if mine is not None:
+            if c in needed_by[rank]:
+                out[c] = mine
+            for dst in range(world_size):
+                if dst != rank and c in needed_by[dst]:
+                    ops.append(dist.P2POp(dist.isend, mine.view(-1), dst, group))
+        for src in range(world_size):
+            cs = base + src
+            if src != rank and cs < n_clients and cs in needed_by[rank]:
+                t = alloc()
+                out[cs] = t
+                ops.append(dist.P2POp(dist.irecv, t.view(-1), src, group))
+        reqs = dist.batch_isend_irecv(ops) if ops else []
+        if pending is not None:
+            finish(pending)
+        pending = (reqs, hold)
+        mark("ciphertext_exchange_s")
+    if pending is not None:
+        finish(pending)
+    mark("ciphertext_exchange_s")
+    return out
 
 
 _COPY_STREAMS = {}
@@ -474,13 +527,15 @@ class EncryptedKrum:
         return vals.real.reshape(-1)[:dim]
 
     # -- one round ---------------------------------------------------------------------------------
-    def round(self, updates, rank=0, world_size=1, group=None, round_seed=0, keep=None, timing=None, exchange="allgather"):
+    def round(self, updates, rank=0, world_size=1, group=None, round_seed=0, keep=None, timing=None, exchange="p2p"):
         """updates: [n_clients][dim] tensor (CUDA, pinned or pageable host).  Every rank runs this; rank 0 returns
         (distances, order), the others (None, None).
-        exchange (only with several ranks): "allgather": every client is encrypted once, by rank
-        client % world_size, and the ciphertexts are all-gathered (NCCL over NVLink) so that encryption
-        scales with the ranks too; "reencrypt": every rank re-derives the ciphertexts of the clients its
-        pairs touch from the shared seeds, and the score gather is the only collective.
+        exchange (only with several ranks): "p2p" (default): every client is encrypted once, by rank
+        client % world_size, and its ciphertexts go to the ranks whose pairs touch that client (batched NCCL
+        isend / irecv over NVLink, overlapped with the next encryption), so that encryption scales with the
+        ranks too; "allgather": the same with one all-gather per slice of clients (every rank receives every
+        client); "reencrypt": every rank re-derives the ciphertexts of the clients its pairs touch from the
+        shared seeds, and the score gather is the only collective.
         timing: optional dict; when given, the phases are separated by device synchronisations and timed."""
         def mark(name, t=[None]):
             if timing is None:
@@ -496,7 +551,18 @@ class EncryptedKrum:
         schedule = pair_schedule(n_clients, world_size)
         mine = schedule[rank]
         cts = {}
-        if world_size > 1 and exchange == "allgather":
+        if world_size > 1 and exchange == "p2p":
+            needed_by = [set(clients_of(seg)) for seg in schedule]
+            feed = self.staged(updates, list(range(rank, n_clients, world_size)))
+            chunks = self.n_chunks(updates.shape[1])
+
+            def produce(c):
+                _, upd = next(feed)
+                return self.encrypt_client(upd, client=c, round_seed=round_seed)
+
+            cts = share_slices(world_size, rank, n_clients, needed_by, produce, lambda: self.lb.empty(chunks, 2, 3, self.N),
+                               group=group, mark=mark)
+        elif world_size > 1 and exchange == "allgather":
             cts = self.encrypt_and_share(updates, rank, world_size, group, round_seed, needed=set(clients_of(mine)), mark=mark)
         else:
             for c, upd in self.staged(updates, clients_of(mine)):

@@ -87,3 +87,44 @@ def test_gather_scores_world_size_n_gloo(world):
     port = 29500 + (os.getpid() % 500) + world
     mp.spawn(_gather_worker, args=(world, port, ret), nprocs=world, join=True)
     assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+def _p2p_worker(rank, world, port, n_clients, out):
+    import torch.distributed as dist
+
+    from lancelot_b200.krum import clients_of, pair_schedule, share_slices
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        schedule = pair_schedule(n_clients, world)
+        needed_by = [set(clients_of(seg)) for seg in schedule]
+        produced = []
+
+        def produce(c):
+            produced.append(c)
+            return torch.full((6,), float(c) + 0.5)
+
+        got = share_slices(world, rank, n_clients, needed_by, produce, lambda: torch.empty(6))
+        ok = sorted(got) == sorted(needed_by[rank]) and all(float(t[0]) == c + 0.5 and float(t[-1]) == c + 0.5 for c, t in got.items())
+        ok = ok and produced == list(range(rank, n_clients, world))
+        out.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n_clients", [(2, 5), (3, 7), (4, 20)])
+def test_point_to_point_ciphertext_exchange_gloo(world, n_clients):
+    """every rank ends up with exactly the clients its pairs touch, each produced once by its owner"""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29610 + world
+    procs = [ctx.Process(target=_p2p_worker, args=(r, world, port, n_clients, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(res) == [(r, True) for r in range(world)]
