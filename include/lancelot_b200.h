@@ -98,6 +98,12 @@ LB_API int lb_ntt_inverse(lb_context *ctx, uint64_t *data, int n_groups, int siz
 LB_API int lb_add(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream);
 LB_API int lb_sub(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream);
 LB_API int lb_multiply_poly(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream);
+/* out[g][n_polys][size_l][N] = sum of the items in[i][n_polys][size_l][N] with i in indices[offsets[g] .. offsets[g+1])
+ * (add_many, cahel-main/src/evaluate.cu:177-197, over chosen subsets in one launch: the per-client sums of the
+ * Krum driver, lancelot-main-GPU/utils/byzantine_fl.py:333-346).  offsets [n_groups + 1] and indices are HOST arrays;
+ * an empty group gives zeros. */
+LB_API int lb_sum_groups(lb_context *ctx, int size_l, int n_polys, int n_groups, const int *offsets, const int *indices, int n_items,
+                  const uint64_t *in, uint64_t *out, void *stream);
 /* element-wise product of two key-level polynomials [size_QP][N] (compute_secret_key_array, cahel-main/src/secretkey.cu:285-320) */
 LB_API int lb_multiply_poly_key_level(lb_context *ctx, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream);
 LB_API int lb_negate(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, uint64_t *out, void *stream);

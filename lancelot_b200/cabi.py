@@ -226,6 +226,19 @@ class Context:
         check(lib.lb_hoisting_batch(self.h, size_l, batch, _p(ct), n, idx, ptrs, _stream()))
         return ct
 
+    def sum_groups(self, size_l, n_polys, items, groups):
+        """items: [n_items][n_polys][size_l][N]; groups: list of index lists -> [len(groups)][n_polys][size_l][N] sums"""
+        offsets = [0]
+        for g in groups:
+            offsets.append(offsets[-1] + len(g))
+        flat = [int(i) for g in groups for i in g]
+        n_items = items.numel() // (n_polys * size_l * self.N)
+        out = self.empty(len(groups), n_polys, size_l, self.N)
+        off = (C.c_int * len(offsets))(*offsets)
+        idx = (C.c_int * max(1, len(flat)))(*flat)
+        check(lib.lb_sum_groups(self.h, size_l, n_polys, len(groups), off, idx, n_items, _p(items), _p(out), _stream()))
+        return out
+
     def krum_accumulate(self, size_l, a, b, acc, accumulate=False, n_chunks=None, stride_a=None, stride_b=None):
         ct_words = 2 * size_l * self.N
         n_chunks = a.numel() // ct_words if n_chunks is None else n_chunks

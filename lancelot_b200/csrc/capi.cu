@@ -197,6 +197,22 @@ int lb_sub(lb_context *h, int size_l, int n, const uint64_t *a, const uint64_t *
 int lb_multiply_poly(lb_context *h, int size_l, int n, const uint64_t *a, const uint64_t *b, uint64_t *out, void *s) { return binary(h, OP_MUL, size_l, n, a, b, out, s); }
 int lb_negate(lb_context *h, int size_l, int n, const uint64_t *a, uint64_t *out, void *s) { return binary(h, OP_NEG, size_l, n, a, nullptr, out, s); }
 
+int lb_sum_groups(lb_context *h, int size_l, int n_polys, int n_groups, const int *offsets, const int *indices, int n_items,
+                  const uint64_t *in, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    if ((rc = level_ok(C(h), size_l))) return rc;
+    REQUIRE(offsets && in && out && n_polys >= 1 && n_groups >= 0, "operand is null");
+    if (n_groups == 0) return LB_OK;
+    REQUIRE(n_groups <= 65535, "too many groups");
+    REQUIRE(offsets[0] == 0, "offsets must start at 0");
+    for (int g = 0; g < n_groups; ++g) REQUIRE(offsets[g + 1] >= offsets[g], "offsets must not decrease");
+    REQUIRE(offsets[n_groups] == 0 || indices, "operand is null");
+    for (int t = 0; t < offsets[n_groups]; ++t) REQUIRE(indices[t] >= 0 && indices[t] < n_items, "item index is out of range");
+    return poly_sum_groups(C(h), size_l, (long)n_polys * size_l, n_groups, offsets, indices, in, out, S(stream));
+}
+
 int lb_multiply_poly_key_level(lb_context *h, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream)
 {
     int rc = bind(h);

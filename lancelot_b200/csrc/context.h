@@ -118,6 +118,8 @@ int poly_binary(Context *ctx, int op, int size_l, long rows, const u64 *a, const
 int poly_tensor(Context *ctx, int size_l, int batch, const u64 *a, const u64 *b, u64 *out, cudaStream_t stream);
 // dst[i] = src[perm[i]] for `rows` limbs
 int poly_galois(Context *ctx, int elt_idx, long rows, const u64 *src, u64 *dst, cudaStream_t stream);
+int poly_sum_groups(Context *ctx, int size_l, long n_rows, int n_groups, const int *h_offsets, const int *h_indices, const u64 *in,
+                    u64 *out, cudaStream_t stream);
 // acc[3][L][N] (+)= sum_c square(b_c - a_c) over n_chunks ciphertext pairs [2][L][N]
 int krum_accumulate(Context *ctx, int size_l, int n_chunks, const u64 *a, const u64 *b, long chunk_stride_a,
                     long chunk_stride_b, u64 *acc, int accumulate, cudaStream_t stream);

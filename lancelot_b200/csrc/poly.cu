@@ -127,6 +127,49 @@ __global__ void __launch_bounds__(kPolyThreads) galois_kernel(const u64 *__restr
     }
 }
 
+// out[g] = sum of the items in[idx] listed for group g (the reference's add_many over a chosen subset):
+// items are n_rows limbs each, row r uses prime r % size_l; lists in CSR form on the device
+__global__ void __launch_bounds__(kPolyThreads) sum_groups_kernel(const ulonglong2 *__restrict__ in, ulonglong2 *__restrict__ out,
+                                                                  const int *__restrict__ offsets, const int *__restrict__ indices,
+                                                                  const ModConst *__restrict__ mc, const int size_l, const int log_half_n,
+                                                                  const long item)
+{
+    const int g = blockIdx.y;
+    const int lo = offsets[g], hi = offsets[g + 1];
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < item; i += (long)gridDim.x * blockDim.x) {
+        const u64 q = mc[(int)((i >> log_half_n) % size_l)].q;
+        ulonglong2 r = make_ulonglong2(0, 0);
+        for (int t = lo; t < hi; ++t) {
+            const ulonglong2 v = in[(long)indices[t] * item + i];
+            r.x = add_mod(r.x, v.x, q);
+            r.y = add_mod(r.y, v.y, q);
+        }
+        out[(long)g * item + i] = r;
+    }
+}
+
+int poly_sum_groups(Context *ctx, int size_l, long n_rows, int n_groups, const int *h_offsets, const int *h_indices, const u64 *in,
+                    u64 *out, cudaStream_t stream)
+{
+    if (n_groups <= 0) return LB_OK;
+    const int n_idx = h_offsets[n_groups];
+    const size_t bytes = ((size_t)n_groups + 1 + n_idx) * sizeof(int);
+    int rc = ctx->ensure_workspace(bytes);
+    if (rc) return rc;
+    int *d = reinterpret_cast<int *>(ctx->ws);
+    LB_CUDA(cudaMemcpyAsync(d, h_offsets, ((size_t)n_groups + 1) * sizeof(int), cudaMemcpyHostToDevice, stream));
+    if (n_idx) LB_CUDA(cudaMemcpyAsync(d + n_groups + 1, h_indices, (size_t)n_idx * sizeof(int), cudaMemcpyHostToDevice, stream));
+    const long item = (n_rows << ctx->hp.logN) / 2;
+    long gx = (item + kPolyThreads - 1) / kPolyThreads;
+    if (gx > 4096) gx = 4096;
+    count_launch();
+    sum_groups_kernel<<<dim3((unsigned)gx, (unsigned)n_groups), kPolyThreads, 0, stream>>>(
+        reinterpret_cast<const ulonglong2 *>(in), reinterpret_cast<ulonglong2 *>(out), d, d + n_groups + 1, ctx->d_mc, size_l,
+        ctx->hp.logN - 1, item);
+    LB_CUDA(cudaGetLastError());
+    return LB_OK;
+}
+
 int poly_galois(Context *ctx, int elt_idx, long rows, const u64 *src, u64 *dst, cudaStream_t stream)
 {
     if (elt_idx < 0 || elt_idx >= (int)ctx->hp.galois_elts.size()) {

@@ -481,13 +481,9 @@ class EncryptedKrum:
         return s
 
     def client_sums(self, scores, pairs, n_clients):
-        """sum of the score ciphertexts of every pair a client belongs to: [n_clients][2][2][N]"""
-        lb, N = self.lb, self.N
-        sums = torch.zeros(n_clients, 2, 2, N, dtype=torch.int64, device=scores.device)
-        for p, (i, j) in enumerate(pairs):
-            lb.add(2, sums[i], scores[p], out=sums[i])
-            lb.add(2, sums[j], scores[p], out=sums[j])
-        return sums
+        """sum of the score ciphertexts of every pair a client belongs to: [n_clients][2][2][N], one launch"""
+        groups = [[p for p, (i, j) in enumerate(pairs) if c in (i, j)] for c in range(n_clients)]
+        return self.lb.sum_groups(2, 2, scores.contiguous(), groups)
 
     def decrypt_slot0(self, ct_level2):
         pt = self.lb.decrypt(2, ct_level2.contiguous(), self.sk.data)
@@ -497,8 +493,14 @@ class EncryptedKrum:
         return float(out[0].real.item())
 
     def select(self, sums):
-        """decrypt every client's summed distance (slot 0) and return (distances, argsort)"""
-        d = [self.decrypt_slot0(sums[i]) for i in range(sums.shape[0])]
+        """decrypt every client's summed distance (slot 0) and return (distances, argsort): one batched decrypt, one
+        batched decode and one copy to the host for all clients"""
+        n = sums.shape[0]
+        pts = self.lb.decrypt_batch(2, sums.contiguous(), self.sk.data, 2, n)
+        q2 = self.context.moduli[2]
+        # after rescale the true scale is 2^80 / q_2; the reference overwrites it with 2^40 (byzantine_fl.py:246)
+        vals = self.lb.decode_batch(2, pts, self.scale * self.scale / q2, self.slots, n)
+        d = [float(x) for x in vals[:, 0].real.cpu().tolist()]
         return d, np.argsort(d)
 
     # -- aggregation phase (byzantine_fl.py:371-429, and the trimmed-mean variant) ---------------------------

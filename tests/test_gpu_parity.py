@@ -246,6 +246,26 @@ def test_krum_tile_shape_errors(torch_cuda):
         ctx.krum_accumulate_tile(3, t[:3], t[3:5], outs[:6])  # three rows
 
 
+def test_sum_groups_equals_repeated_add(torch_cuda):
+    from lancelot_b200 import cabi
+    from lancelot_b200._lib import InvalidArgument
+
+    logn, L = 10, 2
+    o, ctx, mods = make(logn, [60, 40, 40, 60], 1)
+    rng = np.random.default_rng(9)
+    n = 1 << logn
+    items = rand_rows(rng, row_moduli(mods, 3, L, 0, 2 * 7), n).reshape(7, 2, L, n)
+    groups = [[0, 3, 6], [], [5], [1, 2, 3, 4, 5, 6, 0]]
+    got = cabi.to_host(ctx.sum_groups(L, 2, cabi.to_device(items), groups))
+    for g, idx in enumerate(groups):
+        want = np.zeros((2, L, n), dtype=np.uint64)
+        for i in idx:
+            want = o.poly_op("add", L, want, items[i])
+        assert np.array_equal(got[g].reshape(-1), np.asarray(want).reshape(-1))
+    with pytest.raises(InvalidArgument):
+        ctx.sum_groups(L, 2, cabi.to_device(items), [[7]])
+
+
 def test_error_reporting_on_gpu(torch_cuda):
     from lancelot_b200 import cabi
     from lancelot_b200._lib import InvalidArgument, LancelotError
