@@ -191,18 +191,53 @@ def _schedule_for_grid(n_clients, world_size, g):
     return [order[(total * r) // world_size:(total * (r + 1)) // world_size] for r in range(world_size)]
 
 
-def pair_schedule(n_clients, world_size):
-    """Pairs i < j in tile-major order over a g x g grid of client groups, cut into
-    ``world_size`` contiguous, equally long segments: a rank touches few distinct clients
-    (so it encrypts or receives few), and segments differ by at most one pair.  The grid size
-    is the one whose busiest rank touches the fewest clients (then the fewest in total)."""
+# Cost of a rank's share in units of one pair's work.  A client the rank must receive costs about three pairs
+# (1 GB of ciphertext over NVLink against the accumulate / relinearize / rotate work of one pair) once the
+# exchange is no longer hidden behind the encryption, which happens as the ranks' own encryption shrinks:
+# the weight grows with the number of ranks (measured: hidden at two ranks, dominant at eight).
+def _client_cost(world_size):
+    return 3.0 * min(1.0, (world_size - 1) / 4.0)
+
+
+def _rank_cost(seg, world_size):
+    return len(seg) + _client_cost(world_size) * len(clients_of(seg))
+
+
+def _schedule_by_tiles(n_clients, world_size, g):
+    """whole tiles of a g x g grid of client groups handed to ranks, largest first, each to the rank whose cost
+    grows least: ranks touch few clients at the price of less even pair counts"""
+    size = int(math.ceil(n_clients / g))
+    tiles = {}
+    for i, j in all_pairs(n_clients):
+        tiles.setdefault((i // size, j // size), []).append((i, j))
+    segs = [[] for _ in range(world_size)]
+    for key in sorted(tiles, key=lambda k: (-len(tiles[k]), k)):
+        best = min(range(world_size), key=lambda r: (_rank_cost(segs[r] + tiles[key], world_size), r))
+        segs[best].extend(tiles[key])
+    return segs
+
+
+def pair_schedule(n_clients, world_size, kinds=None):
+    """Splits the pairs i < j over ``world_size`` ranks so that the busiest rank is as cheap as possible, counting
+    its pairs and the distinct clients it touches (it must encrypt or receive each of them).  Candidates: the
+    tile-major pair order over a g x g grid of client groups cut into equal contiguous segments ("cuts", the
+    default: measured best on eight GPUs), and whole tiles handed out greedily ("tiles": fewer clients per rank,
+    less even pair counts; opt in with kinds="cuts,tiles" or LANCELOT_KRUM_SCHEDULE), for every grid size g; one
+    rank always gets the plain list.  Every rank must use the same setting."""
+    if world_size == 1:
+        return [all_pairs(n_clients)]
     best = None
+    kinds = (kinds or os.environ.get("LANCELOT_KRUM_SCHEDULE", "cuts")).split(",")
     for g in range(1, n_clients + 1):
-        sched = _schedule_for_grid(n_clients, world_size, g)
-        touched = [len(clients_of(seg)) for seg in sched]
-        key = (max(touched) if touched else 0, sum(touched), g)
-        if best is None or key < best[0]:
-            best = (key, sched)
+        cands = []
+        if "cuts" in kinds:
+            cands.append((0, _schedule_for_grid(n_clients, world_size, g)))
+        if "tiles" in kinds:
+            cands.append((1, _schedule_by_tiles(n_clients, world_size, g)))
+        for kind, sched in cands:
+            key = (max(_rank_cost(seg, world_size) for seg in sched), sum(_rank_cost(seg, world_size) for seg in sched), kind, g)
+            if best is None or key < best[0]:
+                best = (key, sched)
     return best[1]
 
 

@@ -1,4 +1,5 @@
 """Host-side logic of the Krum driver: pair scheduling and the world_size-2 gather (gloo, CPU)."""
+import math
 import os
 
 import numpy as np
@@ -16,10 +17,17 @@ def test_pair_schedule_covers_every_pair_once_and_balances():
             flat = [p for s in sched for p in s]
             assert sorted(flat) == all_pairs(n)
             sizes = [len(s) for s in sched]
-            assert max(sizes) - min(sizes) <= 1
-    # the tiling keeps the number of clients a rank must encrypt well below "all of them"
+            # pair counts stay close to even: nobody carries more than a third above the mean (plus one)
+            assert max(sizes) <= 1 + math.ceil(len(flat) / world * 4 / 3)
+    # two ranks: the exchange hides behind the encryption, so the split is the even one
+    sizes = [len(s) for s in pair_schedule(20, 2)]
+    assert max(sizes) - min(sizes) <= 1
+    # eight ranks: a rank touches at most 13 of the 20 clients with equal cuts, 10 when whole tiles may be handed out
     sched = pair_schedule(20, 8)
-    assert max(len(clients_of(s)) for s in sched) <= 15
+    assert max(len(clients_of(s)) for s in sched) <= 13 and max(len(s) for s in sched) - min(len(s) for s in sched) <= 1
+    sched = pair_schedule(20, 8, kinds="cuts,tiles")
+    assert sorted(p for s in sched for p in s) == all_pairs(20)
+    assert max(len(clients_of(s)) for s in sched) <= 10 and max(len(s) for s in sched) <= 25
 
 
 def test_pair_tiles_cover_every_pair_once_with_valid_shapes():
