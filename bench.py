@@ -10,10 +10,11 @@ with inputs resident in HBM, `e2e` the same metric through the C ABI with host b
 measured HBM peak, `cpu_baseline` the CPU checker timed on a bounded sample of the same
 workload on this box's host cores.
 
-Workloads (BASELINE.json configs):
-  ntt    batched NTT + INTT, N = 2^16, 24 fifty-bit primes, 128 polynomials per step
+Workloads (bench_workloads.py):
+  krum   encrypted-Krum distance round (lancelot_b200/krum.py), the default; its line also carries short runs of
+         the other two as the sub-records "hmult" and "ntt"
   hmult  multiply + relinearize + rescale, N = 2^16, L = 24, dnum = 3 (8 special primes)
-  krum   encrypted-Krum distance round (see lancelot_b200/krum.py)
+  ntt    batched NTT + INTT, N = 2^16, 24 fifty-bit primes, 128 polynomials per step
 """
 import argparse
 import json
@@ -107,113 +108,6 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------
-# workloads
-# ------------------------------------------------------------------------------------------
-
-class NttWorkload:
-    """configs[1]: batched NTT/INTT sweep at N = 2^16 over 24 fifty-bit primes."""
-    name = "ntt"
-    metric = "ntt_hbm_gbs"
-    unit = "GB/s"
-    higher_is_better = True
-    dtype = "u64"
-
-    def __init__(self, batch=128, logn=16, limbs=24):
-        self.batch, self.logn, self.limbs = batch, logn, limbs
-        self.N = 1 << logn
-
-    def config(self):
-        return {"workload": "C2 batched NTT+INTT, N=2^16, 24 x 50-bit primes, %d polynomials per step" % self.batch,
-                "l2": "inputs (%.1f GiB per step) exceed the 126 MB L2" % (self.batch * self.limbs * self.N * 8 / 2 ** 30)}
-
-    def moduli(self):
-        from lancelot_b200 import cabi
-        return cabi.coeff_modulus_create(self.N, [50] * self.limbs)
-
-    def algorithmic_bytes_per_step(self):
-        # 16 bytes per coefficient per transform, forward + inverse
-        return 2 * 16 * self.N * self.limbs * self.batch
-
-    def setup_gpu(self, device):
-        import torch
-        from lancelot_b200 import cabi
-        self.ctx = cabi.Context(self.logn, self.moduli(), 0, device=device)
-        g = torch.Generator(device="cuda:%d" % device)
-        g.manual_seed(1234)
-        # residues uniform below 2^49 < q_i for every 50-bit prime
-        self.data = torch.randint(0, 1 << 49, (self.batch, self.limbs, self.N), dtype=torch.int64, device="cuda:%d" % device, generator=g)
-        self.orig = self.data.clone()
-        self.host = torch.empty_like(self.data, device="cpu").pin_memory()
-        self.host.copy_(self.data)
-        self.host_out = torch.empty_like(self.host).pin_memory()
-        self.launches_per_step = 2
-
-    def step_gpu(self):
-        self.ctx.ntt_forward(self.data, self.batch, self.limbs, 0)
-        self.ctx.ntt_inverse(self.data, self.batch, self.limbs, 0)
-
-    def step_e2e(self):
-        self.data.copy_(self.host, non_blocking=True)
-        self.step_gpu()
-        self.host_out.copy_(self.data, non_blocking=True)
-        return self.host.numel() * 8, self.host_out.numel() * 8
-
-    def check_gpu(self):
-        import torch
-        return bool(torch.equal(self.data, self.orig))
-
-    def units_per_step(self):
-        return self.algorithmic_bytes_per_step() / 1e9  # GB
-
-    def roofline_kernel_bytes(self):
-        # one launch transforms the whole batch once
-        return 16 * self.N * self.limbs * self.batch
-
-    @property
-    def ncu_traffic_bytes(self):
-        # dram read + write of one captured 16-polynomial launch was 404.1 MB for 402.7 MB of
-        # algorithmic bytes; traffic grows with the limb count, so scale that ratio
-        return int(self.roofline_kernel_bytes() * 404.1 / 402.7)
-
-    def int_roof(self):
-        """arithmetic ceiling of the transform: the register-only butterfly rate converted to transform traffic"""
-        per_limb = (self.N // 2) * self.logn
-        to_gbs = lambda rate: rate / per_limb * 16 * self.N / 1e9
-        rate = self.ctx.butterfly_rate()  # the variant this workload's primes take
-        names = ["int_strict", "int_lazy", "fp64_strict", "fp64_lazy"]
-        return {"butterflies_per_s": rate, "equivalent_transform_gbs": to_gbs(rate),
-                "variants_gbs": {n: to_gbs(self.ctx.butterfly_rate(i)) for i, n in enumerate(names)},
-                "note": "min(HBM, arithmetic) roof for the NTT is equivalent_transform_gbs"}
-
-    def cpu_sample(self, threads):
-        """forward + inverse of one polynomial (24 limbs) on the CPU checker"""
-        import numpy as np
-        from oracle import binding
-        o = binding.Oracle(self.logn, self.moduli(), 0)
-        rng = np.random.default_rng(0)
-        data = rng.integers(0, 1 << 49, (self.limbs, self.N), dtype=np.uint64)
-        reps = 0
-        t0 = time.perf_counter()
-        while time.perf_counter() - t0 < 4.0 or reps < 2:
-            f = o.ntt_rows(data, 1, self.limbs, 0)
-            b = o.ntt_rows(f, 1, self.limbs, 0, inverse=True)
-            reps += 1
-        dt = time.perf_counter() - t0
-        assert np.array_equal(b, data)
-        gb = reps * 2 * 16 * self.N * self.limbs / 1e9
-        return gb / dt, "%d x (NTT+INTT of 1 polynomial, 24 limbs)" % reps
-
-
-WORKLOADS = {"ntt": NttWorkload}
-
-
-def load_workloads():
-    try:
-        from lancelot_b200 import bench_workloads
-        WORKLOADS.update(bench_workloads.WORKLOADS)
-    except ImportError:
-        pass
-
 
 def host_threads():
     try:
@@ -222,35 +116,86 @@ def host_threads():
         return os.cpu_count() or 1
 
 
-# ------------------------------------------------------------------------------------------
-
 def run_reference(args, wl):
-    """CPU arm: the checker (a port of the reference's algorithm; the reference's own CPU path
-    is OpenFHE, which is not installable here) on a bounded sample per step."""
+    """CPU arm: the checker under oracle/ (a restatement of the reference's algorithm; the reference's own CPU
+    path is OpenFHE, which cannot be installed here) with every host core, on a bounded sample per step.  Rank 0
+    alone runs it.  Neither torch nor the CUDA library is imported on this path."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = host_threads()
-    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
     vals = []
-    sample = ""
+    sample, used = "", threads
     for i in range(args.warmup + args.steps):
-        v, sample = wl.cpu_sample(threads)
+        v, sample, used = wl.cpu_sample(threads)
         if i >= args.warmup:
             vals.append(v)
-    if wl.higher_is_better:
-        value = sum(vals) / len(vals)
-    else:
-        value = sum(vals) / len(vals)
+    value = sum(vals) / len(vals)
     line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": None, "higher_is_better": wl.higher_is_better, "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None, "dtype": wl.dtype,
             "data": "synthetic", "config": wl.config(), "impl": "reference",
-            "cpu_baseline": {"value": value, "unit": wl.unit, "cores": threads, "kind": "port", "sample": sample},
+            "cpu_baseline": {"value": value, "unit": wl.unit, "cores": used, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
-def run_gpu(args, wl):
+def kernel_table(report, peak):
+    """per-kernel rows of the diagnostic timer, largest share first"""
+    total = sum(r["ms"] for r in report.values()) or 1.0
+    rows = []
+    for name, r in sorted(report.items(), key=lambda kv: -kv[1]["ms"]):
+        row = {"kernel": name, "launches": r["launches"], "ms": round(r["ms"], 3), "share": round(r["ms"] / total, 4)}
+        if r["bytes"] > 0 and r["ms"] > 0:
+            gbs = r["bytes"] / (r["ms"] * 1e-3) / 1e9
+            row.update(algorithmic_bytes=r["bytes"], gbs=round(gbs, 1), frac_of_hbm=round(gbs / peak, 4))
+        rows.append(row)
+    return rows
+
+
+def roofline_from(rows, peak, peak_kind, traffic_table):
+    """the roofline entry of the kernel with the largest share of the step among those with stated algorithmic bytes"""
+    for row in rows:
+        if "gbs" not in row:
+            continue
+        per_launch = row["algorithmic_bytes"] / row["launches"]
+        traffic = None
+        cap = traffic_table.get(row["kernel"])
+        if cap:
+            traffic = int(per_launch * cap["dram_bytes"] / cap["algorithmic_bytes"])
+        return {"bound": "hbm", "achieved": row["gbs"], "peak": peak, "unit": "GB/s", "frac": row["gbs"] / peak, "traffic": traffic,
+                "kernel": row["kernel"], "peak_kind": "of " + peak_kind, "share_of_step": row["share"], "launches_per_step": row["launches"],
+                "algorithmic_bytes_per_launch": per_launch, "avg_launch_ms": row["ms"] / row["launches"],
+                "how": "CUDA events recorded in front of every launch during one instrumented repeat of the timed step"}
+    return None
+
+
+def short_run(cls, batch, timed, steps, peak, device, threads, with_cpu):
+    """a short run of another headline workload on this GPU: metric value, its dominant kernel against the HBM peak,
+    and (on one GPU) its CPU baseline"""
+    from lancelot_b200 import cabi
+    wl = cls(batch=batch)
+    wl.setup_gpu(device)
+    for _ in range(3):
+        wl.step_gpu()
+    ms, _ = timed(wl.step_gpu, steps)
+    ok = wl.check_gpu()
+    cabi.kernel_timing(True)
+    wl.step_gpu()
+    rows = kernel_table(cabi.kernel_report(), peak)
+    cabi.kernel_timing(False)
+    value = wl.units_per_step() / (ms * 1e-3 / steps)
+    out = {"metric": wl.metric, "value": value, "unit": wl.unit, "config": wl.config()["workload"], "steps": steps, "parity_check": ok,
+           "algorithmic_gbs": wl.algorithmic_bytes_per_step() / (ms * 1e-3 / steps) / 1e9,
+           "frac_of_hbm": wl.algorithmic_bytes_per_step() / (ms * 1e-3 / steps) / 1e9 / peak, "kernels": rows[:4]}
+    if hasattr(wl, "butterfly_roofs"):
+        out["arithmetic_roof_gbs"] = wl.butterfly_roofs()
+    if with_cpu:
+        v, sample, used = wl.cpu_sample(threads)
+        out["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": used, "kind": "port", "sample": sample}
+    return out
+
+
+def run_gpu(args, wl, default_line):
     import torch
     import torch.distributed as dist
 
@@ -262,6 +207,8 @@ def run_gpu(args, wl):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from lancelot_b200 import cabi
+    import bench_workloads
     wl.setup_gpu(local)
 
     def barrier():
@@ -286,59 +233,69 @@ def run_gpu(args, wl):
             ms = float(t.item())
         return ms, extra
 
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         wl.step_gpu()
     with ClockSampler(local) as clocks:
         ms, _ = timed(wl.step_gpu, args.steps)
     ok = wl.check_gpu()
+    launches = wl.launches_per_step
     if hasattr(wl, "profile_phases"):  # one extra, untimed pass with per-phase synchronisation for the breakdown
         wl.profile_phases = True
         wl.step_gpu()
         wl.profile_phases = False
-    for _ in range(max(args.warmup, 3)):
+    # one instrumented repeat of the same step: an event in front of every launch gives per-kernel device times
+    peak, peak_kind = measured_peaks()
+    barrier()
+    cabi.kernel_timing(True)
+    wl.step_gpu()
+    rows = kernel_table(cabi.kernel_report(), peak)
+    cabi.kernel_timing(False)
+    for _ in range(warm):
         wl.step_e2e()
     ms_e2e, io = timed(wl.step_e2e, args.steps)
+    pair = wl.time_pair_tile(timed) if hasattr(wl, "time_pair_tile") and world == 1 else None
+    roofs = wl.butterfly_roofs() if hasattr(wl, "butterfly_roofs") and world == 1 else None
 
-    # dominant kernel alone, for the roofline entry
-    peak, peak_kind = measured_peaks()
-    kms, kname = wl.time_dominant_kernel(timed) if hasattr(wl, "time_dominant_kernel") else (ms / (args.steps * wl.launches_per_step), "step average")
-    achieved = wl.roofline_kernel_bytes() / (kms * 1e-3) / 1e9
-
+    line = None
     if rank == 0:
-        units = wl.units_per_step() * world
+        units = wl.units_per_step() * (world if getattr(wl, "scaling", "weak") == "weak" else 1)
         sec = ms * 1e-3 / args.steps
         sec_e2e = ms_e2e * 1e-3 / args.steps
         if wl.higher_is_better:
             value, e2e_value = units / sec, units / sec_e2e
         else:
             value, e2e_value = sec, sec_e2e
-        threads = host_threads()
-        os.environ.setdefault("OMP_NUM_THREADS", str(threads))
-        cpu = None
-        if world == 1:
-            v, sample = wl.cpu_sample(threads)
-            cpu = {"value": v, "unit": wl.unit, "cores": threads, "kind": "port", "sample": sample}
-        line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps, "warmup": warm,
                 "ms_per_step": ms / args.steps, "higher_is_better": wl.higher_is_better, "scaling": getattr(wl, "scaling", "weak"),
                 "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config(),
                 "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": io[0], "d2h_bytes_per_step": io[1]},
-                "gpu_launches": args.steps * wl.launches_per_step,
-                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "traffic": getattr(wl, "ncu_traffic_bytes", None), "kernel": kname, "peak_kind": "of " + peak_kind},
-                "cpu_baseline": cpu, "clocks": clocks.summary(), "parity_check": ok}
-        if hasattr(wl, "int_roof"):
-            line["int_roof"] = wl.int_roof()
-        if hasattr(wl, "int_roof_gbs"):
-            line["roofline"]["arithmetic_roof_gbs"] = wl.int_roof_gbs
-            line["roofline"]["frac_of_arithmetic_roof"] = achieved / wl.int_roof_gbs
-        if hasattr(wl, "pair_kernel"):
-            wl.pair_kernel["peak"] = peak
-            wl.pair_kernel["frac"] = wl.pair_kernel["achieved"] / peak
-            line["roofline_pair_kernel"] = wl.pair_kernel
+                "gpu_launches": args.steps * launches,
+                "roofline": roofline_from(rows, peak, peak_kind, bench_workloads.NCU_TRAFFIC),
+                "kernels": rows[:8], "cpu_baseline": None, "clocks": clocks.summary(), "parity_check": ok}
+        if roofs:
+            line["arithmetic_roof_gbs"] = roofs
+        if pair:
+            pair["peak"] = peak
+            pair["frac"] = pair["achieved"] / peak
+            line["roofline_pair_kernel"] = pair
         if getattr(wl, "breakdown", None):
             line["breakdown"] = wl.breakdown
         if hasattr(wl, "rel_err"):
             line["max_rel_err_vs_float64_plaintext"] = wl.rel_err
+    # the other two headline metrics, from short runs of their workloads on this same GPU (default line, one GPU)
+    if default_line and world == 1:
+        del wl
+        torch.cuda.empty_cache()
+        threads = host_threads()
+        line["hmult"] = short_run(bench_workloads.HmultWorkload, 8, timed, 3, peak, local, threads, True)
+        torch.cuda.empty_cache()
+        line["ntt"] = short_run(bench_workloads.NttWorkload, 128, timed, 3, peak, local, threads, True)
+        wl = bench_workloads.WORKLOADS[args.workload_name]() if args.batch is None else bench_workloads.WORKLOADS[args.workload_name](batch=args.batch)
+    if rank == 0:
+        if world == 1:
+            v, sample, used = wl.cpu_sample(host_threads())
+            line["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": used, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -350,17 +307,19 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None)
+    ap.add_argument("--workload", default=None, help="krum (default), hmult or ntt")
     ap.add_argument("--batch", type=int, default=None)
     args = ap.parse_args()
-    load_workloads()
-    name = args.workload or os.environ.get("LB_BENCH_WORKLOAD") or ("krum" if "krum" in WORKLOADS else "ntt")
-    cls = WORKLOADS[name]
+    import bench_workloads
+    name = args.workload or os.environ.get("LB_BENCH_WORKLOAD") or "krum"
+    args.workload_name = name
+    cls = bench_workloads.WORKLOADS[name]
     wl = cls(batch=args.batch) if args.batch else cls()
     if args.impl == "reference":
         run_reference(args, wl)
     else:
-        run_gpu(args, wl)
+        # the default line (no --workload) also carries the other two headline metrics as sub-records
+        run_gpu(args, wl, default_line=args.workload is None and name == "krum" and args.batch is None)
 
 
 if __name__ == "__main__":

@@ -16,6 +16,7 @@
 #include <array>
 #include <functional>
 #include <istream>
+#include <map>
 #include <memory>
 #include <ostream>
 #include <random>
@@ -120,18 +121,91 @@ inline std::vector<std::uint8_t> seeds(std::size_t n)
     return s;
 }
 
-// device array of 64-bit words with value semantics
+// Device blocks are recycled instead of being handed back to the driver: like the reference's global memory pool
+// (cahel-main/include/mempool.cuh:471-492,600-606), a container that goes out of scope returns its block to a
+// free list, bucketed by size (powers of two from 256 bytes), and the next container of that bucket takes it
+// without a cudaMalloc / cudaFree (both synchronise the device).  Every call of this layer runs on the default
+// stream, so a recycled block is never handed out while earlier work on it is still queued behind later work.
+// Single-threaded use, like the reference's pool.  trim() frees what is cached.
+class DevicePool {
+public:
+    static DevicePool &instance()
+    {
+        static DevicePool pool;
+        return pool;
+    }
+    static std::size_t bucket_bytes(std::size_t bytes)
+    {
+        std::size_t b = 256;
+        while (b < bytes) b <<= 1;
+        return b;
+    }
+    void *take(std::size_t bytes)
+    {
+        const std::size_t b = bucket_bytes(bytes);
+        int dev = 0;
+        cuda_check(cudaGetDevice(&dev));
+        auto &list = free_[{dev, b}];
+        if (!list.empty()) {
+            void *p = list.back();
+            list.pop_back();
+            cached_ -= b;
+            ++reused_;
+            return p;
+        }
+        void *p = nullptr;
+        cudaError_t e = cudaMalloc(&p, b);
+        if (e != cudaSuccess) { // give cached blocks back to the driver and try once more
+            (void)cudaGetLastError();
+            trim();
+            cuda_check(cudaMalloc(&p, b));
+        }
+        ++allocated_;
+        owner_[p] = {dev, b};
+        return p;
+    }
+    void give(void *p)
+    {
+        auto it = owner_.find(p);
+        if (it == owner_.end()) return;
+        free_[it->second].push_back(p);
+        cached_ += it->second.second;
+    }
+    void trim()
+    {
+        for (auto &kv : free_) {
+            for (void *p : kv.second) {
+                owner_.erase(p);
+                cudaFree(p);
+            }
+            kv.second.clear();
+        }
+        cached_ = 0;
+    }
+    std::size_t device_allocations() const { return allocated_; }
+    std::size_t reuses() const { return reused_; }
+    std::size_t cached_bytes() const { return cached_; }
+    ~DevicePool() { trim(); }
+
+private:
+    DevicePool() = default;
+    std::map<std::pair<int, std::size_t>, std::vector<void *>> free_;
+    std::map<void *, std::pair<int, std::size_t>> owner_;
+    std::size_t cached_ = 0, allocated_ = 0, reused_ = 0;
+};
+
+// device array of 64-bit words with value semantics, backed by the pool
 class DeviceWords {
 public:
     DeviceWords() = default;
     explicit DeviceWords(std::size_t n) { resize(n); }
     DeviceWords(const DeviceWords &o) { *this = o; }
-    DeviceWords(DeviceWords &&o) noexcept : p_(o.p_), n_(o.n_) { o.p_ = nullptr; o.n_ = 0; }
+    DeviceWords(DeviceWords &&o) noexcept : p_(o.p_), n_(o.n_), cap_(o.cap_) { o.p_ = nullptr; o.n_ = 0; o.cap_ = 0; }
     DeviceWords &operator=(const DeviceWords &o)
     {
         if (this != &o) {
             resize(o.n_);
-            if (n_) cuda_check(cudaMemcpy(p_, o.p_, n_ * 8, cudaMemcpyDeviceToDevice));
+            if (n_) cuda_check(cudaMemcpyAsync(p_, o.p_, n_ * 8, cudaMemcpyDeviceToDevice, nullptr));
         }
         return *this;
     }
@@ -139,17 +213,25 @@ public:
     {
         if (this != &o) {
             release();
-            p_ = o.p_; n_ = o.n_;
-            o.p_ = nullptr; o.n_ = 0;
+            p_ = o.p_; n_ = o.n_; cap_ = o.cap_;
+            o.p_ = nullptr; o.n_ = 0; o.cap_ = 0;
         }
         return *this;
     }
     ~DeviceWords() { release(); }
+    // contents are not kept; a block whose bucket already fits is reused as it is
     void resize(std::size_t n)
     {
         if (n == n_) return;
+        if (n && p_ && DevicePool::bucket_bytes(n * 8) == cap_) {
+            n_ = n;
+            return;
+        }
         release();
-        if (n) cuda_check(cudaMalloc((void **)&p_, n * 8));
+        if (n) {
+            cap_ = DevicePool::bucket_bytes(n * 8);
+            p_ = static_cast<std::uint64_t *>(DevicePool::instance().take(n * 8));
+        }
         n_ = n;
     }
     std::uint64_t *get() const { return p_; }
@@ -158,12 +240,13 @@ public:
 private:
     void release()
     {
-        if (p_) cudaFree(p_);
+        if (p_) DevicePool::instance().give(p_);
         p_ = nullptr;
         n_ = 0;
+        cap_ = 0;
     }
     std::uint64_t *p_ = nullptr;
-    std::size_t n_ = 0;
+    std::size_t n_ = 0, cap_ = 0;
 };
 
 } // namespace cahel_b200
@@ -497,12 +580,79 @@ struct CAHELGPURelinKey {
     cahel_b200::DeviceWords keys_; // [dnum][2][size_QP][N]
     CAHELGPURelinKey() = default;
     explicit CAHELGPURelinKey(const CAHELGPUContext &) {}
+    // cahel-main/include/secretkey.h:212-256: key-level parms_id, generated flag, pair count, then every key pair as a
+    // size-2 ciphertext stream over all primes with chain index 0 and scale 1 (seed block zero)
+    void save(const CAHELGPUContext &context, std::ostream &stream) const
+    {
+        if (!keys_.size()) throw std::logic_error("relinearization key has not been generated");
+        const std::size_t n = context.poly_degree_, pair = 2 * context.size_QP_ * n, dnum = keys_.size() / pair;
+        cahel_b200::put(stream, context.parms_id(0));
+        cahel_b200::put(stream, true);
+        cahel_b200::put<std::uint64_t>(stream, dnum);
+        for (std::size_t j = 0; j < dnum; ++j) {
+            cahel_b200::put(stream, context.parms_id(0));
+            cahel_b200::put(stream, true);
+            cahel_b200::put<std::uint64_t>(stream, 0);
+            cahel_b200::put<std::uint64_t>(stream, 2);
+            cahel_b200::put<std::uint64_t>(stream, n);
+            cahel_b200::put<std::uint64_t>(stream, context.size_QP_);
+            cahel_b200::put(stream, 1.0);
+            cahel_b200::put_words(stream, keys_.get() + j * pair, pair);
+            const char seed[64] = {0};
+            stream.write(seed, sizeof(seed));
+        }
+        if (!stream) throw std::runtime_error("I/O error");
+    }
+    void load(const CAHELGPUContext &context, std::istream &stream)
+    {
+        const std::size_t n = context.poly_degree_, pair = 2 * context.size_QP_ * n;
+        const auto id = cahel_b200::get<cahel::parms_id_type>(stream);
+        (void)cahel_b200::get<bool>(stream);
+        const auto dnum = cahel_b200::get<std::uint64_t>(stream);
+        if (id != context.parms_id(0) || dnum != context.size_Q_ / context.size_P_) throw std::invalid_argument("relinearization key data is invalid");
+        cahel_b200::DeviceWords all(dnum * pair), one;
+        for (std::uint64_t j = 0; j < dnum; ++j) {
+            const auto pid = cahel_b200::get<cahel::parms_id_type>(stream);
+            (void)cahel_b200::get<bool>(stream);
+            (void)cahel_b200::get<std::uint64_t>(stream);
+            const auto size = cahel_b200::get<std::uint64_t>(stream), pn = cahel_b200::get<std::uint64_t>(stream),
+                       limbs = cahel_b200::get<std::uint64_t>(stream);
+            (void)cahel_b200::get<double>(stream);
+            if (pid != id || size != 2 || pn != n || limbs != context.size_QP_) throw std::invalid_argument("relinearization key data is invalid");
+            cahel_b200::get_words(stream, one, pair);
+            cahel_b200::cuda_check(cudaMemcpy(all.get() + j * pair, one.get(), pair * 8, cudaMemcpyDeviceToDevice));
+            char seed[64];
+            stream.read(seed, sizeof(seed));
+            if (!stream) throw std::runtime_error("I/O error");
+        }
+        keys_ = std::move(all);
+    }
 };
 
 struct CAHELGPUGaloisKey {
     std::vector<CAHELGPURelinKey> relin_keys_; // one per Galois element of the context
     CAHELGPUGaloisKey() = default;
     explicit CAHELGPUGaloisKey(const CAHELGPUContext &) {}
+    // cahel-main/include/secretkey.h:354-400: key-level parms_id, generated flag, key count, then one
+    // relinearization-key stream per Galois element
+    void save(const CAHELGPUContext &context, std::ostream &stream) const
+    {
+        if (relin_keys_.empty()) throw std::logic_error("Galois keys have not been generated");
+        cahel_b200::put(stream, context.parms_id(0));
+        cahel_b200::put(stream, true);
+        cahel_b200::put<std::uint64_t>(stream, relin_keys_.size());
+        for (const auto &k : relin_keys_) k.save(context, stream);
+    }
+    void load(const CAHELGPUContext &context, std::istream &stream)
+    {
+        const auto id = cahel_b200::get<cahel::parms_id_type>(stream);
+        (void)cahel_b200::get<bool>(stream);
+        const auto count = cahel_b200::get<std::uint64_t>(stream);
+        if (id != context.parms_id(0) || count != context.galois_elts_.size()) throw std::invalid_argument("Galois key data is invalid");
+        std::vector<CAHELGPURelinKey> keys(count);
+        for (auto &k : keys) k.load(context, stream);
+        relin_keys_ = std::move(keys);
+    }
 };
 
 // cahel-main/include/secretkey.h, src/secretkey.cu:254-654
@@ -611,14 +761,13 @@ struct CAHELGPUCKKSEncoder {
         }
         if (sparse_slots_ < 2) throw std::invalid_argument("single value encoding is not available");
         const int L = context.size_l(chain_index);
-        double *d_vals = nullptr;
-        cahel_b200::cuda_check(cudaMalloc((void **)&d_vals, (values.size() + 1) * sizeof(double)));
+        cahel_b200::DeviceWords staging(values.size() + 1); // pooled scratch: one word per double
+        double *d_vals = reinterpret_cast<double *>(staging.get());
         cahel_b200::cuda_check(cudaMemcpy(d_vals, values.data(), values.size() * sizeof(double), cudaMemcpyHostToDevice));
         destination.data_.resize((std::size_t)L * context.poly_degree_);
         int rc = lb_encode(context.lb_handle_, L, d_vals, 0, values.size(), (int)values.size(), (int)sparse_slots_, 1, scale,
                            destination.data(), nullptr);
         if (rc == LB_OK) rc = lb_check_status(context.lb_handle_, nullptr);
-        cudaFree(d_vals);
         cahel_b200::check(rc);
         destination.chain_index() = chain_index;
         destination.scale() = scale;
@@ -646,12 +795,11 @@ struct CAHELGPUCKKSEncoder {
         if (!plain.is_ntt_form()) throw std::invalid_argument("plain is not in NTT form");
         if (sparse_slots_ == 0) sparse_slots_ = slots_;
         const int L = context.size_l(plain.chain_index());
-        double *d_out = nullptr;
-        cahel_b200::cuda_check(cudaMalloc((void **)&d_out, sparse_slots_ * 2 * sizeof(double)));
+        cahel_b200::DeviceWords staging(sparse_slots_ * 2); // pooled scratch for the complex slots
+        double *d_out = reinterpret_cast<double *>(staging.get());
         int rc = lb_decode(context.lb_handle_, L, plain.data(), plain.scale(), (int)sparse_slots_, d_out, nullptr);
         std::vector<double> host(2 * sparse_slots_);
         if (rc == LB_OK) cahel_b200::cuda_check(cudaMemcpy(host.data(), d_out, host.size() * sizeof(double), cudaMemcpyDeviceToHost));
-        cudaFree(d_out);
         cahel_b200::check(rc);
         destination.resize(sparse_slots_);
         for (std::size_t i = 0; i < sparse_slots_; ++i) destination[i] = host[2 * i];
@@ -863,7 +1011,7 @@ inline void rotate_vector_inplace(const CAHELGPUContext &context, CAHELGPUCipher
         for (int i = 0; v; ++i) {
             int zi = (v & 1) ? 2 - (v & 3) : 0;
             v = (v - zi) >> 1;
-            if (zi) parts.insert(parts.begin(), (sign ? -zi : zi) * (1 << i));
+            if (zi) parts.push_back((sign ? -zi : zi) * (1 << i)); // least significant first, the order the reference applies
         }
     }
     if (parts.size() == 1) throw std::invalid_argument("Galois key not present");

@@ -18,6 +18,12 @@
  * LB_ERR_INVALID_ARG marks the conditions where the reference throws std::invalid_argument,
  * LB_ERR_LOGIC / LB_ERR_CUDA where it throws std::logic_error (cahel-main/include/common.h:50-62).
  * The library never falls back to the CPU: without a usable GPU every compute call fails.
+ *
+ * Every call on a context uses that context's scratch workspace and tables; calls on one context
+ * must therefore be issued on ONE stream (or be ordered by the caller with events).  Use one context
+ * per concurrent stream.  A call makes the context's device current for the calling thread.
+ * Benchmark diagnostics (launch counter, per-kernel timer, butterfly-rate probe) are declared in
+ * lancelot_b200_diag.h and are not part of this boundary.
  */
 #ifndef LANCELOT_B200_H
 #define LANCELOT_B200_H
@@ -44,8 +50,6 @@ extern "C" {
 typedef struct lb_context lb_context;
 
 LB_API const char *lb_last_error(void);
-/* number of kernels this library has launched in this process (benchmark bookkeeping) */
-LB_API unsigned long long lb_launch_count(void);
 
 /* ---- host-only parameter helpers (no GPU needed) ---------------------------------------- */
 
@@ -83,13 +87,6 @@ LB_API size_t lb_keyswitch_workspace_bytes(const lb_context *ctx, int size_l);
 /* data: n_groups x (size_l + size_p) limbs; inside a group the first size_l limbs use data
  * primes 0..size_l-1 and the next size_p the special primes.  In place. */
 LB_API int lb_ntt_forward(lb_context *ctx, uint64_t *data, int n_groups, int size_l, int size_p, void *stream);
-/* Measures the register-only rate of one of the transform's butterfly variants on this GPU (butterflies per
- * second, synchronous, a few milliseconds): the arithmetic ceiling of any NTT schedule for primes of that size.
- * variant: 0 integer Shoup product with conditional subtraction (primes of 58 bits and more), 1 the same without
- * it (below 2^58), 2 / 3 quotient estimated on the FP64 pipe with / without conditional subtraction (primes below
- * 2^50 / 2^46), -1 the variant the context's first prime takes.  One limb needs (N/2) log2 N butterflies for
- * its 16 N bytes. */
-LB_API int lb_probe_butterfly_rate(lb_context *ctx, int variant, double *butterflies_per_second);
 LB_API int lb_ntt_inverse(lb_context *ctx, uint64_t *data, int n_groups, int size_l, int size_p, void *stream);
 
 /* ---- element-wise evaluator ops (cahel-main/src/evaluate.cu:15,42,199; polymath.cu:16-227) ---- */
@@ -107,6 +104,10 @@ LB_API int lb_sum_groups(lb_context *ctx, int size_l, int n_polys, int n_groups,
 /* element-wise product of two key-level polynomials [size_QP][N] (compute_secret_key_array, cahel-main/src/secretkey.cu:285-320) */
 LB_API int lb_multiply_poly_key_level(lb_context *ctx, const uint64_t *a, const uint64_t *b, uint64_t *out, void *stream);
 LB_API int lb_negate(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, uint64_t *out, void *stream);
+/* out = a mod q per limb for ANY 64-bit words a (out may alias a).  The reference has no such call: its additions
+ * reduce one by one (cahel-main/src/polymath.cu:16-60).  It closes a plain 64-bit sum of residues, such as the
+ * reduce-scatter of per-GPU partial pair sums in the Krum driver, in one pass. */
+LB_API int lb_reduce_mod(lb_context *ctx, int size_l, int n_polys, const uint64_t *a, uint64_t *out, void *stream);
 /* ckks_multiply / ckks_square (cahel-main/src/evaluate.cu:447,1433): batch of size-2 ciphertexts -> size-3 */
 LB_API int lb_multiply(lb_context *ctx, int size_l, int batch, const uint64_t *a, const uint64_t *b, uint64_t *out3, void *stream);
 LB_API int lb_square(lb_context *ctx, int size_l, int batch, const uint64_t *a, uint64_t *out3, void *stream);

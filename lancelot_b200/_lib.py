@@ -3,8 +3,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# LANCELOT_B200_LIB selects another build of the same library (kernel tuning sweeps)
-lib_path = os.environ.get("LANCELOT_B200_LIB") or os.path.join(_HERE, "liblancelot_b200.so")
+lib_path = os.path.join(_HERE, "liblancelot_b200.so")
 
 LB_OK, LB_ERR_INVALID_ARG, LB_ERR_LOGIC, LB_ERR_CUDA, LB_ERR_NO_MEMORY = range(5)
 

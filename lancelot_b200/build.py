@@ -31,6 +31,7 @@ def build(force=False, verbose=False):
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "lancelot_b200.h"))
+    headers.append(os.path.join(os.path.dirname(HERE), "include", "lancelot_b200_diag.h"))
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     if not os.path.exists(nvcc):
         nvcc = "nvcc"
@@ -56,7 +57,9 @@ def build(force=False, verbose=False):
     if verbose:
         sys.stderr.write("\n".join(logs))
     if jobs or force or _stale(OUT, objs):
-        run([nvcc, "-shared", "-o", OUT] + objs + ["-Xcompiler", "-fPIC", "-lcudart"])
+        # link beside the target and rename, so that a reader never sees a half-written library
+        run([nvcc, "-shared", "-o", OUT + ".tmp"] + objs + ["-Xcompiler", "-fPIC", "-lcudart"])
+        os.replace(OUT + ".tmp", OUT)
     return OUT
 
 

@@ -22,10 +22,6 @@ def _p(t):
     return C.c_void_p(t.data_ptr())
 
 
-def _stream():
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
-
-
 def to_device(a, device="cuda"):
     """numpy uint64 array -> CUDA int64 tensor with the same bits."""
     a = np.ascontiguousarray(a, dtype=np.uint64)
@@ -81,6 +77,10 @@ class Context:
         except Exception:
             pass
 
+    def _stream(self):
+        """the current torch stream of THIS context's device (not of whatever device is current)"""
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
     def reserve_workspace(self, nbytes):
         check(lib.lb_context_reserve_workspace(self.h, C.c_size_t(int(nbytes))))
 
@@ -108,114 +108,120 @@ class Context:
 
     # -- transforms
     def ntt_forward(self, data, n_groups, size_l, size_p):
-        check(lib.lb_ntt_forward(self.h, _p(data), n_groups, size_l, size_p, _stream()))
+        check(lib.lb_ntt_forward(self.h, _p(data), n_groups, size_l, size_p, self._stream()))
 
     def ntt_inverse(self, data, n_groups, size_l, size_p):
-        check(lib.lb_ntt_inverse(self.h, _p(data), n_groups, size_l, size_p, _stream()))
+        check(lib.lb_ntt_inverse(self.h, _p(data), n_groups, size_l, size_p, self._stream()))
 
     # -- element-wise
     def add(self, size_l, a, b, out=None):
         out = torch.empty_like(a) if out is None else out
-        check(lib.lb_add(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(b), _p(out), _stream()))
+        check(lib.lb_add(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(b), _p(out), self._stream()))
         return out
 
     def sub(self, size_l, a, b, out=None):
         out = torch.empty_like(a) if out is None else out
-        check(lib.lb_sub(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(b), _p(out), _stream()))
+        check(lib.lb_sub(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(b), _p(out), self._stream()))
         return out
 
     def multiply_poly(self, size_l, a, b, out=None):
         out = torch.empty_like(a) if out is None else out
-        check(lib.lb_multiply_poly(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(b), _p(out), _stream()))
+        check(lib.lb_multiply_poly(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(b), _p(out), self._stream()))
         return out
 
     def multiply_poly_qp(self, a, b):
         """element-wise product over the key-level limb list Q || P (used for s^2)"""
         out = torch.empty_like(a)
-        check(lib.lb_multiply_poly_key_level(self.h, _p(a), _p(b), _p(out), _stream()))
+        check(lib.lb_multiply_poly_key_level(self.h, _p(a), _p(b), _p(out), self._stream()))
         return out
 
     def negate(self, size_l, a, out=None):
         out = torch.empty_like(a) if out is None else out
-        check(lib.lb_negate(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(out), _stream()))
+        check(lib.lb_negate(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(out), self._stream()))
+        return out
+
+    def reduce_mod(self, size_l, a, out=None):
+        """a mod q per limb for arbitrary 64-bit words (in place unless ``out`` is given)"""
+        out = a if out is None else out
+        check(lib.lb_reduce_mod(self.h, size_l, a.numel() // (size_l * self.N), _p(a), _p(out), self._stream()))
         return out
 
     def multiply(self, size_l, a, b, batch=1):
         out = self.empty(batch, 3, size_l, self.N) if batch > 1 else self.empty(3, size_l, self.N)
-        check(lib.lb_multiply(self.h, size_l, batch, _p(a), _p(b), _p(out), _stream()))
+        check(lib.lb_multiply(self.h, size_l, batch, _p(a), _p(b), _p(out), self._stream()))
         return out
 
     def square(self, size_l, a, batch=1):
         out = self.empty(batch, 3, size_l, self.N) if batch > 1 else self.empty(3, size_l, self.N)
-        check(lib.lb_square(self.h, size_l, batch, _p(a), _p(out), _stream()))
+        check(lib.lb_square(self.h, size_l, batch, _p(a), _p(out), self._stream()))
         return out
 
     def mod_switch_drop(self, size_l, ct):
         n_polys = ct.numel() // (size_l * self.N)
         out = self.empty(n_polys, size_l - 1, self.N)
-        check(lib.lb_mod_switch_drop(self.h, size_l, n_polys, _p(ct), _p(out), _stream()))
+        check(lib.lb_mod_switch_drop(self.h, size_l, n_polys, _p(ct), _p(out), self._stream()))
         return out
 
     def galois_permute(self, elt_index, data):
         out = torch.empty_like(data)
-        check(lib.lb_galois_permute(self.h, elt_index, data.numel() // self.N, _p(data), _p(out), _stream()))
+        check(lib.lb_galois_permute(self.h, elt_index, data.numel() // self.N, _p(data), _p(out), self._stream()))
         return out
 
     # -- key switching
     def modup(self, size_l, cks):
         out = self.empty(self.beta(size_l), size_l + self.size_P, self.N)
-        check(lib.lb_modup(self.h, size_l, _p(cks), _p(out), _stream()))
+        check(lib.lb_modup(self.h, size_l, _p(cks), _p(out), self._stream()))
         return out
 
     def inner_product(self, size_l, digits, evk):
         out = self.empty(2, size_l + self.size_P, self.N)
-        check(lib.lb_keyswitch_inner_product(self.h, size_l, _p(digits), _p(evk), _p(out), _stream()))
+        check(lib.lb_keyswitch_inner_product(self.h, size_l, _p(digits), _p(evk), _p(out), self._stream()))
         return out
 
     def moddown(self, size_l, cx):
         out = self.empty(size_l, self.N)
-        check(lib.lb_moddown(self.h, size_l, _p(cx), _p(out), _stream()))
+        check(lib.lb_moddown(self.h, size_l, _p(cx), _p(out), self._stream()))
         return out
 
     def keyswitch(self, size_l, ct, cks, evk):
-        check(lib.lb_keyswitch(self.h, size_l, _p(ct), _p(cks), _p(evk), _stream()))
+        check(lib.lb_keyswitch(self.h, size_l, _p(ct), _p(cks), _p(evk), self._stream()))
         return ct
 
     def relinearize(self, size_l, ct3, rlk):
-        check(lib.lb_relinearize(self.h, size_l, _p(ct3), _p(rlk), _stream()))
+        check(lib.lb_relinearize(self.h, size_l, _p(ct3), _p(rlk), self._stream()))
         return ct3[:2]
 
     def rescale(self, size_l, ct):
         n_polys = ct.numel() // (size_l * self.N)
         out = self.empty(n_polys, size_l - 1, self.N)
-        check(lib.lb_rescale(self.h, size_l, n_polys, _p(ct), _p(out), _stream()))
+        check(lib.lb_rescale(self.h, size_l, n_polys, _p(ct), _p(out), self._stream()))
         return out
 
     def rescale_strided(self, size_l, ct, batch, polys_per_ct, ct_stride):
         out = self.empty(batch, polys_per_ct, size_l - 1, self.N)
-        check(lib.lb_rescale_strided(self.h, size_l, batch, polys_per_ct, _p(ct), C.c_size_t(ct_stride), _p(out), _stream()))
+        check(lib.lb_rescale_strided(self.h, size_l, batch, polys_per_ct, _p(ct), C.c_size_t(ct_stride), _p(out), self._stream()))
         return out
 
     def rotate(self, size_l, ct, elt_index, glk):
-        check(lib.lb_rotate(self.h, size_l, _p(ct), elt_index, _p(glk), _stream()))
+        check(lib.lb_rotate(self.h, size_l, _p(ct), elt_index, _p(glk), self._stream()))
         return ct
 
     def hoisting(self, size_l, ct, elt_indices, glks):
         n = len(elt_indices)
         idx = (C.c_int * n)(*elt_indices)
         ptrs = (C.c_void_p * n)(*[g.data_ptr() for g in glks])
-        check(lib.lb_hoisting(self.h, size_l, _p(ct), n, idx, ptrs, _stream()))
+        check(lib.lb_hoisting(self.h, size_l, _p(ct), n, idx, ptrs, self._stream()))
         return ct
 
     def relinearize_batch(self, size_l, ct3, rlk):
         """ct3: [batch][3][size_l][N]; the first two polynomials of each hold the result"""
         batch = ct3.numel() // (3 * size_l * self.N)
-        check(lib.lb_relinearize_batch(self.h, size_l, batch, _p(ct3), _p(rlk), _stream()))
+        check(lib.lb_relinearize_batch(self.h, size_l, batch, _p(ct3), _p(rlk), self._stream()))
         return ct3
 
     def rotate_batch(self, size_l, ct, elt_index, glk):
         batch = ct.numel() // (2 * size_l * self.N)
-        check(lib.lb_rotate_batch(self.h, size_l, batch, _p(ct), elt_index, _p(glk), _stream()))
+        check(lib.lb_rotate_batch(self.h, size_l, batch, _p(ct), elt_index, _p(glk), self._stream()))
         return ct
 
     def hoisting_batch(self, size_l, ct, elt_indices, glks):
@@ -223,7 +229,7 @@ class Context:
         n = len(elt_indices)
         idx = (C.c_int * n)(*elt_indices)
         ptrs = (C.c_void_p * n)(*[g.data_ptr() for g in glks])
-        check(lib.lb_hoisting_batch(self.h, size_l, batch, _p(ct), n, idx, ptrs, _stream()))
+        check(lib.lb_hoisting_batch(self.h, size_l, batch, _p(ct), n, idx, ptrs, self._stream()))
         return ct
 
     def sum_groups(self, size_l, n_polys, items, groups):
@@ -236,7 +242,7 @@ class Context:
         out = self.empty(len(groups), n_polys, size_l, self.N)
         off = (C.c_int * len(offsets))(*offsets)
         idx = (C.c_int * max(1, len(flat)))(*flat)
-        check(lib.lb_sum_groups(self.h, size_l, n_polys, len(groups), off, idx, n_items, _p(items), _p(out), _stream()))
+        check(lib.lb_sum_groups(self.h, size_l, n_polys, len(groups), off, idx, n_items, _p(items), _p(out), self._stream()))
         return out
 
     def krum_accumulate(self, size_l, a, b, acc, accumulate=False, n_chunks=None, stride_a=None, stride_b=None):
@@ -245,7 +251,7 @@ class Context:
         stride_a = ct_words if stride_a is None else stride_a
         stride_b = ct_words if stride_b is None else stride_b
         check(lib.lb_krum_accumulate(self.h, size_l, n_chunks, _p(a), _p(b), C.c_size_t(stride_a), C.c_size_t(stride_b),
-                                     _p(acc), int(accumulate), _stream()))
+                                     _p(acc), int(accumulate), self._stream()))
         return acc
 
     def krum_accumulate_tile(self, size_l, a, b, outs, n_chunks=None):
@@ -258,13 +264,13 @@ class Context:
         po = (C.c_void_p * len(outs))(*[t.data_ptr() for t in outs])
         n_pairs = len(a) * len(b) if b else len(a) * (len(a) - 1) // 2
         assert len(outs) == n_pairs, "one output per pair"
-        check(lib.lb_krum_accumulate_tile(self.h, size_l, n_chunks, len(a), pa, len(b), pb, C.c_size_t(ct_words), po, _stream()))
+        check(lib.lb_krum_accumulate_tile(self.h, size_l, n_chunks, len(a), pa, len(b), pb, C.c_size_t(ct_words), po, self._stream()))
         return outs
 
     def decrypt(self, size_l, ct, sk):
         n_polys = ct.numel() // (size_l * self.N)
         pt = self.empty(size_l, self.N)
-        check(lib.lb_decrypt(self.h, size_l, n_polys, _p(ct), _p(sk), _p(pt), _stream()))
+        check(lib.lb_decrypt(self.h, size_l, n_polys, _p(ct), _p(sk), _p(pt), self._stream()))
         return pt
 
     # -- samplers, keys, encryption (seeds are host bytes; 64 per seed)
@@ -278,27 +284,27 @@ class Context:
         s, sp = self._seed(seed)
         out = self.empty(size_l + size_p, self.N)
         fn = {"ternary": lib.lb_sample_ternary, "error": lib.lb_sample_error, "uniform": lib.lb_sample_uniform}[kind]
-        check(fn(self.h, sp, size_l, size_p, _p(out), _stream()))
+        check(fn(self.h, sp, size_l, size_p, _p(out), self._stream()))
         return out
 
     def gen_secret_key(self, seed):
         s, sp = self._seed(seed)
         sk = self.empty(self.size_QP, self.N)
-        check(lib.lb_gen_secret_key(self.h, sp, _p(sk), _stream()))
+        check(lib.lb_gen_secret_key(self.h, sp, _p(sk), self._stream()))
         return sk
 
     def gen_public_key(self, sk, seed_error, seed_uniform):
         se, pe = self._seed(seed_error)
         su, pu = self._seed(seed_uniform)
         pk = self.empty(2, self.size_QP, self.N)
-        check(lib.lb_gen_public_key(self.h, _p(sk), pe, pu, _p(pk), _stream()))
+        check(lib.lb_gen_public_key(self.h, _p(sk), pe, pu, _p(pk), self._stream()))
         return pk
 
     def gen_switch_key(self, sk, sk_target, seeds):
         dnum = self.size_Q // self.size_P
         s, sp = self._seed(seeds, 2 * dnum)
         out = self.empty(dnum, 2, self.size_QP, self.N)
-        check(lib.lb_gen_switch_key(self.h, _p(sk), _p(sk_target), sp, _p(out), _stream()))
+        check(lib.lb_gen_switch_key(self.h, _p(sk), _p(sk_target), sp, _p(out), self._stream()))
         return out
 
     def encrypt_asymmetric(self, pk, pt, seeds, batch=1, out=None):
@@ -307,7 +313,7 @@ class Context:
             ct = out
         else:
             ct = self.empty(batch, 2, self.size_Q, self.N) if batch > 1 else self.empty(2, self.size_Q, self.N)
-        check(lib.lb_encrypt_asymmetric(self.h, _p(pk), _p(pt), sp, batch, _p(ct), _stream()))
+        check(lib.lb_encrypt_asymmetric(self.h, _p(pk), _p(pt), sp, batch, _p(ct), self._stream()))
         return ct
 
     # -- encoder
@@ -321,7 +327,7 @@ class Context:
             sparse_slots = 1 << max(1, int(np.ceil(np.log2(max(n, 2)))))
         pt = self.empty(batch, size_l, self.N) if batch > 1 else self.empty(size_l, self.N)
         check(lib.lb_encode(self.h, size_l, C.c_void_p(values.data_ptr()), dt, C.c_size_t(stride), n, sparse_slots, batch,
-                            C.c_double(scale), _p(pt), _stream()))
+                            C.c_double(scale), _p(pt), self._stream()))
         return pt
 
     def encode_encrypt(self, pk, values, scale, seeds, sparse_slots, batch=1, out=None):
@@ -331,22 +337,22 @@ class Context:
         s, sp = self._seed(seeds, 2 * batch)
         ct = out if out is not None else self.empty(batch, 2, self.size_Q, self.N)
         check(lib.lb_encode_encrypt(self.h, _p(pk), C.c_void_p(values.data_ptr()), dt, C.c_size_t(values.shape[-1]), values.shape[-1],
-                                    sparse_slots, batch, C.c_double(scale), sp, _p(ct), _stream()))
+                                    sparse_slots, batch, C.c_double(scale), sp, _p(ct), self._stream()))
         return ct
 
     def decode(self, size_l, pt, scale, sparse_slots):
         out = torch.empty(sparse_slots, dtype=torch.complex128, device=pt.device)
-        check(lib.lb_decode(self.h, size_l, _p(pt), C.c_double(scale), sparse_slots, C.c_void_p(out.data_ptr()), _stream()))
+        check(lib.lb_decode(self.h, size_l, _p(pt), C.c_double(scale), sparse_slots, C.c_void_p(out.data_ptr()), self._stream()))
         return out
 
     def decode_batch(self, size_l, pts, scale, sparse_slots, batch):
         out = torch.empty(batch, sparse_slots, dtype=torch.complex128, device=pts.device)
-        check(lib.lb_decode_batch(self.h, size_l, batch, _p(pts), C.c_double(scale), sparse_slots, C.c_void_p(out.data_ptr()), _stream()))
+        check(lib.lb_decode_batch(self.h, size_l, batch, _p(pts), C.c_double(scale), sparse_slots, C.c_void_p(out.data_ptr()), self._stream()))
         return out
 
     def decrypt_batch(self, size_l, cts, sk, n_polys, batch):
         pt = self.empty(batch, size_l, self.N)
-        check(lib.lb_decrypt_batch(self.h, size_l, n_polys, batch, _p(cts), _p(sk), _p(pt), _stream()))
+        check(lib.lb_decrypt_batch(self.h, size_l, n_polys, batch, _p(cts), _p(sk), _p(pt), self._stream()))
         return pt
 
     def mask_accumulate(self, size_l, client_cts, masks, n_chunks):
@@ -354,8 +360,33 @@ class Context:
         n = len(client_cts)
         ptrs = (C.c_void_p * n)(*[t.data_ptr() for t in client_cts])
         out = self.empty(n_chunks, 3, size_l, self.N)
-        check(lib.lb_mask_accumulate(self.h, size_l, n, n_chunks, ptrs, C.c_size_t(2 * size_l * self.N), _p(masks), _p(out), _stream()))
+        check(lib.lb_mask_accumulate(self.h, size_l, n, n_chunks, ptrs, C.c_size_t(2 * size_l * self.N), _p(masks), _p(out), self._stream()))
         return out
 
     def check_status(self):
-        check(lib.lb_check_status(self.h, _stream()))
+        check(lib.lb_check_status(self.h, self._stream()))
+
+
+# -- benchmark diagnostics (include/lancelot_b200_diag.h); not part of the drop-in boundary
+def launch_count():
+    """kernels this library has launched in this process"""
+    lib.lb_launch_count.restype = C.c_ulonglong
+    return int(lib.lb_launch_count())
+
+
+def kernel_timing(enable=True):
+    """start (and clear) or stop the per-kernel device timer"""
+    check(lib.lb_diag_kernel_timing(int(bool(enable))))
+
+
+def kernel_report():
+    """{kernel name: {"launches", "ms", "bytes"}} since the timer was started; synchronises and clears the record"""
+    import json
+
+    buf = C.create_string_buffer(1 << 16)
+    check(lib.lb_diag_kernel_report(buf, C.c_size_t(len(buf))))
+    out = json.loads(buf.value.decode())
+    overflow = out.pop("_overflow", False)
+    if overflow:
+        raise RuntimeError("more launches than the kernel timer records")
+    return out

@@ -18,6 +18,9 @@ struct lb_context {
 };
 
 static inline Context *C(lb_context *h) { return h ? h->c : nullptr; }
+namespace lb {
+Context *lb_context_impl(lb_context *h) { return h ? h->c : nullptr; }
+} // namespace lb
 static inline const Context *C(const lb_context *h) { return h ? h->c : nullptr; }
 static inline cudaStream_t S(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
@@ -48,8 +51,6 @@ static int level_ok(const Context *c, int size_l)
 extern "C" {
 
 const char *lb_last_error(void) { return last_error().c_str(); }
-
-unsigned long long lb_launch_count(void) { return launch_count(); }
 
 int lb_coeff_modulus_create(uint64_t n, const int *bit_sizes, int count, uint64_t *out)
 {
@@ -165,14 +166,6 @@ static int ntt_rows(lb_context *h, uint64_t *data, int n_groups, int size_l, int
     return fwd ? ntt_forward(c, job, S(stream)) : ntt_inverse(c, job, S(stream));
 }
 
-int lb_probe_butterfly_rate(lb_context *h, int mode, double *butterflies_per_second)
-{
-    int rc = bind(h);
-    if (rc) return rc;
-    REQUIRE(butterflies_per_second, "destination cannot be null");
-    return probe_butterfly_rate(C(h), mode, butterflies_per_second);
-}
-
 int lb_ntt_forward(lb_context *h, uint64_t *data, int n_groups, int size_l, int size_p, void *stream)
 {
     return ntt_rows(h, data, n_groups, size_l, size_p, true, stream);
@@ -188,7 +181,7 @@ static int binary(lb_context *h, int op, int size_l, int n_polys, const uint64_t
     int rc = bind(h);
     if (rc) return rc;
     if ((rc = level_ok(C(h), size_l))) return rc;
-    REQUIRE(n_polys >= 0 && a && out && (b || op == OP_NEG), "operand is null");
+    REQUIRE(n_polys >= 0 && a && out && (b || op == OP_NEG || op == OP_REDUCE), "operand is null");
     return poly_binary(C(h), op, size_l, (long)n_polys * size_l, a, b, out, S(stream));
 }
 
@@ -196,6 +189,7 @@ int lb_add(lb_context *h, int size_l, int n, const uint64_t *a, const uint64_t *
 int lb_sub(lb_context *h, int size_l, int n, const uint64_t *a, const uint64_t *b, uint64_t *out, void *s) { return binary(h, OP_SUB, size_l, n, a, b, out, s); }
 int lb_multiply_poly(lb_context *h, int size_l, int n, const uint64_t *a, const uint64_t *b, uint64_t *out, void *s) { return binary(h, OP_MUL, size_l, n, a, b, out, s); }
 int lb_negate(lb_context *h, int size_l, int n, const uint64_t *a, uint64_t *out, void *s) { return binary(h, OP_NEG, size_l, n, a, nullptr, out, s); }
+int lb_reduce_mod(lb_context *h, int size_l, int n, const uint64_t *a, uint64_t *out, void *s) { return binary(h, OP_REDUCE, size_l, n, a, nullptr, out, s); }
 
 int lb_sum_groups(lb_context *h, int size_l, int n_polys, int n_groups, const int *offsets, const int *indices, int n_items,
                   const uint64_t *in, uint64_t *out, void *stream)

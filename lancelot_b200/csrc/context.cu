@@ -10,9 +10,6 @@ static thread_local std::string g_error;
 
 void set_error(const std::string &msg) { g_error = msg; }
 
-static unsigned long long g_launches = 0;
-void count_launch() { ++g_launches; }
-unsigned long long launch_count() { return g_launches; }
 const std::string &last_error() { return g_error; }
 
 int cuda_fail(cudaError_t e, const char *what)
@@ -26,22 +23,32 @@ int cuda_fail(cudaError_t e, const char *what)
 // every round (as the reference's Krum driver does) then pays for cudaMalloc / cudaFree of
 // gigabytes only once per process.
 constexpr int kMaxCachedDevices = 64;
+static std::mutex g_ws_mu; // guards the two arrays below
 static void *g_ws_cache[kMaxCachedDevices];
 static size_t g_ws_cache_bytes[kMaxCachedDevices];
 
 int Context::ensure_workspace(size_t bytes)
 {
     if (bytes <= ws_bytes) return LB_OK;
-    if (device >= 0 && device < kMaxCachedDevices && g_ws_cache[device] && g_ws_cache_bytes[device] >= bytes) {
+    void *cached = nullptr;
+    size_t cached_bytes = 0;
+    if (device >= 0 && device < kMaxCachedDevices) {
+        std::lock_guard<std::mutex> lock(g_ws_mu);
+        if (g_ws_cache[device] && g_ws_cache_bytes[device] >= bytes) {
+            cached = g_ws_cache[device];
+            cached_bytes = g_ws_cache_bytes[device];
+            g_ws_cache[device] = nullptr;
+            g_ws_cache_bytes[device] = 0;
+        }
+    }
+    if (cached) {
         // work queued on the previous block (if any) must finish before it is dropped
         if (ws) {
             LB_CUDA(cudaDeviceSynchronize());
             LB_CUDA(cudaFree(ws));
         }
-        ws = g_ws_cache[device];
-        ws_bytes = g_ws_cache_bytes[device];
-        g_ws_cache[device] = nullptr;
-        g_ws_cache_bytes[device] = 0;
+        ws = cached;
+        ws_bytes = cached_bytes;
         return LB_OK;
     }
     // the old block may still be in use by work queued earlier
@@ -236,13 +243,16 @@ void context_destroy(Context *ctx)
     cudaDeviceSynchronize();
     if (ctx->ws) {
         const int d = ctx->device;
-        if (d >= 0 && d < kMaxCachedDevices && ctx->ws_bytes > g_ws_cache_bytes[d]) {
-            if (g_ws_cache[d]) cudaFree(g_ws_cache[d]);
-            g_ws_cache[d] = ctx->ws;
-            g_ws_cache_bytes[d] = ctx->ws_bytes;
-        } else {
-            cudaFree(ctx->ws);
+        void *drop = ctx->ws;
+        if (d >= 0 && d < kMaxCachedDevices) {
+            std::lock_guard<std::mutex> lock(g_ws_mu);
+            if (ctx->ws_bytes > g_ws_cache_bytes[d]) {
+                drop = g_ws_cache[d];
+                g_ws_cache[d] = ctx->ws;
+                g_ws_cache_bytes[d] = ctx->ws_bytes;
+            }
         }
+        if (drop) cudaFree(drop);
         ctx->ws = nullptr;
         ctx->ws_bytes = 0;
     }

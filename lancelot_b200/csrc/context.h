@@ -35,10 +35,9 @@ struct Context {
     // encoder tables
     double2 *d_croots = nullptr; // [2N] complex roots of unity
     uint32_t *d_rot_group = nullptr; // [N/4] powers of 5 mod 2N
-    // inverse-FFT twiddles of the encoder in the order its stages use them, for ifft_tw_logn = log2(slots):
-    // entry (n - (n >> u)) + k is the twiddle of butterfly group k at stage u (built on first use)
-    double2 *d_ifft_tw = nullptr;
-    int ifft_tw_logn = 0;
+    // inverse-FFT twiddles of the encoder in the order its stages use them, one table per log2(slots), each built
+    // on first use: entry (n - (n >> u)) + k is the twiddle of butterfly group k at stage u
+    double2 *d_ifft_tw[20] = {};
     int *d_status = nullptr;         // sticky device-side condition flags (bit 0: encoded values are too large)
     // scratch owned by the context, grown on demand between operations
     void *ws = nullptr;
@@ -49,8 +48,13 @@ struct Context {
 };
 
 void set_error(const std::string &msg);
-void count_launch();            // every kernel launch of this library is counted (lb_launch_count)
+// every kernel launch of this library goes through this (diag.cu): counted always, timed per kernel name while
+// the diagnostic timer is on
+// algorithmic_bytes: what the launch must read and write at least (each datum once, tables excluded), 0 = not stated
+void count_launch(const char *kernel_name, cudaStream_t stream, double algorithmic_bytes = 0.0);
 unsigned long long launch_count();
+struct Context;
+Context *lb_context_impl(lb_context *h); // the context behind a C-ABI handle (capi.cu)
 int cuda_fail(cudaError_t e, const char *what);
 
 #define LB_CUDA(call)                                         \
@@ -112,7 +116,7 @@ int ntt_inverse(Context *ctx, const NttJob &job, cudaStream_t stream);
 int probe_butterfly_rate(Context *ctx, int mode, double *butterflies_per_second);
 
 // element-wise kernels (poly.cu).  Rows are limbs of N residues; row r uses prime r % size_l.
-enum PolyOp { OP_ADD = 0, OP_SUB = 1, OP_MUL = 2, OP_NEG = 3 };
+enum PolyOp { OP_ADD = 0, OP_SUB = 1, OP_MUL = 2, OP_NEG = 3, OP_REDUCE = 4 };
 int poly_binary(Context *ctx, int op, int size_l, long rows, const u64 *a, const u64 *b, u64 *out, cudaStream_t stream);
 // out[3][L][N] = a[2][L][N] (x) b[2][L][N], batched over `batch` ciphertexts
 int poly_tensor(Context *ctx, int size_l, int batch, const u64 *a, const u64 *b, u64 *out, cudaStream_t stream);

@@ -25,12 +25,18 @@ struct cplx {
 
 LB_D cplx c_add(cplx a, cplx b) { return {__dadd_rn(a.x, b.x), __dadd_rn(a.y, b.y)}; }
 LB_D cplx c_sub(cplx a, cplx b) { return {__dsub_rn(a.x, b.x), __dsub_rn(a.y, b.y)}; }
-// cuCmul as the device compiler contracts it: one rounded product feeding one fma per part
-LB_D cplx c_mul(cplx a, cplx b)
+// cuCmul as the device compiler contracts it in the reference's kernels: one rounded product feeding one fused
+// multiply-add per part.  Which product of the imaginary part is the rounded one differs between the reference's two
+// inverse-FFT kernels: the multi-stage kernel that runs the first eleven stages (cahel-main/src/fft.cu:194-268,
+// SWITCH_POINT = 2048) rounds a.x * b.y, the per-stage kernel of the later stages (fft.cu:279-344) rounds a.y * b.x.
+// Plaintexts at scale 2^50, whose largest coefficients keep two or three bits below the rounding point, pin this
+// (reference-made fixtures n4096_s50, n8192_s50, n65536_a8).
+constexpr int kRefIfftFirstKernelStages = 11;
+LB_D cplx c_mul(cplx a, cplx b, const bool first_kernel_stage = false)
 {
     cplx r;
     r.x = __fma_rn(a.x, b.x, -__dmul_rn(a.y, b.y));
-    r.y = __fma_rn(a.x, b.y, __dmul_rn(a.y, b.x));
+    r.y = first_kernel_stage ? __fma_rn(a.y, b.x, __dmul_rn(a.x, b.y)) : __fma_rn(a.x, b.y, __dmul_rn(a.y, b.x));
     return r;
 }
 
@@ -161,12 +167,13 @@ LB_D void ifft_pass(cplx *sm, const EncK &a, const long msg, const bool first, c
                 // global butterfly group index of this pair
                 const unsigned k = ((c << logn_loc) >> (u + 1)) + (hi << (S - 1 - s)) + b;
                 const cplx w = ifft_twiddle(a, k, u);
+                const bool early = u < kRefIfftFirstKernelStages; // uniform over the CTA
 #pragma unroll
                 for (int i = 0; i < dist; ++i) {
                     cplx &x0 = v[b * 2 * dist + i], &x1 = v[b * 2 * dist + i + dist];
                     const cplx s0 = c_add(x0, x1), s1 = c_sub(x0, x1);
                     x0 = s0;
-                    x1 = c_mul(s1, w);
+                    x1 = c_mul(s1, w, early);
                 }
             }
         }
@@ -310,7 +317,7 @@ static int launch_encode(const EncK &k, int batch, size_t smem, cudaStream_t str
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    count_launch();
+    count_launch("encode_ifft_kernel", stream);
     LB_CUDA(cudaLaunchKernelEx(&cfg, kern, k));
     return LB_OK;
 }
@@ -353,17 +360,19 @@ int encode(Context *ctx, int size_l, const void *values, int dtype, long value_s
     k.mc = ctx->d_mc;
     k.logN = hp.logN;
     k.logn = logn;
-    if (ctx->ifft_tw_logn != logn) {
+    if (!ctx->d_ifft_tw[logn]) {
+        // one table per slot count, built once and kept with the context; the build is synchronous so that a
+        // later encode on another stream never reads a table still being filled
         double2 *tbl = nullptr;
         LB_CUDA(cudaMalloc((void **)&tbl, sizeof(double2) << logn));
         ctx->owned.push_back(tbl);
-        count_launch();
+        count_launch("ifft_twiddle_table_kernel", stream);
         ifft_twiddle_table_kernel<<<(unsigned)(((1u << logn) + 255) / 256), 256, 0, stream>>>(k, tbl);
         LB_CUDA(cudaGetLastError());
-        ctx->d_ifft_tw = tbl;
-        ctx->ifft_tw_logn = logn;
+        LB_CUDA(cudaStreamSynchronize(stream));
+        ctx->d_ifft_tw[logn] = tbl;
     }
-    k.tw = ctx->d_ifft_tw;
+    k.tw = ctx->d_ifft_tw[logn];
     k.size_l = size_l;
     k.fix = scale / (double)sparse_slots;
     k.too_large = ldexp(1.0, total_bits - 2);
@@ -394,7 +403,7 @@ int encode(Context *ctx, int size_l, const void *values, int dtype, long value_s
 
 // ---- decode -----------------------------------------------------------------------------
 
-constexpr int kMaxComposeLimbs = 8;
+constexpr int kMaxComposeLimbs = 32; // the constants travel as a kernel argument (17 KiB at 32 limbs, below the 32 KiB limit)
 
 struct ComposeConst {
     u64 radix[kMaxComposeLimbs][kMaxComposeLimbs + 1]; // q_0 ... q_{r-1} as a multi-word integer
@@ -504,7 +513,7 @@ size_t decode_workspace_bytes(const Context *ctx, int size_l, int batch)
 int decode(Context *ctx, int size_l, int batch, const u64 *pt, double scale, int sparse_slots, double *out_complex, cudaStream_t stream)
 {
     const HostParams &hp = ctx->hp;
-    if (size_l > kMaxComposeLimbs) { set_error("decode supports at most 8 limbs"); return LB_ERR_INVALID_ARG; }
+    if (size_l > kMaxComposeLimbs) { set_error("decode supports at most 32 limbs"); return LB_ERR_INVALID_ARG; }
     int logn = 0;
     while ((1 << logn) < sparse_slots) ++logn;
     if ((1 << logn) != sparse_slots || sparse_slots < 2 || (u64)sparse_slots > hp.N / 2) {
@@ -548,16 +557,16 @@ int decode(Context *ctx, int size_l, int batch, const u64 *pt, double scale, int
         cc.Qhalf[i] = (Q[i] >> 1) | (i + 1 < W ? Q[i + 1] << 63 : 0);
     }
     const unsigned n = (unsigned)sparse_slots;
-    count_launch();
+    count_launch("compose_kernel", stream);
     compose_kernel<<<dim3((2 * n + 255) / 256, batch), 256, 0, stream>>>(buf, coef, ctx->d_mc, cc, hp.logN, logn, size_l, 1.0 / scale);
     LB_CUDA(cudaGetLastError());
     for (int iter = 0; iter < logn; ++iter) {
         const int u = logn - iter - 1;
-        count_launch();
+        count_launch("fft_stage_kernel", stream);
         fft_stage_kernel<<<dim3((n / 2 + 255) / 256, batch), 256, 0, stream>>>(buf, ctx->d_croots, ctx->d_rot_group, hp.logN, logn, u);
     }
     LB_CUDA(cudaGetLastError());
-    count_launch();
+    count_launch("bitrev_out_kernel", stream);
     bitrev_out_kernel<<<dim3((n + 255) / 256, batch), 256, 0, stream>>>(reinterpret_cast<cplx *>(out_complex), buf, logn);
     LB_CUDA(cudaGetLastError());
     return LB_OK;

@@ -208,7 +208,10 @@ static int inner_product_steps(Context *ctx, int L, int batch, const u64 *digits
     long gx = ((long)hp.N / per_thread + kKsThreads - 1) / kKsThreads;
     if (gx < 1) gx = 1;
     const dim3 grid((unsigned)gx, (unsigned)LP, (unsigned)(batch < 65535 ? batch : 65535));
-    count_launch();
+    // digits (beta rows per output row, the own limbs included), both key polynomials per step and digit, two outputs
+    count_launch("inner_product_kernel", stream,
+                 8.0 * hp.N * LP * batch * (double)hp.level[L].beta + 8.0 * hp.N * LP * 2.0 * hp.level[L].beta * args.n_steps +
+                     8.0 * hp.N * LP * 2.0 * batch);
     if (gather)
         inner_product_kernel<true><<<grid, kKsThreads, 0, stream>>>(digits, own, own_stride, cx, ctx->d_mc, args, hp.logN, L, LP, hp.size_Q,
                                                                    hp.size_QP, hp.size_P, hp.level[L].beta, batch);
@@ -466,7 +469,7 @@ int hoisting(Context *ctx, int L, int batch, u64 *ct, int n_steps, const int *el
         long blocks = (total + kKsThreads - 1) / kKsThreads;
         const long cap = (long)ctx->sm_count * 16;
         if (blocks > cap) blocks = cap;
-        count_launch();
+        count_launch("galois_sum_kernel", stream);
         galois_sum_kernel<<<(int)blocks, kKsThreads, 0, stream>>>(ct_b, 2L * L, w.tmp, ctx->d_mc, args, hp.logN, L, total);
         LB_CUDA(cudaGetLastError());
         if ((rc = moddown_into(ctx, L, nb, 2, w.cx, w.pc, ct_b, Placement{2L * L, L}, w.tmp, Placement{L, L}, 1, stream))) return rc;

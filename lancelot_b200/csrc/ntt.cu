@@ -21,6 +21,7 @@
 #include <cooperative_groups.h>
 
 #include "context.h"
+#include "ntt_butterfly.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -77,48 +78,6 @@ struct NttK {
 
 // one spare word per 16 keeps the stride-8 and stride-1 passes off the same banks
 LB_D int sidx(int i) { return i + (i >> 4); }
-
-// Butterfly variants, chosen per prime:
-//   integer, strict: Shoup product on the integer multiplier, values kept in [0, 4q);
-//   integer, lazy:   the prime is below 2^58, so x may grow by 2q per stage over all seventeen
-//                    possible stages (bound 35q < 2^64) and the per-butterfly conditional
-//                    subtraction is dropped; the closing pass reduces once;
-//   FP64, strict / lazy: primes below 2^50 / 2^46, quotient estimated on the FP64 pipe
-//                    (fp_mul_signed), which takes the 64 x 64 -> 128 bit product off the
-//                    integer multiplier, the pipe that bounds these kernels.
-// Every variant leaves the same canonical residues in memory.
-enum { kIntStrict = 0, kIntLazy = 1, kFpStrict = 2, kFpLazy = 3 };
-
-LB_D int butterfly_mode(const u64 q)
-{
-    if (q < kFpLazyLimit) return kFpLazy;
-    if (q < kFpPrimeLimit) return kFpStrict;
-    return (q >> 58) == 0 ? kIntLazy : kIntStrict;
-}
-
-template <int MODE>
-LB_D void fwd_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
-{
-    if (MODE == kIntStrict || MODE == kFpStrict) x = csub(x, q2);
-    if (MODE == kFpStrict || MODE == kFpLazy) {
-        const u64 r = fp_mul_signed(y, w.x, w.y, q), xq = x + q; // r in (-q, q)
-        y = xq - r;
-        x = xq + r;
-    } else {
-        const u64 t = shoup_lazy(y, w.x, w.y, q);
-        y = x + q2 - t;
-        x = x + t;
-    }
-}
-
-template <bool FP>
-LB_D void inv_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
-{
-    const u64 s = csub(x + y, q2);
-    const u64 d = x + q2 - y; // below 4q
-    x = s;
-    y = FP ? fp_mul_signed(d, w.x, w.y, q) + q : shoup_lazy(d, w.x, w.y, q);
-}
 
 // S consecutive forward stages on 2^S register values; stage u uses twiddle (t0 << u) + block
 template <int S, int MODE>
@@ -929,14 +888,14 @@ static PassPlan plan_passes(int logn_loc, bool forward)
 #endif
 
 template <int LOGC>
-static int launch(bool forward, bool fixed, const NttK &k, int rows, size_t smem, cudaStream_t stream)
+static int launch(bool forward, bool fixed, const NttK &k, int rows, size_t smem, cudaStream_t stream, double bytes)
 {
     auto kern = forward ? ntt_fwd_kernel<LOGC> : ntt_inv_kernel<LOGC>;
     int which = 0;
+    const bool plain = k.bconv_n == 0 && k.digit_alpha == 0 && !k.presub && !k.esmall && !k.aux;
 #if LB_NTT_HAS_FIXED
     if constexpr (LOGC <= 3) {
         if (fixed) {
-            const bool plain = k.bconv_n == 0 && k.digit_alpha == 0 && !k.presub && !k.esmall && !k.aux;
             kern = !forward ? ntt_inv_fixed_kernel<LOGC> : plain ? ntt_fwd_fixed_kernel<LOGC, true> : ntt_fwd_fixed_kernel<LOGC, false>;
             which = plain ? 2 : 1;
         }
@@ -965,7 +924,7 @@ static int launch(bool forward, bool fixed, const NttK &k, int rows, size_t smem
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    count_launch();
+    count_launch(!forward ? "ntt_inv_kernel" : plain ? "ntt_fwd_kernel(plain input)" : "ntt_fwd_kernel(fused input)", stream, bytes);
     LB_CUDA(cudaLaunchKernelEx(&cfg, kern, k));
     return LB_OK;
 }
@@ -1025,98 +984,28 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     const size_t n_loc = size_t(1) << logn_loc;
     const size_t smem = (n_loc + (n_loc >> 4) + 2) * sizeof(u64);
     const bool fixed = LB_NTT_FIXED && LB_NTT_HAS_FIXED && logn_loc == 13;
+    // algorithmic bytes of this launch (diagnostics): rows written once; plain rows read once; fused loaders read the
+    // group's source rows once per group, plus the rows the epilogue and the prologue fold in
+    const double limb = 8.0 * (double)hp.N;
+    const int live = job.per_group - (job.skip_hi > job.skip_lo ? job.skip_hi - job.skip_lo : 0);
+    const double out_rows = (double)job.n_groups * live;
+    double bytes = out_rows * limb;
+    if (job.digit_alpha > 0) bytes += (double)job.n_groups * job.digit_alpha * limb;
+    else if (job.bconv_n > 0) bytes += (double)job.n_groups * job.bconv_n * limb;
+    else bytes += out_rows * limb;
+    const double outer = (double)job.n_groups / k.split;
+    if (job.aux) bytes += out_rows * limb;
+    if (job.add) bytes += outer * (job.add_inner < k.split ? job.add_inner : k.split) * live * limb;
+    if (job.presub) bytes += outer * (k.presub_inner < k.split ? k.presub_inner : k.split) * live * limb;
+    if (job.esmall) bytes += outer * (double)hp.N;
     switch (logc) {
-    case 0: return launch<0>(forward, fixed, k, rows, smem, stream);
-    case 1: return launch<1>(forward, fixed, k, rows, smem, stream);
-    case 2: return launch<2>(forward, fixed, k, rows, smem, stream);
-    case 3: return launch<3>(forward, fixed, k, rows, smem, stream);
-    case 4: return launch<4>(forward, fixed, k, rows, smem, stream);
+    case 0: return launch<0>(forward, fixed, k, rows, smem, stream, bytes);
+    case 1: return launch<1>(forward, fixed, k, rows, smem, stream, bytes);
+    case 2: return launch<2>(forward, fixed, k, rows, smem, stream, bytes);
+    case 3: return launch<3>(forward, fixed, k, rows, smem, stream, bytes);
+    case 4: return launch<4>(forward, fixed, k, rows, smem, stream, bytes);
     default: set_error("poly_modulus_degree above 65536 is not supported"); return LB_ERR_INVALID_ARG;
     }
-}
-
-// ---- arithmetic ceiling probe -------------------------------------------------------------------
-// The same forward butterfly as the transform kernels, on registers only (no shared or global
-// memory traffic inside the loop), at the transform kernels' occupancy.  Its rate is the ceiling
-// the modular arithmetic of that butterfly variant sets for any NTT schedule on this GPU; one
-// limb of N points needs (N/2) log2 N butterflies for 16 N bytes of traffic.
-template <int MODE>
-__global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) butterfly_probe_kernel(u64 *out, const u64 q, const u64 w0, const u64 ws0,
-                                                                                       const int iters)
-{
-    u64 v[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = (u64)threadIdx.x * 8 + i + blockIdx.x;
-    const u64 q2 = q << 1;
-    for (int it = 0; it < iters; ++it) {
-#pragma unroll
-        for (int s = 0; s < 3; ++s) {
-            const int half = 4 >> s;
-#pragma unroll
-            for (int b = 0; b < (1 << s); ++b) {
-                const ulonglong2 w = make_ulonglong2(w0 + threadIdx.x + b, ws0 + threadIdx.x + s);
-#pragma unroll
-                for (int i = 0; i < half; ++i) fwd_bf<MODE>(v[b * 2 * half + i], v[b * 2 * half + i + half], w, q, q2);
-            }
-        }
-        // keep the lazy ranges bounded, as the closing reduction does
-        if (MODE == kIntLazy) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] &= 0x03FFFFFFFFFFFFFFull;
-        }
-        if (MODE == kFpLazy) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] &= 0x0003FFFFFFFFFFFFull;
-        }
-    }
-    u64 acc = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc ^= v[i];
-    out[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = acc;
-}
-
-// mode: 0 integer strict, 1 integer lazy, 2 FP64-assisted strict, 3 FP64-assisted lazy,
-// -1 the variant the context's first prime takes.
-int probe_butterfly_rate(Context *ctx, int mode, double *butterflies_per_second)
-{
-    if (mode < 0) {
-        const u64 q0 = ctx->hp.q[0];
-        mode = q0 < kFpLazyLimit ? kFpLazy : q0 < kFpPrimeLimit ? kFpStrict : (q0 >> 58) == 0 ? kIntLazy : kIntStrict;
-    }
-    if (mode > kFpLazy) {
-        set_error("butterfly variant must be 0..3 or -1");
-        return LB_ERR_INVALID_ARG;
-    }
-    const int blocks = ctx->sm_count * LB_NTT_MINBLOCKS, iters = 2000;
-    int rc = ctx->ensure_workspace((size_t)blocks * kNttThreads * sizeof(u64));
-    if (rc) return rc;
-    u64 *out = reinterpret_cast<u64 *>(ctx->ws);
-    // any odd modulus of the variant's size gives the variant's instruction stream
-    static const u64 size_of_mode[4] = {(u64(1) << 60) - 93, (u64(1) << 50) - 27, (u64(1) << 49) - 69, (u64(1) << 40) - 87};
-    const u64 q = size_of_mode[mode], w = q / 3, ws = mode >= kFpStrict ? h_fp_quot(w, q) : h_shoup(w, q);
-    cudaEvent_t e0, e1;
-    LB_CUDA(cudaEventCreate(&e0));
-    LB_CUDA(cudaEventCreate(&e1));
-    float best = 1e30f;
-    for (int rep = 0; rep < 4; ++rep) {
-        LB_CUDA(cudaEventRecord(e0, 0));
-        count_launch();
-        switch (mode) {
-        case kIntStrict: butterfly_probe_kernel<kIntStrict><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
-        case kIntLazy: butterfly_probe_kernel<kIntLazy><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
-        case kFpStrict: butterfly_probe_kernel<kFpStrict><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
-        default: butterfly_probe_kernel<kFpLazy><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
-        }
-        LB_CUDA(cudaEventRecord(e1, 0));
-        LB_CUDA(cudaEventSynchronize(e1));
-        float ms = 0;
-        LB_CUDA(cudaEventElapsedTime(&ms, e0, e1));
-        if (rep > 0 && ms < best) best = ms;
-    }
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
-    *butterflies_per_second = (double)blocks * kNttThreads * iters * 12.0 / (best * 1e-3);
-    return LB_OK;
 }
 
 int ntt_forward(Context *ctx, const NttJob &job, cudaStream_t stream) { return run(ctx, job, true, stream); }

@@ -134,7 +134,9 @@ bool HostParams::init(int logN_, const std::vector<u64> &moduli, int size_P_, co
     if (size_P < 0 || size_Q < 1) { error = "special_modulus_size is invalid"; return false; }
     q = moduli;
     for (int i = 0; i < size_QP; ++i) {
-        if (q[i] >> 61) { error = "coeff_modulus primes must be below 2^61"; return false; }
+        // 60 bits at most, as CoeffModulus::Create hands them out (cahel-main/src/modulus.cu:93-125); the lazy ranges
+        // of the kernels (differences below 2^61, sums of 63 products in 128 bits, eight residues in 64) rely on it
+        if (q[i] >> 60) { error = "coeff_modulus primes must be below 2^60"; return false; }
         for (int j = 0; j < i; ++j)
             if (q[i] == q[j]) { error = "coeff_modulus primes must be distinct"; return false; }
     }

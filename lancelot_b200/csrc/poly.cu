@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(kPolyThreads) binary_kernel(const ulonglong2 *
         const ModConst m = mc[row % size_l];
         const ulonglong2 x = a[i];
         ulonglong2 y = make_ulonglong2(0, 0), r;
-        if (OP != OP_NEG) y = b[i];
+        if (OP != OP_NEG && OP != OP_REDUCE) y = b[i];
         if (OP == OP_ADD) {
             r.x = add_mod(x.x, y.x, m.q);
             r.y = add_mod(x.y, y.y, m.q);
@@ -40,6 +40,10 @@ __global__ void __launch_bounds__(kPolyThreads) binary_kernel(const ulonglong2 *
         } else if (OP == OP_MUL) {
             r.x = mul_mod(x.x, y.x, m.q, m.r0, m.r1);
             r.y = mul_mod(x.y, y.y, m.q, m.r0, m.r1);
+        } else if (OP == OP_REDUCE) {
+            // any 64-bit word, e.g. a plain sum of residues, back to its canonical residue
+            r.x = barrett128(u128d{x.x, 0}, m.q, m.r0, m.r1);
+            r.y = barrett128(u128d{x.y, 0}, m.q, m.r0, m.r1);
         } else {
             r.x = x.x ? m.q - x.x : 0;
             r.y = x.y ? m.q - x.y : 0;
@@ -56,12 +60,13 @@ int poly_binary(Context *ctx, int op, int size_l, long rows, const u64 *a, const
     const int grid = grid_for(ctx, total, kPolyThreads);
     const ulonglong2 *pa = reinterpret_cast<const ulonglong2 *>(a), *pb = reinterpret_cast<const ulonglong2 *>(b);
     ulonglong2 *po = reinterpret_cast<ulonglong2 *>(out);
-    count_launch();
+    count_launch("binary_kernel", stream);
     switch (op) {
     case OP_ADD: binary_kernel<OP_ADD><<<grid, kPolyThreads, 0, stream>>>(pa, pb, po, ctx->d_mc, size_l, log_half_n, total); break;
     case OP_SUB: binary_kernel<OP_SUB><<<grid, kPolyThreads, 0, stream>>>(pa, pb, po, ctx->d_mc, size_l, log_half_n, total); break;
     case OP_MUL: binary_kernel<OP_MUL><<<grid, kPolyThreads, 0, stream>>>(pa, pb, po, ctx->d_mc, size_l, log_half_n, total); break;
     case OP_NEG: binary_kernel<OP_NEG><<<grid, kPolyThreads, 0, stream>>>(pa, pb, po, ctx->d_mc, size_l, log_half_n, total); break;
+    case OP_REDUCE: binary_kernel<OP_REDUCE><<<grid, kPolyThreads, 0, stream>>>(pa, pb, po, ctx->d_mc, size_l, log_half_n, total); break;
     default: set_error("unknown element-wise operation"); return LB_ERR_INVALID_ARG;
     }
     LB_CUDA(cudaGetLastError());
@@ -107,7 +112,7 @@ int poly_tensor(Context *ctx, int size_l, int batch, const u64 *a, const u64 *b,
     const int log_half_n = ctx->hp.logN - 1;
     const long per_ct = (long)size_l << log_half_n;
     const long total = per_ct * batch;
-    count_launch();
+    count_launch("tensor_kernel", stream);
     tensor_kernel<<<grid_for(ctx, total, kPolyThreads), kPolyThreads, 0, stream>>>(
         reinterpret_cast<const ulonglong2 *>(a), reinterpret_cast<const ulonglong2 *>(b), reinterpret_cast<ulonglong2 *>(out),
         ctx->d_mc, size_l, log_half_n, per_ct, total);
@@ -162,7 +167,7 @@ int poly_sum_groups(Context *ctx, int size_l, long n_rows, int n_groups, const i
     const long item = (n_rows << ctx->hp.logN) / 2;
     long gx = (item + kPolyThreads - 1) / kPolyThreads;
     if (gx > 4096) gx = 4096;
-    count_launch();
+    count_launch("sum_groups_kernel", stream);
     sum_groups_kernel<<<dim3((unsigned)gx, (unsigned)n_groups), kPolyThreads, 0, stream>>>(
         reinterpret_cast<const ulonglong2 *>(in), reinterpret_cast<ulonglong2 *>(out), d, d + n_groups + 1, ctx->d_mc, size_l,
         ctx->hp.logN - 1, item);
@@ -177,7 +182,7 @@ int poly_galois(Context *ctx, int elt_idx, long rows, const u64 *src, u64 *dst, 
         return LB_ERR_LOGIC;
     }
     const long total = rows << ctx->hp.logN;
-    count_launch();
+    count_launch("galois_kernel", stream);
     galois_kernel<<<grid_for(ctx, total, kPolyThreads), kPolyThreads, 0, stream>>>(
         src, dst, ctx->d_perm + ((size_t)elt_idx << ctx->hp.logN), ctx->hp.logN, total);
     LB_CUDA(cudaGetLastError());
@@ -278,14 +283,14 @@ int krum_accumulate(Context *ctx, int size_l, int n_chunks, const u64 *a, const 
         if (rc) return rc;
         dst = reinterpret_cast<ulonglong2 *>(ctx->ws);
     }
-    count_launch();
+    count_launch("krum_accumulate_kernel", stream);
     krum_accumulate_kernel<<<dim3((unsigned)blocks, (unsigned)slices), kKrumThreads, 0, stream>>>(
         reinterpret_cast<const ulonglong2 *>(a), reinterpret_cast<const ulonglong2 *>(b), dst, ctx->d_mc, log_half_n, per_poly,
         chunk_stride_a / 2, chunk_stride_b / 2, n_chunks, accumulate);
     LB_CUDA(cudaGetLastError());
     if (slices > 1) {
         const long total = 3 * per_poly;
-        count_launch();
+        count_launch("krum_reduce_kernel", stream);
         krum_reduce_kernel<<<grid_for(ctx, total, kPolyThreads), kPolyThreads, 0, stream>>>(
             dst, reinterpret_cast<ulonglong2 *>(acc), ctx->d_mc, log_half_n, size_l, total, (int)slices, accumulate);
         LB_CUDA(cudaGetLastError());
@@ -369,7 +374,7 @@ static void launch_tile(Context *ctx, const KrumTileArgs &args, int size_l, int 
 {
     const long per_poly = (long)size_l << ctx->hp.logN;
     const long blocks = (per_poly + kTileThreads - 1) / kTileThreads;
-    count_launch();
+    count_launch("krum_tile_kernel", stream, 8.0 * per_poly * ((double)(NA + NB) * 2 * n_chunks + 3.0 * (NB ? NA * NB : NA * (NA - 1) / 2)));
     krum_tile_kernel<NA, NB><<<(unsigned)blocks, kTileThreads, 0, stream>>>(args, ctx->d_mc, ctx->hp.logN, per_poly, chunk_stride, n_chunks);
 }
 
@@ -466,7 +471,7 @@ int mask_accumulate(Context *ctx, int size_l, int n_clients, int n_chunks, const
     const int log_half_n = ctx->hp.logN - 1;
     const long per_poly = (long)size_l << log_half_n;
     long blocks = (per_poly + kKrumThreads - 1) / kKrumThreads;
-    count_launch();
+    count_launch("mask_accumulate_kernel", stream);
     mask_accumulate_kernel<<<dim3((unsigned)blocks, (unsigned)n_chunks), kKrumThreads, 0, stream>>>(
         args, reinterpret_cast<const ulonglong2 *>(masks), reinterpret_cast<ulonglong2 *>(out), ctx->d_mc, log_half_n, per_poly,
         chunk_stride / 2);
@@ -507,7 +512,7 @@ int poly_decrypt(Context *ctx, int size_l, int n_polys, int batch, const u64 *ct
 {
     const long per_poly = (long)size_l << ctx->hp.logN;
     const long total = per_poly * batch;
-    count_launch();
+    count_launch("decrypt_kernel", stream);
     decrypt_kernel<<<grid_for(ctx, total, kPolyThreads), kPolyThreads, 0, stream>>>(ct, sk, pt, ctx->d_mc, ctx->hp.logN, n_polys,
                                                                                     per_poly, total);
     LB_CUDA(cudaGetLastError());

@@ -128,7 +128,7 @@ int sample_small(Context *ctx, int kind, const uint32_t *d_seeds, int seed_strid
 {
     const long total = (long)batch << ctx->hp.logN;
     if (total == 0) return LB_OK;
-    count_launch();
+    count_launch("sample_small_kernel", stream, 8.0 * total * (size_l + size_p));
     sample_small_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(out, d_seeds, seed_stride, ctx->d_mc, kind, ctx->hp.logN, size_l, size_p,
                                                                           ctx->hp.size_Q, total);
     LB_CUDA(cudaGetLastError());
@@ -139,7 +139,7 @@ int sample_uniform(Context *ctx, const uint32_t *d_seeds, int seed_stride, int b
 {
     const long total = ((long)batch * (size_l + size_p) << ctx->hp.logN) >> 3;
     if (total == 0) return LB_OK;
-    count_launch();
+    count_launch("sample_uniform_kernel", stream);
     sample_uniform_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(out, d_seeds, seed_stride, ctx->d_mc, ctx->hp.logN, size_l, size_p,
                                                                             ctx->hp.size_Q, total);
     LB_CUDA(cudaGetLastError());
@@ -193,7 +193,7 @@ int gen_public_key(Context *ctx, const u64 *sk, const uint32_t *d_seed_e, const 
     j.size_l = hp.size_Q;
     if ((rc = ntt_forward(ctx, j, stream))) return rc;
     if ((rc = sample_uniform(ctx, d_seed_a, 16, 1, hp.size_Q, hp.size_P, pk + poly, stream))) return rc;
-    count_launch();
+    count_launch("pk_combine_kernel", stream);
     pk_combine_kernel<<<grid_for(ctx, poly), kSampThreads, 0, stream>>>(pk, pk + poly, sk, scratch, ctx->d_mc, hp.logN, poly);
     LB_CUDA(cudaGetLastError());
     return LB_OK;
@@ -209,7 +209,7 @@ int gen_switch_key(Context *ctx, const u64 *sk, const u64 *skp, const uint32_t *
         if (rc) return rc;
     }
     const long total = (long)hp.size_Q << hp.logN;
-    count_launch();
+    count_launch("ksk_add_kernel", stream);
     ksk_add_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(out, skp, ctx->d_p_mod_q, ctx->d_p_mod_q_s, ctx->d_mc, hp.logN,
                                                                      hp.size_P, 2 * poly, total);
     LB_CUDA(cudaGetLastError());
@@ -285,7 +285,7 @@ int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, int pt_is_coe
     const long total = batch * poly;
     if (fold_e) {
         const long n_small = (long)batch << hp.logN;
-        count_launch();
+        count_launch("sample_small_i8_kernel", stream, (double)n_small);
         sample_small_i8_kernel<<<grid_for(ctx, n_small), kSampThreads, 0, stream>>>(reinterpret_cast<signed char *>(e), seeds + 16, 32, 1,
                                                                                    hp.logN, n_small);
         LB_CUDA(cudaGetLastError());
@@ -296,8 +296,8 @@ int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, int pt_is_coe
         j.per_group = QP;
         j.size_l = Q;
         if ((rc = ntt_forward(ctx, j, stream))) return rc;
-        count_launch();
         const long half_poly = poly / 2;
+        count_launch("encrypt_product_kernel", stream, 8.0 * poly * (3.0 * batch + 2.0)); // u read, two products written, pk once
         const unsigned gx = (unsigned)((half_poly + kSampThreads - 1) / kSampThreads);
         encrypt_product_kernel<<<dim3(gx, (unsigned)(batch < 65535 ? batch : 65535)), kSampThreads, 0, stream>>>(
             reinterpret_cast<ulonglong2 *>(cx), reinterpret_cast<const ulonglong2 *>(pk), reinterpret_cast<const ulonglong2 *>(u), ctx->d_mc,
@@ -312,7 +312,7 @@ int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, int pt_is_coe
         j.per_group = QP;
         j.size_l = Q;
         if ((rc = ntt_forward(ctx, j, stream))) return rc;
-        count_launch();
+        count_launch("encrypt_combine_kernel", stream);
         encrypt_combine_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(cx, pk, u, e, ctx->d_mc, hp.logN, poly, total);
         LB_CUDA(cudaGetLastError());
     }

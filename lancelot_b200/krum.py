@@ -352,7 +352,10 @@ class EncryptedKrum:
         self.N = 2 * self.slots
         self.scale = 2.0 ** 40
         self.encrypt_batch = encrypt_batch
+        # seed: None = every key and ciphertext seed comes from os.urandom; an integer makes keys and
+        # ciphertexts reproducible (tests, benchmarks) and must not be used with real data
         self._rng = np.random.default_rng(seed) if seed is not None else None
+        self._test_seed = int(seed) if seed is not None else 0
         steps = [i for i in range(1, 16) if i < self.slots] + [2 ** i for i in range(4, log_slots)]
         self.first_steps = [i for i in range(1, 16) if i < self.slots]
         self.pow_steps = [2 ** i for i in range(4, log_slots)]
@@ -391,13 +394,19 @@ class EncryptedKrum:
     def n_chunks(self, dim):
         return (dim + self.slots - 1) // self.slots
 
-    def client_seeds(self, client, n_chunks, round_seed=0):
-        """Deterministic per-(round, client, chunk) seeds: every rank derives the same ciphertexts."""
-        rng = np.random.default_rng([int(round_seed), int(client), 0x4C42])
+    def client_seeds(self, client, n_chunks, first_chunk=0):
+        """128 seed bytes per ciphertext (ternary u, then the error polynomials).  By default they come from
+        the operating system, as the reference draws them for every encryption (cahel-main/include/prng.cuh:12-23):
+        whoever can predict them can strip the mask u * pk + e off the ciphertext without the secret key.
+        Only an instance built with ``seed=...`` (tests and reproducible benchmarks) derives them from that
+        seed, the client index and the chunk range; such an instance must never encrypt real updates."""
+        if self._rng is None:
+            return np.frombuffer(os.urandom(128 * n_chunks), dtype=np.uint8)
+        rng = np.random.default_rng([self._test_seed, int(client), int(first_chunk), 0x4C42])
         return rng.integers(0, 256, 128 * n_chunks, dtype=np.uint8)
 
-    def encrypt_client(self, update, client=0, round_seed=0, out=None):
-        """update: 1-D float32/float64 tensor (CUDA or CPU) -> ciphertexts [chunks][2][3][N]."""
+    def _as_chunks(self, update):
+        """1-D float tensor (any device) -> zero-padded [chunks][slots] on this context's device"""
         dev = "cuda:%d" % self.lb.device
         v = update.to(dev) if isinstance(update, torch.Tensor) else torch.from_numpy(np.asarray(update)).to(dev)
         if v.dtype not in (torch.float32, torch.float64):
@@ -407,14 +416,23 @@ class EncryptedKrum:
         pad = chunks * self.slots - dim
         if pad:
             v = torch.cat([v.reshape(-1), torch.zeros(pad, dtype=v.dtype, device=dev)])
-        v = v.reshape(chunks, self.slots).contiguous()
-        seeds = self.client_seeds(client, chunks, round_seed)
-        cts = self.lb.empty(chunks, 2, 3, self.N) if out is None else out
-        for c0 in range(0, chunks, self.encrypt_batch):
-            nb = min(self.encrypt_batch, chunks - c0)
-            self.lb.encode_encrypt(self.pk.data, v[c0:c0 + nb], self.scale, seeds[128 * c0:128 * (c0 + nb)], self.slots, nb,
+        return v.reshape(chunks, self.slots).contiguous()
+
+    def encrypt_chunks(self, values, seeds, out=None):
+        """values [k][slots] on the device, seeds 128 bytes per row -> ciphertexts [k][2][3][N] (fused encode + encrypt,
+        at most ``encrypt_batch`` per launch group)"""
+        k = values.shape[0]
+        cts = self.lb.empty(k, 2, 3, self.N) if out is None else out
+        for c0 in range(0, k, self.encrypt_batch):
+            nb = min(self.encrypt_batch, k - c0)
+            self.lb.encode_encrypt(self.pk.data, values[c0:c0 + nb], self.scale, seeds[128 * c0:128 * (c0 + nb)], self.slots, nb,
                                    out=cts[c0:c0 + nb])
         return cts
+
+    def encrypt_client(self, update, client=0, out=None):
+        """update: 1-D float32/float64 tensor (CUDA or CPU) -> ciphertexts [chunks][2][3][N]."""
+        v = self._as_chunks(update)
+        return self.encrypt_chunks(v, self.client_seeds(client, v.shape[0]), out=out)
 
     def staged(self, updates, clients):
         """Yields (client, update on the device) for the given clients.  Updates that live in host
@@ -448,60 +466,84 @@ class EncryptedKrum:
             yield c, bufs[k % 2]
             free[k % 2].record(main)
 
-    def encrypt_and_share(self, updates, rank, world_size, group, round_seed, needed, mark=lambda name: None):
-        """Client c is encrypted by rank c % world_size; one all_gather per slice of world_size clients
-        hands every rank every ciphertext.  Only the clients in ``needed`` are kept."""
-        import torch.distributed as dist
+    def encrypt_slices(self, updates, c_lo, c_hi):
+        """Encodes and encrypts chunks [c_lo, c_hi) of EVERY client: updates [n_clients][dim] (CUDA, pinned or pageable
+        host) -> ciphertexts [n_clients][c_hi - c_lo][2][3][N].  Several clients' slices share one fused encode + encrypt
+        call so that a launch fills the GPU in whole waves even when a rank only holds a few dozen chunks per client;
+        rows are copied into a zero-padded staging buffer (on a side stream, one group ahead, when they come from
+        host memory)."""
+        n_clients, dim = updates.shape
+        k = c_hi - c_lo
+        e_lo, e_hi = c_lo * self.slots, min(c_hi * self.slots, dim)
+        per_call = max(1, self.encrypt_batch // max(k, 1))
+        dev = torch.device("cuda", self.lb.device)
+        main = torch.cuda.current_stream(dev)
+        cts = self.lb.empty(n_clients, k, 2, 3, self.N)
+        if k == 0:
+            return cts
+        groups = [list(range(g, min(g + per_call, n_clients))) for g in range(0, n_clients, per_call)]
+        dtype = updates.dtype if updates.dtype in (torch.float32, torch.float64) else torch.float64
+        n_buf = 2 if len(groups) > 1 else 1
+        bufs = [torch.zeros(per_call, k * self.slots, dtype=dtype, device=dev) for _ in range(n_buf)]
+        side = not updates.is_cuda
+        copy = _copy_stream(dev) if side else main
+        ready = [torch.cuda.Event() for _ in range(n_buf)]
+        free = [torch.cuda.Event() for _ in range(n_buf)]
+        for e in free:
+            e.record(main)
 
-        n_clients, dim = updates.shape[0], updates.shape[1]
-        chunks = self.n_chunks(dim)
-        # two send buffers: the gather of one slice runs (on NCCL's stream) while the next slice is encrypted
-        mine = [self.lb.empty(chunks, 2, 3, self.N) for _ in range(2)]
-        cts = {}
-        feed = self.staged(updates, list(range(rank, n_clients, world_size)))
-        pending = None
+        def start(i):
+            b = i % n_buf
+            with torch.cuda.stream(copy):
+                if side:
+                    copy.wait_event(free[b])
+                for row, c in enumerate(groups[i]):
+                    # one contiguous copy per client: a strided host tensor would go through a pageable temporary
+                    bufs[b][row, : e_hi - e_lo].copy_(updates[c, e_lo:e_hi], non_blocking=True)
+                if side:
+                    ready[b].record(copy)
 
-        def collect(p):
-            work, recv, base = p
-            work.wait()
-            for r in range(world_size):
-                if base + r < n_clients and (base + r) in needed:
-                    cts[base + r] = recv[r]
-
-        for k, base in enumerate(range(0, n_clients, world_size)):
-            buf = mine[k % 2]
-            c = base + rank
-            if c < n_clients:
-                _, upd = next(feed)
-                self.encrypt_client(upd, client=c, round_seed=round_seed, out=buf)
-            mark("encode_encrypt_s")
-            recv = self.lb.empty(world_size, chunks, 2, 3, self.N)
-            work = dist.all_gather_into_tensor(recv.view(-1), buf.view(-1), group=group, async_op=True)
-            if pending is not None:
-                collect(pending)
-            pending = (work, recv, base)
-            mark("ciphertext_allgather_s")
-        if pending is not None:
-            collect(pending)
-        mark("ciphertext_allgather_s")
+        start(0)
+        for i, grp in enumerate(groups):
+            if i + 1 < len(groups) and side:
+                start(i + 1)
+            b = i % n_buf
+            if side:
+                main.wait_event(ready[b])
+            seeds = np.concatenate([self.client_seeds(c, k, first_chunk=c_lo) for c in grp])
+            self.encrypt_chunks(bufs[b][: len(grp)].view(len(grp) * k, self.slots), seeds,
+                                out=cts[grp[0]: grp[-1] + 1].view(len(grp) * k, 2, 3, self.N))
+            if side:
+                free[b].record(main)
+            elif i + 1 < len(groups):
+                start(i + 1)
         return cts
 
     # -- server side ---------------------------------------------------------------------------
-    def pair_scores(self, cts, pairs, mark=lambda name: None):
-        """cts: dict client -> [chunks][2][3][N].  Returns [len(pairs)][2][2][N] level-2 score ciphertexts."""
+    def pair_sums(self, cts, pairs, n_slots=None):
+        """cts: client -> [chunks][2][3][N] (dict or tensor indexed by client).  Returns acc [n_slots][3][3][N] with
+        acc[p] = sum over the chunks of (ct_j - ct_i)^2 for pairs[p] = (i, j); rows past len(pairs) are zero."""
         lb, N = self.lb, self.N
         P = len(pairs)
-        if P == 0:
-            return lb.empty(0, 2, 2, N)
-        acc = lb.empty(P, 3, 3, N)
+        n_slots = P if n_slots is None else n_slots
+        acc = lb.empty(n_slots, 3, 3, N)
+        if n_slots > P:
+            acc[P:].zero_()
         slot = {pair: p for p, pair in enumerate(pairs)}
         for tile in pair_tiles(pairs):
             outs = [acc[slot[pair]] for pair in tile_pairs(tile)]
             lb.krum_accumulate_tile(3, [cts[i] for i in tile[1]], [cts[j] for j in tile[2]], outs)
-        mark("pair_accumulate_s")
+        return acc
+
+    def finish_scores(self, acc, mark=lambda name: None):
+        """acc [P][3][3][N] (pair sums, scale 2^80, level 1) -> [P][2][2][N]: relinearize, rescale, then the
+        rotate-and-sum that leaves the squared distance in every slot (byzantine_fl.py:244-273)"""
+        lb, N = self.lb, self.N
+        P = acc.shape[0]
+        if P == 0:
+            return lb.empty(0, 2, 2, N)
         lb.relinearize_batch(3, acc, self.rlk.data)
         s = lb.rescale_strided(3, acc, P, 2, 3 * 3 * N)  # [P][2][2][N], scale 2^80 / q_2 ~ 2^40
-        del acc
         mark("relin_rescale_s")
         rot = s.clone()
         idx = [self.elt_index[k] for k in self.first_steps]
@@ -514,6 +556,14 @@ class EncryptedKrum:
             lb.add(2, s, rot, out=s)
         mark("rotate_sum_s")
         return s
+
+    def pair_scores(self, cts, pairs, mark=lambda name: None):
+        """cts: dict client -> [chunks][2][3][N].  Returns [len(pairs)][2][2][N] level-2 score ciphertexts."""
+        if len(pairs) == 0:
+            return self.lb.empty(0, 2, 2, self.N)
+        acc = self.pair_sums(cts, pairs)
+        mark("pair_accumulate_s")
+        return self.finish_scores(acc, mark)
 
     def client_sums(self, scores, pairs, n_clients):
         """sum of the score ciphertexts of every pair a client belongs to: [n_clients][2][2][N], one launch"""
@@ -564,15 +614,20 @@ class EncryptedKrum:
         return vals.real.reshape(-1)[:dim]
 
     # -- one round ---------------------------------------------------------------------------------
-    def round(self, updates, rank=0, world_size=1, group=None, round_seed=0, keep=None, timing=None, exchange="p2p"):
+    def round(self, updates, rank=0, world_size=1, group=None, keep=None, timing=None, exchange="chunks"):
         """updates: [n_clients][dim] tensor (CUDA, pinned or pageable host).  Every rank runs this; rank 0 returns
         (distances, order), the others (None, None).
-        exchange (only with several ranks): "p2p" (default): every client is encrypted once, by rank
-        client % world_size, and its ciphertexts go to the ranks whose pairs touch that client (batched NCCL
-        isend / irecv over NVLink, overlapped with the next encryption), so that encryption scales with the
-        ranks too; "allgather": the same with one all-gather per slice of clients (every rank receives every
-        client); "reencrypt": every rank re-derives the ciphertexts of the clients its pairs touch from the
-        shared seeds, and the score gather is the only collective.
+        exchange: how several ranks share the work.
+        "chunks" (default): the pair sum is linear in the chunk axis, so rank r encrypts chunks
+        [chunks r / world, chunks (r+1) / world) of EVERY client, forms the partial sums of ALL pairs over its
+        chunks, and one reduce-scatter of the partial sums (0.9 GB per rank at 20 clients and N = 2^16, instead
+        of the clients' ciphertexts) leaves every rank with the complete sums of its block of pairs; it
+        relinearizes, rescales and rotate-sums those, and the scores are all-gathered.  No ciphertext of a
+        client ever leaves the GPU that encrypted it.  Residues are below 2^60, so the sum of up to eight
+        partial sums fits a signed 64-bit word; it is reduced mod q once afterwards, which equals the
+        single-GPU sum word for word.
+        "p2p": pairs are sharded instead; client c is encrypted by rank c % world_size and its ciphertexts are
+        sent to the ranks whose pairs touch it (batched NCCL isend / irecv overlapped with the next encryption).
         timing: optional dict; when given, the phases are separated by device synchronisations and timed."""
         def mark(name, t=[None]):
             if timing is None:
@@ -585,34 +640,42 @@ class EncryptedKrum:
 
         mark("start")
         n_clients = updates.shape[0]
-        schedule = pair_schedule(n_clients, world_size)
-        mine = schedule[rank]
-        cts = {}
         if world_size > 1 and exchange == "p2p":
-            needed_by = [set(clients_of(seg)) for seg in schedule]
-            feed = self.staged(updates, list(range(rank, n_clients, world_size)))
-            chunks = self.n_chunks(updates.shape[1])
+            return self._round_pair_sharded(updates, rank, world_size, group, keep, mark)
+        if exchange not in ("chunks", "p2p"):
+            raise ValueError("exchange is 'chunks' or 'p2p'")
+        import torch.distributed as dist
 
-            def produce(c):
-                _, upd = next(feed)
-                return self.encrypt_client(upd, client=c, round_seed=round_seed)
-
-            cts = share_slices(world_size, rank, n_clients, needed_by, produce, lambda: self.lb.empty(chunks, 2, 3, self.N),
-                               group=group, mark=mark)
-        elif world_size > 1 and exchange == "allgather":
-            cts = self.encrypt_and_share(updates, rank, world_size, group, round_seed, needed=set(clients_of(mine)), mark=mark)
-        else:
-            for c, upd in self.staged(updates, clients_of(mine)):
-                cts[c] = self.encrypt_client(upd, client=c, round_seed=round_seed)
-            mark("encode_encrypt_s")
-        scores = self.pair_scores(cts, mine, mark)
+        pairs = all_pairs(n_clients)
+        chunks = self.n_chunks(updates.shape[1])
+        c_lo, c_hi = chunk_range(chunks, rank, world_size)
+        cts = self.encrypt_slices(updates, c_lo, c_hi)
+        mark("encode_encrypt_s")
+        block = (len(pairs) + world_size - 1) // world_size
+        if world_size > 8:
+            raise ValueError("the 64-bit sum of partial pair sums holds for up to eight ranks")
+        acc = self.pair_sums(cts, pairs, n_slots=block * world_size)
+        mark("pair_accumulate_s")
         if keep is not None:
-            keep["cts"], keep["scores"], keep["pairs"] = cts, scores, mine
+            keep["cts"], keep["pairs"], keep["partial_sums"] = cts, pairs, acc
         del cts
         if world_size > 1:
-            scores, pairs = gather_scores(scores, schedule, rank, world_size, group)
-        else:
-            pairs = mine
+            acc = scatter_pair_sums(acc, rank, world_size, group)
+            self.lb.reduce_mod(3, acc)
+            mark("pair_reduce_scatter_s")
+        mine = pairs[rank * block: (rank + 1) * block]
+        scores = self.finish_scores(acc[: len(mine)], mark)
+        del acc
+        if keep is not None:
+            keep["scores"], keep["my_pairs"] = scores, mine
+        if world_size > 1:
+            send = scores
+            if len(mine) < block:
+                send = torch.zeros((block,) + tuple(scores.shape[1:]), dtype=scores.dtype, device=scores.device)
+                send[: len(mine)] = scores
+            recv = torch.empty((block * world_size,) + tuple(scores.shape[1:]), dtype=scores.dtype, device=scores.device)
+            dist.all_gather_into_tensor(recv.view(-1), send.contiguous().view(-1), group=group)
+            scores = recv[: len(pairs)]
         mark("gather_s")
         if rank != 0:
             return None, None
@@ -620,6 +683,54 @@ class EncryptedKrum:
         out = self.select(sums)
         mark("sum_decrypt_s")
         return out
+
+    def _round_pair_sharded(self, updates, rank, world_size, group, keep, mark):
+        """the "p2p" exchange of round(): pairs sharded over ranks, ciphertexts sent to the ranks that need them"""
+        n_clients = updates.shape[0]
+        schedule = pair_schedule(n_clients, world_size)
+        mine = schedule[rank]
+        needed_by = [set(clients_of(seg)) for seg in schedule]
+        feed = self.staged(updates, list(range(rank, n_clients, world_size)))
+        chunks = self.n_chunks(updates.shape[1])
+
+        def produce(c):
+            _, upd = next(feed)
+            return self.encrypt_client(upd, client=c)
+
+        cts = share_slices(world_size, rank, n_clients, needed_by, produce, lambda: self.lb.empty(chunks, 2, 3, self.N),
+                           group=group, mark=mark)
+        scores = self.pair_scores(cts, mine, mark)
+        if keep is not None:
+            keep["cts"], keep["scores"], keep["pairs"] = cts, scores, mine
+        del cts
+        scores, pairs = gather_scores(scores, schedule, rank, world_size, group)
+        mark("gather_s")
+        if rank != 0:
+            return None, None
+        sums = self.client_sums(scores, pairs, n_clients)
+        out = self.select(sums)
+        mark("sum_decrypt_s")
+        return out
+
+
+def chunk_range(n_chunks, rank, world_size):
+    """the contiguous chunk range rank ``rank`` of ``world_size`` encrypts and sums"""
+    return (n_chunks * rank) // world_size, (n_chunks * (rank + 1)) // world_size
+
+
+def scatter_pair_sums(partial, rank, world_size, group=None):
+    """partial: [world_size * block][...] 64-bit partial sums of every pair over this rank's chunks.  Returns
+    [block][...]: the sums over all ranks of block ``rank`` (plain 64-bit addition: the caller reduces mod q).
+    NCCL: one reduce-scatter.  gloo (the CPU tests) has no reduce-scatter, so it all-reduces and slices."""
+    import torch.distributed as dist
+
+    block = partial.shape[0] // world_size
+    if dist.get_backend(group) == "gloo":
+        dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=group)
+        return partial[rank * block: (rank + 1) * block].clone()
+    out = torch.empty((block,) + tuple(partial.shape[1:]), dtype=partial.dtype, device=partial.device)
+    dist.reduce_scatter_tensor(out.view(-1), partial.view(-1), op=dist.ReduceOp.SUM, group=group)
+    return out
 
 
 def gather_scores(local, schedule, rank, world_size, group=None):

@@ -314,10 +314,39 @@ class relin_key:
     def __init__(self, ctx):
         self.data = None
 
+    def save(self, ctx, stream):
+        """cahel-main/include/secretkey.h:212-233: the dnum key pairs, each as a size-2 ciphertext over all primes"""
+        if self.data is None:
+            raise RuntimeError("relinearization key has not been generated")
+        stream.write(wire.pack_switch_key(ctx.N, ctx.moduli, ctx.size_P, self.data.cpu().numpy()))
+
+    def load(self, ctx, stream):
+        """cahel-main/include/secretkey.h:235-256"""
+        f = _stream_bytes(stream, wire.unpack_switch_key)
+        if f["poly_modulus_degree"] != ctx.N or f["parms_id"] != wire.parms_id(ctx.N, ctx.moduli, ctx.size_P, 0) \
+                or f["coeff_modulus_size"] != ctx.size_QP or f["data"].shape[0] != ctx.size_Q // ctx.size_P:
+            raise ValueError("relinearization key data is invalid")
+        self.data = _to_device(ctx, f["data"])
+
 
 class galois_key:
     def __init__(self, ctx):
         self.keys = []  # one switch key per Galois element of the context
+
+    def save(self, ctx, stream):
+        """cahel-main/include/secretkey.h:354-375: one relinearization-key stream per Galois element"""
+        if not self.keys:
+            raise RuntimeError("Galois keys have not been generated")
+        stream.write(wire.pack_galois_keys(ctx.N, ctx.moduli, ctx.size_P, [k.cpu().numpy() for k in self.keys]))
+
+    def load(self, ctx, stream):
+        """cahel-main/include/secretkey.h:377-400"""
+        f = _stream_bytes(stream, wire.unpack_galois_keys)
+        dnum = ctx.size_Q // ctx.size_P
+        if f["parms_id"] != wire.parms_id(ctx.N, ctx.moduli, ctx.size_P, 0) or len(f["keys"]) != len(ctx.galois_elts) \
+                or any(k.shape != (dnum, 2, ctx.size_QP, ctx.N) for k in f["keys"]):
+            raise ValueError("Galois key data is invalid")
+        self.keys = [_to_device(ctx, k) for k in f["keys"]]
 
 
 class secret_key:
@@ -712,7 +741,8 @@ def mod_switch_to(ctx, obj, dst, chain_index):
 
 
 def _naf(value):
-    """non-adjacent form, most significant term first (cahel-main/src/util/numth.cu naf)"""
+    """non-adjacent form, least significant term first, which is also the order rotate_internal applies the terms in
+    (cahel-main/include/util/numth.h:18-35, src/evaluate.cu:2396-2407): 5 -> [1, 4], 6 -> [-2, 8], 3 -> [-1, 4]"""
     res = []
     sign = value < 0
     value = abs(value)
@@ -723,7 +753,7 @@ def _naf(value):
         if zi:
             res.append((-zi if sign else zi) * (1 << i))
         i += 1
-    return res[::-1]
+    return res
 
 
 def apply_galois_inplace(ctx, ct, galois_elt_index, glk):

@@ -17,6 +17,15 @@ carries all primes, 1 drops the special ones, every further level drops one more
 (cahel-main/src/context.cu:352-403).  A public key is a size-2 ciphertext over all primes with the
 key level's parms_id; the reference stores chain index 1 and scale 1.0 in it.
 
+    relinearization key:      parms_id[32] (key level) | generated u8 | pair count u64 | that many key pairs, each a
+                              size-2 ciphertext stream over all primes with chain index 0 and scale 1.0
+                              (cahel-main/include/secretkey.h:212-256, src/secretkey.cu:322-370)
+    Galois keys:              parms_id[32] (key level) | generated u8 | key count u64 | that many relinearization-key
+                              streams, one per Galois element of the context (secretkey.h:354-400)
+
+The reference's secret key has no stream of its own.  Its save_seed flags are accepted but never acted on
+(cahel-main/src/secretkey.cu:459: "current version not support"), so no seeded form exists to be compatible with.
+
 Pure host code: it packs and unpacks numpy arrays and knows nothing about devices.
 """
 import hashlib
@@ -114,3 +123,61 @@ def unpack_plaintext(buf):
     data = np.frombuffer(buf, dtype="<u8", count=total, offset=off).reshape(limbs, n).copy()
     return dict(parms_id=pid, chain_index=chain, poly_modulus_degree=n, coeff_modulus_size=limbs, scale=scale, data=data,
                 consumed=off + 8 * total)
+
+
+def pack_switch_key(poly_modulus_degree, moduli, size_p, data):
+    """data: [dnum][2][size_QP][N] -> the reference's CAHELGPURelinKey stream"""
+    a = np.ascontiguousarray(data)
+    n_qp = len(moduli)
+    dnum = a.size // (2 * n_qp * poly_modulus_degree)
+    if dnum * 2 * n_qp * poly_modulus_degree != a.size or dnum < 1:
+        raise ValueError("data does not match [dnum][2][size_QP][N]")
+    pid = parms_id(poly_modulus_degree, moduli, size_p, 0)
+    a = a.reshape(dnum, -1)
+    parts = [pid, struct.pack("<BQ", 1, dnum)]
+    for j in range(dnum):
+        parts.append(pack_ciphertext(pid, 0, 2, poly_modulus_degree, n_qp, 1.0, a[j]))
+    return b"".join(parts)
+
+
+def unpack_switch_key(buf):
+    buf = bytes(buf)
+    if len(buf) < 41:
+        raise RuntimeError("I/O error")
+    pid = buf[:32]
+    (generated, dnum), off = _take(buf, 32, "<BQ")
+    if dnum < 1 or dnum > 64:
+        raise RuntimeError("I/O error")
+    pairs = []
+    for _ in range(dnum):
+        f = unpack_ciphertext(buf[off:])
+        if f["size"] != 2 or f["parms_id"] != pid:
+            raise ValueError("relinearization key data is invalid")
+        pairs.append(f["data"])
+        off += f["consumed"]
+    return dict(parms_id=pid, generated=bool(generated), poly_modulus_degree=pairs[0].shape[2], coeff_modulus_size=pairs[0].shape[1],
+                data=np.stack(pairs), consumed=off)
+
+
+def pack_galois_keys(poly_modulus_degree, moduli, size_p, keys):
+    """keys: one [dnum][2][size_QP][N] array per Galois element -> the reference's CAHELGPUGaloisKey stream"""
+    pid = parms_id(poly_modulus_degree, moduli, size_p, 0)
+    return b"".join([pid, struct.pack("<BQ", 1, len(keys))] + [pack_switch_key(poly_modulus_degree, moduli, size_p, k) for k in keys])
+
+
+def unpack_galois_keys(buf):
+    buf = bytes(buf)
+    if len(buf) < 41:
+        raise RuntimeError("I/O error")
+    pid = buf[:32]
+    (generated, count), off = _take(buf, 32, "<BQ")
+    if count > 4096:
+        raise RuntimeError("I/O error")
+    keys = []
+    for _ in range(count):
+        f = unpack_switch_key(buf[off:])
+        if f["parms_id"] != pid:
+            raise ValueError("Galois key data is invalid")
+        keys.append(f["data"])
+        off += f["consumed"]
+    return dict(parms_id=pid, generated=bool(generated), keys=keys, consumed=off)

@@ -83,6 +83,14 @@ def _load():
     lib.orc_encode.argtypes = [vp, I, pd, C.c_size_t, C.c_size_t, C.c_double, _p64]
     lib.orc_decode.argtypes = [vp, I, _p64, C.c_double, C.c_size_t, pd]
     lib.orc_croot.argtypes = [C.c_size_t, C.c_size_t, pd]
+    lib.orc_max_threads.restype = I
+    lib.orc_set_threads.argtypes = [I]
+    lib.orc_encode_encrypt_batch.argtypes = [vp, _p64, pd, C.c_size_t, C.c_double, _p8, I, _p64]
+    lib.orc_pair_chunk_batch.argtypes = [vp, I, _p64, _p64, _p64, I]
+    lib.orc_relin_rescale_batch.argtypes = [vp, I, _p64, _p64, _p64, I]
+    lib.orc_hmult_batch.argtypes = [vp, I, _p64, _p64, _p64, _p64, I]
+    lib.orc_rotate_batch.argtypes = [vp, I, _p64, I, _p64, I]
+    lib.orc_ntt_roundtrip_batch.argtypes = [vp, _p64, I, I]
     return lib
 
 
@@ -322,3 +330,50 @@ class Oracle:
         lib.orc_decode(self.h, L, _u(np.ascontiguousarray(pt)), float(scale), sparse_slots,
                        out.view(np.float64).ctypes.data_as(C.POINTER(C.c_double)))
         return out
+
+    # -- batched forms (one OpenMP thread per item) used by the timed CPU baseline
+    def encode_encrypt_batch(self, pk, values, scale, seeds):
+        values = np.ascontiguousarray(values, dtype=np.float64)
+        batch, slots = values.shape
+        seeds, sp = _s(seeds)
+        assert seeds.size == 128 * batch
+        ct = np.empty((batch, 2, self.size_Q, self.N), dtype=np.uint64)
+        lib.orc_encode_encrypt_batch(self.h, _u(np.ascontiguousarray(pk)), values.ctypes.data_as(C.POINTER(C.c_double)), slots,
+                                     float(scale), sp, batch, _u(ct))
+        return ct
+
+    def pair_chunk_batch(self, L, x, y, acc):
+        """acc[b] += (y[b] - x[b])^2 in place"""
+        lib.orc_pair_chunk_batch(self.h, L, _u(x), _u(y), _u(acc), x.shape[0])
+        return acc
+
+    def relin_rescale_batch(self, L, ct3, rlk):
+        ct3 = np.ascontiguousarray(ct3, dtype=np.uint64).copy()
+        out = np.empty((ct3.shape[0], 2, L - 1, self.N), dtype=np.uint64)
+        lib.orc_relin_rescale_batch(self.h, L, _u(ct3), _u(np.ascontiguousarray(rlk)), _u(out), ct3.shape[0])
+        return out
+
+    def hmult_batch(self, L, x, y, rlk):
+        out = np.empty((x.shape[0], 2, L - 1, self.N), dtype=np.uint64)
+        lib.orc_hmult_batch(self.h, L, _u(x), _u(y), _u(np.ascontiguousarray(rlk)), _u(out), x.shape[0])
+        return out
+
+    def rotate_batch(self, L, ct, elt_idx, glk):
+        """in place"""
+        lib.orc_rotate_batch(self.h, L, _u(ct), elt_idx, _u(np.ascontiguousarray(glk)), ct.shape[0])
+        return ct
+
+    def ntt_roundtrip_batch(self, data, size_l):
+        """forward then inverse transform in place"""
+        lib.orc_ntt_roundtrip_batch(self.h, _u(data), data.shape[0], size_l)
+        return data
+
+
+def set_threads(n):
+    """number of OpenMP threads for later calls (overrides whatever OMP_NUM_THREADS said at load time)"""
+    lib.orc_set_threads(int(n))
+
+
+def max_threads():
+    """threads the library's OpenMP runtime will use (what OMP_NUM_THREADS resolved to at load time)"""
+    return int(lib.orc_max_threads())

@@ -757,15 +757,21 @@ void orc_decrypt(const orc_ctx *c, int L, int n_polys, const u64 *ct, const u64 
 
 typedef struct { double x, y; } cplx;
 
-/* cuCmul with the product-difference contracted into one fused multiply-add, which is how
- * the device compiler emits cahel-main/src/fft.cu:12-41 under its default -fmad=true. */
-static inline cplx cmul(cplx a, cplx b)
+/* cuCmul with each part contracted into one rounded product and one fused multiply-add, which is how
+ * the device compiler emits cahel-main/src/fft.cu:12-41 under its default -fmad=true.  Which product of
+ * the imaginary part is the rounded one differs between the reference's two inverse-FFT kernels: the
+ * multi-stage kernel that runs the first eleven stages (fft.cu:194-268, SWITCH_POINT = 2048) rounds
+ * a.x * b.y (first_kernel != 0), the per-stage kernel (fft.cu:279-344) rounds a.y * b.x.  Pinned by the
+ * reference-made plaintexts at scale 2^50 (fixtures n4096_s50, n8192_s50, n65536_a8). */
+#define ORC_IFFT_FIRST_KERNEL_STAGES 11
+static inline cplx cmul2(cplx a, cplx b, int first_kernel)
 {
     cplx r;
     r.x = fma(a.x, b.x, -(a.y * b.y));
-    r.y = fma(a.x, b.y, a.y * b.x);
+    r.y = first_kernel ? fma(a.y, b.x, a.x * b.y) : fma(a.x, b.y, a.y * b.x);
     return r;
 }
+static inline cplx cmul(cplx a, cplx b) { return cmul2(a, b, 0); }
 
 /* cahel-main/src/croots.cu:14-66: one eighth of the M-th roots from polar(), the rest by symmetry */
 static cplx croot(size_t index, size_t M)
@@ -844,7 +850,7 @@ void orc_encode(const orc_ctx *c, int L, const double *values, size_t n_values, 
             cplx x0 = a[g], x1 = a[g + pairs], s0, s1;
             s0.x = x0.x + x1.x; s0.y = x0.y + x1.y;
             s1.x = x0.x - x1.x; s1.y = x0.y - x1.y;
-            s1 = cmul(s1, w);
+            s1 = cmul2(s1, w, logPairs < ORC_IFFT_FIRST_KERNEL_STAGES);
             if (iter == 0 && fix != 0.0) { s0.x *= fix; s0.y *= fix; s1.x *= fix; s1.y *= fix; }
             a[g] = s0; a[g + pairs] = s1;
         }
@@ -977,3 +983,91 @@ void orc_decode(const orc_ctx *c, int L, const u64 *pt, double scale, size_t spa
 /* coefficient-domain output of the encoder's inverse FFT (before rounding), for
  * tests that want to look at near-half rounding cases */
 size_t orc_N(const orc_ctx *c) { return c->N; }
+
+/* ---------------------------------------------------------------- batched forms for the timed CPU baseline
+ * The same functions over a batch of independent items, one OpenMP thread per item; the inner loops of the
+ * functions above then run serially (nested parallel regions are off by default).  This is how a CPU
+ * implementation would use its cores on the Krum workload: parallel over ciphertexts and pairs, not over
+ * the three or four limbs of one polynomial. */
+#ifdef _OPENMP
+#include <omp.h>
+int orc_max_threads(void) { return omp_get_max_threads(); }
+void orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+#else
+int orc_max_threads(void) { return 1; }
+void orc_set_threads(int n) { (void)n; }
+#endif
+
+/* values [batch][slots] doubles, seeds [batch][2][64] (ternary, error) -> ct [batch][2][size_Q][N] */
+void orc_encode_encrypt_batch(const orc_ctx *c, const u64 *pk, const double *values, size_t slots, double scale, const uint8_t *seeds,
+                              int batch, u64 *ct)
+{
+    size_t N = c->N;
+    int Q = c->size_Q;
+#pragma omp parallel for schedule(dynamic)
+    for (int b = 0; b < batch; b++) {
+        u64 *pt = (u64 *)malloc((size_t)Q * N * 8);
+        double *v = (double *)malloc(slots * 2 * sizeof(double));
+        for (size_t i = 0; i < slots; i++) { v[2 * i] = values[(size_t)b * slots + i]; v[2 * i + 1] = 0.0; }
+        orc_encode(c, Q, v, slots, slots, scale, pt);
+        u64 *out = ct + (size_t)b * 2 * Q * N;
+        orc_encrypt_zero_asym(c, pk, seeds + (size_t)b * 128, seeds + (size_t)b * 128 + 64, out);
+        orc_poly_op(c, 0, Q, 1, out, pt, out);
+        free(pt); free(v);
+    }
+}
+
+/* acc[b] += (y[b] - x[b])^2 for a batch of ciphertext pairs: x, y [batch][2][L][N], acc [batch][3][L][N] */
+void orc_pair_chunk_batch(const orc_ctx *c, int L, const u64 *x, const u64 *y, u64 *acc, int batch)
+{
+    size_t N = c->N;
+#pragma omp parallel for schedule(dynamic)
+    for (int b = 0; b < batch; b++) {
+        u64 *d = (u64 *)malloc((size_t)2 * L * N * 8), *sq = (u64 *)malloc((size_t)3 * L * N * 8);
+        orc_poly_op(c, 1, L, 2, y + (size_t)b * 2 * L * N, x + (size_t)b * 2 * L * N, d);
+        orc_tensor(c, L, d, d, sq);
+        orc_poly_op(c, 0, L, 3, acc + (size_t)b * 3 * L * N, sq, acc + (size_t)b * 3 * L * N);
+        free(d); free(sq);
+    }
+}
+
+/* relinearize + rescale of a batch: ct3 [batch][3][L][N] (clobbered) -> out [batch][2][L-1][N] */
+void orc_relin_rescale_batch(const orc_ctx *c, int L, u64 *ct3, const u64 *rlk, u64 *out, int batch)
+{
+    size_t N = c->N;
+#pragma omp parallel for schedule(dynamic)
+    for (int b = 0; b < batch; b++) {
+        u64 *ct = ct3 + (size_t)b * 3 * L * N;
+        orc_relinearize(c, L, ct, rlk);
+        orc_rescale(c, L, 2, ct, out + (size_t)b * 2 * (L - 1) * N);
+    }
+}
+
+/* multiply + relinearize + rescale of a batch: x, y [batch][2][L][N] -> out [batch][2][L-1][N] */
+void orc_hmult_batch(const orc_ctx *c, int L, const u64 *x, const u64 *y, const u64 *rlk, u64 *out, int batch)
+{
+    size_t N = c->N;
+#pragma omp parallel for schedule(dynamic)
+    for (int b = 0; b < batch; b++) {
+        u64 *ct = (u64 *)malloc((size_t)3 * L * N * 8);
+        orc_tensor(c, L, x + (size_t)b * 2 * L * N, y + (size_t)b * 2 * L * N, ct);
+        orc_relinearize(c, L, ct, rlk);
+        orc_rescale(c, L, 2, ct, out + (size_t)b * 2 * (L - 1) * N);
+        free(ct);
+    }
+}
+
+/* ct[b] <- rot(ct[b]) for a batch [batch][2][L][N] with one Galois key */
+void orc_rotate_batch(const orc_ctx *c, int L, u64 *ct, int elt_idx, const u64 *glk, int batch)
+{
+    size_t N = c->N;
+#pragma omp parallel for schedule(dynamic)
+    for (int b = 0; b < batch; b++) orc_rotate(c, L, ct + (size_t)b * 2 * L * N, elt_idx, glk);
+}
+
+/* forward then inverse transform of a batch of polynomials [batch][size_l][N], one thread per limb */
+void orc_ntt_roundtrip_batch(const orc_ctx *c, u64 *data, int batch, int size_l)
+{
+    orc_ntt_rows(c, data, batch, size_l, 0, 0);
+    orc_ntt_rows(c, data, batch, size_l, 0, 1);
+}

@@ -4,7 +4,12 @@
 // are logged by the force-included seed shim, so the CPU restatement and the product
 // library can replay the same keys and ciphertexts and must reproduce the same digests.
 //
-// Test infrastructure only.  Usage: ref_harness <out.json> [dump_dir]
+// Test infrastructure only.
+// Usage: ref_harness <out.json> [--cases a,b,...] [--dump dir [--dump-only stage,...]] [--time timings.json]
+//   --cases  run only the named parameter sets (default: all of them)
+//   --dump   also write the raw bytes of every (or only the named) recorded stage to <dir>/<case>.<stage>.bin
+//   --time   also time the reference's own operations with CUDA events and write them as JSON
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <fstream>
@@ -102,6 +107,7 @@ struct Sha256 {
 static std::ostringstream g_json;
 static bool g_first = true;
 static std::string g_dump_dir;
+static std::vector<std::string> g_dump_only; // stage names to dump (empty: every stage)
 static std::string g_case;
 
 static void record_host(const std::string &name, const void *data, size_t bytes, bool is_double = false)
@@ -123,7 +129,7 @@ static void record_host(const std::string &name, const void *data, size_t bytes,
         }
     }
     g_json << "]}";
-    if (!g_dump_dir.empty()) {
+    if (!g_dump_dir.empty() && (g_dump_only.empty() || std::find(g_dump_only.begin(), g_dump_only.end(), name) != g_dump_only.end())) {
         std::ofstream f(g_dump_dir + "/" + g_case + "." + name + ".bin", std::ios::binary);
         f.write((const char *)data, bytes);
     }
@@ -178,12 +184,24 @@ static std::vector<double> message(size_t n, uint32_t salt)
     return v;
 }
 
-static void run_case(const std::string &name, size_t n, const std::vector<int> &bits, size_t size_P, double scale,
-                     const std::vector<int> &steps, bool last)
+static std::vector<std::string> g_only;
+static bool g_first_case = true;
+
+static bool wanted(const std::string &name)
 {
+    return g_only.empty() || std::find(g_only.begin(), g_only.end(), name) != g_only.end();
+}
+
+// naf_step: a rotation step that has no key of its own, so that rotate_vector goes through the
+// non-adjacent-form decomposition (0 = skip)
+static void run_case(const std::string &name, size_t n, const std::vector<int> &bits, size_t size_P, double scale,
+                     const std::vector<int> &steps, int naf_step = 0)
+{
+    if (!wanted(name)) return;
     g_case = name;
     g_first = true;
-    g_json << "  \"" << name << "\": {\n";
+    g_json << (g_first_case ? "" : ",\n") << "  \"" << name << "\": {\n";
+    g_first_case = false;
     EncryptionParameters parms(scheme_type::ckks);
     parms.set_poly_modulus_degree(n);
     auto moduli = CoeffModulus::Create(n, bits);
@@ -246,6 +264,8 @@ static void run_case(const std::string &name, size_t n, const std::vector<int> &
     record_stream("stream_pt1", pt1, false);
     record_stream("stream_ct1", ct1, true);
     record_stream("stream_pk", pk, true);
+    record_stream("stream_rlk", rlk, false);
+    record_stream("stream_glk", glk, false);
 
     CAHELGPUCiphertext diff(context), prod(context);
     sub(context, ct2, ct1, diff);
@@ -268,6 +288,12 @@ static void run_case(const std::string &name, size_t n, const std::vector<int> &
     rotate_vector(context, prod, steps[0], glk, rot);
     record_dev("rotate", rot.data(), 2 * L2 * n);
 
+    if (naf_step) {
+        CAHELGPUCiphertext rn(context);
+        rotate_vector(context, prod, naf_step, glk, rn);
+        record_dev("rotate_naf", rn.data(), 2 * L2 * n);
+    }
+
     CAHELGPUCiphertext hoist = hoisting(context, prod, glk, steps);
     record_dev("hoisting", hoist.data(), 2 * L2 * n);
 
@@ -288,30 +314,208 @@ static void run_case(const std::string &name, size_t n, const std::vector<int> &
     encoder.decode(context, dec, out);
     record_host("decode", out.data(), out.size() * sizeof(cuDoubleComplex), true);
 
-    g_json << "\n  }" << (last ? "\n" : ",\n");
+    g_json << "\n  }";
+}
+
+// ---- the reference's own operations timed with CUDA events -------------------------------
+static std::ostringstream g_time_json;
+static bool g_time_first_case = true;
+
+template <class F, class G>
+static double median_ms(int reps, G &&prepare, F &&op)
+{
+    cudaEvent_t a, b;
+    CUDA_CHECK(cudaEventCreate(&a));
+    CUDA_CHECK(cudaEventCreate(&b));
+    std::vector<float> ms;
+    for (int r = 0; r < reps + 2; r++) {
+        prepare();
+        CUDA_CHECK(cudaDeviceSynchronize());
+        CUDA_CHECK(cudaEventRecord(a, 0));
+        op();
+        CUDA_CHECK(cudaEventRecord(b, 0));
+        CUDA_CHECK(cudaEventSynchronize(b));
+        float t;
+        CUDA_CHECK(cudaEventElapsedTime(&t, a, b));
+        if (r >= 2) ms.push_back(t);  // two untimed warm-up runs
+    }
+    cudaEventDestroy(a);
+    cudaEventDestroy(b);
+    std::sort(ms.begin(), ms.end());
+    return ms[ms.size() / 2];
+}
+
+// Median milliseconds of each operation of cahel-main/examples/7_performance.cu:540-757 (host call to result on
+// the device, legacy default stream as the reference uses it), plus the per-chunk body of the Krum driver
+// (lancelot-main-GPU/utils/byzantine_fl.py:201-223) and the plain forward / inverse transform of all data limbs.
+static void time_case(const std::string &name, size_t n, const std::vector<int> &bits, size_t size_P, double scale,
+                      const std::vector<int> &steps, int reps)
+{
+    if (!wanted(name)) return;
+    EncryptionParameters parms(scheme_type::ckks);
+    parms.set_poly_modulus_degree(n);
+    auto moduli = CoeffModulus::Create(n, bits);
+    parms.set_coeff_modulus(moduli);
+    parms.set_special_modulus_size(size_P);
+    parms.set_galois_elts(get_elts_from_steps(steps, n));
+    CAHELGPUContext context(parms, true, sec_level_type::none);
+    const size_t size_Q = moduli.size() - size_P;
+    CAHELGPUSecretKey sk(parms);
+    sk.gen_secretkey(context);
+    CAHELGPUPublicKey pk(context);
+    sk.gen_publickey(context, pk);
+    CAHELGPURelinKey rlk(context);
+    sk.gen_relinkey(context, rlk);
+    CAHELGPUGaloisKey glk(context);
+    sk.create_galois_keys(context, glk);
+    CAHELGPUCKKSEncoder encoder(context);
+    auto m1 = message(encoder.slot_count(), 1), m2 = message(encoder.slot_count(), 77);
+    CAHELGPUPlaintext pt1(context), pt2(context);
+    CAHELGPUCiphertext ct1(context), ct2(context), work(context), work2(context), acc(context);
+    auto nothing = [] {};
+    std::vector<std::pair<std::string, double>> out;
+    out.push_back({"keygen_all", median_ms(3, nothing, [&] {
+                       CAHELGPUSecretKey s2(parms);
+                       s2.gen_secretkey(context);
+                       CAHELGPUPublicKey p2(context);
+                       s2.gen_publickey(context, p2);
+                       CAHELGPURelinKey r2(context);
+                       s2.gen_relinkey(context, r2);
+                       CAHELGPUGaloisKey g2(context);
+                       s2.create_galois_keys(context, g2);
+                   })});
+    out.push_back({"encode", median_ms(reps, nothing, [&] { encoder.encode(context, m1, scale, pt1); })});
+    encoder.encode(context, m2, scale, pt2);
+    out.push_back({"encrypt", median_ms(reps, nothing, [&] { pk.encrypt_asymmetric(context, pt1, ct1, false); })});
+    pk.encrypt_asymmetric(context, pt2, ct2, false);
+    out.push_back({"sub", median_ms(reps, nothing, [&] { sub(context, ct2, ct1, work); })});
+    out.push_back({"multiply", median_ms(reps, nothing, [&] { multiply(context, ct1, ct2, work); })});
+    out.push_back({"square_inplace", median_ms(reps, [&] { work2 = ct1; }, [&] { square_inplace(context, work2); })});
+    acc = work2;
+    out.push_back({"add_inplace_size3", median_ms(reps, nothing, [&] { add_inplace(context, acc, work2); })});
+    // one chunk of one pair as the reference's driver runs it: two encodes, two encryptions, sub, square, add
+    out.push_back({"krum_pair_chunk", median_ms(reps, nothing, [&] {
+                       encoder.encode(context, m1, scale, pt1);
+                       encoder.encode(context, m2, scale, pt2);
+                       pk.encrypt_asymmetric(context, pt1, ct1, false);
+                       pk.encrypt_asymmetric(context, pt2, ct2, false);
+                       sub(context, ct2, ct1, work2);
+                       square_inplace(context, work2);
+                       add_inplace(context, acc, work2);
+                   })});
+    out.push_back({"relinearize", median_ms(reps, [&] { work2 = work; }, [&] { relinearize_inplace(context, work2, rlk); })});
+    out.push_back({"multiply_relin_rescale", median_ms(reps, nothing, [&] {
+                       multiply(context, ct1, ct2, work2);
+                       relinearize_inplace(context, work2, rlk);
+                       rescale_to_next_inplace(context, work2);
+                   })});
+    multiply(context, ct1, ct2, work);
+    relinearize_inplace(context, work, rlk);
+    out.push_back({"rescale", median_ms(reps, [&] { work2 = work; }, [&] { rescale_to_next_inplace(context, work2); })});
+    out.push_back({"rotate_vector", median_ms(reps, nothing, [&] { rotate_vector(context, ct1, steps[0], glk, work2); })});
+    if (steps.size() > 1)
+        out.push_back({"hoisting_" + std::to_string(steps.size()), median_ms(reps, nothing, [&] { work2 = hoisting(context, ct1, glk, steps); })});
+    out.push_back({"ntt_forward_data_limbs", median_ms(reps, nothing, [&] {
+                       nwt_2d_radix8_forward_inplace(ct1.data(), context.gpu_rns_tables(), size_Q, 0);
+                   })});
+    out.push_back({"ntt_inverse_data_limbs", median_ms(reps, nothing, [&] {
+                       nwt_2d_radix8_backward_inplace(ct1.data(), context.gpu_rns_tables(), size_Q, 0);
+                   })});
+    CAHELGPUPlaintext dec(context);
+    out.push_back({"decrypt", median_ms(reps, nothing, [&] { sk.decrypt(context, ct2, dec); })});
+    std::vector<cuDoubleComplex> vals;
+    out.push_back({"decode", median_ms(reps, nothing, [&] { encoder.decode(context, dec, vals); })});
+
+    g_time_json << (g_time_first_case ? "" : ",\n") << "  \"" << name << "\": {\"n\": " << n << ", \"size_Q\": " << size_Q
+                << ", \"size_P\": " << size_P << ", \"reps\": " << reps << ", \"ms\": {";
+    g_time_first_case = false;
+    for (size_t i = 0; i < out.size(); i++) {
+        char b[64];
+        snprintf(b, sizeof(b), "%.4f", out[i].second);
+        g_time_json << (i ? ", " : "") << "\"" << out[i].first << "\": " << b;
+    }
+    g_time_json << "}}";
+}
+
+static std::vector<int> range_steps(int lo, int hi)
+{
+    std::vector<int> v;
+    for (int i = lo; i <= hi; i++) v.push_back(i);
+    return v;
 }
 
 int main(int argc, char **argv)
 {
     if (argc < 2) {
-        fprintf(stderr, "usage: %s out.json [dump_dir]\n", argv[0]);
+        fprintf(stderr, "usage: %s out.json [--cases a,b,...] [--dump dir [--dump-only stage,...]] [--time timings.json]\n", argv[0]);
         return 2;
     }
-    if (argc > 2) g_dump_dir = argv[2];
+    std::string time_out;
+    for (int i = 2; i < argc; i++) {
+        std::string a = argv[i];
+        if (a == "--cases" && i + 1 < argc) {
+            std::stringstream ss(argv[++i]);
+            std::string item;
+            while (std::getline(ss, item, ',')) g_only.push_back(item);
+        } else if (a == "--dump" && i + 1 < argc) {
+            g_dump_dir = argv[++i];
+        } else if (a == "--dump-only" && i + 1 < argc) {
+            std::stringstream ss(argv[++i]);
+            std::string item;
+            while (std::getline(ss, item, ',')) g_dump_only.push_back(item);
+        } else if (a == "--time" && i + 1 < argc) {
+            time_out = argv[++i];
+        } else {
+            fprintf(stderr, "unknown argument %s\n", a.c_str());
+            return 2;
+        }
+    }
+    const double s40 = 1099511627776.0, s50 = 1125899906842624.0;
+    // 60 + 23 x 50 data bits and 8 x 60 special bits: the hybrid key-switching benchmark shape (alpha 8, dnum 3)
+    std::vector<int> wide = {60};
+    for (int i = 0; i < 23; i++) wide.push_back(50);
+    for (int i = 0; i < 8; i++) wide.push_back(60);
     g_json << "{\n";
     try {
         // Lancelot's own chain shape {60,40,40 | 60}, alpha = 1, at the smallest 2-D NTT size
-        run_case("n4096_a1", 4096, {60, 40, 40, 60}, 1, 1099511627776.0, {1, 2, 3}, false);
+        run_case("n4096_a1", 4096, {60, 40, 40, 60}, 1, s40, {1, 2, 3});
         // the ring degree of the primitive-chain benchmark configuration
-        run_case("n8192_a1", 8192, {60, 40, 40, 60}, 1, 1099511627776.0, {1, 2, 3}, false);
+        run_case("n8192_a1", 8192, {60, 40, 40, 60}, 1, s40, {1, 2, 3});
         // alpha = 2, dnum = 3: generic base-conversion path and, one level down, a partial digit
-        run_case("n4096_a2", 4096, {50, 40, 40, 40, 40, 40, 50, 50}, 2, 1099511627776.0, {1, 5}, true);
+        run_case("n4096_a2", 4096, {50, 40, 40, 40, 40, 40, 50, 50}, 2, s40, {1, 5});
+        // the ring degrees of the two Krum benchmark configurations, with a rotation (5 = 4 + 1) that has no key
+        run_case("n32768_a1", 32768, {60, 40, 40, 60}, 1, s40, {1, 2, 4}, 5);
+        run_case("n65536_a1", 65536, {60, 40, 40, 60}, 1, s40, {1, 2, 4}, 5);
+        // the hybrid key-switching benchmark configuration
+        run_case("n65536_a8", 65536, wide, 8, s50, {1, 4}, 5);
+        // scale 2^50 leaves two or three bits below the rounding point of the largest coefficients, so these plaintexts
+        // pin the encoder's floating-point order: slots = 2048 runs the single-kernel inverse FFT, 4096 adds one
+        // stage kernel (cahel-main/src/fft.cu:407-449)
+        run_case("n4096_s50", 4096, {60, 60, 60}, 1, s50, {1});
+        run_case("n8192_s50", 8192, {60, 60, 60}, 1, s50, {1});
     } catch (const std::exception &e) {
         fprintf(stderr, "reference threw: %s\n", e.what());
         return 1;
     }
-    g_json << "}\n";
-    std::ofstream f(argv[1]);
-    f << g_json.str();
+    g_json << "\n}\n";
+    {
+        std::ofstream f(argv[1]);
+        f << g_json.str();
+    }
+    if (!time_out.empty()) {
+        g_time_json << "{\n";
+        try {
+            time_case("n8192_a1", 8192, {60, 40, 40, 60}, 1, s40, range_steps(1, 15), 20);
+            time_case("n32768_a1", 32768, {60, 40, 40, 60}, 1, s40, range_steps(1, 15), 20);
+            time_case("n65536_a1", 65536, {60, 40, 40, 60}, 1, s40, range_steps(1, 15), 20);
+            time_case("n65536_a8", 65536, wide, 8, s50, {1}, 10);
+        } catch (const std::exception &e) {
+            fprintf(stderr, "reference threw while timing: %s\n", e.what());
+            return 1;
+        }
+        g_time_json << "\n}\n";
+        std::ofstream f(time_out);
+        f << g_time_json.str();
+    }
     return 0;
 }

@@ -116,14 +116,48 @@ int main(int argc, char **argv)
         } catch (const std::invalid_argument &) {
             refused_stream = true;
         }
+        // relinearization and Galois key streams: saved, loaded, and the loaded keys give the same ciphertext words
+        std::stringstream kwire(std::ios::in | std::ios::out | std::ios::binary);
+        rlk.save(context, kwire);
+        glk.save(context, kwire);
+        CAHELGPURelinKey rlk2;
+        CAHELGPUGaloisKey glk2;
+        rlk2.load(context, kwire);
+        glk2.load(context, kwire);
+        CAHELGPUCiphertext m1(context), m2(context);
+        {
+            CAHELGPUCiphertext a(context), b(context);
+            pk.encrypt_asymmetric(context, px, a);
+            pk.encrypt_asymmetric(context, py, b);
+            multiply(context, a, b, m1);
+            m2 = m1;
+            relinearize_inplace(context, m1, rlk);
+            relinearize_inplace(context, m2, rlk2);
+            rotate_vector_inplace(context, m1, 2, glk);
+            rotate_vector_inplace(context, m2, 2, glk2);
+        }
+        const bool keys_same = words_of(m1.data(), 2 * 3 * n) == words_of(m2.data(), 2 * 3 * n);
+        // steady state: a loop of evaluator calls takes its blocks from the pool, not from the driver
+        const size_t allocs_before = cahel_b200::DevicePool::instance().device_allocations();
+        for (int it = 0; it < 20; ++it) {
+            CAHELGPUCiphertext t(context), r(context);
+            multiply(context, cx2, cx2, t);
+            relinearize_inplace(context, t, rlk);
+            rotate_vector(context, t, 1, glk, r);
+            CAHELGPUCiphertext hs = hoisting(context, r, glk, {1, 2, 3});
+            (void)encoder.decode(context, sk.decrypt(context, hs));
+        }
+        const size_t new_allocs = cahel_b200::DevicePool::instance().device_allocations() - allocs_before;
+        // the first pass may still meet sizes it has not seen; twenty passes must not keep allocating
+        const bool pooled = new_allocs <= 8 && cahel_b200::DevicePool::instance().reuses() > 100;
         if (const char *path = std::getenv("CPP_API_CHECK_STREAM")) {
             std::ofstream f(path, std::ios::binary);
             const std::string b = wire.str();
             f.write(b.data(), (std::streamsize)b.size());
         }
-        printf("multiply %.3g rotate %.3g hoisting %.3g refused %d streams %d bad-stream-refused %d\n", e1, e2, e3, (int)threw, (int)same,
-               (int)refused_stream);
-        return (e1 < 1e-3 && e2 < 1e-3 && e3 < 1e-3 && threw && same && refused_stream) ? 0 : 1;
+        printf("multiply %.3g rotate %.3g hoisting %.3g refused %d streams %d bad-stream-refused %d key-streams %d pooled %d (new device allocations %zu)\n",
+               e1, e2, e3, (int)threw, (int)same, (int)refused_stream, (int)keys_same, (int)pooled, new_allocs);
+        return (e1 < 1e-3 && e2 < 1e-3 && e3 < 1e-3 && threw && same && refused_stream && keys_same && pooled) ? 0 : 1;
     } catch (const std::exception &e) {
         printf("exception: %s\n", e.what());
         return 2;

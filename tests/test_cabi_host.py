@@ -11,8 +11,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _declared_symbols():
-    text = open(os.path.join(ROOT, "include", "lancelot_b200.h")).read()
-    return sorted(set(re.findall(r"LB_API[^;(]*?\b(lb_[a-z0-9_]+)\s*\(", text)))
+    names = set()
+    for header in ("lancelot_b200.h", "lancelot_b200_diag.h"):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        names.update(re.findall(r"LB_API[^;(]*?\b(lb_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_library_exports_every_declared_symbol():
@@ -59,3 +62,20 @@ def test_invalid_arguments_are_reported_not_crashed():
     # a null context is refused by every compute entry point
     assert lib.lb_ntt_forward(None, None, 1, 1, 0, None) == 1
     assert b"context" in lib.lb_last_error()
+
+
+def test_context_refuses_primes_of_more_than_60_bits():
+    """the kernels' lazy ranges (unreduced differences, 63 products per 128-bit sum, 64-bit sums of eight residues)
+    hold for primes below 2^60, the reference's own limit; a larger prime is refused before any device work"""
+    from lancelot_b200 import cabi
+    from lancelot_b200._lib import InvalidArgument
+
+    n = 1 << 10
+    # a 61-bit prime congruent to 1 mod 2n
+    q = (1 << 61) - (1 << 61) % (2 * n) + 1
+    from oracle import binding
+    while not binding.lib.orc_is_prime(q):
+        q -= 2 * n
+    assert q >> 60
+    with pytest.raises(InvalidArgument, match="2\\^60"):
+        cabi.Context(10, [q], 0)

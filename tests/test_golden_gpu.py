@@ -3,7 +3,7 @@
 import numpy as np
 import pytest
 
-from golden_replay import CASES, load_fixture, replay
+from golden_replay import CASES, load_fixture, moduli_of, replay
 
 pytestmark = pytest.mark.gpu
 
@@ -92,7 +92,7 @@ def test_cuda_library_reproduces_reference_digests(case):
 
     fix = load_fixture()[case]
     cfg = CASES[case]
-    mods = [int(x) for x in fix["moduli"]["head"]]
+    mods = moduli_of(case, fix, cabi.coeff_modulus_create)
     elts = [int(x) for x in fix["galois_elts"]["head"]]
     ctx = cabi.Context(cfg["logn"], mods, cfg["size_p"], elts)
     report = replay(case, fix, CudaOps(ctx))

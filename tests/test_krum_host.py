@@ -136,3 +136,88 @@ def test_point_to_point_ciphertext_exchange_gloo(world, n_clients):
     for p in procs:
         p.join(timeout=60)
     assert sorted(res) == [(r, True) for r in range(world)]
+
+
+def _chunk_worker(rank, world, port, out):
+    import torch.distributed as dist
+
+    from lancelot_b200.krum import all_pairs, chunk_range, scatter_pair_sums
+    from oracle import binding
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        logn, L, n_clients, chunks = 8, 3, 5, 7
+        n = 1 << logn
+        mods = binding.coeff_modulus_create(n, [60, 40, 40, 60])
+        o = binding.Oracle(logn, mods, 1)
+        rng = np.random.default_rng(42)  # every rank draws the same "ciphertexts"
+        cts = np.stack([np.stack([rng.integers(0, mods[r], n, dtype=np.uint64) for r in range(L)] * 2).reshape(2, L, n)
+                        for _ in range(n_clients * chunks)]).reshape(n_clients, chunks, 2, L, n)
+        cts[0, 0] = 0
+        for r in range(L):
+            cts[1, 0][:, r, :] = mods[r] - 1  # largest residues: the 64-bit sum of partial sums must not wrap
+        pairs = all_pairs(n_clients)
+
+        def pair_sum(i, j, lo, hi):
+            acc = np.zeros((3, L, n), dtype=np.uint64)
+            for c in range(lo, hi):
+                acc = o.poly_op("add", L, acc, o.square(L, o.poly_op("sub", L, cts[j, c], cts[i, c]).reshape(2, L, n)))
+            return acc
+
+        lo, hi = chunk_range(chunks, rank, world)
+        block = (len(pairs) + world - 1) // world
+        partial = np.zeros((block * world, 3, L, n), dtype=np.uint64)
+        for p, (i, j) in enumerate(pairs):
+            partial[p] = pair_sum(i, j, lo, hi)
+        mine = scatter_pair_sums(torch.from_numpy(partial.view(np.int64)), rank, world).numpy().view(np.uint64)
+        q = np.array(mods[:L], dtype=np.uint64).reshape(1, 1, L, 1)
+        mine = mine % q
+        ok = True
+        for k, (i, j) in enumerate(pairs[rank * block:(rank + 1) * block]):
+            ok = ok and np.array_equal(mine[k], pair_sum(i, j, 0, chunks))
+        ok = ok and not mine[len(pairs[rank * block:(rank + 1) * block]):].any()
+        out.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_chunk_sharded_pair_sums_equal_single_rank_sums_gloo(world):
+    """ranks sum the pairs over their own chunk ranges; the scattered 64-bit sums, reduced mod q once, equal the
+    sums one rank forms over all chunks, word for word"""
+    import torch.multiprocessing as mp
+
+    from lancelot_b200.krum import chunk_range
+
+    assert [chunk_range(342, r, 8) for r in (0, 7)] == [(0, 42), (299, 342)]
+    assert sum(hi - lo for lo, hi in (chunk_range(7, r, 4) for r in range(4))) == 7
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29710 + world
+    procs = [ctx.Process(target=_chunk_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(res) == [(r, True) for r in range(world)]
+
+
+def test_rotation_steps_decompose_like_the_reference():
+    """non-adjacent form, least significant term first: the order the reference key-switches a rotation step that
+    has no key of its own (cahel-main/include/util/numth.h:18-35, src/evaluate.cu:2396-2407); the reference-made
+    fixture entry "rotate_naf" pins that the order matters bit for bit"""
+    from lancelot_b200.pycahel import _naf
+
+    assert _naf(5) == [1, 4]
+    assert _naf(6) == [-2, 8]
+    assert _naf(3) == [-1, 4]
+    assert _naf(-3) == [1, -4]
+    assert _naf(16) == [16]
+    for v in range(-70, 71):
+        parts = _naf(v)
+        assert sum(parts) == v
+        mags = [abs(p) for p in parts]
+        assert mags == sorted(mags) and all(m & (m - 1) == 0 for m in mags)
+        assert all(b >= 4 * a for a, b in zip(mags, mags[1:]))  # no two adjacent powers
