@@ -170,7 +170,7 @@ class KrumWorkload:
         n = ek.N
         per_limb = (n // 2) * (self.log_slots + 1)
         roofs = [ek.lb.butterfly_rate(v) / per_limb * 16 * n / 1e9 for v in (0, 3)]
-        return {"int_strict_60bit": roofs[0], "fp64_lazy_40bit": roofs[1], "chain_mean": 2.0 / (1.0 / roofs[0] + 1.0 / roofs[1])}
+        return {"int_strict_60bit": roofs[0], "fp64_40bit": roofs[1], "chain_mean": 2.0 / (1.0 / roofs[0] + 1.0 / roofs[1])}
 
     # -- CPU baseline -----------------------------------------------------------------------------------
     def cpu_sample(self, threads):
@@ -378,7 +378,7 @@ class NttWorkload:
         """arithmetic ceiling of the transform: the register-only butterfly rate converted to transform traffic"""
         per_limb = (self.N // 2) * self.logn
         to_gbs = lambda rate: rate / per_limb * 16 * self.N / 1e9
-        names = ["int_strict", "int_lazy", "fp64_strict", "fp64_lazy"]
+        names = ["int_strict", "int_lazy", "fp64_assisted", "fp64"]
         out = {n: to_gbs(self.ctx.butterfly_rate(i)) for i, n in enumerate(names)}
         out["this_workload"] = to_gbs(self.ctx.butterfly_rate())  # the variant this workload's primes take
         return out
@@ -403,4 +403,87 @@ class NttWorkload:
         return gb / dt, "%d x (NTT+INTT of %d polynomials, 24 limbs each)" % (reps, b), binding.max_threads()
 
 
-WORKLOADS = {"krum": KrumWorkload, "hmult": HmultWorkload, "ntt": NttWorkload}
+class EncryptWorkload:
+    """Fused encode + public-key encryption of float32 chunks at the 20-client round's parameters (N = 2^16, chain
+    {60,40,40|60}, 32768 slots): the phase that takes the largest share of a round, as a component benchmark and as the
+    small case for profiler captures of its kernels."""
+    name = "encrypt"
+    metric = "encode_encrypt_ciphertexts_per_s"
+    unit = "ciphertexts/s"
+    higher_is_better = True
+    dtype = "u64"
+    scaling = "weak"
+
+    def __init__(self, batch=342):
+        self.batch = int(batch)
+        self.log_slots = 15
+        self.slots = 1 << self.log_slots
+        self.launches_per_step = 0
+
+    def config(self):
+        return {"workload": "encode + encrypt of %d chunks of 32768 float32, N=2^16, chain {60,40,40|60}, scale 2^40" % self.batch,
+                "l2": "scratch and output of one call (%.2f GiB) exceed the 126 MB L2" % (self.batch * 27 * 2 * self.slots * 8 / 2 ** 30)}
+
+    def algorithmic_bytes_per_step(self):
+        # values in, ciphertext out; everything between is scratch
+        return self.batch * (self.slots * 4 + 6 * 2 * self.slots * 8)
+
+    def setup_gpu(self, device):
+        import torch
+        from lancelot_b200 import krum
+        self.torch = torch
+        self.ek = krum.EncryptedKrum(log_slots=self.log_slots, device=device, seed=1, encrypt_batch=max(self.batch, 64))
+        g = torch.Generator(device="cuda:%d" % device)
+        g.manual_seed(4)
+        self.vals = torch.randn(self.batch, self.slots, generator=g, device="cuda:%d" % device, dtype=torch.float32) * 1e-2
+        self.host = torch.empty(self.vals.shape, dtype=torch.float32).pin_memory()
+        self.host.copy_(self.vals)
+        self.seeds = self.ek.client_seeds(0, self.batch)
+        self.out = self.ek.lb.empty(self.batch, 2, 3, self.ek.N)
+        self.hout = torch.empty((2, 3, self.ek.N), dtype=torch.int64).pin_memory()
+
+    def step_gpu(self):
+        l0 = _launches()
+        self.ek.encrypt_chunks(self.vals, self.seeds, out=self.out)
+        self.launches_per_step = _launches() - l0
+
+    def step_e2e(self):
+        self.vals.copy_(self.host, non_blocking=True)
+        self.step_gpu()
+        self.hout.copy_(self.out[-1], non_blocking=True)  # the ciphertexts stay on the device; one is read back
+        return self.host.numel() * 4, self.hout.numel() * 8
+
+    def check_gpu(self):
+        """the last ciphertext against the CPU checker, bit for bit (same keys and seeds)"""
+        from oracle import binding
+        ek = self.ek
+        o = binding.Oracle(self.log_slots + 1, ek.context.moduli, 1, [])
+        pk = ek.pk.data.cpu().numpy().view(np.uint64)
+        k = self.batch - 1
+        v = self.host[k].numpy().astype(np.float64)
+        want = o.encrypt_asym(pk, o.encode(3, v, ek.scale, sparse_slots=self.slots), self.seeds[128 * k:128 * k + 64], self.seeds[128 * k + 64:128 * k + 128])
+        got = self.out[k].cpu().numpy().view(np.uint64)
+        return bool(np.array_equal(got.reshape(-1), want.reshape(-1)))
+
+    def units_per_step(self):
+        return float(self.batch)
+
+    def cpu_sample(self, threads):
+        binding = _oracle(threads)
+        n = 2 * self.slots
+        o = binding.Oracle(self.log_slots + 1, binding.coeff_modulus_create(n, KRUM_BITS), 1, [])
+        rng = np.random.default_rng(0)
+        seed = lambda k=1: rng.integers(0, 256, 64 * k, dtype=np.uint8)
+        sk = o.gen_sk(seed())
+        pk = o.gen_pk(sk, seed(), seed())
+        b = 2 * max(int(threads), 1)
+        vals = rng.normal(0, 1e-2, (b, self.slots))
+        seeds = seed(2 * b)
+        o.encode_encrypt_batch(pk, vals[:2], 2.0 ** 40, seeds[:256])
+        t0 = time.perf_counter()
+        o.encode_encrypt_batch(pk, vals, 2.0 ** 40, seeds)
+        dt = time.perf_counter() - t0
+        return b / dt, "%d encode+encrypt, one per thread at a time" % b, binding.max_threads()
+
+
+WORKLOADS = {"krum": KrumWorkload, "hmult": HmultWorkload, "ntt": NttWorkload, "encrypt": EncryptWorkload}

@@ -102,18 +102,21 @@ inline void cuda_check(cudaError_t e)
 // Seeds: the reference reads std::random_device for every key and encryption
 // (cahel-main/include/prng.cuh:12-23).  A replacement source makes runs reproducible.
 using SeedSource = std::function<void(std::uint8_t *out, std::size_t n_seeds)>;
+inline void system_seeds(std::uint8_t *out, std::size_t n)
+{
+    std::random_device rd("/dev/urandom");
+    for (std::size_t i = 0; i < n * 16; ++i) {
+        std::uint32_t w = rd();
+        std::memcpy(out + 4 * i, &w, 4);
+    }
+}
 inline SeedSource &seed_source()
 {
-    static SeedSource src = [](std::uint8_t *out, std::size_t n) {
-        std::random_device rd("/dev/urandom");
-        for (std::size_t i = 0; i < n * 16; ++i) {
-            std::uint32_t w = rd();
-            std::memcpy(out + 4 * i, &w, 4);
-        }
-    };
+    static SeedSource src = system_seeds;
     return src;
 }
-inline void set_seed_source(SeedSource s) { seed_source() = std::move(s); }
+inline void set_seed_source(SeedSource s) { seed_source() = s ? std::move(s) : SeedSource(system_seeds); }
+inline void reset_seed_source() { seed_source() = system_seeds; }
 inline std::vector<std::uint8_t> seeds(std::size_t n)
 {
     std::vector<std::uint8_t> s(64 * n);
@@ -710,6 +713,34 @@ struct CAHELGPUSecretKey {
             gen_switch_key(context, rotated.get(), glk.relin_keys_[i]);
         }
     }
+    // cahel-main/src/secretkey.cu:451-560: (c0, c1) = (-(a s + e) + pt, a) at the plaintext's level
+    void encrypt_symmetric(const CAHELGPUContext &context, const CAHELGPUPlaintext &plain, CAHELGPUCiphertext &cipher,
+                           bool save_seed = false) const
+    {
+        (void)save_seed;
+        if (!plain.is_ntt_form()) throw std::invalid_argument("CKKS plain must be in NTT form");
+        const int L = context.size_l(plain.chain_index());
+        const std::size_t poly = (std::size_t)L * context.poly_degree_;
+        cipher.resize(context, plain.chain_index(), 2);
+        auto s = cahel_b200::seeds(2);
+        cahel_b200::DeviceWords e(poly);
+        std::uint64_t *c0 = cipher.data(), *a = cipher.data() + poly;
+        cahel_b200::check(lb_sample_error(context.lb_handle_, s.data(), L, 0, e.get(), nullptr));
+        cahel_b200::check(lb_ntt_forward(context.lb_handle_, e.get(), 1, L, 0, nullptr));
+        cahel_b200::check(lb_sample_uniform(context.lb_handle_, s.data() + 64, L, 0, a, nullptr));
+        // the first L limbs of the key-level secret are its data-level limbs
+        cahel_b200::check(lb_multiply_poly(context.lb_handle_, L, 1, a, secret_key_array(), c0, nullptr));
+        cahel_b200::check(lb_add(context.lb_handle_, L, 1, c0, e.get(), c0, nullptr));
+        cahel_b200::check(lb_negate(context.lb_handle_, L, 1, c0, c0, nullptr));
+        cahel_b200::check(lb_add(context.lb_handle_, L, 1, c0, plain.data(), c0, nullptr));
+        cipher.scale() = plain.scale();
+    }
+    CAHELGPUCiphertext encrypt_symmetric(const CAHELGPUContext &context, const CAHELGPUPlaintext &plain, bool save_seed = false) const
+    {
+        CAHELGPUCiphertext c(context);
+        encrypt_symmetric(context, plain, c, save_seed);
+        return c;
+    }
     // ckks_decrypt without the noise-flooding term
     void decrypt(const CAHELGPUContext &context, const CAHELGPUCiphertext &cipher, CAHELGPUPlaintext &plain)
     {
@@ -1045,4 +1076,127 @@ inline CAHELGPUCiphertext hoisting(const CAHELGPUContext &context, const CAHELGP
     CAHELGPUCiphertext out = encrypted;
     hoisting_inplace(context, out, glk, steps);
     return out;
+}
+
+// ---- out-of-place forms and the remaining names of cahel-main/include/evaluate.h -------------------------------
+// (the reference writes them as copy + in-place call, evaluate.h:35-61,120-160,383-400,566-600)
+inline void add_plain(const CAHELGPUContext &context, const CAHELGPUCiphertext &encrypted, const CAHELGPUPlaintext &plain,
+                      CAHELGPUCiphertext &destination)
+{
+    if (&destination != &encrypted) destination = encrypted;
+    add_plain_inplace(context, destination, plain);
+}
+inline void sub_plain(const CAHELGPUContext &context, const CAHELGPUCiphertext &encrypted, const CAHELGPUPlaintext &plain,
+                      CAHELGPUCiphertext &destination)
+{
+    if (&destination != &encrypted) destination = encrypted;
+    sub_plain_inplace(context, destination, plain);
+}
+inline void multiply_plain(const CAHELGPUContext &context, const CAHELGPUCiphertext &encrypted, const CAHELGPUPlaintext &plain,
+                           CAHELGPUCiphertext &destination)
+{
+    if (&destination != &encrypted) destination = encrypted;
+    multiply_plain_inplace(context, destination, plain);
+}
+inline void square(const CAHELGPUContext &context, const CAHELGPUCiphertext &encrypted, CAHELGPUCiphertext &destination)
+{
+    if (&destination != &encrypted) destination = encrypted;
+    square_inplace(context, destination);
+}
+inline void relinearize(const CAHELGPUContext &context, const CAHELGPUCiphertext &encrypted, const CAHELGPURelinKey &relin_keys,
+                        CAHELGPUCiphertext &destination)
+{
+    if (&destination != &encrypted) destination = encrypted;
+    relinearize_inplace(context, destination, relin_keys);
+}
+inline void rescale_to_next(const CAHELGPUContext &context, const CAHELGPUCiphertext &encrypted, CAHELGPUCiphertext &destination)
+{
+    if (&destination != &encrypted) destination = encrypted;
+    rescale_to_next_inplace(context, destination);
+}
+inline void mod_switch_to_next(const CAHELGPUContext &context, const CAHELGPUCiphertext &encrypted, CAHELGPUCiphertext &destination)
+{
+    if (&destination != &encrypted) destination = encrypted;
+    mod_switch_to_next_inplace(context, destination);
+}
+inline void mod_switch_to(const CAHELGPUContext &context, const CAHELGPUCiphertext &encrypted, CAHELGPUCiphertext &destination,
+                          std::size_t chain_index)
+{
+    if (&destination != &encrypted) destination = encrypted;
+    mod_switch_to_inplace(context, destination, chain_index);
+}
+// plaintexts in NTT form drop their last limb like ciphertexts do (cahel-main/src/evaluate.cu:2253-2300)
+inline void mod_switch_to_next_inplace(const CAHELGPUContext &context, CAHELGPUPlaintext &plain)
+{
+    if (plain.chain_index() >= context.max_chain()) throw std::invalid_argument("end of modulus switching chain reached");
+    const int L = context.size_l(plain.chain_index());
+    cahel_b200::DeviceWords out((std::size_t)(L - 1) * context.poly_degree_);
+    cahel_b200::check(lb_mod_switch_drop(context.lb_handle_, L, 1, plain.data(), out.get(), nullptr));
+    plain.data_ = std::move(out);
+    plain.chain_index() += 1;
+    plain.coeff_modulus_size_ = (std::size_t)(L - 1);
+}
+inline void mod_switch_to_inplace(const CAHELGPUContext &context, CAHELGPUPlaintext &plain, std::size_t chain_index)
+{
+    if (plain.chain_index() > chain_index) throw std::invalid_argument("cannot switch to higher level modulus");
+    while (plain.chain_index() < chain_index) mod_switch_to_next_inplace(context, plain);
+}
+inline void mod_switch_to_next(const CAHELGPUContext &context, const CAHELGPUPlaintext &plain, CAHELGPUPlaintext &destination)
+{
+    if (&destination != &plain) destination = plain;
+    mod_switch_to_next_inplace(context, destination);
+}
+inline void mod_switch_to(const CAHELGPUContext &context, const CAHELGPUPlaintext &plain, CAHELGPUPlaintext &destination, std::size_t chain_index)
+{
+    if (&destination != &plain) destination = plain;
+    mod_switch_to_inplace(context, destination, chain_index);
+}
+inline void apply_galois(const CAHELGPUContext &context, const CAHELGPUCiphertext &encrypted, std::size_t galois_elt_index,
+                         const CAHELGPUGaloisKey &galois_keys, CAHELGPUCiphertext &destination)
+{
+    if (&destination != &encrypted) destination = encrypted;
+    apply_galois_inplace(context, destination, galois_elt_index, galois_keys);
+}
+// conjugation is the Galois element 2N - 1 (cahel-main/include/evaluate.h:577-600)
+inline void complex_conjugate_inplace(const CAHELGPUContext &context, CAHELGPUCiphertext &encrypted, const CAHELGPUGaloisKey &galois_key)
+{
+    const int idx = context.elt_index((std::uint32_t)(2 * context.poly_degree_ - 1));
+    if (idx < 0) throw std::logic_error("Galois key not present");
+    apply_galois_inplace(context, encrypted, (std::size_t)idx, galois_key);
+}
+inline void complex_conjugate(const CAHELGPUContext &context, const CAHELGPUCiphertext &encrypted, const CAHELGPUGaloisKey &galois_key,
+                              CAHELGPUCiphertext &destination)
+{
+    if (&destination != &encrypted) destination = encrypted;
+    complex_conjugate_inplace(context, destination, galois_key);
+}
+// Names the reference exports for its BFV / BGV schemes or that fall outside the encrypted-aggregation path; they
+// exist so that code written against the reference still links, and refuse at run time.
+inline void rotate_rows_inplace(const CAHELGPUContext &, CAHELGPUCiphertext &, int, const CAHELGPUGaloisKey &)
+{
+    throw std::logic_error("unsupported scheme: rotate_rows is a BFV / BGV operation");
+}
+inline void rotate_rows(const CAHELGPUContext &, const CAHELGPUCiphertext &, int, const CAHELGPUGaloisKey &, CAHELGPUCiphertext &)
+{
+    throw std::logic_error("unsupported scheme: rotate_rows is a BFV / BGV operation");
+}
+inline void rotate_columns_inplace(const CAHELGPUContext &, CAHELGPUCiphertext &, const CAHELGPUGaloisKey &)
+{
+    throw std::logic_error("unsupported scheme: rotate_columns is a BFV / BGV operation");
+}
+inline void rotate_columns(const CAHELGPUContext &, const CAHELGPUCiphertext &, const CAHELGPUGaloisKey &, CAHELGPUCiphertext &)
+{
+    throw std::logic_error("unsupported scheme: rotate_columns is a BFV / BGV operation");
+}
+inline void exponentiate_inplace(const CAHELGPUContext &, CAHELGPUCiphertext &, std::uint64_t, const CAHELGPURelinKey &)
+{
+    throw std::logic_error("exponentiate is not part of the encrypted-aggregation path");
+}
+inline void exponentiate(const CAHELGPUContext &, const CAHELGPUCiphertext &, std::uint64_t, const CAHELGPURelinKey &, CAHELGPUCiphertext &)
+{
+    throw std::logic_error("exponentiate is not part of the encrypted-aggregation path");
+}
+inline void multiply_many(const CAHELGPUContext &, std::vector<CAHELGPUCiphertext> &, const CAHELGPURelinKey &, CAHELGPUCiphertext &)
+{
+    throw std::logic_error("multiply_many is not part of the encrypted-aggregation path");
 }

@@ -74,16 +74,22 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) butterfly_probe
     u64 v[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = (u64)threadIdx.x * 8 + i + blockIdx.x;
-    const u64 q2 = q << 1;
+    if (MODE == kF64) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = bits_of(f64_from_u52(v[i]));
+    }
+    const u64 q2 = bf_scalar_q2<MODE>(q), q1 = bf_scalar_q<MODE>(q);
     for (int it = 0; it < iters; ++it) {
 #pragma unroll
         for (int s = 0; s < 3; ++s) {
             const int half = 4 >> s;
 #pragma unroll
             for (int b = 0; b < (1 << s); ++b) {
-                const ulonglong2 w = make_ulonglong2(w0 + threadIdx.x + b, ws0 + threadIdx.x + s);
+                // twiddles that differ per thread and stage, so that nothing is hoisted out of the loop
+                const ulonglong2 w = MODE == kF64 ? make_ulonglong2(bits_of(f64_of(w0) + (double)(threadIdx.x + b)), bits_of(f64_of(ws0) * (double)(1 + s)))
+                                                  : make_ulonglong2(w0 + threadIdx.x + b, ws0 + threadIdx.x + s);
 #pragma unroll
-                for (int i = 0; i < half; ++i) fwd_bf<MODE>(v[b * 2 * half + i], v[b * 2 * half + i + half], w, q, q2);
+                for (int i = 0; i < half; ++i) fwd_bf<MODE>(v[b * 2 * half + i], v[b * 2 * half + i + half], w, q1, q2);
             }
         }
         // keep the lazy ranges bounded, as the closing reduction does
@@ -91,9 +97,9 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) butterfly_probe
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] &= 0x03FFFFFFFFFFFFFFull;
         }
-        if (MODE == kFpLazy) {
+        if (MODE == kF64) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] &= 0x0003FFFFFFFFFFFFull;
+            for (int i = 0; i < 8; ++i) v[i] = bits_of(f64_centre(f64_of(v[i]), f64_of(q1), f64_of(q2)));
         }
     }
     u64 acc = 0;
@@ -102,15 +108,15 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) butterfly_probe
     out[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = acc;
 }
 
-// mode: 0 integer strict, 1 integer lazy, 2 FP64-assisted strict, 3 FP64-assisted lazy,
+// mode: 0 integer strict, 1 integer lazy, 2 FP64-assisted (quotient on the FP64 pipe), 3 all on the FP64 pipe,
 // -1 the variant the context's first prime takes.
 int probe_butterfly_rate(Context *ctx, int mode, double *butterflies_per_second)
 {
     if (mode < 0) {
         const u64 q0 = ctx->hp.q[0];
-        mode = q0 < kFpLazyLimit ? kFpLazy : q0 < kFpPrimeLimit ? kFpStrict : (q0 >> 58) == 0 ? kIntLazy : kIntStrict;
+        mode = q0 < kF64PrimeLimit ? kF64 : q0 < kFpPrimeLimit ? kFpStrict : (q0 >> 58) == 0 ? kIntLazy : kIntStrict;
     }
-    if (mode > kFpLazy) {
+    if (mode > kF64) {
         set_error("butterfly variant must be 0..3 or -1");
         return LB_ERR_INVALID_ARG;
     }
@@ -120,7 +126,7 @@ int probe_butterfly_rate(Context *ctx, int mode, double *butterflies_per_second)
     u64 *out = reinterpret_cast<u64 *>(ctx->ws);
     // any odd modulus of the variant's size gives the variant's instruction stream
     static const u64 size_of_mode[4] = {(u64(1) << 60) - 93, (u64(1) << 50) - 27, (u64(1) << 49) - 69, (u64(1) << 40) - 87};
-    const u64 q = size_of_mode[mode], w = q / 3, ws = mode >= kFpStrict ? h_fp_quot(w, q) : h_shoup(w, q);
+    const u64 q = size_of_mode[mode], w = h_twiddle_value(q / 3, q), ws = h_twiddle_quot(q / 3, q);
     cudaEvent_t e0, e1;
     LB_CUDA(cudaEventCreate(&e0));
     LB_CUDA(cudaEventCreate(&e1));
@@ -132,7 +138,7 @@ int probe_butterfly_rate(Context *ctx, int mode, double *butterflies_per_second)
         case kIntStrict: butterfly_probe_kernel<kIntStrict><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
         case kIntLazy: butterfly_probe_kernel<kIntLazy><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
         case kFpStrict: butterfly_probe_kernel<kFpStrict><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
-        default: butterfly_probe_kernel<kFpLazy><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
+        default: butterfly_probe_kernel<kF64><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
         }
         LB_CUDA(cudaEventRecord(e1, 0));
         LB_CUDA(cudaEventSynchronize(e1));

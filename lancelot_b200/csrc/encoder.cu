@@ -459,11 +459,11 @@ __global__ void __launch_bounds__(256) compose_kernel(cplx *__restrict__ out, co
                 x[i] = d;
             }
         }
-        double val = 0.0, rad = 1.0;
-        for (int i = 0; i < W; ++i) {
-            val += (double)x[i] * rad;
-            rad *= 18446744073709551616.0;
-        }
+        // only the non-zero words count: with many limbs 2^(64 i) leaves the range of a double long before the
+        // words of a centred coefficient stop being zero, and 0 * inf would poison the sum
+        double val = 0.0;
+        for (int i = 0; i < W; ++i)
+            if (x[i]) val += ldexp((double)x[i], 64 * i);
         if (gt) val = -val;
         val *= inv_scale;
         if (id < n) out[id].x = val;

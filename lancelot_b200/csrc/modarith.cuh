@@ -64,23 +64,30 @@ inline u64 h_shoup(u64 w, u64 q)
 inline u64 h_shoup(u64 w, u64 q) { return (u64)(((u128)w << 64) / q); }
 #endif
 
-// ---- quotient estimate on the FP64 pipe ---------------------------------------------------
-// For primes below 2^50 the transform kernels estimate the quotient floor(x w / q) with one
-// double-precision fused multiply-add instead of a 64 x 64 -> 128 bit integer product: the
-// integer multiplier then only has to produce the two low products x w and Q q.  The twiddle
-// tables of such primes carry the double w / q in place of the Shoup quotient.
-constexpr u64 kFpPrimeLimit = u64(1) << 50; // operands stay below 4q <= 2^52, the exact-integer range of the trick
-constexpr u64 kFpLazyLimit = u64(1) << 46;  // 35 q < 2^52: no conditional subtraction for seventeen stages
+// ---- the FP64 pipe in the transform kernels -----------------------------------------------------
+// Primes of [2^47, 2^50): the quotient floor(x w / q) is estimated with one double-precision fused
+// multiply-add instead of a 64 x 64 -> 128 bit integer product; the integer multiplier then only has
+// to produce the two low products x w and Q q.  Their twiddle entries are (w, double(w / q)).
+// Primes below 2^47: the whole butterfly runs on the FP64 pipe.  Residues travel through the
+// transform as integer-valued doubles (their bit patterns sit in the same 64-bit words), products
+// are formed error-free with fused multiply-adds, and values may grow over all stages without a
+// reduction (13 q < 2^51).  Their twiddle entries are (double(w), double(w / q)).
+constexpr u64 kFpPrimeLimit = u64(1) << 50; // operands stay below 4q <= 2^52, the exact-integer range of the estimate
+constexpr u64 kF64PrimeLimit = u64(1) << 47;
 
-inline u64 h_fp_quot(u64 w, u64 q)
+inline u64 h_bits_of(double d)
 {
-    const double d = (double)w / (double)q; // both exact in double, so the quotient is correctly rounded
     u64 bits;
     static_assert(sizeof(bits) == sizeof(d), "double is 64 bits");
     __builtin_memcpy(&bits, &d, sizeof(bits));
     return bits;
 }
-// the second word of a twiddle-table entry for prime q
+inline u64 h_fp_quot(u64 w, u64 q)
+{
+    return h_bits_of((double)w / (double)q); // both exact in double, so the quotient is correctly rounded
+}
+// the two words of a twiddle-table entry for the power w of a root modulo prime q
+inline u64 h_twiddle_value(u64 w, u64 q) { return q < kF64PrimeLimit ? h_bits_of((double)w) : w; }
 inline u64 h_twiddle_quot(u64 w, u64 q) { return q < kFpPrimeLimit ? h_fp_quot(w, q) : h_shoup(w, q); }
 
 #if defined(__CUDACC__)
@@ -96,6 +103,40 @@ LB_D u64 fp_mul_signed(u64 x, u64 w, u64 wq, u64 q)
     const double u = __fma_rn(xd, __longlong_as_double((long long)wq), 4503599627370496.0);
     const u64 Q = (u64)__double_as_longlong(u) & 0x000FFFFFFFFFFFFFull;
     return x * w - Q * q;
+}
+
+// ---- residues as integer-valued doubles (primes below 2^47) --------------------------------------
+LB_D double f64_of(u64 bits) { return __longlong_as_double((long long)bits); }
+LB_D u64 bits_of(double d) { return (u64)__double_as_longlong(d); }
+// an integer below 2^52 as a double: its bits under the exponent of 2^52, minus 2^52
+LB_D double f64_from_u52(u64 x) { return __dadd_rn(__longlong_as_double((long long)(x | 0x4330000000000000ull)), -4503599627370496.0); }
+// back: a double holding an integer of [0, 2^52)
+LB_D u64 u52_from_f64(double d) { return (u64)__double_as_longlong(__dadd_rn(d, 4503599627370496.0)) & 0x000FFFFFFFFFFFFFull; }
+
+// r = y w - Q q with Q the integer nearest to y w / q: r is congruent to y w and |r| <= 0.75 q.
+// Needs integer-valued |y| < 2^51, w < q < 2^47, wq = double(w / q).  y w is split error-free into
+// h + l (l = fma(y, w, -h) is exact); Q comes from one fused multiply-add into 1.5 * 2^52, whose
+// rounding is the rounding to an integer (|y wq| < 2^51 keeps the sum inside [2^52, 2^53)); the
+// estimate is off by at most 0.5 + 2^-2.  h - Q q = (y w - Q q) - l is an integer below 2^50 in
+// magnitude, so the second fused multiply-add is exact, and so is the final sum.
+LB_D double f64_mulmod(const double y, const double w, const double wq, const double q)
+{
+    const double h = __dmul_rn(y, w);
+    const double l = __fma_rn(y, w, -h);
+    const double Q = __dadd_rn(__fma_rn(y, wq, 6755399441055744.0), -6755399441055744.0);
+    return __dadd_rn(__fma_rn(-Q, q, h), l);
+}
+// the residue of an integer-valued |v| < 2^52 nearest to zero: |result| <= q / 2 (+ rounding of 1 / q)
+LB_D double f64_centre(const double v, const double q, const double qinv)
+{
+    const double Q = __dadd_rn(__fma_rn(v, qinv, 6755399441055744.0), -6755399441055744.0);
+    return __fma_rn(-Q, q, v);
+}
+// the canonical residue in [0, q) as an integer
+LB_D u64 f64_canon(const double v, const double q, const double qinv)
+{
+    const double r = f64_centre(v, q, qinv);
+    return u52_from_f64(r < 0.0 ? __dadd_rn(r, q) : r);
 }
 
 // x * w mod q in [0, 2q) for any 64-bit x, given ws = floor(w 2^64 / q), w < q.

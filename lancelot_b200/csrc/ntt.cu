@@ -96,8 +96,10 @@ LB_D void fwd_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ tw, const un
 }
 
 // S consecutive inverse stages; stage u pairs distance 2^u and uses twiddle (tb >> u) + block.
-// CLOSE: the last of them is the transform's last stage and carries the N^-1 scaling.
-template <int S, bool CLOSE, bool FP>
+// CLOSE: the last of them is the transform's last stage and carries the N^-1 scaling; it leaves
+// canonical residues (as integers in every mode).  In kInvF64 mode q, q2 carry double(q), double(1 / q)
+// and (cn, cns), (cw, cws) the closing constants and their quotients by q, all as doubles.
+template <int S, bool CLOSE, int IM>
 LB_D void inv_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ itw, const unsigned tb, const u64 q, const u64 q2,
                    const u64 cn, const u64 cns, const u64 cw, const u64 cws)
 {
@@ -110,14 +112,20 @@ LB_D void inv_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ itw, const u
 #pragma unroll
                 for (int i = 0; i < dist; ++i) {
                     u64 &x = v[b * 2 * dist + i], &y = v[b * 2 * dist + i + dist];
-                    const u64 s = x + y, d = x + q2 - y;
-                    x = shoup_mul(s, cn, cns, q);
-                    y = shoup_mul(d, cw, cws, q);
+                    if (IM == kInvF64) {
+                        const double xd = f64_of(x), yd = f64_of(y), qd = f64_of(q), qi = f64_of(q2);
+                        x = f64_canon(f64_mulmod(__dadd_rn(xd, yd), f64_of(cn), f64_of(cns), qd), qd, qi);
+                        y = f64_canon(f64_mulmod(__dadd_rn(xd, -yd), f64_of(cw), f64_of(cws), qd), qd, qi);
+                    } else {
+                        const u64 s = x + y, d = x + q2 - y;
+                        x = shoup_mul(s, cn, cns, q);
+                        y = shoup_mul(d, cw, cws, q);
+                    }
                 }
             } else {
                 const ulonglong2 w = __ldg(itw + ((tb >> u) + b));
 #pragma unroll
-                for (int i = 0; i < dist; ++i) inv_bf<FP>(v[b * 2 * dist + i], v[b * 2 * dist + i + dist], w, q, q2);
+                for (int i = 0; i < dist; ++i) inv_bf<IM>(v[b * 2 * dist + i], v[b * 2 * dist + i + dist], w, q, q2);
             }
         }
     }
@@ -234,15 +242,23 @@ LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, 
         if (from_global) {
 #pragma unroll
             for (int i = 0; i < R; ++i) v[i] = load_in(in, base + (i << logst));
+            if (MODE == kF64) {
+#pragma unroll
+                for (int i = 0; i < R; ++i) v[i] = bits_of(f64_from_u52(v[i]));
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < R; ++i) v[i] = sm[sidx(base + (i << logst))];
         }
         fwd_core<S, MODE>(v, tw, (cc << logm0) + hi, q, q2);
         if (gdst) { // closing pass: logst == 0, the 2^S results are contiguous
-            if (MODE == kIntLazy || MODE == kFpLazy) {
+            const u64 qi = in.q; // the prime as an integer (q, q2 are the butterflies' scalars)
+            if (MODE == kF64) {
 #pragma unroll
-                for (int i = 0; i < R; ++i) v[i] = barrett64(v[i], q, in.r1);
+                for (int i = 0; i < R; ++i) v[i] = f64_canon(f64_of(v[i]), f64_of(q), f64_of(q2));
+            } else if (MODE == kIntLazy) {
+#pragma unroll
+                for (int i = 0; i < R; ++i) v[i] = barrett64(v[i], qi, in.r1);
             } else {
 #pragma unroll
                 for (int i = 0; i < R; ++i) v[i] = csub(csub(v[i], q2), q);
@@ -251,11 +267,11 @@ LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, 
                 u64 t[R];
                 load_contig<R>(t, epi.aux + base);
 #pragma unroll
-                for (int i = 0; i < R; ++i) v[i] = shoup_mul(sub_mod(t[i], v[i], q), epi.scal, epi.scal_s, q);
+                for (int i = 0; i < R; ++i) v[i] = shoup_mul(sub_mod(t[i], v[i], qi), epi.scal, epi.scal_s, qi);
                 if (epi.add) {
                     load_contig<R>(t, epi.add + base);
 #pragma unroll
-                    for (int i = 0; i < R; ++i) v[i] = add_mod(v[i], t[i], q);
+                    for (int i = 0; i < R; ++i) v[i] = add_mod(v[i], t[i], qi);
                 }
             }
             store_contig<R>(v, gdst + base);
@@ -348,8 +364,9 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(
     FwdEpi &epi = fr.epi;
     u64 *dst = fr.dst;
     const ulonglong2 *tw = fr.tw;
-    const u64 q = fr.q, q2 = q << 1;
     const int mode = fr.mode;
+    // the butterflies' two scalars: (q, 2q), or (double(q), double(1 / q)) when they run on the FP64 pipe
+    const u64 q = mode == kF64 ? bf_scalar_q<kF64>(fr.q) : fr.q, q2 = mode == kF64 ? bf_scalar_q2<kF64>(fr.q) : fr.q << 1;
     const int logn_loc = a.logN - LOGC, n_loc = 1 << logn_loc;
 
     unsigned c = 0;
@@ -368,8 +385,12 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(
             u64 v[C];
 #pragma unroll
             for (int k = 0; k < C; ++k) v[k] = load_in(in, j + k * n_loc);
+            if (mode == kF64) {
+#pragma unroll
+                for (int k = 0; k < C; ++k) v[k] = bits_of(f64_from_u52(v[k]));
+            }
             switch (mode) {
-            case kFpLazy: fwd_core<LOGC, kFpLazy>(v, tw, 1u, q, q2); break;
+            case kF64: fwd_core<LOGC, kF64>(v, tw, 1u, q, q2); break;
             case kFpStrict: fwd_core<LOGC, kFpStrict>(v, tw, 1u, q, q2); break;
             case kIntLazy: fwd_core<LOGC, kIntLazy>(v, tw, 1u, q, q2); break;
             default: fwd_core<LOGC, kIntStrict>(v, tw, 1u, q, q2); break;
@@ -395,7 +416,7 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(
         u64 *gdst = (p == a.npass - 1) ? dst + (size_t)c * n_loc : nullptr;
         const int wlog = p < a.nwide ? -1 : a.wlog;
         switch (mode) {
-        case kFpLazy: fwd_pass_any<kFpLazy>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
+        case kF64: fwd_pass_any<kF64>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
         case kFpStrict: fwd_pass_any<kFpStrict>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
         case kIntLazy: fwd_pass_any<kIntLazy>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
         default: fwd_pass_any<kIntStrict>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
@@ -410,10 +431,34 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(
 
 // ---- inverse --------------------------------------------------------------------------
 
-template <int S, bool CLOSE, bool FP>
+// Stages a run of FP64 inverse butterflies may take before the sums, which double per stage, must be brought
+// back to the residue nearest zero: operands of a butterfly stay below 2^50 (their difference below 2^51).
+// `fresh`: the run starts from canonical residues below 2^bits; otherwise from |v| <= 2^(bits - 1).
+struct F64Run {
+    int bits, since, allowed;
+    LB_D explicit F64Run(const u64 q) : bits(0), since(0), allowed(0)
+    {
+        while (bits < 64 && (q >> bits) != 0) ++bits; // q < 2^bits
+        allowed = 51 - bits;
+    }
+    // true: reduce before the next `stages` stages
+    LB_D bool before(const int stages)
+    {
+        const bool reduce = since + stages > allowed;
+        if (reduce) {
+            since = 0;
+            allowed = 52 - bits;
+        }
+        since += stages;
+        return reduce;
+    }
+};
+
+// IM == kInvF64: `reduce` asks for the centred reduction of the loaded values (see F64Run)
+template <int S, bool CLOSE, int IM>
 LB_D void inv_pass(u64 *sm, const u64 *gsrc, u64 *gdst, const int logn_loc, const int logt, const unsigned cc,
                    const ulonglong2 *itw, const u64 q, const u64 q2, const u64 cn, const u64 cns, const u64 cw,
-                   const u64 cws, const int wlog)
+                   const u64 cws, const int wlog, const bool reduce)
 {
     constexpr int R = 1 << S;
     const int logst = logt;
@@ -426,11 +471,19 @@ LB_D void inv_pass(u64 *sm, const u64 *gsrc, u64 *gdst, const int logn_loc, cons
         u64 v[R];
         if (gsrc) { // opening pass: logst == 0, contiguous
             load_contig<R>(v, gsrc + base);
+            if (IM == kInvF64) {
+#pragma unroll
+                for (int i = 0; i < R; ++i) v[i] = bits_of(f64_from_u52(v[i]));
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < R; ++i) v[i] = sm[sidx(base + (i << logst))];
+            if (IM == kInvF64 && reduce) {
+#pragma unroll
+                for (int i = 0; i < R; ++i) v[i] = bits_of(f64_centre(f64_of(v[i]), f64_of(q), f64_of(q2)));
+            }
         }
-        inv_core<S, CLOSE, FP>(v, itw, (cc << logm0) + (hi << (S - 1)), q, q2, cn, cns, cw, cws);
+        inv_core<S, CLOSE, IM>(v, itw, (cc << logm0) + (hi << (S - 1)), q, q2, cn, cns, cw, cws);
         if (gdst) {
 #pragma unroll
             for (int i = 0; i < R; ++i) gdst[base + (i << logst)] = v[i];
@@ -441,16 +494,38 @@ LB_D void inv_pass(u64 *sm, const u64 *gsrc, u64 *gdst, const int logn_loc, cons
     }
 }
 
-template <bool CLOSE, bool FP>
+template <bool CLOSE, int IM>
 LB_D void inv_pass_any(const int S, u64 *sm, const u64 *gsrc, u64 *gdst, const int logn_loc, const int logt, const unsigned cc,
                        const ulonglong2 *itw, const u64 q, const u64 q2, const u64 cn, const u64 cns, const u64 cw, const u64 cws,
-                       const int wlog)
+                       const int wlog, const bool reduce)
 {
     constexpr int RMAX = LB_NTT_MAX_RADIX_LOG >= 4 ? 4 : 3;
-    if (RMAX == 4 && S == 4) inv_pass<RMAX, CLOSE, FP>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
-    else if (S == 3) inv_pass<3, CLOSE, FP>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
-    else if (S == 2) inv_pass<2, CLOSE, FP>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
-    else inv_pass<1, CLOSE, FP>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
+    if (RMAX == 4 && S == 4) inv_pass<RMAX, CLOSE, IM>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, reduce);
+    else if (S == 3) inv_pass<3, CLOSE, IM>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, reduce);
+    else if (S == 2) inv_pass<2, CLOSE, IM>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, reduce);
+    else inv_pass<1, CLOSE, IM>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, reduce);
+}
+
+// The closing constants of an inverse transform for the butterflies' mode: integers with their Shoup quotients,
+// or (kInvF64) the constants and their quotients by q as doubles.
+struct InvConst {
+    u64 q, q2, cn, cns, cw, cws;
+};
+LB_D InvConst inv_constants(const int im, const u64 q, const u64 cn, const u64 cns, const u64 cw, const u64 cws)
+{
+    InvConst k;
+    if (im == kInvF64) {
+        const double qd = (double)q;
+        k.q = bits_of(qd);
+        k.q2 = bits_of(1.0 / qd);
+        k.cn = bits_of((double)cn);
+        k.cns = bits_of((double)cn / qd);
+        k.cw = bits_of((double)cw);
+        k.cws = bits_of((double)cw / qd);
+    } else {
+        k.q = q; k.q2 = q << 1; k.cn = cn; k.cns = cns; k.cw = cw; k.cws = cws;
+    }
+    return k;
 }
 
 template <int LOGC>
@@ -477,7 +552,9 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_inv_kernel(
     unsigned c = 0;
     if constexpr (LOGC > 0) c = cg::this_cluster().block_rank();
     const unsigned cc = C + c;
-    const bool fp = q < kFpPrimeLimit;
+    const int im = inverse_mode(q);
+    const InvConst ic = inv_constants(im, q, cn, cns, cw, cws);
+    F64Run run(q);
     int logt = 0;
     for (int p = 0; p < a.npass; ++p) {
         const int S = a.S[p];
@@ -489,12 +566,16 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_inv_kernel(
             if (wlog < 0) __syncthreads();
             else __syncwarp();
         }
-        if (fp) {
-            if (closing) inv_pass_any<true, true>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
-            else inv_pass_any<false, true>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
+        const bool red = run.before(S);
+        if (im == kInvF64) {
+            if (closing) inv_pass_any<true, kInvF64>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, ic.q, ic.q2, ic.cn, ic.cns, ic.cw, ic.cws, wlog, red);
+            else inv_pass_any<false, kInvF64>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, ic.q, ic.q2, ic.cn, ic.cns, ic.cw, ic.cws, wlog, red);
+        } else if (im == kInvFp) {
+            if (closing) inv_pass_any<true, kInvFp>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, false);
+            else inv_pass_any<false, kInvFp>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, false);
         } else {
-            if (closing) inv_pass_any<true, false>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
-            else inv_pass_any<false, false>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog);
+            if (closing) inv_pass_any<true, kInvInt>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, false);
+            else inv_pass_any<false, kInvInt>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, false);
         }
         logt += S;
     }
@@ -505,15 +586,25 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_inv_kernel(
 #pragma unroll
         for (int k = 0; k < C; ++k) remote[k] = cluster.map_shared_rank(sm, k);
         const int share = n_loc >> LOGC;
+        const bool red = run.before(LOGC);
         for (int jj = threadIdx.x; jj < share; jj += kNttThreads) {
             const int j = c * share + jj;
             u64 v[C];
 #pragma unroll
-            for (int k = 0; k < C; ++k) v[k] = remote[k][sidx(j)];
-            if (fp) inv_core<LOGC, true, true>(v, itw, C / 2, q, q2, cn, cns, cw, cws);
-            else inv_core<LOGC, true, false>(v, itw, C / 2, q, q2, cn, cns, cw, cws);
+            for (int kk = 0; kk < C; ++kk) v[kk] = remote[kk][sidx(j)];
+            if (im == kInvF64) {
+                if (red) {
 #pragma unroll
-            for (int k = 0; k < C; ++k) dst[j + k * n_loc] = v[k];
+                    for (int kk = 0; kk < C; ++kk) v[kk] = bits_of(f64_centre(f64_of(v[kk]), f64_of(ic.q), f64_of(ic.q2)));
+                }
+                inv_core<LOGC, true, kInvF64>(v, itw, C / 2, ic.q, ic.q2, ic.cn, ic.cns, ic.cw, ic.cws);
+            } else if (im == kInvFp) {
+                inv_core<LOGC, true, kInvFp>(v, itw, C / 2, q, q2, cn, cns, cw, cws);
+            } else {
+                inv_core<LOGC, true, kInvInt>(v, itw, C / 2, q, q2, cn, cns, cw, cws);
+            }
+#pragma unroll
+            for (int kk = 0; kk < C; ++kk) dst[j + kk * n_loc] = v[kk];
         }
         cluster.sync(); // shared memory stays alive until every peer has read it
     }
@@ -567,10 +658,11 @@ LB_D int fixed_group(const int it)
 // conversions is compiled in (sixteen inlined copies of the input ones make the instruction stream
 // of this pass miss the cache).
 template <int LOGC, int MODE, bool PLAIN>
-LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulonglong2 *tw, const u64 q, const u64 q2)
+LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulonglong2 *tw, const u64 bq, const u64 bq2)
 {
     constexpr int F = LOGC + 1, R0 = 1 << F, COLS = kHalfLoc >> LOGC;
     const uint32_t sbase = smem_addr(sm);
+    const u64 q = in.q; // the prime as an integer for the loaders; bq, bq2 are the butterflies' scalars
     for (int col = threadIdx.x; col < COLS; col += 256) {
         const int j = c * COLS + col;
         u64 v[R0];
@@ -628,7 +720,11 @@ LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulon
 #pragma unroll
             for (int k = 0; k < R0; ++k) v[k] = load_in(in, j + k * kHalfLoc);
         }
-        fwd_core<F, MODE>(v, tw, 1u, q, q2);
+        if (MODE == kF64) {
+#pragma unroll
+            for (int k = 0; k < R0; ++k) v[k] = bits_of(f64_from_u52(v[k]));
+        }
+        fwd_core<F, MODE>(v, tw, 1u, bq, bq2);
         const int s0 = sidx(j);
         if constexpr (LOGC == 0) {
             sm[s0] = v[0];
@@ -647,9 +743,10 @@ LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulon
 }
 
 // three forward stages starting at span 2^LOGT
+// q, q2: the butterflies' scalars; qi, r1: the prime as an integer and floor(2^64 / q) for the closing pass
 template <int LOGT, int MODE, bool PLAIN = false>
-LB_D void fwd_pass_fixed(u64 *sm, u64 *gdst, const unsigned cc, const ulonglong2 *tw, const u64 q, const u64 q2, const u64 r1,
-                         const FwdEpi &epi)
+LB_D void fwd_pass_fixed(u64 *sm, u64 *gdst, const unsigned cc, const ulonglong2 *tw, const u64 q, const u64 q2, const u64 qi,
+                         const u64 r1, const FwdEpi &epi)
 {
     constexpr int LOGST = LOGT - 2;
     constexpr bool WIDE = LOGT + 1 > 10, CLOSING = LOGST == 0;
@@ -666,20 +763,23 @@ LB_D void fwd_pass_fixed(u64 *sm, u64 *gdst, const unsigned cc, const ulonglong2
         for (int i = 0; i < 8; ++i) v[i] = p[pad_off<LOGST>(i)];
         fwd_core<3, MODE>(v, tw, (cc << (12 - LOGT)) + hi, q, q2);
         if constexpr (CLOSING) {
-            if (MODE == kIntLazy || MODE == kFpLazy) {
+            if (MODE == kF64) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = barrett64(v[i], q, r1);
+                for (int i = 0; i < 8; ++i) v[i] = f64_canon(f64_of(v[i]), f64_of(q), f64_of(q2));
+            } else if (MODE == kIntLazy) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = barrett64(v[i], qi, r1);
             } else {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] = csub(csub(v[i], q2), q);
             }
             if (!PLAIN && epi.aux) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = shoup_mul(sub_mod(t[i], v[i], q), epi.scal, epi.scal_s, q);
+                for (int i = 0; i < 8; ++i) v[i] = shoup_mul(sub_mod(t[i], v[i], qi), epi.scal, epi.scal_s, qi);
                 if (epi.add) {
                     load_contig<8>(t, epi.add + base);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] = add_mod(v[i], t[i], q);
+                    for (int i = 0; i < 8; ++i) v[i] = add_mod(v[i], t[i], qi);
                 }
             }
             store_contig<8>(v, gdst + base);
@@ -693,18 +793,18 @@ LB_D void fwd_pass_fixed(u64 *sm, u64 *gdst, const unsigned cc, const ulonglong2
 template <int LOGC, int MODE, bool PLAIN>
 LB_D void fwd_body_fixed(u64 *sm, const FwdRow &fr, const unsigned c)
 {
-    const u64 q = fr.q, q2 = q << 1;
+    const u64 q = bf_scalar_q<MODE>(fr.q), q2 = bf_scalar_q2<MODE>(fr.q);
     const unsigned cc = (1u << LOGC) + c;
     fwd_first_fixed<LOGC, MODE, PLAIN>(sm, fr.in, c, fr.tw, q, q2);
     if constexpr (LOGC > 0) cg::this_cluster().sync(); // all scatters into this CTA have landed
     else __syncthreads();
-    fwd_pass_fixed<11, MODE>(sm, nullptr, cc, fr.tw, q, q2, fr.in.r1, fr.epi);
+    fwd_pass_fixed<11, MODE>(sm, nullptr, cc, fr.tw, q, q2, fr.q, fr.in.r1, fr.epi);
     __syncthreads();
-    fwd_pass_fixed<8, MODE>(sm, nullptr, cc, fr.tw, q, q2, fr.in.r1, fr.epi);
+    fwd_pass_fixed<8, MODE>(sm, nullptr, cc, fr.tw, q, q2, fr.q, fr.in.r1, fr.epi);
     __syncwarp();
-    fwd_pass_fixed<5, MODE>(sm, nullptr, cc, fr.tw, q, q2, fr.in.r1, fr.epi);
+    fwd_pass_fixed<5, MODE>(sm, nullptr, cc, fr.tw, q, q2, fr.q, fr.in.r1, fr.epi);
     __syncwarp();
-    fwd_pass_fixed<2, MODE, PLAIN>(sm, fr.dst + (size_t)c * (2 * kHalfLoc), cc, fr.tw, q, q2, fr.in.r1, fr.epi);
+    fwd_pass_fixed<2, MODE, PLAIN>(sm, fr.dst + (size_t)c * (2 * kHalfLoc), cc, fr.tw, q, q2, fr.q, fr.in.r1, fr.epi);
 }
 
 template <int LOGC, bool PLAIN>
@@ -722,7 +822,7 @@ __global__ void __launch_bounds__(256, LB_NTT_MINBLOCKS) ntt_fwd_fixed_kernel(co
         if (fr.epi.add) fr.epi.add += off;
     }
     switch (fr.mode) {
-    case kFpLazy: fwd_body_fixed<LOGC, kFpLazy, PLAIN>(sm, fr, c); break;
+    case kF64: fwd_body_fixed<LOGC, kF64, PLAIN>(sm, fr, c); break;
     case kFpStrict: fwd_body_fixed<LOGC, kFpStrict, PLAIN>(sm, fr, c); break;
     case kIntLazy: fwd_body_fixed<LOGC, kIntLazy, PLAIN>(sm, fr, c); break;
     default: fwd_body_fixed<LOGC, kIntStrict, PLAIN>(sm, fr, c); break;
@@ -730,8 +830,8 @@ __global__ void __launch_bounds__(256, LB_NTT_MINBLOCKS) ntt_fwd_fixed_kernel(co
 }
 
 // three inverse stages starting at distance 2^LOGT
-template <int LOGT, bool FP>
-LB_D void inv_pass_fixed(u64 *sm, const u64 *gsrc, const unsigned cc, const ulonglong2 *itw, const u64 q, const u64 q2)
+template <int LOGT, int IM>
+LB_D void inv_pass_fixed(u64 *sm, const u64 *gsrc, const unsigned cc, const ulonglong2 *itw, const u64 q, const u64 q2, const bool reduce)
 {
     constexpr bool WIDE = LOGT + 3 > 10, OPENING = LOGT == 0;
     LB_UNROLL(LB_NTT_GROUP_UNROLL)
@@ -743,19 +843,27 @@ LB_D void inv_pass_fixed(u64 *sm, const u64 *gsrc, const unsigned cc, const ulon
         u64 v[8];
         if constexpr (OPENING) {
             load_contig<8>(v, gsrc + base);
+            if (IM == kInvF64) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = bits_of(f64_from_u52(v[i]));
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] = p[pad_off<LOGT>(i)];
+            if (IM == kInvF64 && reduce) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = bits_of(f64_centre(f64_of(v[i]), f64_of(q), f64_of(q2)));
+            }
         }
-        inv_core<3, false, FP>(v, itw, (cc << (12 - LOGT)) + (hi << 2), q, q2, 0, 0, 0, 0);
+        inv_core<3, false, IM>(v, itw, (cc << (12 - LOGT)) + (hi << 2), q, q2, 0, 0, 0, 0);
 #pragma unroll
         for (int i = 0; i < 8; ++i) p[pad_off<LOGT>(i)] = v[i];
     }
 }
 
-template <int LOGC, bool FP>
+template <int LOGC, int IM>
 LB_D void inv_last_fixed(u64 *sm, u64 *dst, const unsigned c, const ulonglong2 *itw, const u64 q, const u64 q2, const u64 cn,
-                         const u64 cns, const u64 cw, const u64 cws)
+                         const u64 cns, const u64 cw, const u64 cws, const bool reduce)
 {
     constexpr int F = LOGC + 1, R0 = 1 << F, COLS = kHalfLoc >> LOGC;
     const uint32_t sbase = smem_addr(sm);
@@ -774,28 +882,36 @@ LB_D void inv_last_fixed(u64 *sm, u64 *dst, const unsigned c, const ulonglong2 *
                 v[2 * r + 1] = ld_cluster(ra + 8u * kHalfLocPad);
             }
         }
-        inv_core<F, true, FP>(v, itw, 1u << LOGC, q, q2, cn, cns, cw, cws);
+        if (IM == kInvF64 && reduce) {
+#pragma unroll
+            for (int k = 0; k < R0; ++k) v[k] = bits_of(f64_centre(f64_of(v[k]), f64_of(q), f64_of(q2)));
+        }
+        inv_core<F, true, IM>(v, itw, 1u << LOGC, q, q2, cn, cns, cw, cws);
 #pragma unroll
         for (int k = 0; k < R0; ++k) dst[j + k * kHalfLoc] = v[k];
     }
 }
 
-template <int LOGC, bool FP>
-LB_D void inv_body_fixed(u64 *sm, const u64 *src, u64 *dst, const unsigned c, const ulonglong2 *itw, const u64 q, const u64 cn,
-                         const u64 cns, const u64 cw, const u64 cws)
+template <int LOGC, int IM>
+LB_D void inv_body_fixed(u64 *sm, const u64 *src, u64 *dst, const unsigned c, const ulonglong2 *itw, const u64 qi, const u64 cn_i,
+                         const u64 cns_i, const u64 cw_i, const u64 cws_i)
 {
-    const u64 q2 = q << 1;
+    const InvConst k = inv_constants(IM, qi, cn_i, cns_i, cw_i, cws_i);
+    const u64 q = k.q, q2 = k.q2;
     const unsigned cc = (1u << LOGC) + c;
-    inv_pass_fixed<0, FP>(sm, src + (size_t)c * (2 * kHalfLoc), cc, itw, q, q2);
+    F64Run run(qi);
+    const bool r0 = run.before(3), r1 = run.before(3), r2 = run.before(3), r3 = run.before(3), r4 = run.before(LOGC + 1);
+    (void)r0; // the opening pass reads canonical residues
+    inv_pass_fixed<0, IM>(sm, src + (size_t)c * (2 * kHalfLoc), cc, itw, q, q2, false);
     __syncwarp();
-    inv_pass_fixed<3, FP>(sm, nullptr, cc, itw, q, q2);
+    inv_pass_fixed<3, IM>(sm, nullptr, cc, itw, q, q2, r1);
     __syncwarp();
-    inv_pass_fixed<6, FP>(sm, nullptr, cc, itw, q, q2);
+    inv_pass_fixed<6, IM>(sm, nullptr, cc, itw, q, q2, r2);
     __syncthreads();
-    inv_pass_fixed<9, FP>(sm, nullptr, cc, itw, q, q2);
+    inv_pass_fixed<9, IM>(sm, nullptr, cc, itw, q, q2, r3);
     if constexpr (LOGC > 0) cg::this_cluster().sync(); // every local transform of the cluster is in shared memory
     else __syncthreads();
-    inv_last_fixed<LOGC, FP>(sm, dst, c, itw, q, q2, cn, cns, cw, cws);
+    inv_last_fixed<LOGC, IM>(sm, dst, c, itw, q, q2, k.cn, k.cns, k.cw, k.cws, r4);
     if constexpr (LOGC > 0) cg::this_cluster().sync(); // shared memory stays alive until every peer has read it
 }
 
@@ -820,8 +936,9 @@ __global__ void __launch_bounds__(256, LB_NTT_MINBLOCKS) ntt_inv_fixed_kernel(co
     }
     unsigned c = 0;
     if constexpr (LOGC > 0) c = cg::this_cluster().block_rank();
-    if (mc.q < kFpPrimeLimit) inv_body_fixed<LOGC, true>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
-    else inv_body_fixed<LOGC, false>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
+    if (mc.q < kF64PrimeLimit) inv_body_fixed<LOGC, kInvF64>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
+    else if (mc.q < kFpPrimeLimit) inv_body_fixed<LOGC, kInvFp>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
+    else inv_body_fixed<LOGC, kInvInt>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
 }
 #else
 #define LB_NTT_HAS_FIXED 0

@@ -10,24 +10,39 @@ namespace lb {
 //   integer, lazy:   the prime is below 2^58, so x may grow by 2q per stage over all seventeen
 //                    possible stages (bound 35q < 2^64) and the per-butterfly conditional
 //                    subtraction is dropped; the closing pass reduces once;
-//   FP64, strict / lazy: primes below 2^50 / 2^46, quotient estimated on the FP64 pipe
-//                    (fp_mul_signed), which takes the 64 x 64 -> 128 bit product off the
-//                    integer multiplier, the pipe that bounds these kernels.
+//   FP64-assisted:   primes of [2^47, 2^50), quotient estimated on the FP64 pipe (fp_mul_signed),
+//                    which takes the 64 x 64 -> 128 bit product off the integer multiplier;
+//   FP64:            primes below 2^47, the whole butterfly on the FP64 pipe (f64_mulmod): eight
+//                    double-precision operations and nothing on the integer pipes.  The 64-bit
+//                    words then hold the bit patterns of integer-valued doubles; in this mode the
+//                    scalars q and q2 of the butterfly functions carry double(q) and double(1 / q).
 // Every variant leaves the same canonical residues in memory.
-enum { kIntStrict = 0, kIntLazy = 1, kFpStrict = 2, kFpLazy = 3 };
+enum { kIntStrict = 0, kIntLazy = 1, kFpStrict = 2, kF64 = 3 };
 
 LB_D int butterfly_mode(const u64 q)
 {
-    if (q < kFpLazyLimit) return kFpLazy;
+    if (q < kF64PrimeLimit) return kF64;
     if (q < kFpPrimeLimit) return kFpStrict;
     return (q >> 58) == 0 ? kIntLazy : kIntStrict;
 }
 
+// the two scalars the butterflies of a mode take: (q, 2q), or (double(q), double(1 / q)) as bit patterns
+template <int MODE>
+LB_D u64 bf_scalar_q(const u64 q) { return MODE == kF64 ? bits_of((double)q) : q; }
+template <int MODE>
+LB_D u64 bf_scalar_q2(const u64 q) { return MODE == kF64 ? bits_of(1.0 / (double)q) : q << 1; }
+
 template <int MODE>
 LB_D void fwd_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
 {
+    if (MODE == kF64) {
+        const double xd = f64_of(x), r = f64_mulmod(f64_of(y), f64_of(w.x), f64_of(w.y), f64_of(q));
+        y = bits_of(__dadd_rn(xd, -r));
+        x = bits_of(__dadd_rn(xd, r));
+        return;
+    }
     if (MODE == kIntStrict || MODE == kFpStrict) x = csub(x, q2);
-    if (MODE == kFpStrict || MODE == kFpLazy) {
+    if (MODE == kFpStrict) {
         const u64 r = fp_mul_signed(y, w.x, w.y, q), xq = x + q; // r in (-q, q)
         y = xq - r;
         x = xq + r;
@@ -38,13 +53,29 @@ LB_D void fwd_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
     }
 }
 
-template <bool FP>
+// inverse butterfly kinds: the integer Shoup product, the FP64-assisted one, all on the FP64 pipe
+enum { kInvInt = 0, kInvFp = 1, kInvF64 = 2 };
+
+LB_D int inverse_mode(const u64 q) { return q < kF64PrimeLimit ? kInvF64 : q < kFpPrimeLimit ? kInvFp : kInvInt; }
+template <int IM>
+LB_D u64 inv_scalar_q(const u64 q) { return IM == kInvF64 ? bits_of((double)q) : q; }
+template <int IM>
+LB_D u64 inv_scalar_q2(const u64 q) { return IM == kInvF64 ? bits_of(1.0 / (double)q) : q << 1; }
+
+template <int IM>
 LB_D void inv_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
 {
+    if (IM == kInvF64) {
+        // the sum doubles its magnitude per stage: the passes reduce where 2^51 comes into reach
+        const double xd = f64_of(x), yd = f64_of(y);
+        x = bits_of(__dadd_rn(xd, yd));
+        y = bits_of(f64_mulmod(__dadd_rn(xd, -yd), f64_of(w.x), f64_of(w.y), f64_of(q)));
+        return;
+    }
     const u64 s = csub(x + y, q2);
     const u64 d = x + q2 - y; // below 4q
     x = s;
-    y = FP ? fp_mul_signed(d, w.x, w.y, q) + q : shoup_lazy(d, w.x, w.y, q);
+    y = IM == kInvFp ? fp_mul_signed(d, w.x, w.y, q) + q : shoup_lazy(d, w.x, w.y, q);
 }
 
 } // namespace lb

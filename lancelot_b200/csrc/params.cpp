@@ -152,12 +152,13 @@ bool HostParams::init(int logN_, const std::vector<u64> &moduli, int size_P_, co
         if (psi[m] == 0) { error = "invalid modulus: no primitive 2N-th root"; return false; }
         const u64 ipsi = h_invmod(psi[m], p);
         u64 *t = &tw[(size_t)m * N * 2], *it = &itw[(size_t)m * N * 2];
-        u64 pw = 1, ipw = 1;
+        u64 pw = 1, ipw = 1, ipw_at_1 = 1; // ipw_at_1: the inverse table's entry 1 as an integer (psi^-(N/2))
         for (u64 i = 0; i < N; ++i) {
             const uint32_t r = bit_reverse((uint32_t)i, logN);
-            t[2 * r] = pw;
+            if (r == 1) ipw_at_1 = ipw;
+            t[2 * r] = h_twiddle_value(pw, p);
             t[2 * r + 1] = h_twiddle_quot(pw, p);
-            it[2 * r] = ipw;
+            it[2 * r] = h_twiddle_value(ipw, p);
             it[2 * r + 1] = h_twiddle_quot(ipw, p);
             pw = h_mulmod(pw, psi[m], p);
             ipw = h_mulmod(ipw, ipsi, p);
@@ -169,7 +170,7 @@ bool HostParams::init(int logN_, const std::vector<u64> &moduli, int size_P_, co
         c.r1 = (u64)(ratio >> 64);
         c.ninv = h_invmod(N % p, p);
         c.ninvs = h_shoup(c.ninv, p);
-        c.iw1n = h_mulmod(it[2 * 1], c.ninv, p);
+        c.iw1n = h_mulmod(ipw_at_1, c.ninv, p);
         c.iw1ns = h_shoup(c.iw1n, p);
         c.pad = 0;
     }

@@ -79,3 +79,41 @@ def test_context_refuses_primes_of_more_than_60_bits():
     assert q >> 60
     with pytest.raises(InvalidArgument, match="2\\^60"):
         cabi.Context(10, [q], 0)
+
+
+def test_pycahel_extension_module_exports_the_reference_binding_names():
+    """the pybind11 module loads without a GPU and carries every name cahel-main/python/src/binding.cu:8-156 exports;
+    its host-only calls agree with the oracle"""
+    import sys
+
+    from oracle import binding
+
+    sys.path.insert(0, os.path.join(ROOT, "lancelot_b200", "pybind"))
+    try:
+        import pyCAHEL as cahel
+    finally:
+        sys.path.pop(0)
+    names = """scheme_type mul_tech_type sec_level_type modulus coeff_modulus_create params context secret_key public_key
+        relin_key galois_key get_elts_from_steps ckks_encoder plaintext ciphertext negate negate_inplace add add_inplace
+        add_plain add_plain_inplace add_many sub sub_inplace sub_plain sub_plain_inplace multiply multiply_inplace
+        multiply_and_relin_inplace multiply_plain multiply_plain_inplace multiply_many square square_inplace exponentiate
+        exponentiate_inplace relinearize relinearize_inplace mod_switch_to mod_switch_to_inplace mod_switch_to_next
+        mod_switch_to_next_inplace rescale_to_next rescale_to_next_inplace apply_galois apply_galois_inplace rotate_rows
+        rotate_rows_inplace rotate_columns rotate_columns_inplace rotate_vector rotate_vector_inplace hoisting
+        hoisting_inplace complex_conjugate complex_conjugate_inplace""".split()
+    for name in names:
+        assert hasattr(cahel, name), "missing: " + name
+    # export_values(): the enumerators are module attributes too
+    assert cahel.ckks == cahel.scheme_type.ckks and cahel.tc128 == cahel.sec_level_type.tc128
+    for cls, methods in [(cahel.params, "set_mul_tech set_poly_modulus_degree set_special_modulus_size set_galois_elts set_coeff_modulus"),
+                         (cahel.secret_key, "gen_secretkey gen_publickey gen_relinkey create_galois_keys encrypt_symmetric decrypt"),
+                         (cahel.public_key, "encrypt_asymmetric"), (cahel.ckks_encoder, "slot_count encode encode_to decode"),
+                         (cahel.ciphertext, "set_scale")]:
+        for m in methods.split():
+            assert hasattr(cls, m), "%s.%s" % (cls.__name__, m)
+    n = 1 << 13
+    mods = cahel.coeff_modulus_create(n, [60, 40, 40, 60])
+    assert [m.value() for m in mods] == binding.coeff_modulus_create(n, [60, 40, 40, 60])
+    assert list(cahel.get_elts_from_steps([1, 2, -3], n)) == binding.elts_from_steps([1, 2, -3], n)
+    with pytest.raises(ValueError):
+        cahel.coeff_modulus_create(1000, [40])

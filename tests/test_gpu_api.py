@@ -195,8 +195,42 @@ def test_round_from_pinned_host_updates_equals_device_updates():
     d_dev, o_dev = ek.round(upd.cuda(), keep=k_dev)
     d_host, o_host = ek.round(upd, keep=k_host)
     assert d_dev == d_host and list(o_dev) == list(o_host)
-    for c in k_dev["cts"]:
-        assert torch.equal(k_dev["cts"][c], k_host["cts"][c])
+    assert torch.equal(k_dev["cts"], k_host["cts"])
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_chunk_sharded_partial_sums_add_up_to_the_single_rank_sums(world):
+    """What several GPUs do in EncryptedKrum.round(exchange="chunks"), on one GPU: every "rank" encrypts its chunk range
+    of all clients and forms the partial sums of all pairs; the plain 64-bit sum of the partial sums, reduced mod q once
+    (lb_reduce_mod), equals the sums one rank forms over all chunks, word for word, and so do the final scores."""
+    import torch
+
+    from lancelot_b200 import krum
+
+    torch.manual_seed(9)
+    ek = krum.EncryptedKrum(log_slots=10, seed=21)
+    n_clients, dim = 4, 11 * 1024 - 300  # 11 chunks, the last one ragged
+    upd = (torch.randn(n_clients, dim, dtype=torch.float32) * 0.4).cuda()
+    chunks = ek.n_chunks(dim)
+    pairs = krum.all_pairs(n_clients)
+    # the deterministic test seeds depend on (client, first chunk of the slice): encrypting a slice twice gives the
+    # same ciphertexts, so both sums below are formed from identical partial sums
+    total, again = None, None
+    for r in range(world):
+        lo, hi = krum.chunk_range(chunks, r, world)
+        part = ek.pair_sums(ek.encrypt_slices(upd, lo, hi), pairs)
+        again_part = ek.pair_sums(ek.encrypt_slices(upd, lo, hi), pairs)
+        assert torch.equal(part, again_part)
+        total = part.clone() if total is None else total + part          # plain 64-bit words, as NCCL sums them
+        again = again_part if again is None else ek.lb.add(3, again, again_part)  # modular additions, one rank
+    ek.lb.reduce_mod(3, total)
+    assert torch.equal(total, again)
+    # and the decrypted distances agree with the plaintext rule
+    scores = ek.finish_scores(total)
+    d, order = ek.select(ek.client_sums(scores, pairs, n_clients))
+    want_d, want_order = krum.plaintext_krum(upd.cpu())
+    assert max(abs(a - b) / b for a, b in zip(d, want_d)) < 1e-6 and list(order) == list(want_order)
+
 
 
 def test_save_load_streams_round_trip_on_the_device(env):
