@@ -403,6 +403,99 @@ class NttWorkload:
         return gb / dt, "%d x (NTT+INTT of %d polynomials, 24 limbs each)" % (reps, b), binding.max_threads()
 
 
+class MaskWorkload:
+    """The aggregation phase of encrypted Krum (GPU_mul_mask_weight, lancelot-main-GPU/utils/byzantine_fl.py:371-429) on
+    the 20-client round's ciphertexts: every client's ciphertexts times its encrypted mask (Enc(1/k) for the k selected
+    clients, Enc(0) for the others), summed per chunk, size-3 decryption, decoding, gather of the averaged update.
+    The ciphertexts are where the distance round left them: each rank holds its chunk range of every client."""
+    name = "mask"
+    metric = "encrypted_mask_multiplication_s"
+    unit = "s"
+    higher_is_better = False
+    dtype = "u64"
+    scaling = "strong"
+
+    def __init__(self, batch=20):
+        self.n_clients = int(batch)
+        self.dim, self.log_slots = (1663370, 14) if self.n_clients == 10 else (11173962, 15)
+        self.slots = 1 << self.log_slots
+        self.chunks = (self.dim + self.slots - 1) // self.slots
+        self.launches_per_step = 0
+        self.selected = [3, 7, 11]  # a 3-hot mask with 1/3: the encrypted trimmed mean of three clients
+
+    def config(self):
+        return {"workload": "mask multiplication over %d clients x %d ciphertexts, N=2^%d, mask of %d clients, decrypt + decode of %d chunks"
+                            % (self.n_clients, self.chunks, self.log_slots + 1, len(self.selected), self.chunks),
+                "l2": "inputs (%.1f GiB of ciphertext) exceed the 126 MB L2" % (self.n_clients * self.chunks * 6 * (2 * self.slots) * 8 / 2 ** 30),
+                "includes": "mask encryption, ct x ct products and sums, size-3 decryption, decoding, gather of the result",
+                "excludes": "encryption of the clients' updates (done by the distance round)"}
+
+    def algorithmic_bytes_per_step(self):
+        # every client ciphertext read once, one size-3 ciphertext per chunk written and read again by the decryption
+        return self.chunks * (2 * self.slots) * 3 * 8 * (2 * self.n_clients + 2 * 3)
+
+    def setup_gpu(self, device):
+        import torch
+        import torch.distributed as dist
+        from lancelot_b200 import krum
+        self.torch = torch
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.ek = krum.EncryptedKrum(log_slots=self.log_slots, device=device, seed=1)
+        g = torch.Generator(device="cuda:%d" % device)
+        g.manual_seed(20240)
+        self.updates = torch.randn(self.n_clients, self.dim, generator=g, device="cuda:%d" % device, dtype=torch.float32) * 1e-2
+        lo, hi = krum.chunk_range(self.chunks, self.rank, self.world)
+        self.cts = self.ek.encrypt_slices(self.updates, lo, hi)
+        self.want = self.updates[self.selected].double().mean(dim=0)
+        self.hout = torch.empty(self.dim, dtype=torch.float64).pin_memory()
+        self.out = None
+
+    def step_gpu(self):
+        l0 = _launches()
+        self.out = self.ek.aggregate_sharded(self.cts, self.selected, self.dim, self.rank, self.world)
+        self.launches_per_step = _launches() - l0
+
+    def step_e2e(self):
+        # the ciphertexts are produced on the device by the distance round; the host hands over the selection and
+        # reads the averaged update back
+        self.step_gpu()
+        self.hout.copy_(self.out, non_blocking=True)
+        return 8 * len(self.selected), self.hout.numel() * 8
+
+    def check_gpu(self):
+        self.max_abs_err = float((self.out - self.want).abs().max())
+        return bool(self.max_abs_err < 1e-6)
+
+    def units_per_step(self):
+        return 1.0
+
+    def cpu_sample(self, threads):
+        binding = _oracle(threads)
+        n = 2 * self.slots
+        o = binding.Oracle(self.log_slots + 1, binding.coeff_modulus_create(n, KRUM_BITS), 1, [])
+        rng = np.random.default_rng(0)
+        b = max(int(threads), 1)
+        mods = o.moduli
+        x = np.stack([rng.integers(0, mods[r % 3], n, dtype=np.uint64) for r in range(b * 6)]).reshape(b, 2, 3, n)
+        mask = np.ascontiguousarray(x[0])
+        acc = np.zeros((b, 3, 3, n), dtype=np.uint64)
+        sk = o.gen_sk(rng.integers(0, 256, 64, dtype=np.uint8))
+        o.mask_chunk_batch(3, x, mask, acc)
+        reps = 3
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            o.mask_chunk_batch(3, x, mask, acc)
+        t_mul = (time.perf_counter() - t0) / (reps * b)
+        t0 = time.perf_counter()
+        pt = o.decrypt(3, acc[0], sk)
+        o.decode(3, pt, 2.0 ** 80, self.slots)
+        t_dec = time.perf_counter() - t0  # single ciphertext, limb-parallel
+        est = self.n_clients * self.chunks * t_mul + self.chunks * t_dec / max(1, min(b, 3))
+        return est, ("%d threads: %d ct x mask products + adds (%.5f s each amortised), 1 size-3 decrypt + decode (%.4f s); phase = "
+                     "%d products + %d decryptions" % (binding.max_threads(), reps * b, t_mul, t_dec, self.n_clients * self.chunks, self.chunks)), binding.max_threads()
+
+
 class EncryptWorkload:
     """Fused encode + public-key encryption of float32 chunks at the 20-client round's parameters (N = 2^16, chain
     {60,40,40|60}, 32768 slots): the phase that takes the largest share of a round, as a component benchmark and as the
@@ -486,4 +579,4 @@ class EncryptWorkload:
         return b / dt, "%d encode+encrypt, one per thread at a time" % b, binding.max_threads()
 
 
-WORKLOADS = {"krum": KrumWorkload, "hmult": HmultWorkload, "ntt": NttWorkload, "encrypt": EncryptWorkload}
+WORKLOADS = {"krum": KrumWorkload, "hmult": HmultWorkload, "ntt": NttWorkload, "encrypt": EncryptWorkload, "mask": MaskWorkload}

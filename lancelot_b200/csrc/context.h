@@ -107,6 +107,10 @@ struct NttJob {
     const u64 *add = nullptr; // optional addend rows; only groups with inner < add_inner have one
     long add_group_stride = -1, add_outer = -1;
     int add_inner = 0;
+    // Forward epilogue, alternative: mul2[2][per_group][N] are two fixed rows per row position (the two polynomials of a
+    // public key); group g stores NTT(x) * mul2[0] at dst rows (go * dst_outer + rr) and NTT(x) * mul2[1] per_group rows
+    // further on, so dst_outer = 2 * per_group lays the products out as [group][2][per_group][N]
+    const u64 *mul2 = nullptr;
     // Inverse epilogue: closing constants per row replaced by fold[rr][4]
     const u64 *fold = nullptr;
 };

@@ -12,13 +12,9 @@
 
 namespace lb {
 
-#ifndef LB_NTT_THREADS
-#define LB_NTT_THREADS 256
-#endif
-#ifndef LB_NTT_MINBLOCKS
-#define LB_NTT_MINBLOCKS 3
-#endif
-constexpr int kNttThreads = LB_NTT_THREADS;
+// the transform kernels' launch shape (ntt.cu): the probe runs at their occupancy
+constexpr int kNttThreads = 256;
+constexpr int kNttMinBlocks = 3;
 
 static unsigned long long g_launches = 0;
 unsigned long long launch_count() { return g_launches; }
@@ -68,7 +64,7 @@ void count_launch(const char *name, cudaStream_t stream, double bytes)
 // the modular arithmetic of that butterfly variant sets for any NTT schedule on this GPU; one
 // limb of N points needs (N/2) log2 N butterflies for 16 N bytes of traffic.
 template <int MODE>
-__global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) butterfly_probe_kernel(u64 *out, const u64 q, const u64 w0, const u64 ws0,
+__global__ void __launch_bounds__(kNttThreads, kNttMinBlocks) butterfly_probe_kernel(u64 *out, const u64 q, const u64 w0, const u64 ws0,
                                                                                        const int iters)
 {
     u64 v[8];
@@ -120,7 +116,7 @@ int probe_butterfly_rate(Context *ctx, int mode, double *butterflies_per_second)
         set_error("butterfly variant must be 0..3 or -1");
         return LB_ERR_INVALID_ARG;
     }
-    const int blocks = ctx->sm_count * LB_NTT_MINBLOCKS, iters = 2000;
+    const int blocks = ctx->sm_count * kNttMinBlocks, iters = 2000;
     int rc = ctx->ensure_workspace((size_t)blocks * kNttThreads * sizeof(u64));
     if (rc) return rc;
     u64 *out = reinterpret_cast<u64 *>(ctx->ws);

@@ -27,30 +27,13 @@ namespace cg = cooperative_groups;
 
 namespace lb {
 
-// Tunables (overridable at build time for sweeps): threads per CTA, CTAs per SM the register
-// allocation aims at, and log2 of the points one CTA keeps in shared memory.
-#ifndef LB_NTT_THREADS
-#define LB_NTT_THREADS 256
-#endif
-#ifndef LB_NTT_MINBLOCKS
-#define LB_NTT_MINBLOCKS 3
-#endif
-#ifndef LB_NTT_LOCAL_LOG
-#define LB_NTT_LOCAL_LOG 13
-#endif
-#ifndef LB_NTT_MAX_RADIX_LOG
-#define LB_NTT_MAX_RADIX_LOG 3 // stages per register pass: 3 = radix 8, 4 = radix 16
-#endif
-#ifndef LB_NTT_WARP_LOCAL
-#define LB_NTT_WARP_LOCAL 1 // 0: every register pass is shared out over the whole CTA
-#endif
-#ifndef LB_NTT_GROUP_UNROLL
-#define LB_NTT_GROUP_UNROLL 1 // register groups of one pass a thread keeps in flight
-#endif
-#define LB_PRAGMA_(x) _Pragma(#x)
-#define LB_UNROLL(n) LB_PRAGMA_(unroll n)
-constexpr int kNttThreads = LB_NTT_THREADS;
-constexpr int kMaxLocalLog = LB_NTT_LOCAL_LOG; // 13: 8192 points (64 KiB + padding) per CTA
+// Launch shape: threads per CTA, CTAs per SM the register allocation aims at, and log2 of the points one
+// CTA keeps in shared memory (8192 points: 64 KiB + padding, three CTAs per SM).  Register passes take at most
+// three stages (radix 8).
+constexpr int kNttThreads = 256;
+constexpr int kNttMinBlocks = 3;
+constexpr int kMaxLocalLog = 13;
+constexpr int kMaxRadixLog = 3;
 
 struct NttK {
     const u64 *src;
@@ -65,6 +48,7 @@ struct NttK {
     const u64 *bconv_mat;
     long mat_group_stride, mat_row_stride;
     const u64 *aux, *scal, *scal_s, *add, *fold;
+    const u64 *mul2; // forward epilogue: two products per row (see NttJob::mul2)
     const u64 *presub, *presub_scal, *presub_scal_s;
     const signed char *esmall;
     u64 esmall_p;
@@ -200,6 +184,11 @@ struct FwdEpi {
     const u64 *aux; // nullptr: plain store
     const u64 *add; // optional addend
     u64 scal, scal_s;
+    // optional: instead of the transform itself, store its products with two fixed rows (the two polynomials of a
+    // public key): dst <- NTT(x) * mul0, dst + dst1_off <- NTT(x) * mul1
+    const u64 *mul0, *mul1;
+    long dst1_off;
+    u64 r0, r1; // floor(2^128 / q) for those products
 };
 
 // Work split of one register pass.  A pass whose largest butterfly span exceeds a warp's chunk
@@ -234,7 +223,6 @@ LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, 
     const int logst = logt - (S - 1);
     const int logm0 = logn_loc - 1 - logt;
     const PassSplit ps = pass_split<S>(logn_loc, wlog);
-    LB_UNROLL(LB_NTT_GROUP_UNROLL)
     for (int g = ps.first; g < ps.end; g += ps.step) {
         const int lo = g & ((1 << logst) - 1), hi = g >> logst;
         const int base = (hi << (logt + 1)) + lo;
@@ -274,6 +262,16 @@ LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, 
                     for (int i = 0; i < R; ++i) v[i] = add_mod(v[i], t[i], qi);
                 }
             }
+            if (epi.mul0) {
+                u64 t[R], w[R];
+                load_contig<R>(t, epi.mul1 + base);
+#pragma unroll
+                for (int i = 0; i < R; ++i) w[i] = mul_mod(v[i], t[i], qi, epi.r0, epi.r1);
+                store_contig<R>(w, gdst + epi.dst1_off + base);
+                load_contig<R>(t, epi.mul0 + base);
+#pragma unroll
+                for (int i = 0; i < R; ++i) v[i] = mul_mod(v[i], t[i], qi, epi.r0, epi.r1);
+            }
             store_contig<R>(v, gdst + base);
         } else {
 #pragma unroll
@@ -286,9 +284,7 @@ template <int MODE>
 LB_D void fwd_pass_any(const int S, u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, const int logn_loc, const int logt,
                        const unsigned cc, const ulonglong2 *tw, const u64 q, const u64 q2, const FwdEpi &epi, const int wlog)
 {
-    constexpr int RMAX = LB_NTT_MAX_RADIX_LOG >= 4 ? 4 : 3;
-    if (RMAX == 4 && S == 4) fwd_pass<RMAX, MODE>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog);
-    else if (S == 3) fwd_pass<3, MODE>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog);
+    if (S == 3) fwd_pass<3, MODE>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog);
     else if (S == 2) fwd_pass<2, MODE>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog);
     else fwd_pass<1, MODE>(sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog);
 }
@@ -350,11 +346,16 @@ LB_D bool fwd_row_setup(const NttK &a, const int row, FwdRow &r)
     epi.add = (a.add && gi < a.add_inner) ? a.add + (((size_t)go * a.add_outer + (size_t)gi * a.add_group_stride + rr) << logN) : nullptr;
     epi.scal = a.aux ? a.scal[rr] : 0;
     epi.scal_s = a.aux ? a.scal_s[rr] : 0;
+    epi.mul0 = a.mul2 ? a.mul2 + ((size_t)rr << logN) : nullptr;
+    epi.mul1 = a.mul2 ? a.mul2 + ((size_t)(a.per_group + rr) << logN) : nullptr;
+    epi.dst1_off = (long)a.per_group << logN;
+    epi.r0 = mc.r0;
+    epi.r1 = mc.r1;
     return true;
 }
 
 template <int LOGC>
-__global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(const NttK a)
+__global__ void __launch_bounds__(kNttThreads, kNttMinBlocks) ntt_fwd_kernel(const NttK a)
 {
     extern __shared__ __align__(16) u64 sm[];
     constexpr int C = 1 << LOGC;
@@ -406,6 +407,7 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_fwd_kernel(
         const size_t off = (size_t)c * n_loc;
         if (epi.aux) epi.aux += off;
         if (epi.add) epi.add += off;
+        if (epi.mul0) { epi.mul0 += off; epi.mul1 += off; }
     }
 
     int logt = logn_loc - 1;
@@ -464,7 +466,6 @@ LB_D void inv_pass(u64 *sm, const u64 *gsrc, u64 *gdst, const int logn_loc, cons
     const int logst = logt;
     const int logm0 = logn_loc - 1 - logt;
     const PassSplit ps = pass_split<S>(logn_loc, wlog);
-    LB_UNROLL(LB_NTT_GROUP_UNROLL)
     for (int g = ps.first; g < ps.end; g += ps.step) {
         const int lo = g & ((1 << logst) - 1), hi = g >> logst;
         const int base = (hi << (logst + S)) + lo;
@@ -499,9 +500,7 @@ LB_D void inv_pass_any(const int S, u64 *sm, const u64 *gsrc, u64 *gdst, const i
                        const ulonglong2 *itw, const u64 q, const u64 q2, const u64 cn, const u64 cns, const u64 cw, const u64 cws,
                        const int wlog, const bool reduce)
 {
-    constexpr int RMAX = LB_NTT_MAX_RADIX_LOG >= 4 ? 4 : 3;
-    if (RMAX == 4 && S == 4) inv_pass<RMAX, CLOSE, IM>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, reduce);
-    else if (S == 3) inv_pass<3, CLOSE, IM>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, reduce);
+    if (S == 3) inv_pass<3, CLOSE, IM>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, reduce);
     else if (S == 2) inv_pass<2, CLOSE, IM>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, reduce);
     else inv_pass<1, CLOSE, IM>(sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, reduce);
 }
@@ -529,7 +528,7 @@ LB_D InvConst inv_constants(const int im, const u64 q, const u64 cn, const u64 c
 }
 
 template <int LOGC>
-__global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_inv_kernel(const NttK a)
+__global__ void __launch_bounds__(kNttThreads, kNttMinBlocks) ntt_inv_kernel(const NttK a)
 {
     extern __shared__ __align__(16) u64 sm[];
     constexpr int C = 1 << LOGC;
@@ -619,8 +618,6 @@ __global__ void __launch_bounds__(kNttThreads, LB_NTT_MINBLOCKS) ntt_inv_kernel(
 //   pass A     : local stages with spans 2048, 1024, 512 (CTA-wide),
 //   passes B-D : spans 256..1 inside each warp's 1024-point chunk (warp barriers only),
 // makes every register pass a radix-8 one: five passes instead of six.  The inverse mirrors it.
-#if LB_NTT_THREADS == 256 && LB_NTT_LOCAL_LOG == 13
-#define LB_NTT_HAS_FIXED 1
 constexpr int kHalfLoc = 4096;                                // points per half of a CTA's part
 constexpr int kHalfLocPad = kHalfLoc + (kHalfLoc >> 4);        // the same distance in padded shared memory
 
@@ -667,6 +664,10 @@ LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulon
         const int j = c * COLS + col;
         u64 v[R0];
         if (PLAIN) {
+#pragma unroll
+            for (int k = 0; k < R0; ++k) v[k] = in.src[j + k * kHalfLoc];
+        } else if (in.n == 0 && in.sub == nullptr) {
+            // a plain row in the instantiation with fused parts (its epilogue is what this launch is after)
 #pragma unroll
             for (int k = 0; k < R0; ++k) v[k] = in.src[j + k * kHalfLoc];
         } else if (in.n == 1 && in.mat == nullptr) {
@@ -750,7 +751,6 @@ LB_D void fwd_pass_fixed(u64 *sm, u64 *gdst, const unsigned cc, const ulonglong2
 {
     constexpr int LOGST = LOGT - 2;
     constexpr bool WIDE = LOGT + 1 > 10, CLOSING = LOGST == 0;
-    LB_UNROLL(LB_NTT_GROUP_UNROLL)
     for (int it = 0; it < 4; ++it) {
         const int g = fixed_group<WIDE>(it);
         const int lo = g & ((1 << LOGST) - 1), hi = g >> LOGST;
@@ -782,6 +782,16 @@ LB_D void fwd_pass_fixed(u64 *sm, u64 *gdst, const unsigned cc, const ulonglong2
                     for (int i = 0; i < 8; ++i) v[i] = add_mod(v[i], t[i], qi);
                 }
             }
+            if (!PLAIN && epi.mul0) {
+                u64 w[8];
+                load_contig<8>(t, epi.mul1 + base);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) w[i] = mul_mod(v[i], t[i], qi, epi.r0, epi.r1);
+                store_contig<8>(w, gdst + epi.dst1_off + base);
+                load_contig<8>(t, epi.mul0 + base);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = mul_mod(v[i], t[i], qi, epi.r0, epi.r1);
+            }
             store_contig<8>(v, gdst + base);
         } else {
 #pragma unroll
@@ -808,7 +818,7 @@ LB_D void fwd_body_fixed(u64 *sm, const FwdRow &fr, const unsigned c)
 }
 
 template <int LOGC, bool PLAIN>
-__global__ void __launch_bounds__(256, LB_NTT_MINBLOCKS) ntt_fwd_fixed_kernel(const NttK a)
+__global__ void __launch_bounds__(256, kNttMinBlocks) ntt_fwd_fixed_kernel(const NttK a)
 {
     extern __shared__ __align__(16) u64 sm[];
     FwdRow fr;
@@ -820,6 +830,7 @@ __global__ void __launch_bounds__(256, LB_NTT_MINBLOCKS) ntt_fwd_fixed_kernel(co
         const size_t off = (size_t)c * (2 * kHalfLoc);
         if (fr.epi.aux) fr.epi.aux += off;
         if (fr.epi.add) fr.epi.add += off;
+        if (fr.epi.mul0) { fr.epi.mul0 += off; fr.epi.mul1 += off; }
     }
     switch (fr.mode) {
     case kF64: fwd_body_fixed<LOGC, kF64, PLAIN>(sm, fr, c); break;
@@ -834,7 +845,6 @@ template <int LOGT, int IM>
 LB_D void inv_pass_fixed(u64 *sm, const u64 *gsrc, const unsigned cc, const ulonglong2 *itw, const u64 q, const u64 q2, const bool reduce)
 {
     constexpr bool WIDE = LOGT + 3 > 10, OPENING = LOGT == 0;
-    LB_UNROLL(LB_NTT_GROUP_UNROLL)
     for (int it = 0; it < 4; ++it) {
         const int g = fixed_group<WIDE>(it);
         const int lo = g & ((1 << LOGT) - 1), hi = g >> LOGT;
@@ -916,7 +926,7 @@ LB_D void inv_body_fixed(u64 *sm, const u64 *src, u64 *dst, const unsigned c, co
 }
 
 template <int LOGC>
-__global__ void __launch_bounds__(256, LB_NTT_MINBLOCKS) ntt_inv_fixed_kernel(const NttK a)
+__global__ void __launch_bounds__(256, kNttMinBlocks) ntt_inv_fixed_kernel(const NttK a)
 {
     extern __shared__ __align__(16) u64 sm[];
     const int row = blockIdx.x >> LOGC;
@@ -940,9 +950,6 @@ __global__ void __launch_bounds__(256, LB_NTT_MINBLOCKS) ntt_inv_fixed_kernel(co
     else if (mc.q < kFpPrimeLimit) inv_body_fixed<LOGC, kInvFp>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
     else inv_body_fixed<LOGC, kInvInt>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
 }
-#else
-#define LB_NTT_HAS_FIXED 0
-#endif
 
 // ---- launchers ------------------------------------------------------------------------
 
@@ -970,14 +977,14 @@ static PassPlan plan_passes(int logn_loc, bool forward)
     // CTA-wide passes; the rest stay inside a warp's contiguous chunk.  Of those, the pass
     // that touches global memory with contiguous per-thread data (forward: last, inverse:
     // first) takes the largest radix.  Short transforms keep every pass CTA-wide.
-    const int R = LB_NTT_MAX_RADIX_LOG;
+    const int R = kMaxRadixLog;
     int lw = 0;
     while ((32 << lw) < kNttThreads) ++lw;
     PassPlan pl;
     unsigned char wide[8], mid[8];
     int nw = 0, local = logn_loc;
     pl.wlog = -1;
-    if (LB_NTT_WARP_LOCAL && logn_loc - lw >= 8) {
+    if (logn_loc - lw >= 8) {
         local = logn_loc - lw;
         pl.wlog = local;
         nw = split_even(lw, R, wide);
@@ -1000,24 +1007,18 @@ static PassPlan plan_passes(int logn_loc, bool forward)
     return pl;
 }
 
-#ifndef LB_NTT_FIXED
-#define LB_NTT_FIXED 1 // 0: rings of 8192 points and more also take the general kernels
-#endif
-
 template <int LOGC>
 static int launch(bool forward, bool fixed, const NttK &k, int rows, size_t smem, cudaStream_t stream, double bytes)
 {
     auto kern = forward ? ntt_fwd_kernel<LOGC> : ntt_inv_kernel<LOGC>;
     int which = 0;
-    const bool plain = k.bconv_n == 0 && k.digit_alpha == 0 && !k.presub && !k.esmall && !k.aux;
-#if LB_NTT_HAS_FIXED
+    const bool plain = k.bconv_n == 0 && k.digit_alpha == 0 && !k.presub && !k.esmall && !k.aux && !k.mul2;
     if constexpr (LOGC <= 3) {
         if (fixed) {
             kern = !forward ? ntt_inv_fixed_kernel<LOGC> : plain ? ntt_fwd_fixed_kernel<LOGC, true> : ntt_fwd_fixed_kernel<LOGC, false>;
             which = plain ? 2 : 1;
         }
     }
-#endif
     // function attributes belong to the device the kernel image is loaded on
     static bool configured[64][2][3] = {};
     int dev = 0;
@@ -1084,6 +1085,7 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     k.scal_s = job.scal_s;
     k.add = job.add;
     k.fold = job.fold;
+    k.mul2 = job.mul2;
     k.presub = job.presub;
     k.esmall = job.esmall;
     k.esmall_p = job.esmall_p;
@@ -1100,7 +1102,7 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     for (int i = 0; i < pl.npass; ++i) k.S[i] = pl.S[i];
     const size_t n_loc = size_t(1) << logn_loc;
     const size_t smem = (n_loc + (n_loc >> 4) + 2) * sizeof(u64);
-    const bool fixed = LB_NTT_FIXED && LB_NTT_HAS_FIXED && logn_loc == 13;
+    const bool fixed = logn_loc == 13; // rings of 8192 points and more take the fixed-schedule kernels
     // algorithmic bytes of this launch (diagnostics): rows written once; plain rows read once; fused loaders read the
     // group's source rows once per group, plus the rows the epilogue and the prologue fold in
     const double limb = 8.0 * (double)hp.N;
@@ -1115,6 +1117,7 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     if (job.add) bytes += outer * (job.add_inner < k.split ? job.add_inner : k.split) * live * limb;
     if (job.presub) bytes += outer * (k.presub_inner < k.split ? k.presub_inner : k.split) * live * limb;
     if (job.esmall) bytes += outer * (double)hp.N;
+    if (job.mul2) bytes += out_rows * limb + 2.0 * job.per_group * limb; // a second output row per row, the two fixed rows once
     switch (logc) {
     case 0: return launch<0>(forward, fixed, k, rows, smem, stream, bytes);
     case 1: return launch<1>(forward, fixed, k, rows, smem, stream, bytes);

@@ -314,43 +314,205 @@ struct KrumTileArgs {
     u64 *out[kTileMaxPairs];
 };
 
+// Data movement: a CTA owns kTileThreads consecutive coefficients of one limb.  Per chunk it needs one 1 KiB
+// segment of either polynomial of every client of the tile; an elected thread fetches them with bulk asynchronous
+// copies (cp.async.bulk, the 1-D form of the tensor memory accelerator; this GPU's own memory, no multicast) into a
+// ring of kTileStages shared-memory stages, each guarded by an mbarrier that counts the bytes.  Nothing of this sits
+// in registers, so three stages of up to 12 KiB per CTA are in flight ahead of the arithmetic at three CTAs per SM,
+// which is what the HBM latency asks for; the threads read their operands from shared memory when they need them.
+//
+// Arithmetic: the limb's prime picks the pipe.  60-bit primes keep differences in (0, 2q) and sum them in 128 bits
+// (reduced in place every 63 chunks).  Primes below 2^41 (the 40-bit primes of Lancelot's chain) take the FP64
+// pipe: a difference d = b - a of two residues (|d| < 2^41) is split into d = h 2^21 + l with 0 <= l < 2^21 and
+// |h| <= 2^20, both exact as doubles; every product of two halves is below 2^42 in magnitude and exact, and a double
+// accumulator takes 2048 of them before 2^53 comes into reach.  Per pair
+//   sum (d0)^2      = LL0 + 2^22 LH0 + 2^42 HH0      (LH0 = sum of l0 h0, counted twice)
+//   sum d0 d1       = LL1 + 2^21 X1  + 2^42 HH1      (X1 = sum of l0 h1 + h0 l1)
+//   sum (d1)^2      = LL2 + 2^22 LH2 + 2^42 HH2
+// are rebuilt as exact 128-bit integers at the end of a window and reduced mod q.  Ten fused multiply-adds per
+// pair, chunk and coefficient replace twelve 32 x 32 -> 64 bit multiplications and their carry chains.
+constexpr u64 kTileF64PrimeLimit = u64(1) << 41;
+constexpr int kTileF64Window = 2048;
+constexpr int kTileStages = 4;
+constexpr unsigned kTileSpinLimit = 1u << 24; // polls of an mbarrier before the kernel gives up and raises status bit 1
+
+LB_D uint32_t tile_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+LB_D void mbar_init(const uint32_t bar, const unsigned count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+LB_D void mbar_expect_tx(const uint32_t bar, const unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+LB_D bool mbar_try_wait(const uint32_t bar, const unsigned parity)
+{
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// global -> this CTA's shared memory, completion counted in bytes on the mbarrier; both addresses 16-byte aligned,
+// size a multiple of 16
+LB_D void bulk_load(const uint32_t dst, const void *src, const unsigned bytes, const uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
+                 "r"(bar)
+                 : "memory");
+}
+
+struct TileHalves {
+    double l, h;
+};
+// a signed difference |d| < 2^41 as d = h 2^21 + l with 0 <= l < 2^21
+LB_D TileHalves tile_split(const long long d)
+{
+    TileHalves r;
+    r.l = __dadd_rn(__hiloint2double(0x43300000, (int)((unsigned)d & 0x1FFFFFu)), -4503599627370496.0);
+    // h in [-2^20, 2^20): biased by 2^20 into an unsigned word, the bias taken off again as a double
+    r.h = __dadd_rn(__hiloint2double(0x43300000, (int)((unsigned)(d >> 21) + 0x100000u)), -(4503599627370496.0 + 1048576.0));
+    return r;
+}
+// (ll + mid 2^shift + hh 2^42) mod q for integer-valued doubles below 2^53 in magnitude; the total may be negative
+LB_D u64 tile_fold(const double ll, const double mid, const int shift, const double hh, const ModConst &m)
+{
+    const __int128 t = (__int128)__double2ll_rn(ll) + (__int128)__double2ll_rn(mid) * ((__int128)1 << shift) +
+                       (__int128)__double2ll_rn(hh) * ((__int128)1 << 42);
+    const bool neg = t < 0;
+    const unsigned __int128 a = neg ? (unsigned __int128)(-t) : (unsigned __int128)t;
+    const u64 r = barrett128(u128d{(u64)a, (u64)(a >> 64)}, m.q, m.r0, m.r1);
+    return neg && r ? m.q - r : r;
+}
+
+// stage layout: row (client i, polynomial t) at words [(2 i + t) * seg, +seg)
 template <int NA, int NB>
-__global__ void __launch_bounds__(kTileThreads, 3) krum_tile_kernel(const KrumTileArgs args, const ModConst *__restrict__ mc, const int logn,
-                                                                    const long per_poly, const long chunk_stride, const int n_chunks)
+__global__ void __launch_bounds__(kTileThreads, (NA + NB > 4 ? 2 : 3)) krum_tile_kernel(const KrumTileArgs args, const ModConst *__restrict__ mc, const int logn,
+                                                                    const long per_poly, const long chunk_stride, const int n_chunks,
+                                                                    int *__restrict__ status)
 {
     constexpr int NI = NA + NB, NP = NB ? NA * NB : NA * (NA - 1) / 2;
-    // chunks a thread keeps in flight: as many as the accumulators of the shape leave registers for
-    constexpr int kTileUnroll = NP <= 4 ? 3 : NP <= 6 ? 2 : 1;
-    for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < per_poly; e += (long)gridDim.x * blockDim.x) {
-        const ModConst m = mc[(int)(e >> logn)];
+    extern __shared__ __align__(128) u64 tile_sm[];
+    __shared__ __align__(8) unsigned long long bars[kTileStages];
+    const int seg = min(kTileThreads, 1 << logn);              // coefficients per CTA
+    const int blocks_per_limb = (1 << logn) / seg;
+    const int limb = blockIdx.x / blocks_per_limb;
+    const long e0 = ((long)limb << logn) + (long)(blockIdx.x - limb * blocks_per_limb) * seg; // first coefficient of this CTA
+    const ModConst m = mc[limb];
+    const unsigned stage_bytes = (unsigned)(2 * NI * seg * sizeof(u64));
+    const uint32_t sm_base = tile_smem(tile_sm), bar_base = tile_smem(bars);
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < kTileStages; ++s) mbar_init(bar_base + 8u * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    auto issue = [&](const int c) { // thread 0: fetch chunk c into stage c % kTileStages
+        const int s = c % kTileStages;
+        const uint32_t bar = bar_base + 8u * s, dst = sm_base + (uint32_t)s * stage_bytes;
+        mbar_expect_tx(bar, stage_bytes);
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            const u64 *src = args.in[i] + c * chunk_stride + e0;
+            bulk_load(dst + (uint32_t)((2 * i) * seg * 8), src, (unsigned)(seg * 8), bar);
+            bulk_load(dst + (uint32_t)((2 * i + 1) * seg * 8), src + per_poly, (unsigned)(seg * 8), bar);
+        }
+    };
+    if (threadIdx.x == 0) {
+        for (int c = 0; c < kTileStages && c < n_chunks; ++c) issue(c);
+    }
+    const bool active = (int)threadIdx.x < seg;
+    const int t = active ? threadIdx.x : 0;
+    const bool f64 = m.q < kTileF64PrimeLimit;
+    bool failed = false;
+
+    // one chunk: waits for its stage, hands the operands of pair (i, j) to `pair`, releases the stage
+    auto chunk = [&](const int c, auto &&pair) {
+        const int s = c % kTileStages;
+        const uint32_t bar = bar_base + 8u * s;
+        const unsigned parity = (unsigned)(c / kTileStages) & 1u;
+        unsigned polls = 0;
+        bool gave_up = false;
+        while (!mbar_try_wait(bar, parity)) {
+            if (++polls > kTileSpinLimit) { // a copy that never lands: give up, say so, leave without touching the data
+                gave_up = true;
+                break;
+            }
+        }
+        failed = __syncthreads_or(gave_up); // the whole CTA goes on or leaves together
+        if (!failed) {
+            const u64 *row = tile_sm + (size_t)s * (2 * NI * seg) + t;
+            int p = 0;
+#pragma unroll
+            for (int i = 0; i < NA; ++i) {
+#pragma unroll
+                for (int j = NB ? NA : i + 1; j < NI; ++j, ++p)
+                    pair(p, row[(2 * i) * seg], row[(2 * i + 1) * seg], row[(2 * j) * seg], row[(2 * j + 1) * seg]);
+            }
+        }
+        __syncthreads(); // every thread has read the stage (or given up) before it is refilled
+        if (threadIdx.x == 0 && !failed && c + kTileStages < n_chunks) issue(c + kTileStages);
+    };
+
+    const long e = e0 + t;
+    if (f64) {
+        u64 r0[NP], r1[NP], r2[NP];
+#pragma unroll
+        for (int p = 0; p < NP; ++p) r0[p] = r1[p] = r2[p] = 0;
+        for (int c0 = 0; c0 < n_chunks && !failed; c0 += kTileF64Window) {
+            const int c1 = min(c0 + kTileF64Window, n_chunks);
+            double ll0[NP], lh0[NP], hh0[NP], ll1[NP], x1[NP], hh1[NP], ll2[NP], lh2[NP], hh2[NP];
+#pragma unroll
+            for (int p = 0; p < NP; ++p) ll0[p] = lh0[p] = hh0[p] = ll1[p] = x1[p] = hh1[p] = ll2[p] = lh2[p] = hh2[p] = 0.0;
+            for (int c = c0; c < c1 && !failed; ++c) {
+                chunk(c, [&](const int p, const u64 a0, const u64 a1, const u64 b0, const u64 b1) {
+                    const TileHalves d0 = tile_split((long long)(b0 - a0)), d1 = tile_split((long long)(b1 - a1));
+                    ll0[p] = __fma_rn(d0.l, d0.l, ll0[p]);
+                    lh0[p] = __fma_rn(d0.l, d0.h, lh0[p]);
+                    hh0[p] = __fma_rn(d0.h, d0.h, hh0[p]);
+                    ll1[p] = __fma_rn(d0.l, d1.l, ll1[p]);
+                    x1[p] = __fma_rn(d0.l, d1.h, x1[p]);
+                    x1[p] = __fma_rn(d0.h, d1.l, x1[p]);
+                    hh1[p] = __fma_rn(d0.h, d1.h, hh1[p]);
+                    ll2[p] = __fma_rn(d1.l, d1.l, ll2[p]);
+                    lh2[p] = __fma_rn(d1.l, d1.h, lh2[p]);
+                    hh2[p] = __fma_rn(d1.h, d1.h, hh2[p]);
+                });
+            }
+#pragma unroll
+            for (int p = 0; p < NP; ++p) {
+                r0[p] = add_mod(r0[p], tile_fold(ll0[p], lh0[p], 22, hh0[p], m), m.q);
+                r1[p] = add_mod(r1[p], tile_fold(ll1[p], x1[p], 21, hh1[p], m), m.q);
+                r2[p] = add_mod(r2[p], tile_fold(ll2[p], lh2[p], 22, hh2[p], m), m.q);
+            }
+        }
+        if (active && !failed) {
+#pragma unroll
+            for (int p = 0; p < NP; ++p) {
+                u64 *dst = args.out[p];
+                dst[e] = r0[p];
+                dst[per_poly + e] = add_mod(r1[p], r1[p], m.q); // middle term is 2 x0 x1
+                dst[2 * per_poly + e] = r2[p];
+            }
+        }
+    } else {
         // 128-bit running sums; every 63 chunks they are reduced in place, which leaves room for
         // 63 more products of differences below 2^61
         u128d s0[NP], s1[NP], s2[NP];
 #pragma unroll
         for (int p = 0; p < NP; ++p) s0[p] = s1[p] = s2[p] = u128d{0, 0};
-        for (int c0 = 0; c0 < n_chunks; c0 += 63) {
+        for (int c0 = 0; c0 < n_chunks && !failed; c0 += 63) {
             const int c1 = min(c0 + 63, n_chunks);
-#pragma unroll(kTileUnroll)
-            for (int c = c0; c < c1; ++c) {
-                u64 v0[NI], v1[NI];
-#pragma unroll
-                for (int i = 0; i < NI; ++i) {
-                    const u64 *base = args.in[i] + c * chunk_stride + e;
-                    v0[i] = __ldcs(base);
-                    v1[i] = __ldcs(base + per_poly);
-                }
-                int p = 0;
-#pragma unroll
-                for (int i = 0; i < NA; ++i) {
-#pragma unroll
-                    for (int j = NB ? NA : i + 1; j < NI; ++j, ++p) {
-                        // differences left in (0, 2q): 63 products below 2^122 and a residue fit 128 bits
-                        const u64 x0 = v0[j] + m.q - v0[i], x1 = v1[j] + m.q - v1[i];
-                        mac_wide(s0[p], x0, x0);
-                        mac_wide(s1[p], x0, x1);
-                        mac_wide(s2[p], x1, x1);
-                    }
-                }
+            for (int c = c0; c < c1 && !failed; ++c) {
+                chunk(c, [&](const int p, const u64 a0, const u64 a1, const u64 b0, const u64 b1) {
+                    // differences left in (0, 2q): 63 products below 2^122 and a residue fit 128 bits
+                    const u64 x0 = b0 + m.q - a0, x1 = b1 + m.q - a1;
+                    mac_wide(s0[p], x0, x0);
+                    mac_wide(s1[p], x0, x1);
+                    mac_wide(s2[p], x1, x1);
+                });
             }
 #pragma unroll
             for (int p = 0; p < NP; ++p) {
@@ -359,23 +521,38 @@ __global__ void __launch_bounds__(kTileThreads, 3) krum_tile_kernel(const KrumTi
                 s2[p] = u128d{barrett128(s2[p], m.q, m.r0, m.r1), 0};
             }
         }
+        if (active && !failed) {
 #pragma unroll
-        for (int p = 0; p < NP; ++p) {
-            u64 *dst = args.out[p];
-            dst[e] = s0[p].lo;
-            dst[per_poly + e] = add_mod(s1[p].lo, s1[p].lo, m.q); // middle term is 2 x0 x1
-            dst[2 * per_poly + e] = s2[p].lo;
+            for (int p = 0; p < NP; ++p) {
+                u64 *dst = args.out[p];
+                dst[e] = s0[p].lo;
+                dst[per_poly + e] = add_mod(s1[p].lo, s1[p].lo, m.q); // middle term is 2 x0 x1
+                dst[2 * per_poly + e] = s2[p].lo;
+            }
         }
     }
+    if (failed && threadIdx.x == 0) atomicOr(status, 2);
 }
 
 template <int NA, int NB>
-static void launch_tile(Context *ctx, const KrumTileArgs &args, int size_l, int n_chunks, long chunk_stride, cudaStream_t stream)
+static int launch_tile(Context *ctx, const KrumTileArgs &args, int size_l, int n_chunks, long chunk_stride, cudaStream_t stream)
 {
     const long per_poly = (long)size_l << ctx->hp.logN;
-    const long blocks = (per_poly + kTileThreads - 1) / kTileThreads;
+    const int seg = (1 << ctx->hp.logN) < kTileThreads ? (1 << ctx->hp.logN) : kTileThreads;
+    const long blocks = (long)size_l * ((1L << ctx->hp.logN) / seg);
+    const size_t smem = (size_t)kTileStages * 2 * (NA + NB) * seg * sizeof(u64);
+    static bool configured[64] = {};
+    int dev = 0;
+    LB_CUDA(cudaGetDevice(&dev));
+    if (!configured[dev & 63]) {
+        LB_CUDA(cudaFuncSetAttribute(krum_tile_kernel<NA, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kTileStages * 2 * 6 * kTileThreads * sizeof(u64))));
+        configured[dev & 63] = true;
+    }
     count_launch("krum_tile_kernel", stream, 8.0 * per_poly * ((double)(NA + NB) * 2 * n_chunks + 3.0 * (NB ? NA * NB : NA * (NA - 1) / 2)));
-    krum_tile_kernel<NA, NB><<<(unsigned)blocks, kTileThreads, 0, stream>>>(args, ctx->d_mc, ctx->hp.logN, per_poly, chunk_stride, n_chunks);
+    krum_tile_kernel<NA, NB><<<(unsigned)blocks, kTileThreads, smem, stream>>>(args, ctx->d_mc, ctx->hp.logN, per_poly, chunk_stride, n_chunks,
+                                                                               ctx->d_status);
+    LB_CUDA(cudaGetLastError());
+    return LB_OK;
 }
 
 int krum_accumulate_tile(Context *ctx, int size_l, int n_chunks, int n_a, const u64 *const *a, int n_b, const u64 *const *b,
@@ -391,21 +568,21 @@ int krum_accumulate_tile(Context *ctx, int size_l, int n_chunks, int n_a, const 
     for (int i = 0; i < n_a; ++i) args.in[i] = a[i];
     for (int i = 0; i < n_b; ++i) args.in[n_a + i] = b[i];
     for (int p = 0; p < n_pairs; ++p) args.out[p] = out[p];
+    int rc = LB_OK;
     switch (n_a * 8 + n_b) {
-    case 2 * 8 + 0: launch_tile<2, 0>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
-    case 3 * 8 + 0: launch_tile<3, 0>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
-    case 4 * 8 + 0: launch_tile<4, 0>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
-    case 1 * 8 + 1: launch_tile<1, 1>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
-    case 1 * 8 + 2: launch_tile<1, 2>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
-    case 1 * 8 + 3: launch_tile<1, 3>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
-    case 1 * 8 + 4: launch_tile<1, 4>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
-    case 2 * 8 + 1: launch_tile<2, 1>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
-    case 2 * 8 + 2: launch_tile<2, 2>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
-    case 2 * 8 + 3: launch_tile<2, 3>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
-    default: launch_tile<2, 4>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 2 * 8 + 0: rc = launch_tile<2, 0>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 3 * 8 + 0: rc = launch_tile<3, 0>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 4 * 8 + 0: rc = launch_tile<4, 0>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 1 * 8 + 1: rc = launch_tile<1, 1>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 1 * 8 + 2: rc = launch_tile<1, 2>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 1 * 8 + 3: rc = launch_tile<1, 3>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 1 * 8 + 4: rc = launch_tile<1, 4>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 2 * 8 + 1: rc = launch_tile<2, 1>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 2 * 8 + 2: rc = launch_tile<2, 2>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    case 2 * 8 + 3: rc = launch_tile<2, 3>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
+    default: rc = launch_tile<2, 4>(ctx, args, size_l, n_chunks, chunk_stride, stream); break;
     }
-    LB_CUDA(cudaGetLastError());
-    return LB_OK;
+    return rc;
 }
 
 // ---- mask multiplication: out[c] = sum_k ct_k[c] (x) mask_k as size-3 ciphertexts -------------

@@ -12,6 +12,8 @@
 // Price: every GPU that loads the library holds the array (kStaticWords * 8 bytes = 1.5 MiB)
 // until the process exits, the size is capped, and all calls on one device share the one
 // array, so two calls that overlap on the GPU (different streams) race.
+#include <atomic>
+
 #include "context.h"
 
 namespace lb {
@@ -23,7 +25,7 @@ static __device__ __align__(256) u64 g_rescale_scratch[kStaticWords];
 constexpr int kMaxDevices = 64;
 // device address of g_rescale_scratch per device; the symbol itself is only a host-side
 // handle and must never be handed to a kernel
-static u64 *g_scratch_addr[kMaxDevices];
+static std::atomic<u64 *> g_scratch_addr[kMaxDevices]; // two host threads may resolve it at once: both store the same value
 
 // Resolves the array's address on the current device once.  Not an allocation: the array
 // already exists in the loaded module.  Do this before any stream capture starts.
@@ -35,12 +37,14 @@ static int static_scratch(u64 **out)
         set_error("device ordinal out of range for the allocation-free rescale");
         return LB_ERR_INVALID_ARG;
     }
-    if (!g_scratch_addr[dev]) {
+    u64 *addr = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!addr) {
         void *p = nullptr;
         LB_CUDA(cudaGetSymbolAddress(&p, g_rescale_scratch));
-        g_scratch_addr[dev] = static_cast<u64 *>(p);
+        addr = static_cast<u64 *>(p);
+        g_scratch_addr[dev].store(addr, std::memory_order_release);
     }
-    *out = g_scratch_addr[dev];
+    *out = addr;
     return LB_OK;
 }
 

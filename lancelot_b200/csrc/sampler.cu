@@ -289,20 +289,16 @@ int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, int pt_is_coe
         sample_small_i8_kernel<<<grid_for(ctx, n_small), kSampThreads, 0, stream>>>(reinterpret_cast<signed char *>(e), seeds + 16, 32, 1,
                                                                                    hp.logN, n_small);
         LB_CUDA(cudaGetLastError());
+        // u's transform stores its products with the two key polynomials straight away: cx[b][p][QP][N] = pk[p] * NTT(u[b])
         NttJob j;
         j.src = u;
-        j.dst = u;
+        j.dst = cx;
         j.n_groups = batch;
         j.per_group = QP;
         j.size_l = Q;
+        j.dst_outer = 2 * QP;
+        j.mul2 = pk;
         if ((rc = ntt_forward(ctx, j, stream))) return rc;
-        const long half_poly = poly / 2;
-        count_launch("encrypt_product_kernel", stream, 8.0 * poly * (3.0 * batch + 2.0)); // u read, two products written, pk once
-        const unsigned gx = (unsigned)((half_poly + kSampThreads - 1) / kSampThreads);
-        encrypt_product_kernel<<<dim3(gx, (unsigned)(batch < 65535 ? batch : 65535)), kSampThreads, 0, stream>>>(
-            reinterpret_cast<ulonglong2 *>(cx), reinterpret_cast<const ulonglong2 *>(pk), reinterpret_cast<const ulonglong2 *>(u), ctx->d_mc,
-            hp.logN - 1, half_poly, batch);
-        LB_CUDA(cudaGetLastError());
     } else {
         if ((rc = sample_small(ctx, 1, seeds + 16, 32, batch, Q, P, e, stream))) return rc;
         NttJob j;

@@ -613,6 +613,29 @@ class EncryptedKrum:
         vals = lb.decode_batch(3, pts, self.scale * self.scale, self.slots, chunks)
         return vals.real.reshape(-1)[:dim]
 
+    def aggregate_sharded(self, cts, selected, dim, rank=0, world_size=1, group=None):
+        """The mask multiplication with the chunk axis sharded over the ranks, as the distance round leaves the
+        ciphertexts: cts holds THIS rank's chunk range of every client ([n_clients][k][2][3][N], k = its share of the
+        chunks).  Every rank multiplies, decrypts and decodes its chunks; the decoded slices are all-gathered.  Returns
+        the averaged update ([dim] float64) on every rank."""
+        import torch.distributed as dist
+
+        k = cts[0].shape[0]
+        local = self.aggregate(cts, selected, k * self.slots) if k else torch.empty(0, dtype=torch.float64, device="cuda:%d" % self.lb.device)
+        if world_size == 1:
+            return local[:dim]
+        chunks = self.n_chunks(dim)
+        most = max(hi - lo for lo, hi in (chunk_range(chunks, r, world_size) for r in range(world_size)))
+        send = torch.zeros(most * self.slots, dtype=torch.float64, device=local.device)
+        send[: local.numel()] = local
+        recv = torch.empty(world_size * most * self.slots, dtype=torch.float64, device=local.device)
+        dist.all_gather_into_tensor(recv, send, group=group)
+        parts = []
+        for r in range(world_size):
+            lo, hi = chunk_range(chunks, r, world_size)
+            parts.append(recv[r * most * self.slots: r * most * self.slots + (hi - lo) * self.slots])
+        return torch.cat(parts)[:dim]
+
     # -- one round ---------------------------------------------------------------------------------
     def round(self, updates, rank=0, world_size=1, group=None, keep=None, timing=None, exchange="chunks"):
         """updates: [n_clients][dim] tensor (CUDA, pinned or pageable host).  Every rank runs this; rank 0 returns

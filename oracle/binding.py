@@ -88,6 +88,7 @@ def _load():
     lib.orc_encode_encrypt_batch.argtypes = [vp, _p64, pd, C.c_size_t, C.c_double, _p8, I, _p64]
     lib.orc_pair_chunk_batch.argtypes = [vp, I, _p64, _p64, _p64, I]
     lib.orc_relin_rescale_batch.argtypes = [vp, I, _p64, _p64, _p64, I]
+    lib.orc_mask_chunk_batch.argtypes = [vp, I, _p64, _p64, _p64, I]
     lib.orc_hmult_batch.argtypes = [vp, I, _p64, _p64, _p64, _p64, I]
     lib.orc_rotate_batch.argtypes = [vp, I, _p64, I, _p64, I]
     lib.orc_ntt_roundtrip_batch.argtypes = [vp, _p64, I, I]
@@ -345,6 +346,11 @@ class Oracle:
     def pair_chunk_batch(self, L, x, y, acc):
         """acc[b] += (y[b] - x[b])^2 in place"""
         lib.orc_pair_chunk_batch(self.h, L, _u(x), _u(y), _u(acc), x.shape[0])
+        return acc
+
+    def mask_chunk_batch(self, L, x, mask, acc):
+        """acc[b] += x[b] (x) mask in place"""
+        lib.orc_mask_chunk_batch(self.h, L, _u(x), _u(np.ascontiguousarray(mask)), _u(acc), x.shape[0])
         return acc
 
     def relin_rescale_batch(self, L, ct3, rlk):

@@ -1031,6 +1031,20 @@ void orc_pair_chunk_batch(const orc_ctx *c, int L, const u64 *x, const u64 *y, u
     }
 }
 
+/* acc[b] += x[b] (x) mask for a batch of ciphertexts: x [batch][2][L][N], mask [2][L][N], acc [batch][3][L][N]
+ * (the per-client step of the mask multiplication, lancelot-main-GPU/utils/byzantine_fl.py:401-409) */
+void orc_mask_chunk_batch(const orc_ctx *c, int L, const u64 *x, const u64 *mask, u64 *acc, int batch)
+{
+    size_t N = c->N;
+#pragma omp parallel for schedule(dynamic)
+    for (int b = 0; b < batch; b++) {
+        u64 *t = (u64 *)malloc((size_t)3 * L * N * 8);
+        orc_tensor(c, L, x + (size_t)b * 2 * L * N, mask, t);
+        orc_poly_op(c, 0, L, 3, acc + (size_t)b * 3 * L * N, t, acc + (size_t)b * 3 * L * N);
+        free(t);
+    }
+}
+
 /* relinearize + rescale of a batch: ct3 [batch][3][L][N] (clobbered) -> out [batch][2][L-1][N] */
 void orc_relin_rescale_batch(const orc_ctx *c, int L, u64 *ct3, const u64 *rlk, u64 *out, int batch)
 {

@@ -354,3 +354,14 @@ def test_mask_multiplication_selects_and_averages():
         else:
             cahel.add_inplace(ctx, acc, t)
     assert torch.equal(acc.data.reshape(-1), fused[1].reshape(-1))
+    # and against the CPU checker: out[c] = sum over clients of tensor(ct_k[c], mask_k), every chunk, bit for bit
+    from oracle import binding
+    o = binding.Oracle(ek.log_slots + 1, ctx.moduli, 1)
+    h_masks = cabi.to_host(masks)
+    h_cts = [cabi.to_host(cts[k]) for k in range(n_clients)]
+    h_fused = cabi.to_host(fused)
+    for c in range(h_fused.shape[0]):
+        want = np.zeros((3, 3, ek.N), dtype=np.uint64)
+        for k in range(n_clients):
+            want = o.poly_op("add", 3, want, o.tensor(3, h_cts[k][c], h_masks[k]))
+        assert np.array_equal(h_fused[c].reshape(-1), want.reshape(-1)), "chunk %d" % c

@@ -122,15 +122,17 @@ def test_keys_and_encryption_at_bench_sizes(torch_cuda, logn, bits, size_p):
     assert np.array_equal(fused, got), "fused encode + encrypt"
 
 
-@pytest.mark.parametrize("logn,n_a,n_b", [(16, 2, 4), (16, 4, 0), (15, 2, 4)])
-def test_pair_tile_at_bench_sizes(torch_cuda, logn, n_a, n_b):
-    """A 342-chunk tile (the chunk count of the 20-client round, past five of the kernel's in-place reductions)
-    against the oracle's per-chunk sub / square / add.  The device holds the full clients; their chunks repeat
-    with period 7 so that the host needs only seven chunks per client."""
+@pytest.mark.parametrize("logn,n_a,n_b,n_chunks", [(16, 2, 4, 342), (16, 4, 0, 342), (15, 2, 4, 342), (10, 2, 2, 2100), (10, 3, 0, 2100),
+                                                   (10, 1, 3, 2049), (5, 2, 4, 9)])
+def test_pair_tile_at_bench_sizes(torch_cuda, logn, n_a, n_b, n_chunks):
+    """Long tiles against the oracle's per-chunk sub / square / add: 342 chunks at the rings of the benchmark rounds
+    (past five in-place reductions of the integer path), more than 2048 chunks (past one window of the FP64 path the
+    40-bit limbs take), and a ring shorter than a CTA.  The device holds the full clients; their chunks repeat with
+    period 7 so that the host needs only seven chunks per client."""
     import torch
     from lancelot_b200 import cabi
 
-    L, n_chunks, period = 3, 342, 7
+    L, period = 3, 7
     o, ctx, mods = make(logn, KRUM_BITS, 1)
     rng = np.random.default_rng(logn * 100 + n_a * 10 + n_b)
     n = 1 << logn

@@ -24,6 +24,8 @@ def test_rescale_no_alloc_matches_rescale_twice_in_a_row():
     logn, n, L = 13, 1 << 13, 3
     mods = cabi.coeff_modulus_create(n, [60, 40, 40, 60])
     ctx = cabi.Context(logn, mods, 1)
+    from oracle import binding
+    oracle = binding.Oracle(logn, mods, 1)
     rng = np.random.default_rng(99)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     for call in range(2):  # the second call reuses the array the first one left dirty
@@ -34,6 +36,7 @@ def test_rescale_no_alloc_matches_rescale_twice_in_a_row():
         check(lib.lb_rescale_no_alloc(ctx.h, L, 3, C.c_void_p(d.data_ptr()), C.c_void_p(out.data_ptr()), stream))
         torch.cuda.synchronize()
         assert np.array_equal(cabi.to_host(out), want), "call %d differs from lb_rescale" % call
+        assert np.array_equal(want, oracle.rescale(L, ct)), "call %d differs from the CPU checker" % call
     # beyond the fixed scratch: refused with a clear message, nothing launched
     too_many = int(lib.lb_rescale_no_alloc_max_words()) // n + 1
     big = ctx.empty(too_many, L, n)
