@@ -283,6 +283,9 @@ def run_gpu(args, wl, default_line):
             line["breakdown"] = wl.breakdown
         if hasattr(wl, "rel_err"):
             line["max_rel_err_vs_float64_plaintext"] = wl.rel_err
+        if hasattr(wl, "abs_err"):
+            line["max_abs_err_vs_float64_plaintext"] = wl.abs_err
+            line["first_chunk_bit_exact_vs_oracle"] = wl.bit_exact
     # the other two headline metrics, from short runs of their workloads on this same GPU (default line, one GPU)
     if default_line and world == 1:
         del wl

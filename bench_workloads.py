@@ -453,7 +453,8 @@ class MaskWorkload:
 
     def step_gpu(self):
         l0 = _launches()
-        self.out = self.ek.aggregate_sharded(self.cts, self.selected, self.dim, self.rank, self.world)
+        self.kept = {}
+        self.out = self.ek.aggregate_sharded(self.cts, self.selected, self.dim, self.rank, self.world, keep=self.kept)
         self.launches_per_step = _launches() - l0
 
     def step_e2e(self):
@@ -464,8 +465,20 @@ class MaskWorkload:
         return 8 * len(self.selected), self.hout.numel() * 8
 
     def check_gpu(self):
-        self.max_abs_err = float((self.out - self.want).abs().max())
-        return bool(self.max_abs_err < 1e-6)
+        """the first chunk's size-3 sum against the CPU checker, bit for bit; the decoded average against the float64
+        mean of the selected updates (the error is the encryption noise of 2^16-coefficient ciphertexts over the
+        scale 2^40, a few 1e-7 on values of 1e-2: the bar is 1e-5 absolute)"""
+        from oracle import binding
+        self.abs_err = float((self.out - self.want).abs().max())
+        o = binding.Oracle(self.log_slots + 1, self.ek.context.moduli, 1, [])
+        masks = self.kept["masks"].cpu().numpy().view(np.uint64)
+        want = np.zeros((3, 3, 2 * self.slots), dtype=np.uint64)
+        for k in range(self.n_clients):
+            ct = self.cts[k][0].cpu().numpy().view(np.uint64)
+            want = o.poly_op("add", 3, want, o.tensor(3, ct, masks[k]))
+        got = self.kept["acc0"].cpu().numpy().view(np.uint64)
+        self.bit_exact = bool(np.array_equal(got.reshape(-1), want.reshape(-1)))
+        return bool(self.bit_exact and self.abs_err < 1e-5)
 
     def units_per_step(self):
         return 1.0

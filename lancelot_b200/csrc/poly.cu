@@ -306,7 +306,6 @@ int krum_accumulate(Context *ctx, int size_l, int n_chunks, const u64 *a, const 
 // (0,1),(0,2),..,(1,2),..; of a rectangle a * NB + b.  HBM reads per pair drop from two clients to
 // (NA + NB) / (NA * NB), 0.75 for the 2 x 4 rectangle.
 
-constexpr int kTileThreads = 128;
 constexpr int kTileMaxIn = 6, kTileMaxPairs = 8;
 
 struct KrumTileArgs {
@@ -314,65 +313,94 @@ struct KrumTileArgs {
     u64 *out[kTileMaxPairs];
 };
 
-// Data movement: a CTA owns kTileThreads consecutive coefficients of one limb.  Per chunk it needs one 1 KiB
-// segment of either polynomial of every client of the tile; an elected thread fetches them with bulk asynchronous
-// copies (cp.async.bulk, the 1-D form of the tensor memory accelerator; this GPU's own memory, no multicast) into a
-// ring of kTileStages shared-memory stages, each guarded by an mbarrier that counts the bytes.  Nothing of this sits
-// in registers, so three stages of up to 12 KiB per CTA are in flight ahead of the arithmetic at three CTAs per SM,
-// which is what the HBM latency asks for; the threads read their operands from shared memory when they need them.
+// Work split.  An item is one chunk of one unit; a unit is kTileSeg consecutive coefficients of one limb.  Items are
+// ordered by unit, then chunk, and every item carries its limb's cost weight (the 128-bit integer path of a 60-bit
+// prime is bound by its arithmetic, the FP64 path of a 40-bit one by its loads).  The grid is one CTA per SM, and CTA b takes the items whose
+// running cost lies in [total b / G, total (b + 1) / G): every CTA gets the same amount of work whatever the number
+// of units, and no wave of CTAs runs half empty.  A CTA's range cuts at most its first and its last unit; the sums
+// of such a partial piece go to a scratch slot of the CTA (slot 0: the piece starts the CTA's range, slot 1: any
+// later one) and a second, small kernel adds the pieces of each cut unit mod q.  Units that lie inside one CTA's
+// range are stored directly.
+//
+// Data movement: one thread per coefficient, and every thread feeds itself.  Thread t copies word t of either
+// polynomial of every client of the tile for the item a ring's length ahead with asynchronous 8-byte copies
+// (cp.async, global to shared memory without passing registers; a warp's copies of one row are 256 contiguous
+// bytes) into its own slots of a ring of shared-memory stages, and waits only for its own oldest copy group before it
+// reads them.  No thread ever reads another thread's slot, so the loop has no barrier of any kind, nothing to spin on
+// and nothing that could hang; with kTileRingBytes of copies in flight per SM the loads run at the rate of HBM while
+// eight warps do the arithmetic.  (A ring filled by bulk copies of the tensor memory accelerator, cp.async.bulk with
+// mbarriers, was built and measured first: one CTA got one item per microsecond out of it whatever the depth of the
+// ring, 3.7 TB/s at one CTA per SM against 6.8 TB/s for this ring.)
 //
 // Arithmetic: the limb's prime picks the pipe.  60-bit primes keep differences in (0, 2q) and sum them in 128 bits
-// (reduced in place every 63 chunks).  Primes below 2^41 (the 40-bit primes of Lancelot's chain) take the FP64
-// pipe: a difference d = b - a of two residues (|d| < 2^41) is split into d = h 2^21 + l with 0 <= l < 2^21 and
-// |h| <= 2^20, both exact as doubles; every product of two halves is below 2^42 in magnitude and exact, and a double
-// accumulator takes 2048 of them before 2^53 comes into reach.  Per pair
+// (reduced in place every 63 chunks).  Primes below 2^41 (the 40-bit primes of Lancelot's chain) take the FP64 pipe.
+// Every operand x < 2^41 is split ONCE per client into x = h 2^21 + l (l < 2^21, h < 2^20), each half planted in the
+// mantissa of a double with exponent 2^52 (two integer instructions and no conversion); the difference of two such
+// doubles is the exact signed difference of the halves, so a pair costs no integer work at all: four subtractions
+// give d = dh 2^21 + dl with |dl| < 2^21, |dh| < 2^20, every product of two halves is below 2^42 in magnitude and
+// exact, and a double accumulator takes 2048 of them before 2^53 comes into reach.  Per pair
 //   sum (d0)^2      = LL0 + 2^22 LH0 + 2^42 HH0      (LH0 = sum of l0 h0, counted twice)
 //   sum d0 d1       = LL1 + 2^21 X1  + 2^42 HH1      (X1 = sum of l0 h1 + h0 l1)
 //   sum (d1)^2      = LL2 + 2^22 LH2 + 2^42 HH2
-// are rebuilt as exact 128-bit integers at the end of a window and reduced mod q.  Ten fused multiply-adds per
-// pair, chunk and coefficient replace twelve 32 x 32 -> 64 bit multiplications and their carry chains.
+// are rebuilt as exact 128-bit integers at the end of a window and reduced mod q.  Ten fused multiply-adds and four
+// subtractions per pair, chunk and coefficient replace twelve 32 x 32 -> 64 bit multiplications, their carry chains
+// and the 64-bit subtractions.
+constexpr int kTileSeg = 256;                        // coefficients per unit = threads per CTA
+constexpr int kTileThreads = kTileSeg;
+constexpr int kTileMaxStages = 16;
+constexpr int kTileRingBytes = 160 * 1024; // shared memory the ring may take: the copies in flight per SM
+constexpr int kTileMaxLimbs = 64;
 constexpr u64 kTileF64PrimeLimit = u64(1) << 41;
 constexpr int kTileF64Window = 2048;
-constexpr int kTileStages = 4;
-constexpr unsigned kTileSpinLimit = 1u << 24; // polls of an mbarrier before the kernel gives up and raises status bit 1
+
+// stages of the ring for a tile of n_in clients: what fits kTileRingBytes at full segments
+constexpr int tile_stages(const int n_in)
+{
+    const int s = kTileRingBytes / (2 * n_in * kTileSeg * 8);
+    return s < 2 ? 2 : s > kTileMaxStages ? kTileMaxStages : s;
+}
+
+struct TilePlan {
+    long cost_base[kTileMaxLimbs + 1]; // running cost in front of limb l's items
+    int weight[kTileMaxLimbs];
+    int size_l, n_chunks, segs_per_limb, seg;
+    long n_items;
+};
 
 LB_D uint32_t tile_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-LB_D void mbar_init(const uint32_t bar, const unsigned count)
+// 8 bytes global -> shared without passing registers; completion is awaited per group of copies
+LB_D void cp_async8(const uint32_t dst, const void *src) { asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory"); }
+LB_D void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+LB_D void cp_async_wait()
 {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-LB_D void mbar_expect_tx(const uint32_t bar, const unsigned bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-LB_D bool mbar_try_wait(const uint32_t bar, const unsigned parity)
-{
-    unsigned ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok)
-                 : "r"(bar), "r"(parity)
-                 : "memory");
-    return ok != 0;
-}
-// global -> this CTA's shared memory, completion counted in bytes on the mbarrier; both addresses 16-byte aligned,
-// size a multiple of 16
-LB_D void bulk_load(const uint32_t dst, const void *src, const unsigned bytes, const uint32_t bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
-                 "r"(bar)
-                 : "memory");
+    asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
 }
 
-struct TileHalves {
-    double l, h;
-};
-// a signed difference |d| < 2^41 as d = h 2^21 + l with 0 <= l < 2^21
-LB_D TileHalves tile_split(const long long d)
+// first item of CTA b of G: the item at which the running cost reaches total * b / G
+LB_D long tile_boundary(const TilePlan &pl, const int b, const int G)
 {
-    TileHalves r;
-    r.l = __dadd_rn(__hiloint2double(0x43300000, (int)((unsigned)d & 0x1FFFFFu)), -4503599627370496.0);
-    // h in [-2^20, 2^20): biased by 2^20 into an unsigned word, the bias taken off again as a double
-    r.h = __dadd_rn(__hiloint2double(0x43300000, (int)((unsigned)(d >> 21) + 0x100000u)), -(4503599627370496.0 + 1048576.0));
+    if (b <= 0) return 0;
+    if (b >= G) return pl.n_items;
+    const long t = pl.cost_base[pl.size_l] / G * b + pl.cost_base[pl.size_l] % G * b / G;
+    int l = 0;
+    while (l + 1 < pl.size_l && pl.cost_base[l + 1] <= t) ++l;
+    const long per_limb = (long)pl.segs_per_limb * pl.n_chunks;
+    return per_limb * l + (t - pl.cost_base[l] + pl.weight[l] - 1) / pl.weight[l];
+}
+
+// the two polynomials' residues of one client as halves planted in doubles of exponent 2^52
+struct TileOperand {
+    double l0, h0, l1, h1;
+};
+LB_D double tile_planted(const unsigned v) { return __hiloint2double(0x43300000, (int)v); }
+LB_D TileOperand tile_operand(const u64 x0, const u64 x1)
+{
+    TileOperand r;
+    r.l0 = tile_planted((unsigned)x0 & 0x1FFFFFu);
+    r.h0 = tile_planted((unsigned)(x0 >> 21));
+    r.l1 = tile_planted((unsigned)x1 & 0x1FFFFFu);
+    r.h1 = tile_planted((unsigned)(x1 >> 21));
     return r;
 }
 // (ll + mid 2^shift + hh 2^42) mod q for integer-valued doubles below 2^53 in magnitude; the total may be negative
@@ -388,169 +416,263 @@ LB_D u64 tile_fold(const double ll, const double mid, const int shift, const dou
 
 // stage layout: row (client i, polynomial t) at words [(2 i + t) * seg, +seg)
 template <int NA, int NB>
-__global__ void __launch_bounds__(kTileThreads, (NA + NB > 4 ? 2 : 3)) krum_tile_kernel(const KrumTileArgs args, const ModConst *__restrict__ mc, const int logn,
-                                                                    const long per_poly, const long chunk_stride, const int n_chunks,
-                                                                    int *__restrict__ status)
+__global__ void __launch_bounds__(kTileThreads, 1) krum_tile_kernel(const __grid_constant__ KrumTileArgs args, const __grid_constant__ TilePlan pl,
+                                                                    const ModConst *__restrict__ mc, const int logn, const long per_poly,
+                                                                    const long chunk_stride, u64 *__restrict__ scratch)
 {
-    constexpr int NI = NA + NB, NP = NB ? NA * NB : NA * (NA - 1) / 2;
+    constexpr int NI = NA + NB, NP = NB ? NA * NB : NA * (NA - 1) / 2, STAGES = tile_stages(NI);
     extern __shared__ __align__(128) u64 tile_sm[];
-    __shared__ __align__(8) unsigned long long bars[kTileStages];
-    const int seg = min(kTileThreads, 1 << logn);              // coefficients per CTA
-    const int blocks_per_limb = (1 << logn) / seg;
-    const int limb = blockIdx.x / blocks_per_limb;
-    const long e0 = ((long)limb << logn) + (long)(blockIdx.x - limb * blocks_per_limb) * seg; // first coefficient of this CTA
-    const ModConst m = mc[limb];
-    const unsigned stage_bytes = (unsigned)(2 * NI * seg * sizeof(u64));
-    const uint32_t sm_base = tile_smem(tile_sm), bar_base = tile_smem(bars);
-
-    if (threadIdx.x == 0) {
-#pragma unroll
-        for (int s = 0; s < kTileStages; ++s) mbar_init(bar_base + 8u * s, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    auto issue = [&](const int c) { // thread 0: fetch chunk c into stage c % kTileStages
-        const int s = c % kTileStages;
-        const uint32_t bar = bar_base + 8u * s, dst = sm_base + (uint32_t)s * stage_bytes;
-        mbar_expect_tx(bar, stage_bytes);
-#pragma unroll
-        for (int i = 0; i < NI; ++i) {
-            const u64 *src = args.in[i] + c * chunk_stride + e0;
-            bulk_load(dst + (uint32_t)((2 * i) * seg * 8), src, (unsigned)(seg * 8), bar);
-            bulk_load(dst + (uint32_t)((2 * i + 1) * seg * 8), src + per_poly, (unsigned)(seg * 8), bar);
-        }
-    };
-    if (threadIdx.x == 0) {
-        for (int c = 0; c < kTileStages && c < n_chunks; ++c) issue(c);
-    }
-    const bool active = (int)threadIdx.x < seg;
-    const int t = active ? threadIdx.x : 0;
-    const bool f64 = m.q < kTileF64PrimeLimit;
-    bool failed = false;
-
-    // one chunk: waits for its stage, hands the operands of pair (i, j) to `pair`, releases the stage
-    auto chunk = [&](const int c, auto &&pair) {
-        const int s = c % kTileStages;
-        const uint32_t bar = bar_base + 8u * s;
-        const unsigned parity = (unsigned)(c / kTileStages) & 1u;
-        unsigned polls = 0;
-        bool gave_up = false;
-        while (!mbar_try_wait(bar, parity)) {
-            if (++polls > kTileSpinLimit) { // a copy that never lands: give up, say so, leave without touching the data
-                gave_up = true;
-                break;
-            }
-        }
-        failed = __syncthreads_or(gave_up); // the whole CTA goes on or leaves together
-        if (!failed) {
-            const u64 *row = tile_sm + (size_t)s * (2 * NI * seg) + t;
-            int p = 0;
-#pragma unroll
-            for (int i = 0; i < NA; ++i) {
-#pragma unroll
-                for (int j = NB ? NA : i + 1; j < NI; ++j, ++p)
-                    pair(p, row[(2 * i) * seg], row[(2 * i + 1) * seg], row[(2 * j) * seg], row[(2 * j + 1) * seg]);
-            }
-        }
-        __syncthreads(); // every thread has read the stage (or given up) before it is refilled
-        if (threadIdx.x == 0 && !failed && c + kTileStages < n_chunks) issue(c + kTileStages);
+    const int seg = pl.seg, n_chunks = pl.n_chunks, segs = pl.segs_per_limb;
+    const int G = gridDim.x, cta = blockIdx.x;
+    const int t = threadIdx.x;
+    if (t >= seg) return; // rings of fewer than kTileSeg coefficients; the kernel has no barrier
+    const long lo = tile_boundary(pl, cta, G), hi = tile_boundary(pl, cta + 1, G);
+    const unsigned row_bytes = (unsigned)(seg * sizeof(u64)), stage_bytes = 2 * NI * row_bytes;
+    const uint32_t sm_t = tile_smem(tile_sm) + (uint32_t)t * 8u;
+    auto unit_offset = [&](const long unit) { // first coefficient of the unit, plus this thread's
+        const int limb = (int)(unit / segs);
+        return ((long)limb << logn) + (unit - (long)limb * segs) * seg + t;
     };
 
-    const long e = e0 + t;
-    if (f64) {
-        u64 r0[NP], r1[NP], r2[NP];
+    // ---- this thread's copies: the ring is filled up front; then one item is requested per item read ----
+    long p_left = hi - lo, p_unit = lo / n_chunks;
+    int p_c = (int)(lo - p_unit * n_chunks), p_s = 0;
+    long p_off = p_c * chunk_stride + unit_offset(p_unit);
+    auto produce = [&]() {
+        if (p_left > 0) {
+            const uint32_t dst = sm_t + (uint32_t)p_s * stage_bytes;
 #pragma unroll
-        for (int p = 0; p < NP; ++p) r0[p] = r1[p] = r2[p] = 0;
-        for (int c0 = 0; c0 < n_chunks && !failed; c0 += kTileF64Window) {
-            const int c1 = min(c0 + kTileF64Window, n_chunks);
-            double ll0[NP], lh0[NP], hh0[NP], ll1[NP], x1[NP], hh1[NP], ll2[NP], lh2[NP], hh2[NP];
-#pragma unroll
-            for (int p = 0; p < NP; ++p) ll0[p] = lh0[p] = hh0[p] = ll1[p] = x1[p] = hh1[p] = ll2[p] = lh2[p] = hh2[p] = 0.0;
-            for (int c = c0; c < c1 && !failed; ++c) {
-                chunk(c, [&](const int p, const u64 a0, const u64 a1, const u64 b0, const u64 b1) {
-                    const TileHalves d0 = tile_split((long long)(b0 - a0)), d1 = tile_split((long long)(b1 - a1));
-                    ll0[p] = __fma_rn(d0.l, d0.l, ll0[p]);
-                    lh0[p] = __fma_rn(d0.l, d0.h, lh0[p]);
-                    hh0[p] = __fma_rn(d0.h, d0.h, hh0[p]);
-                    ll1[p] = __fma_rn(d0.l, d1.l, ll1[p]);
-                    x1[p] = __fma_rn(d0.l, d1.h, x1[p]);
-                    x1[p] = __fma_rn(d0.h, d1.l, x1[p]);
-                    hh1[p] = __fma_rn(d0.h, d1.h, hh1[p]);
-                    ll2[p] = __fma_rn(d1.l, d1.l, ll2[p]);
-                    lh2[p] = __fma_rn(d1.l, d1.h, lh2[p]);
-                    hh2[p] = __fma_rn(d1.h, d1.h, hh2[p]);
-                });
+            for (int i = 0; i < NI; ++i) {
+                const u64 *src = args.in[i] + p_off;
+                cp_async8(dst + (uint32_t)(2 * i) * row_bytes, src);
+                cp_async8(dst + (uint32_t)(2 * i + 1) * row_bytes, src + per_poly);
             }
-#pragma unroll
-            for (int p = 0; p < NP; ++p) {
-                r0[p] = add_mod(r0[p], tile_fold(ll0[p], lh0[p], 22, hh0[p], m), m.q);
-                r1[p] = add_mod(r1[p], tile_fold(ll1[p], x1[p], 21, hh1[p], m), m.q);
-                r2[p] = add_mod(r2[p], tile_fold(ll2[p], lh2[p], 22, hh2[p], m), m.q);
+            --p_left;
+            p_off += chunk_stride;
+            if (++p_c == n_chunks) {
+                p_c = 0;
+                ++p_unit;
+                if (p_left > 0) p_off = unit_offset(p_unit);
             }
+            if (++p_s == STAGES) p_s = 0;
         }
-        if (active && !failed) {
+        cp_async_commit(); // one group per call, empty at the tail, so the group count below stays fixed
+    };
+#pragma unroll 1
+    for (int i = 0; i < STAGES - 1; ++i) produce();
+
+    {
+        int s = 0;
+        // requests the item a ring's length ahead, waits for this thread's copies of the next item, returns its rows
+        auto acquire = [&]() -> const u64 * {
+            produce();
+            cp_async_wait<STAGES - 1>();
+            return tile_sm + (size_t)s * (2 * NI * seg) + t;
+        };
+        auto release = [&]() {
+            if (++s == STAGES) s = 0;
+        };
+
+        long it = lo;
+        long unit = lo / n_chunks;
+        int c = (int)(lo - unit * n_chunks);
+        while (it < hi) {
+            // one piece: chunks [c, c_end) of this unit
+            const int c_end = (int)min((long)n_chunks, (long)c + (hi - it));
+            const int limb = (int)(unit / segs);
+            const ModConst m = mc[limb];
+            const long e = ((long)limb << logn) + (unit - (long)limb * segs) * seg + t;
+            // where this piece's sums go: the whole unit is final; a cut piece goes to this CTA's slot and is added
+            // up by krum_tile_combine_kernel
+            const bool whole = c == 0 && c_end == n_chunks;
+            u64 *const piece = scratch + ((size_t)cta * 2 + (it == lo ? 0 : 1)) * (NP * 3) * seg + t;
+            auto emit = [&](const int p, u64 v0, u64 v1, u64 v2, const bool add) {
+                u64 *const d = whole ? args.out[p] + e : piece + (size_t)(p * 3) * seg;
+                const long st = whole ? per_poly : (long)seg;
+                v1 = add_mod(v1, v1, m.q); // middle term is 2 x0 x1
+                if (add) { // a later window of a piece of more than kTileF64Window chunks
+                    v0 = add_mod(v0, d[0], m.q);
+                    v1 = add_mod(v1, d[st], m.q);
+                    v2 = add_mod(v2, d[2 * st], m.q);
+                }
+                d[0] = v0;
+                d[st] = v1;
+                d[2 * st] = v2;
+            };
+            if (m.q < kTileF64PrimeLimit) {
+                for (int w0 = c; w0 < c_end; w0 += kTileF64Window) {
+                    const int w1 = min(w0 + kTileF64Window, c_end);
+                    double ll0[NP], lh0[NP], hh0[NP], ll1[NP], x1[NP], hh1[NP], ll2[NP], lh2[NP], hh2[NP];
 #pragma unroll
-            for (int p = 0; p < NP; ++p) {
-                u64 *dst = args.out[p];
-                dst[e] = r0[p];
-                dst[per_poly + e] = add_mod(r1[p], r1[p], m.q); // middle term is 2 x0 x1
-                dst[2 * per_poly + e] = r2[p];
-            }
-        }
-    } else {
-        // 128-bit running sums; every 63 chunks they are reduced in place, which leaves room for
-        // 63 more products of differences below 2^61
-        u128d s0[NP], s1[NP], s2[NP];
+                    for (int p = 0; p < NP; ++p) ll0[p] = lh0[p] = hh0[p] = ll1[p] = x1[p] = hh1[p] = ll2[p] = lh2[p] = hh2[p] = 0.0;
+                    auto pair = [&](const int p, const TileOperand &a, const TileOperand &b) {
+                        const double dl0 = __dsub_rn(b.l0, a.l0), dh0 = __dsub_rn(b.h0, a.h0);
+                        const double dl1 = __dsub_rn(b.l1, a.l1), dh1 = __dsub_rn(b.h1, a.h1);
+                        ll0[p] = __fma_rn(dl0, dl0, ll0[p]);
+                        lh0[p] = __fma_rn(dl0, dh0, lh0[p]);
+                        hh0[p] = __fma_rn(dh0, dh0, hh0[p]);
+                        ll1[p] = __fma_rn(dl0, dl1, ll1[p]);
+                        x1[p] = __fma_rn(dl0, dh1, x1[p]);
+                        x1[p] = __fma_rn(dh0, dl1, x1[p]);
+                        hh1[p] = __fma_rn(dh0, dh1, hh1[p]);
+                        ll2[p] = __fma_rn(dl1, dl1, ll2[p]);
+                        lh2[p] = __fma_rn(dl1, dh1, lh2[p]);
+                        hh2[p] = __fma_rn(dh1, dh1, hh2[p]);
+                    };
+                    for (int cc = w0; cc < w1; ++cc) {
+                        const u64 *row = acquire();
+                        TileOperand a[NA];
 #pragma unroll
-        for (int p = 0; p < NP; ++p) s0[p] = s1[p] = s2[p] = u128d{0, 0};
-        for (int c0 = 0; c0 < n_chunks && !failed; c0 += 63) {
-            const int c1 = min(c0 + 63, n_chunks);
-            for (int c = c0; c < c1 && !failed; ++c) {
-                chunk(c, [&](const int p, const u64 a0, const u64 a1, const u64 b0, const u64 b1) {
-                    // differences left in (0, 2q): 63 products below 2^122 and a residue fit 128 bits
-                    const u64 x0 = b0 + m.q - a0, x1 = b1 + m.q - a1;
-                    mac_wide(s0[p], x0, x0);
-                    mac_wide(s1[p], x0, x1);
-                    mac_wide(s2[p], x1, x1);
-                });
-            }
+                        for (int i = 0; i < NA; ++i) a[i] = tile_operand(row[(2 * i) * seg], row[(2 * i + 1) * seg]);
+                        if (NB) {
 #pragma unroll
-            for (int p = 0; p < NP; ++p) {
-                s0[p] = u128d{barrett128(s0[p], m.q, m.r0, m.r1), 0};
-                s1[p] = u128d{barrett128(s1[p], m.q, m.r0, m.r1), 0};
-                s2[p] = u128d{barrett128(s2[p], m.q, m.r0, m.r1), 0};
-            }
-        }
-        if (active && !failed) {
+                            for (int j = 0; j < NB; ++j) {
+                                const TileOperand b = tile_operand(row[(2 * (NA + j)) * seg], row[(2 * (NA + j) + 1) * seg]);
 #pragma unroll
-            for (int p = 0; p < NP; ++p) {
-                u64 *dst = args.out[p];
-                dst[e] = s0[p].lo;
-                dst[per_poly + e] = add_mod(s1[p].lo, s1[p].lo, m.q); // middle term is 2 x0 x1
-                dst[2 * per_poly + e] = s2[p].lo;
+                                for (int i = 0; i < NA; ++i) pair(i * NB + j, a[i], b);
+                            }
+                        } else {
+                            int p = 0;
+#pragma unroll
+                            for (int i = 0; i < NA; ++i) {
+#pragma unroll
+                                for (int j = i + 1; j < NA; ++j, ++p) pair(p, a[i], a[j]);
+                            }
+                        }
+                        release();
+                    }
+                    {
+#pragma unroll
+                        for (int p = 0; p < NP; ++p)
+                            emit(p, tile_fold(ll0[p], lh0[p], 22, hh0[p], m), tile_fold(ll1[p], x1[p], 21, hh1[p], m),
+                                 tile_fold(ll2[p], lh2[p], 22, hh2[p], m), w0 != c);
+                    }
+                }
+            } else {
+                // 128-bit running sums; every 63 chunks they are reduced in place, which leaves room for
+                // 63 more products of differences below 2^61
+                u128d s0[NP], s1[NP], s2[NP];
+#pragma unroll
+                for (int p = 0; p < NP; ++p) s0[p] = s1[p] = s2[p] = u128d{0, 0};
+                for (int w0 = c; w0 < c_end; w0 += 63) {
+                    const int w1 = min(w0 + 63, c_end);
+                    for (int cc = w0; cc < w1; ++cc) {
+                        const u64 *row = acquire();
+                        int p = 0;
+#pragma unroll
+                        for (int i = 0; i < NA; ++i) {
+                            const u64 a0 = row[(2 * i) * seg], a1 = row[(2 * i + 1) * seg];
+#pragma unroll
+                            for (int j = NB ? NA : i + 1; j < NI; ++j, ++p) {
+                                // differences left in (0, 2q): 63 products below 2^122 and a residue fit 128 bits
+                                const u64 d0 = row[(2 * j) * seg] + m.q - a0, d1 = row[(2 * j + 1) * seg] + m.q - a1;
+                                mac_wide(s0[p], d0, d0);
+                                mac_wide(s1[p], d0, d1);
+                                mac_wide(s2[p], d1, d1);
+                            }
+                        }
+                        release();
+                    }
+#pragma unroll
+                    for (int p = 0; p < NP; ++p) {
+                        s0[p] = u128d{barrett128(s0[p], m.q, m.r0, m.r1), 0};
+                        s1[p] = u128d{barrett128(s1[p], m.q, m.r0, m.r1), 0};
+                        s2[p] = u128d{barrett128(s2[p], m.q, m.r0, m.r1), 0};
+                    }
+                }
+#pragma unroll
+                for (int p = 0; p < NP; ++p) emit(p, s0[p].lo, s1[p].lo, s2[p].lo, false);
             }
+            it += c_end - c;
+            c = c_end;
+            if (c == n_chunks) c = 0, ++unit;
         }
     }
-    if (failed && threadIdx.x == 0) atomicOr(status, 2);
+}
+
+// adds the pieces of every unit that more than one CTA of krum_tile_kernel worked on; one CTA per unit
+__global__ void __launch_bounds__(kTileSeg) krum_tile_combine_kernel(const __grid_constant__ KrumTileArgs args, const __grid_constant__ TilePlan pl,
+                                                                     const ModConst *__restrict__ mc, const int logn, const long per_poly,
+                                                                     const u64 *__restrict__ scratch, const int G, const int n_pairs)
+{
+    const int seg = pl.seg, n_chunks = pl.n_chunks, segs = pl.segs_per_limb;
+    const int t = threadIdx.x;
+    if (t >= seg) return;
+    const long unit = blockIdx.x;
+    const int limb = (int)(unit / segs);
+    const u64 q = mc[limb].q;
+    const long e = ((long)limb << logn) + (unit - (long)limb * segs) * seg + t;
+    const long first = unit * n_chunks, last = first + n_chunks;
+    int b0 = 0;
+    if (n_chunks > 0) {
+        // the CTA that holds the unit's first item: an estimate from the cost, then exact
+        const long cpos = pl.cost_base[limb] + (first - (long)limb * segs * n_chunks) * pl.weight[limb];
+        const long total = pl.cost_base[pl.size_l];
+        b0 = (int)min((long)G - 1, (long)((double)cpos / (double)total * G));
+        while (b0 + 1 < G && tile_boundary(pl, b0 + 1, G) <= first) ++b0;
+        while (b0 > 0 && tile_boundary(pl, b0, G) > first) --b0;
+        if (tile_boundary(pl, b0 + 1, G) >= last) return; // one CTA had the whole unit and stored it
+    }
+    for (int w = 0; w < n_pairs * 3; ++w) {
+        u64 acc = 0;
+        for (int b = b0; n_chunks > 0 && b < G; ++b) {
+            const long blo = tile_boundary(pl, b, G);
+            if (blo >= last) break;
+            const long plo = max(blo, first), phi = min(tile_boundary(pl, b + 1, G), last);
+            if (plo >= phi) continue;
+            acc = add_mod(acc, scratch[(((size_t)b * 2 + (plo == blo ? 0 : 1)) * (n_pairs * 3) + w) * seg + t], q);
+        }
+        args.out[w / 3][(w % 3) * per_poly + e] = acc;
+    }
 }
 
 template <int NA, int NB>
 static int launch_tile(Context *ctx, const KrumTileArgs &args, int size_l, int n_chunks, long chunk_stride, cudaStream_t stream)
 {
-    const long per_poly = (long)size_l << ctx->hp.logN;
-    const int seg = (1 << ctx->hp.logN) < kTileThreads ? (1 << ctx->hp.logN) : kTileThreads;
-    const long blocks = (long)size_l * ((1L << ctx->hp.logN) / seg);
-    const size_t smem = (size_t)kTileStages * 2 * (NA + NB) * seg * sizeof(u64);
-    static bool configured[64] = {};
+    constexpr int NP = NB ? NA * NB : NA * (NA - 1) / 2;
+    const int logn = ctx->hp.logN;
+    const long per_poly = (long)size_l << logn;
+    if (size_l > kTileMaxLimbs) {
+        set_error("a Krum tile takes at most 64 limbs");
+        return LB_ERR_INVALID_ARG;
+    }
+    TilePlan pl = {};
+    pl.seg = (1 << logn) < kTileSeg ? (1 << logn) : kTileSeg;
+    pl.segs_per_limb = (1 << logn) / pl.seg;
+    pl.size_l = size_l;
+    pl.n_chunks = n_chunks;
+    const long per_limb = (long)pl.segs_per_limb * n_chunks;
+    pl.n_items = per_limb * size_l;
+    for (int l = 0; l < size_l; ++l) {
+        // measured on B200: an item of the FP64 path takes the time of its loads (2 units per client), one of the
+        // integer path the time of its arithmetic (3 units per pair) where that is more
+        const int loads = 2 * (NA + NB), sums = 3 * NP;
+        pl.weight[l] = ctx->hp.q[l] < kTileF64PrimeLimit ? loads : (sums > loads ? sums : loads);
+        pl.cost_base[l + 1] = pl.cost_base[l] + per_limb * pl.weight[l];
+    }
+    const size_t smem = (size_t)tile_stages(NA + NB) * 2 * (NA + NB) * pl.seg * sizeof(u64);
+    static int ctas_per_sm[64] = {};
     int dev = 0;
     LB_CUDA(cudaGetDevice(&dev));
-    if (!configured[dev & 63]) {
-        LB_CUDA(cudaFuncSetAttribute(krum_tile_kernel<NA, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kTileStages * 2 * 6 * kTileThreads * sizeof(u64))));
-        configured[dev & 63] = true;
+    if (!ctas_per_sm[dev & 63]) {
+        const size_t most = (size_t)tile_stages(NA + NB) * 2 * (NA + NB) * kTileSeg * sizeof(u64); // full segments
+        LB_CUDA(cudaFuncSetAttribute(krum_tile_kernel<NA, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
+        int occ = 0;
+        LB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, krum_tile_kernel<NA, NB>, kTileThreads, most));
+        ctas_per_sm[dev & 63] = occ > 0 ? occ : 1;
     }
-    count_launch("krum_tile_kernel", stream, 8.0 * per_poly * ((double)(NA + NB) * 2 * n_chunks + 3.0 * (NB ? NA * NB : NA * (NA - 1) / 2)));
-    krum_tile_kernel<NA, NB><<<(unsigned)blocks, kTileThreads, smem, stream>>>(args, ctx->d_mc, ctx->hp.logN, per_poly, chunk_stride, n_chunks,
-                                                                               ctx->d_status);
+    long G = (long)ctas_per_sm[dev & 63] * ctx->sm_count;
+    if (G > pl.n_items) G = pl.n_items > 0 ? pl.n_items : 1;
+    int rc = ctx->ensure_workspace((size_t)G * 2 * NP * 3 * pl.seg * sizeof(u64));
+    if (rc) return rc;
+    u64 *scratch = reinterpret_cast<u64 *>(ctx->ws);
+    if (pl.n_items > 0) {
+        count_launch("krum_tile_kernel", stream, 8.0 * per_poly * ((double)(NA + NB) * 2 * n_chunks + 3.0 * NP));
+        krum_tile_kernel<NA, NB><<<(unsigned)G, kTileThreads, smem, stream>>>(args, pl, ctx->d_mc, logn, per_poly, chunk_stride, scratch);
+        LB_CUDA(cudaGetLastError());
+    }
+    count_launch("krum_tile_combine_kernel", stream);
+    krum_tile_combine_kernel<<<(unsigned)(size_l * pl.segs_per_limb), kTileSeg, 0, stream>>>(args, pl, ctx->d_mc, logn, per_poly, scratch, (int)G, NP);
     LB_CUDA(cudaGetLastError());
     return LB_OK;
 }
@@ -648,7 +770,8 @@ int mask_accumulate(Context *ctx, int size_l, int n_clients, int n_chunks, const
     const int log_half_n = ctx->hp.logN - 1;
     const long per_poly = (long)size_l << log_half_n;
     long blocks = (per_poly + kKrumThreads - 1) / kKrumThreads;
-    count_launch("mask_accumulate_kernel", stream);
+    // every client's ciphertext read once, one size-3 sum per chunk written
+    count_launch("mask_accumulate_kernel", stream, 8.0 * (size_l << ctx->hp.logN) * n_chunks * (2.0 * n_clients + 3.0));
     mask_accumulate_kernel<<<dim3((unsigned)blocks, (unsigned)n_chunks), kKrumThreads, 0, stream>>>(
         args, reinterpret_cast<const ulonglong2 *>(masks), reinterpret_cast<ulonglong2 *>(out), ctx->d_mc, log_half_n, per_poly,
         chunk_stride / 2);

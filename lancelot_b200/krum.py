@@ -596,11 +596,12 @@ class EncryptedKrum:
         seeds = cahel._seeds(2)
         return self.lb.encode_encrypt(self.pk.data, v, self.scale, seeds, self.slots, 1).reshape(2, 3, self.N)
 
-    def aggregate(self, cts, selected, dim):
+    def aggregate(self, cts, selected, dim, keep=None):
         """cts: dict client -> [chunks][2][3][N] for ALL clients 0..n-1.  Multiplies every client's ciphertexts
         with its mask ciphertext (Enc(1/k) for the k selected clients, Enc(0) for the rest), adds the products,
         decrypts the size-3 results and decodes them: the plaintext average of the selected updates.
-        With one selected client this is GPU_mul_mask_weight; with several it is an encrypted trimmed mean."""
+        With one selected client this is GPU_mul_mask_weight; with several it is an encrypted trimmed mean.
+        keep: optional dict that receives the mask ciphertexts and the first chunk's size-3 sum (for checks)."""
         lb, N = self.lb, self.N
         n_clients = len(cts)
         chunks = cts[0].shape[0]
@@ -608,12 +609,14 @@ class EncryptedKrum:
         zero = self.encrypt_constant(0.0)
         masks = torch.stack([one if k in set(int(x) for x in selected) else zero for k in range(n_clients)]).contiguous()
         acc = lb.mask_accumulate(3, [cts[k] for k in range(n_clients)], masks, chunks)
+        if keep is not None:
+            keep["masks"], keep["acc0"] = masks, acc[0].clone()
         pts = lb.decrypt_batch(3, acc, self.sk.data, 3, chunks)
         del acc
         vals = lb.decode_batch(3, pts, self.scale * self.scale, self.slots, chunks)
         return vals.real.reshape(-1)[:dim]
 
-    def aggregate_sharded(self, cts, selected, dim, rank=0, world_size=1, group=None):
+    def aggregate_sharded(self, cts, selected, dim, rank=0, world_size=1, group=None, keep=None):
         """The mask multiplication with the chunk axis sharded over the ranks, as the distance round leaves the
         ciphertexts: cts holds THIS rank's chunk range of every client ([n_clients][k][2][3][N], k = its share of the
         chunks).  Every rank multiplies, decrypts and decodes its chunks; the decoded slices are all-gathered.  Returns
@@ -621,7 +624,7 @@ class EncryptedKrum:
         import torch.distributed as dist
 
         k = cts[0].shape[0]
-        local = self.aggregate(cts, selected, k * self.slots) if k else torch.empty(0, dtype=torch.float64, device="cuda:%d" % self.lb.device)
+        local = self.aggregate(cts, selected, k * self.slots, keep=keep) if k else torch.empty(0, dtype=torch.float64, device="cuda:%d" % self.lb.device)
         if world_size == 1:
             return local[:dim]
         chunks = self.n_chunks(dim)
