@@ -109,7 +109,7 @@ class KrumWorkload:
         from lancelot_b200 import krum
         t0 = time.perf_counter()
         l0 = _launches()
-        ek = krum.EncryptedKrum(log_slots=self.log_slots, device=self.device, seed=1)
+        ek = krum.EncryptedKrum(log_slots=self.log_slots, device=self.device, seed=1, rank=self.rank, world_size=self.world)
         self.torch.cuda.synchronize()
         t1 = time.perf_counter()
         timing = {} if self.profile_phases else None

@@ -173,6 +173,22 @@ LB_API int lb_krum_accumulate(lb_context *ctx, int size_l, int n_chunks, const u
 LB_API int lb_krum_accumulate_tile(lb_context *ctx, int size_l, int n_chunks, int n_a, const uint64_t *const *a, int n_b,
                             const uint64_t *const *b, size_t chunk_stride, uint64_t *const *out, void *stream);
 
+/* The pair sums of a round in one call: out[p][3][size_l][N] = sum over chunks of square(ct_j - ct_i) for
+ * pairs[2p] = i < pairs[2p+1] = j (the loop over pairs and chunks of byzantine_fl.py:466-514 with the diagonal left
+ * out).  cts: HOST array of n_clients device pointers (only the clients that occur in a pair are read), chunk c of a
+ * client chunk_stride words after chunk c - 1; pairs: HOST array.  The call covers the list with the tiles of
+ * lb_krum_accumulate_tile that read the least (triangles of four clients, two clients against four). */
+LB_API int lb_krum_pair_sums(lb_context *ctx, int size_l, int n_clients, const uint64_t *const *cts, int n_chunks, size_t chunk_stride,
+                      int n_pairs, const int *pairs, uint64_t *out, void *stream);
+/* From pair sums to score ciphertexts (byzantine_fl.py:244-273) for a batch: relinearize_inplace and
+ * rescale_to_next_inplace of acc [n_pairs][3][size_l][N] (overwritten), scores <- result [n_pairs][2][size_l-1][N],
+ * scores += hoisting(scores, first steps), then scores += rotate(scores, step) for every further step in order.
+ * first_keys / pow_keys: HOST arrays of device pointers to the Galois keys of first_elts / pow_elts (indices into
+ * the context's Galois elements); scratch: device words of the size of scores. */
+LB_API int lb_krum_scores(lb_context *ctx, int size_l, int n_pairs, uint64_t *acc, const uint64_t *relin_key, int n_first,
+                   const int *first_elts, const uint64_t *const *first_keys, int n_pow, const int *pow_elts,
+                   const uint64_t *const *pow_keys, uint64_t *scores, uint64_t *scratch, void *stream);
+
 /* Mask multiplication of the aggregation phase (lancelot-main-GPU/utils/byzantine_fl.py:371-429):
  * out[c][3][size_l][N] = sum over clients k of ct_k[c] (x) mask_k (ckks_multiply + add_inplace per client
  * in the reference).  client_cts: HOST array of n_clients device pointers, chunk c of client k at

@@ -267,6 +267,35 @@ class Context:
         check(lib.lb_krum_accumulate_tile(self.h, size_l, n_chunks, len(a), pa, len(b), pb, C.c_size_t(ct_words), po, self._stream()))
         return outs
 
+    def krum_pair_sums(self, size_l, cts, n_clients, pairs, out):
+        """cts: client -> [chunks][2][size_l][N] (dict, list or tensor indexed by client; clients in no pair may be
+        missing); pairs: list of (i, j), i < j; out: [>= len(pairs)][3][size_l][N], pair p's sums at out[p]"""
+        ct_words = 2 * size_l * self.N
+        used = sorted({c for p in pairs for c in p})
+        n_chunks = cts[used[0]].numel() // ct_words if used else 0
+        ptrs = (C.c_void_p * max(1, n_clients))()
+        for c in used:
+            ptrs[c] = cts[c].data_ptr()
+        flat = (C.c_int * max(1, 2 * len(pairs)))(*[int(x) for p in pairs for x in p])
+        check(lib.lb_krum_pair_sums(self.h, size_l, n_clients, ptrs, n_chunks, C.c_size_t(ct_words), len(pairs), flat, _p(out),
+                                    self._stream()))
+        return out
+
+    def krum_scores(self, size_l, acc, rlk, first_elts, first_keys, pow_elts, pow_keys):
+        """acc [P][3][size_l][N] (overwritten) -> scores [P][2][size_l-1][N]: relinearize, rescale, hoisted rotations
+        by first_elts added, then rotate + add for every element of pow_elts in order"""
+        n_pairs = acc.numel() // (3 * size_l * self.N)
+        scores = self.empty(n_pairs, 2, size_l - 1, self.N)
+        scratch = self.empty(n_pairs, 2, size_l - 1, self.N)
+        nf, npw = len(first_elts), len(pow_elts)
+        fe = (C.c_int * max(1, nf))(*first_elts)
+        fk = (C.c_void_p * max(1, nf))(*[g.data_ptr() for g in first_keys])
+        pe = (C.c_int * max(1, npw))(*pow_elts)
+        pk = (C.c_void_p * max(1, npw))(*[g.data_ptr() for g in pow_keys])
+        check(lib.lb_krum_scores(self.h, size_l, n_pairs, _p(acc), _p(rlk), nf, fe, fk, npw, pe, pk, _p(scores), _p(scratch),
+                                 self._stream()))
+        return scores
+
     def decrypt(self, size_l, ct, sk):
         n_polys = ct.numel() // (size_l * self.N)
         pt = self.empty(size_l, self.N)

@@ -1,6 +1,8 @@
 // extern "C" surface declared in include/lancelot_b200.h.  Argument validation lives here
 // (the kernels trust their launchers); nothing below ever computes on the CPU.
+#include <algorithm>
 #include <cstring>
+#include <vector>
 
 #include "context.h"
 
@@ -401,6 +403,122 @@ int lb_krum_accumulate_tile(lb_context *h, int size_l, int n_chunks, int n_a, co
     const int n_pairs = n_b ? n_a * n_b : n_a * (n_a - 1) / 2;
     for (int i = 0; i < n_pairs && i < 8; ++i) REQUIRE(out[i], "operand is null");
     return krum_accumulate_tile(C(h), size_l, n_chunks, n_a, a, n_b, b, (long)chunk_stride, out, S(stream));
+}
+
+// The pair list of a round as tiles of lb_krum_accumulate_tile.  Clients are blocked by index in groups of four; a
+// diagonal block whose pairs are all the pairs of its clients is one triangle, anything else is cut into rectangles of
+// one or two first clients that share their set of second clients.
+int lb_krum_pair_sums(lb_context *h, int size_l, int n_clients, const uint64_t *const *cts, int n_chunks, size_t chunk_stride,
+                      int n_pairs, const int *pairs, uint64_t *out, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    if ((rc = level_ok(C(h), size_l))) return rc;
+    REQUIRE(cts && out && (pairs || n_pairs == 0) && n_chunks >= 0 && n_pairs >= 0 && n_clients >= 0, "operand is null");
+    for (int p = 0; p < n_pairs; ++p) {
+        const int i = pairs[2 * p], j = pairs[2 * p + 1];
+        REQUIRE(i >= 0 && i < j && j < n_clients, "a pair is (i, j) with 0 <= i < j < n_clients");
+        REQUIRE(cts[i] && cts[j], "operand is null");
+    }
+    constexpr int W = 4;
+    const size_t acc_words = (size_t)3 * size_l * C(h)->hp.N;
+    const int n_blocks = (n_clients + W - 1) / W;
+    // slot[i * n_clients + j] = index of pair (i, j) in the caller's list, -1 if absent (a pair listed twice is refused)
+    std::vector<int> slot((size_t)n_clients * n_clients, -1);
+    for (int p = 0; p < n_pairs; ++p) {
+        int &sl = slot[(size_t)pairs[2 * p] * n_clients + pairs[2 * p + 1]];
+        REQUIRE(sl < 0, "a pair is listed twice");
+        sl = p;
+    }
+    auto launch = [&](const std::vector<int> &rows, const std::vector<int> &cols) -> int {
+        const uint64_t *a[4], *b[4];
+        uint64_t *o[8];
+        const int na = (int)rows.size(), nb = (int)cols.size();
+        for (int r = 0; r < na; ++r) a[r] = cts[rows[r]];
+        for (int c = 0; c < nb; ++c) b[c] = cts[cols[c]];
+        int n = 0;
+        if (nb == 0) {
+            for (int r = 0; r < na; ++r)
+                for (int c = r + 1; c < na; ++c) o[n++] = out + (size_t)slot[(size_t)rows[r] * n_clients + rows[c]] * acc_words;
+        } else {
+            for (int r = 0; r < na; ++r)
+                for (int c = 0; c < nb; ++c) o[n++] = out + (size_t)slot[(size_t)rows[r] * n_clients + cols[c]] * acc_words;
+        }
+        return krum_accumulate_tile(C(h), size_l, n_chunks, na, a, nb, nb ? b : nullptr, (long)chunk_stride, o, S(stream));
+    };
+    for (int ga = 0; ga < n_blocks; ++ga) {
+        for (int gb = ga; gb < n_blocks; ++gb) {
+            // the block's pairs by first client
+            std::vector<int> first;
+            std::vector<std::vector<int>> second;
+            int count = 0;
+            std::vector<char> seen(n_clients, 0);
+            std::vector<int> members;
+            for (int i = ga * W; i < (ga + 1) * W && i < n_clients; ++i) {
+                std::vector<int> cols;
+                for (int j = gb * W; j < (gb + 1) * W && j < n_clients; ++j)
+                    if (j > i && slot[(size_t)i * n_clients + j] >= 0) {
+                        cols.push_back(j);
+                        if (!seen[i]) seen[i] = 1, members.push_back(i);
+                        if (!seen[j]) seen[j] = 1, members.push_back(j);
+                    }
+                if (!cols.empty()) {
+                    first.push_back(i);
+                    count += (int)cols.size();
+                    second.push_back(cols);
+                }
+            }
+            if (count == 0) continue;
+            const int m = (int)members.size();
+            if (ga == gb && count == m * (m - 1) / 2) {
+                std::sort(members.begin(), members.end());
+                if ((rc = launch(members, {}))) return rc;
+                continue;
+            }
+            for (size_t k = 0; k < first.size();) {
+                if (k + 1 < first.size() && second[k + 1] == second[k]) {
+                    if ((rc = launch({first[k], first[k + 1]}, second[k]))) return rc;
+                    k += 2;
+                } else {
+                    if ((rc = launch({first[k]}, second[k]))) return rc;
+                    k += 1;
+                }
+            }
+        }
+    }
+    return LB_OK;
+}
+
+// byzantine_fl.py:244-273 for a batch of pair sums: relinearize_inplace, rescale_to_next_inplace, hoisting over
+// the first steps added to the ciphertext, then rotate_vector + add_inplace for every further step
+int lb_krum_scores(lb_context *h, int size_l, int n_pairs, uint64_t *acc, const uint64_t *relin_key, int n_first, const int *first_elts,
+                   const uint64_t *const *first_keys, int n_pow, const int *pow_elts, const uint64_t *const *pow_keys, uint64_t *scores,
+                   uint64_t *scratch, void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    if ((rc = level_ok(C(h), size_l))) return rc;
+    REQUIRE(size_l >= 2, "the pair sums must have a level to rescale to");
+    REQUIRE(acc && relin_key && scores && scratch && n_pairs >= 0 && n_first >= 0 && n_pow >= 0, "operand is null");
+    REQUIRE((n_first == 0 || (first_elts && first_keys)) && (n_pow == 0 || (pow_elts && pow_keys)), "operand is null");
+    if (n_pairs == 0) return LB_OK;
+    Context *c = C(h);
+    cudaStream_t st = S(stream);
+    const int L = size_l - 1;
+    const size_t words = (size_t)n_pairs * 2 * L * c->hp.N;
+    if ((rc = relinearize(c, size_l, n_pairs, acc, relin_key, st))) return rc;
+    if ((rc = rescale(c, size_l, n_pairs, 2, acc, 3L * size_l, scores, st))) return rc;
+    if (n_first > 0) {
+        LB_CUDA(cudaMemcpyAsync(scratch, scores, words * sizeof(uint64_t), cudaMemcpyDeviceToDevice, st));
+        if ((rc = hoisting(c, L, n_pairs, scratch, n_first, first_elts, first_keys, st))) return rc;
+        if ((rc = poly_binary(c, OP_ADD, L, (long)n_pairs * 2 * L, scores, scratch, scores, st))) return rc;
+    }
+    for (int k = 0; k < n_pow; ++k) {
+        LB_CUDA(cudaMemcpyAsync(scratch, scores, words * sizeof(uint64_t), cudaMemcpyDeviceToDevice, st));
+        if ((rc = rotate(c, L, n_pairs, scratch, pow_elts[k], pow_keys[k], st))) return rc;
+        if ((rc = poly_binary(c, OP_ADD, L, (long)n_pairs * 2 * L, scores, scratch, scores, st))) return rc;
+    }
+    return LB_OK;
 }
 
 int lb_decrypt(lb_context *h, int size_l, int n_polys, const uint64_t *ct, const uint64_t *sk, uint64_t *pt, void *stream)

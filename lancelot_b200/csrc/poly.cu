@@ -590,39 +590,70 @@ __global__ void __launch_bounds__(kTileThreads, 1) krum_tile_kernel(const __grid
     }
 }
 
-// adds the pieces of every unit that more than one CTA of krum_tile_kernel worked on; one CTA per unit
+// adds the pieces of every unit that more than one CTA of krum_tile_kernel worked on; one CTA per unit.  Thread 0 walks
+// the CTAs that share the unit (a handful) and lists their scratch slots, every thread then adds its coefficient.
+constexpr int kTileListed = 64;
 __global__ void __launch_bounds__(kTileSeg) krum_tile_combine_kernel(const __grid_constant__ KrumTileArgs args, const __grid_constant__ TilePlan pl,
                                                                      const ModConst *__restrict__ mc, const int logn, const long per_poly,
                                                                      const u64 *__restrict__ scratch, const int G, const int n_pairs)
 {
+    __shared__ int listed[kTileListed];
+    __shared__ int n_listed, next_cta; // next_cta < 0: nothing (left) to add
     const int seg = pl.seg, n_chunks = pl.n_chunks, segs = pl.segs_per_limb;
-    const int t = threadIdx.x;
-    if (t >= seg) return;
+    const int t = (int)threadIdx.x < seg ? threadIdx.x : 0;
     const long unit = blockIdx.x;
     const int limb = (int)(unit / segs);
     const u64 q = mc[limb].q;
     const long e = ((long)limb << logn) + (unit - (long)limb * segs) * seg + t;
     const long first = unit * n_chunks, last = first + n_chunks;
-    int b0 = 0;
-    if (n_chunks > 0) {
-        // the CTA that holds the unit's first item: an estimate from the cost, then exact
-        const long cpos = pl.cost_base[limb] + (first - (long)limb * segs * n_chunks) * pl.weight[limb];
-        const long total = pl.cost_base[pl.size_l];
-        b0 = (int)min((long)G - 1, (long)((double)cpos / (double)total * G));
-        while (b0 + 1 < G && tile_boundary(pl, b0 + 1, G) <= first) ++b0;
-        while (b0 > 0 && tile_boundary(pl, b0, G) > first) --b0;
-        if (tile_boundary(pl, b0 + 1, G) >= last) return; // one CTA had the whole unit and stored it
-    }
-    for (int w = 0; w < n_pairs * 3; ++w) {
-        u64 acc = 0;
-        for (int b = b0; n_chunks > 0 && b < G; ++b) {
-            const long blo = tile_boundary(pl, b, G);
-            if (blo >= last) break;
-            const long plo = max(blo, first), phi = min(tile_boundary(pl, b + 1, G), last);
-            if (plo >= phi) continue;
-            acc = add_mod(acc, scratch[(((size_t)b * 2 + (plo == blo ? 0 : 1)) * (n_pairs * 3) + w) * seg + t], q);
+    const int n_words = n_pairs * 3;
+    if (threadIdx.x == 0) {
+        next_cta = 0;
+        if (n_chunks > 0) {
+            // the CTA that holds the unit's first item: an estimate from the cost, then exact
+            const long cpos = pl.cost_base[limb] + (first - (long)limb * segs * n_chunks) * pl.weight[limb];
+            int b0 = (int)min((long)G - 1, (long)((double)cpos / (double)pl.cost_base[pl.size_l] * G));
+            while (b0 + 1 < G && tile_boundary(pl, b0 + 1, G) <= first) ++b0;
+            while (b0 > 0 && tile_boundary(pl, b0, G) > first) --b0;
+            next_cta = tile_boundary(pl, b0 + 1, G) >= last ? -2 : b0; // -2: one CTA had the whole unit and stored it
         }
-        args.out[w / 3][(w % 3) * per_poly + e] = acc;
+    }
+    u64 acc[kTileMaxPairs * 3];
+#pragma unroll
+    for (int w = 0; w < kTileMaxPairs * 3; ++w) acc[w] = 0;
+    for (;;) {
+        if (threadIdx.x == 0) {
+            int n = 0, b = next_cta;
+            if (n_chunks == 0) b = -1; // no chunks: the sums are zero
+            while (b >= 0 && b < G && n < kTileListed) {
+                const long blo = tile_boundary(pl, b, G);
+                if (blo >= last) {
+                    b = -1;
+                    break;
+                }
+                const long plo = max(blo, first), phi = min(tile_boundary(pl, b + 1, G), last);
+                if (plo < phi) listed[n++] = b * 2 + (plo == blo ? 0 : 1);
+                ++b;
+            }
+            n_listed = n;
+            next_cta = b >= G ? -1 : b;
+        }
+        __syncthreads();
+        const int n = n_listed, more = next_cta;
+        if (more == -2) return;
+        for (int i = 0; i < n; ++i) {
+            const u64 *src = scratch + (size_t)listed[i] * n_words * seg + t;
+#pragma unroll
+            for (int w = 0; w < kTileMaxPairs * 3; ++w)
+                if (w < n_words) acc[w] = add_mod(acc[w], src[(size_t)w * seg], q);
+        }
+        __syncthreads();
+        if (more < 0) break;
+    }
+    if ((int)threadIdx.x < seg) {
+#pragma unroll
+        for (int w = 0; w < kTileMaxPairs * 3; ++w)
+            if (w < n_words) args.out[w / 3][(w % 3) * per_poly + e] = acc[w];
     }
 }
 

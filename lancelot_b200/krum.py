@@ -341,12 +341,42 @@ def _copy_stream(dev):
     return _COPY_STREAMS[dev.index]
 
 
+def shared_seed_stream(device, group=None):
+    """A seed source (see pycahel.set_seed_source) that gives every rank of the group the same unpredictable stream:
+    rank 0 draws 64 bytes from the operating system, broadcasts them, and block k of the stream is
+    BLAKE2b(key = those bytes, message = k)."""
+    import hashlib
+
+    import torch.distributed as dist
+
+    backend = dist.get_backend(group)
+    dev = "cuda:%d" % device if backend == "nccl" else "cpu"
+    master = torch.from_numpy(np.frombuffer(os.urandom(64), dtype=np.uint8).copy()).to(dev)
+    dist.broadcast(master, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    key = bytes(master.cpu().numpy().tobytes())
+    counter = [0]
+
+    def source(count):
+        out = bytearray()
+        for _ in range(count):
+            out += hashlib.blake2b(counter[0].to_bytes(8, "little"), digest_size=64, key=key).digest()
+            counter[0] += 1
+        return bytes(out)
+
+    return source
+
+
 class EncryptedKrum:
     """Persistent context + keys, batched encrypt, batched pair scores, plaintext selection.
 
     log_slots = log2(N/2).  chain {60,40,40 | 60}, scale 2^40 (byzantine_fl.py:432-448)."""
 
-    def __init__(self, log_slots=15, device=None, seed=None, encrypt_batch=384, workspace_bytes=None):
+    def __init__(self, log_slots=15, device=None, seed=None, encrypt_batch=384, workspace_bytes=None, rank=0, world_size=1,
+                 group=None):
+        """rank / world_size / group: the ranks of one job hold the SAME keys.  With ``seed=None`` rank 0 draws a
+        64-byte master secret from the operating system and broadcasts it, and every rank expands it with keyed
+        BLAKE2b into the same stream of key seeds; the Galois keys (27 switch keys of 12.6 MB at N = 2^16) are
+        generated a share per rank and all-gathered instead of being generated by every rank."""
         self.log_slots = log_slots
         self.slots = 1 << log_slots
         self.N = 2 * self.slots
@@ -377,6 +407,8 @@ class EncryptedKrum:
         prev = cahel._seed_source
         if self._rng is not None:
             cahel.set_seed_source(lambda k: self._rng.integers(0, 256, 64 * k, dtype=np.uint8))
+        elif world_size > 1:
+            cahel.set_seed_source(shared_seed_stream(self.lb.device, group))
         try:
             self.sk = cahel.secret_key(params)
             self.sk.gen_secretkey(self.context)
@@ -385,10 +417,35 @@ class EncryptedKrum:
             self.rlk = cahel.relin_key(self.context)
             self.sk.gen_relinkey(self.context, self.rlk)
             self.glk = cahel.galois_key(self.context)
-            self.sk.create_galois_keys(self.context, self.glk)
+            if world_size > 1:
+                self._galois_keys_shared(rank, world_size, group)
+            else:
+                self.sk.create_galois_keys(self.context, self.glk)
         finally:
             cahel.set_seed_source(prev)
         self.elt_index = {s: self.context.elt_index(e) for s, e in zip(steps, cahel.get_elts_from_steps(steps, self.N))}
+
+    def _galois_keys_shared(self, rank, world_size, group):
+        """Galois key i is generated by rank i % world_size; one all-gather hands every rank all of them.  Every rank
+        draws every key's seeds from the shared stream, so key i is what a single rank would have generated."""
+        import torch.distributed as dist
+
+        ctx, lb = self.context, self.lb
+        dnum = ctx.size_Q // ctx.size_P
+        n_keys = len(ctx.galois_elts)
+        per = (n_keys + world_size - 1) // world_size
+        key_shape = (dnum, 2, ctx.size_Q + ctx.size_P, self.N)
+        key_words = int(np.prod(key_shape))
+        everything = lb.empty(world_size, per, key_words)
+        mine = everything[rank]
+        for i in range(n_keys):
+            seeds = cahel._seeds(2 * dnum)
+            if i % world_size != rank:
+                continue
+            rotated = lb.galois_permute(i, self.sk.data)
+            mine[i // world_size].copy_(lb.gen_switch_key(self.sk.data, rotated, seeds).reshape(-1))
+        dist.all_gather_into_tensor(everything.view(-1), mine.reshape(-1).clone(), group=group)
+        self.glk.keys = [everything[i % world_size, i // world_size].view(key_shape) for i in range(n_keys)]
 
     # -- client side ---------------------------------------------------------------------------
     def n_chunks(self, dim):
@@ -529,41 +586,43 @@ class EncryptedKrum:
         acc = lb.empty(n_slots, 3, 3, N)
         if n_slots > P:
             acc[P:].zero_()
-        slot = {pair: p for p, pair in enumerate(pairs)}
-        for tile in pair_tiles(pairs):
-            outs = [acc[slot[pair]] for pair in tile_pairs(tile)]
-            lb.krum_accumulate_tile(3, [cts[i] for i in tile[1]], [cts[j] for j in tile[2]], outs)
+        if P:
+            n_clients = 1 + max(j for _, j in pairs)
+            lb.krum_pair_sums(3, cts, n_clients, pairs, acc)  # the tile schedule is chosen inside the library
         return acc
 
-    def finish_scores(self, acc, mark=lambda name: None):
+    def finish_scores(self, acc, mark=lambda name: None, stepwise=False):
         """acc [P][3][3][N] (pair sums, scale 2^80, level 1) -> [P][2][2][N]: relinearize, rescale, then the
         rotate-and-sum that leaves the squared distance in every slot (byzantine_fl.py:244-273)"""
         lb, N = self.lb, self.N
         P = acc.shape[0]
         if P == 0:
             return lb.empty(0, 2, 2, N)
-        lb.relinearize_batch(3, acc, self.rlk.data)
-        s = lb.rescale_strided(3, acc, P, 2, 3 * 3 * N)  # [P][2][2][N], scale 2^80 / q_2 ~ 2^40
-        mark("relin_rescale_s")
-        rot = s.clone()
-        idx = [self.elt_index[k] for k in self.first_steps]
-        lb.hoisting_batch(2, rot, idx, [self.glk.keys[i] for i in idx])
-        lb.add(2, s, rot, out=s)
-        for k in self.pow_steps:
-            rot.copy_(s)
-            e = self.elt_index[k]
-            lb.rotate_batch(2, rot, e, self.glk.keys[e])
+        first = [self.elt_index[k] for k in self.first_steps]
+        power = [self.elt_index[k] for k in self.pow_steps]
+        if stepwise:
+            # phases timed apart: the same steps through the single operations
+            lb.relinearize_batch(3, acc, self.rlk.data)
+            s = lb.rescale_strided(3, acc, P, 2, 3 * 3 * N)  # [P][2][2][N], scale 2^80 / q_2 ~ 2^40
+            mark("relin_rescale_s")
+            rot = s.clone()
+            lb.hoisting_batch(2, rot, first, [self.glk.keys[i] for i in first])
             lb.add(2, s, rot, out=s)
-        mark("rotate_sum_s")
-        return s
+            for e in power:
+                rot.copy_(s)
+                lb.rotate_batch(2, rot, e, self.glk.keys[e])
+                lb.add(2, s, rot, out=s)
+            mark("rotate_sum_s")
+            return s
+        return lb.krum_scores(3, acc, self.rlk.data, first, [self.glk.keys[i] for i in first], power, [self.glk.keys[e] for e in power])
 
-    def pair_scores(self, cts, pairs, mark=lambda name: None):
+    def pair_scores(self, cts, pairs, mark=lambda name: None, stepwise=False):
         """cts: dict client -> [chunks][2][3][N].  Returns [len(pairs)][2][2][N] level-2 score ciphertexts."""
         if len(pairs) == 0:
             return self.lb.empty(0, 2, 2, self.N)
         acc = self.pair_sums(cts, pairs)
         mark("pair_accumulate_s")
-        return self.finish_scores(acc, mark)
+        return self.finish_scores(acc, mark, stepwise)
 
     def client_sums(self, scores, pairs, n_clients):
         """sum of the score ciphertexts of every pair a client belongs to: [n_clients][2][2][N], one launch"""
@@ -667,7 +726,7 @@ class EncryptedKrum:
         mark("start")
         n_clients = updates.shape[0]
         if world_size > 1 and exchange == "p2p":
-            return self._round_pair_sharded(updates, rank, world_size, group, keep, mark)
+            return self._round_pair_sharded(updates, rank, world_size, group, keep, mark, stepwise=timing is not None)
         if exchange not in ("chunks", "p2p"):
             raise ValueError("exchange is 'chunks' or 'p2p'")
         import torch.distributed as dist
@@ -690,7 +749,7 @@ class EncryptedKrum:
             self.lb.reduce_mod(3, acc)
             mark("pair_reduce_scatter_s")
         mine = pairs[rank * block: (rank + 1) * block]
-        scores = self.finish_scores(acc[: len(mine)], mark)
+        scores = self.finish_scores(acc[: len(mine)], mark, stepwise=timing is not None)
         del acc
         if keep is not None:
             keep["scores"], keep["my_pairs"] = scores, mine
@@ -710,7 +769,7 @@ class EncryptedKrum:
         mark("sum_decrypt_s")
         return out
 
-    def _round_pair_sharded(self, updates, rank, world_size, group, keep, mark):
+    def _round_pair_sharded(self, updates, rank, world_size, group, keep, mark, stepwise=False):
         """the "p2p" exchange of round(): pairs sharded over ranks, ciphertexts sent to the ranks that need them"""
         n_clients = updates.shape[0]
         schedule = pair_schedule(n_clients, world_size)
@@ -725,7 +784,7 @@ class EncryptedKrum:
 
         cts = share_slices(world_size, rank, n_clients, needed_by, produce, lambda: self.lb.empty(chunks, 2, 3, self.N),
                            group=group, mark=mark)
-        scores = self.pair_scores(cts, mine, mark)
+        scores = self.pair_scores(cts, mine, mark, stepwise=stepwise)
         if keep is not None:
             keep["cts"], keep["scores"], keep["pairs"] = cts, scores, mine
         del cts

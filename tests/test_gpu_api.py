@@ -365,3 +365,39 @@ def test_mask_multiplication_selects_and_averages():
         for k in range(n_clients):
             want = o.poly_op("add", 3, want, o.tensor(3, h_cts[k][c], h_masks[k]))
         assert np.array_equal(h_fused[c].reshape(-1), want.reshape(-1)), "chunk %d" % c
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n_clients,drop", [(9, 0), (9, 7), (6, 3), (2, 0), (5, 9)])
+def test_round_entries_pair_sums_and_scores_equal_the_single_operations(n_clients, drop):
+    """lb_krum_pair_sums (tile schedule inside the library) against the one-pair kernel for full and ragged pair
+    lists, and lb_krum_scores against relinearize / rescale / hoisting / rotate / add issued one by one: word for word"""
+    import random
+
+    import torch
+
+    from lancelot_b200 import krum
+
+    torch.manual_seed(13)
+    ek = krum.EncryptedKrum(log_slots=9, seed=5)
+    dim = 3 * 512 - 41
+    upd = (torch.randn(n_clients, dim, dtype=torch.float32) * 0.2).cuda()
+    cts = ek.encrypt_slices(upd, 0, ek.n_chunks(dim))
+    pairs = krum.all_pairs(n_clients)
+    random.Random(drop).shuffle(pairs)
+    pairs = sorted(pairs[: len(pairs) - drop]) if drop < len(pairs) else pairs[:1]
+    acc = ek.pair_sums(cts, pairs, n_slots=len(pairs) + 2)
+    assert not acc[len(pairs):].any()
+    for p, (i, j) in enumerate(pairs):
+        one = ek.lb.empty(3, 3, ek.N)
+        ek.lb.krum_accumulate(3, cts[i], cts[j], one)
+        assert torch.equal(acc[p], one), "pair %d %d" % (i, j)
+    fused = ek.finish_scores(acc[: len(pairs)].clone())
+    single = ek.finish_scores(acc[: len(pairs)].clone(), stepwise=True)
+    assert torch.equal(fused, single)
+    # refusals of the entry: a pair out of order, a pair listed twice
+    with pytest.raises(ValueError):
+        ek.lb.krum_pair_sums(3, cts, n_clients, [(1, 0)], acc)
+    if len(pairs) > 1:
+        with pytest.raises(ValueError):
+            ek.lb.krum_pair_sums(3, cts, n_clients, [pairs[0], pairs[0]], acc)

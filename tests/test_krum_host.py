@@ -204,6 +204,41 @@ def test_chunk_sharded_pair_sums_equal_single_rank_sums_gloo(world):
     assert sorted(res) == [(r, True) for r in range(world)]
 
 
+def _seed_stream_worker(rank, world, port, out):
+    import hashlib
+
+    import torch.distributed as dist
+
+    from lancelot_b200.krum import shared_seed_stream
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        src = shared_seed_stream(0)
+        a, b = src(3), src(2)
+        out.put((rank, len(a), len(b), hashlib.sha256(a + b).hexdigest(), a[:64] != a[64:128] and a[:64] != b[:64]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ranks_expand_one_broadcast_secret_into_the_same_key_seeds_gloo():
+    """several ranks must hold the same keys: rank 0's 64 random bytes reach every rank and give the same stream"""
+    import torch.multiprocessing as mp
+
+    world = 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_seed_stream_worker, args=(r, world, 29731, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert [r[0] for r in res] == list(range(world))
+    assert all(r[1] == 192 and r[2] == 128 and r[4] for r in res)
+    assert len({r[3] for r in res}) == 1
+
+
 def test_rotation_steps_decompose_like_the_reference():
     """non-adjacent form, least significant term first: the order the reference key-switches a rotation step that
     has no key of its own (cahel-main/include/util/numth.h:18-35, src/evaluate.cu:2396-2407); the reference-made
