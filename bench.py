@@ -278,6 +278,8 @@ def run_gpu(args, wl, default_line):
         if pair:
             pair["peak"] = peak
             pair["frac"] = pair["achieved"] / peak
+            cap = bench_workloads.NCU_TRAFFIC.get("krum_tile_kernel")
+            pair["traffic"] = int(pair["bytes_per_launch"] * cap["dram_bytes"] / cap["algorithmic_bytes"]) if cap else None
             line["roofline_pair_kernel"] = pair
         if getattr(wl, "breakdown", None):
             line["breakdown"] = wl.breakdown

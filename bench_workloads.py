@@ -18,7 +18,13 @@ WIDE_BITS = [60] + [50] * 23 + [60] * 8
 # DRAM traffic of one captured launch (ncu, dram__bytes_read.sum + dram__bytes_write.sum) beside the algorithmic
 # bytes of that same launch; the summary each pair comes from is named.  bench.py scales a kernel's algorithmic
 # bytes by this ratio for "traffic"; a kernel without a capture reports null.
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {
+    # mod-down transform of 128 encryptions, N = 2^16: 750.1 MB read + 386.7 MB written
+    "ntt_fwd_kernel(fused input)": {"dram_bytes": 1136815360, "algorithmic_bytes": 1149239296,
+                                    "summary": "profiles/ntt_fwd_fused_encrypt_batch128.md"},
+    # <2,2> tile of the 10-client round, N = 2^15: 641.8 MB read + 11.9 MB written
+    "krum_tile_kernel": {"dram_bytes": 653734400, "algorithmic_bytes": 651165696, "summary": "profiles/krum_tile_kernel_c4.md"},
+}
 
 
 def _oracle(threads):

@@ -100,6 +100,9 @@ struct NttJob {
     // the single source row is (INTT(pk u) on p); the load forms ((x + e) mod p) mod q_rr - e
     const signed char *esmall = nullptr;
     u64 esmall_p = 0;
+    // The transform input itself as signed bytes, small[group][N]: every row of a group transforms the same small
+    // polynomial (the ternary u of an encryption), reduced into the row's prime by the load; src is not read
+    const signed char *small = nullptr;
     // Forward epilogue: dst = (aux - NTT(x)) * scal[rr] (+ add), the closing step of mod-down and rescale
     const u64 *aux = nullptr;
     long aux_group_stride = -1, aux_outer = -1;

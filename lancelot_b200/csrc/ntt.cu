@@ -51,6 +51,7 @@ struct NttK {
     const u64 *mul2; // forward epilogue: two products per row (see NttJob::mul2)
     const u64 *presub, *presub_scal, *presub_scal_s;
     const signed char *esmall;
+    const signed char *small;
     u64 esmall_p;
     long presub_outer;
     int presub_inner;
@@ -147,6 +148,7 @@ struct FwdIn {
     const u64 *mat;
     const u64 *sub; // optional: the loaded value becomes value - sub[k] * sub_w (plaintext folded into a mod-down)
     const signed char *es; // optional small error polynomial e of an encryption (see the encrypt path)
+    const signed char *small; // the input itself as signed bytes (then src is not read)
     int n, logN;
     u64 q, r0, r1, sub_w, sub_ws, es_p;
 };
@@ -154,7 +156,10 @@ struct FwdIn {
 LB_D u64 load_in(const FwdIn &in, const int idx)
 {
     u64 v;
-    if (in.n == 0) {
+    if (in.small) {
+        const int ev = in.small[idx];
+        v = ev < 0 ? in.q - (u64)(-ev) : (u64)ev;
+    } else if (in.n == 0) {
         v = in.src[idx];
     } else if (in.mat == nullptr) {
         u64 x = in.src[idx];
@@ -338,6 +343,7 @@ LB_D bool fwd_row_setup(const NttK &a, const int row, FwdRow &r)
     in.sub_w = in.sub ? a.presub_scal[rr] : 0;
     in.sub_ws = in.sub ? a.presub_scal_s[rr] : 0;
     in.es = a.esmall ? a.esmall + ((size_t)go << logN) : nullptr;
+    in.small = a.small ? a.small + ((size_t)grp << logN) : nullptr;
     in.es_p = a.esmall_p;
     r.mode = butterfly_mode(mc.q);
     r.dst = a.dst + (((size_t)go * a.dst_outer + (size_t)gi * a.dst_group_stride + rr) << logN);
@@ -666,6 +672,13 @@ LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulon
         if (PLAIN) {
 #pragma unroll
             for (int k = 0; k < R0; ++k) v[k] = in.src[j + k * kHalfLoc];
+        } else if (in.small) {
+            // the small polynomial of an encryption as signed bytes, the same for every prime
+            int ev[R0];
+#pragma unroll
+            for (int k = 0; k < R0; ++k) ev[k] = in.small[j + k * kHalfLoc];
+#pragma unroll
+            for (int k = 0; k < R0; ++k) v[k] = ev[k] < 0 ? q - (u64)(-ev[k]) : (u64)ev[k];
         } else if (in.n == 0 && in.sub == nullptr) {
             // a plain row in the instantiation with fused parts (its epilogue is what this launch is after)
 #pragma unroll
@@ -1012,7 +1025,7 @@ static int launch(bool forward, bool fixed, const NttK &k, int rows, size_t smem
 {
     auto kern = forward ? ntt_fwd_kernel<LOGC> : ntt_inv_kernel<LOGC>;
     int which = 0;
-    const bool plain = k.bconv_n == 0 && k.digit_alpha == 0 && !k.presub && !k.esmall && !k.aux && !k.mul2;
+    const bool plain = k.bconv_n == 0 && k.digit_alpha == 0 && !k.presub && !k.esmall && !k.small && !k.aux && !k.mul2;
     if constexpr (LOGC <= 3) {
         if (fixed) {
             kern = !forward ? ntt_inv_fixed_kernel<LOGC> : plain ? ntt_fwd_fixed_kernel<LOGC, true> : ntt_fwd_fixed_kernel<LOGC, false>;
@@ -1088,6 +1101,7 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     k.mul2 = job.mul2;
     k.presub = job.presub;
     k.esmall = job.esmall;
+    k.small = job.small;
     k.esmall_p = job.esmall_p;
     k.presub_scal = job.presub_scal;
     k.presub_scal_s = job.presub_scal_s;
@@ -1111,6 +1125,7 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     double bytes = out_rows * limb;
     if (job.digit_alpha > 0) bytes += (double)job.n_groups * job.digit_alpha * limb;
     else if (job.bconv_n > 0) bytes += (double)job.n_groups * job.bconv_n * limb;
+    else if (job.small) bytes += (double)job.n_groups * (double)hp.N; // one byte per coefficient and group
     else bytes += out_rows * limb;
     const double outer = (double)job.n_groups / k.split;
     if (job.aux) bytes += out_rows * limb;

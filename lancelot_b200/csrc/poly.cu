@@ -592,13 +592,14 @@ __global__ void __launch_bounds__(kTileThreads, 1) krum_tile_kernel(const __grid
 
 // adds the pieces of every unit that more than one CTA of krum_tile_kernel worked on; one CTA per unit.  Thread 0 walks
 // the CTAs that share the unit (a handful) and lists their scratch slots, every thread then adds its coefficient.
-constexpr int kTileListed = 64;
+constexpr int kTileListed = 64, kTileMaxGrid = 1024;
 __global__ void __launch_bounds__(kTileSeg) krum_tile_combine_kernel(const __grid_constant__ KrumTileArgs args, const __grid_constant__ TilePlan pl,
                                                                      const ModConst *__restrict__ mc, const int logn, const long per_poly,
                                                                      const u64 *__restrict__ scratch, const int G, const int n_pairs)
 {
     __shared__ int listed[kTileListed];
     __shared__ int n_listed, next_cta; // next_cta < 0: nothing (left) to add
+    __shared__ long bound[kTileMaxGrid + 1]; // first item of every CTA of krum_tile_kernel (the divisions, done side by side)
     const int seg = pl.seg, n_chunks = pl.n_chunks, segs = pl.segs_per_limb;
     const int t = (int)threadIdx.x < seg ? threadIdx.x : 0;
     const long unit = blockIdx.x;
@@ -607,15 +608,19 @@ __global__ void __launch_bounds__(kTileSeg) krum_tile_combine_kernel(const __gri
     const long e = ((long)limb << logn) + (unit - (long)limb * segs) * seg + t;
     const long first = unit * n_chunks, last = first + n_chunks;
     const int n_words = n_pairs * 3;
+    for (int b = threadIdx.x; b <= G; b += blockDim.x) bound[b] = tile_boundary(pl, b, G);
+    __syncthreads();
     if (threadIdx.x == 0) {
         next_cta = 0;
         if (n_chunks > 0) {
-            // the CTA that holds the unit's first item: an estimate from the cost, then exact
-            const long cpos = pl.cost_base[limb] + (first - (long)limb * segs * n_chunks) * pl.weight[limb];
-            int b0 = (int)min((long)G - 1, (long)((double)cpos / (double)pl.cost_base[pl.size_l] * G));
-            while (b0 + 1 < G && tile_boundary(pl, b0 + 1, G) <= first) ++b0;
-            while (b0 > 0 && tile_boundary(pl, b0, G) > first) --b0;
-            next_cta = tile_boundary(pl, b0 + 1, G) >= last ? -2 : b0; // -2: one CTA had the whole unit and stored it
+            // the CTA that holds the unit's first item: the last one that starts at or before it
+            int lo = 0, hi = G - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (bound[mid] <= first) lo = mid;
+                else hi = mid - 1;
+            }
+            next_cta = bound[lo + 1] >= last ? -2 : lo; // -2: one CTA had the whole unit and stored it
         }
     }
     u64 acc[kTileMaxPairs * 3];
@@ -626,12 +631,12 @@ __global__ void __launch_bounds__(kTileSeg) krum_tile_combine_kernel(const __gri
             int n = 0, b = next_cta;
             if (n_chunks == 0) b = -1; // no chunks: the sums are zero
             while (b >= 0 && b < G && n < kTileListed) {
-                const long blo = tile_boundary(pl, b, G);
+                const long blo = bound[b];
                 if (blo >= last) {
                     b = -1;
                     break;
                 }
-                const long plo = max(blo, first), phi = min(tile_boundary(pl, b + 1, G), last);
+                const long plo = max(blo, first), phi = min(bound[b + 1], last);
                 if (plo < phi) listed[n++] = b * 2 + (plo == blo ? 0 : 1);
                 ++b;
             }
@@ -693,6 +698,7 @@ static int launch_tile(Context *ctx, const KrumTileArgs &args, int size_l, int n
         ctas_per_sm[dev & 63] = occ > 0 ? occ : 1;
     }
     long G = (long)ctas_per_sm[dev & 63] * ctx->sm_count;
+    if (G > kTileMaxGrid) G = kTileMaxGrid;
     if (G > pl.n_items) G = pl.n_items > 0 ? pl.n_items : 1;
     int rc = ctx->ensure_workspace((size_t)G * 2 * NP * 3 * pl.seg * sizeof(u64));
     if (rc) return rc;

@@ -280,18 +280,22 @@ int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, int pt_is_coe
     uint32_t *seeds = reinterpret_cast<uint32_t *>(pc + (((size_t)2 * batch * P) << hp.logN));
     // seeds arrive as [batch][2][64 bytes]: (ternary seed, error seed) per ciphertext
     LB_CUDA(cudaMemcpyAsync(seeds, host_seeds, (size_t)batch * 128, cudaMemcpyHostToDevice, stream));
-    if ((rc = sample_small(ctx, 0, seeds, 32, batch, Q, P, u, stream))) return rc;
     const bool fold_e = (P == 1); // one special prime: the error never needs its own transforms
     const long total = batch * poly;
     if (fold_e) {
+        // u and e stay signed bytes: the transforms that consume them reduce them into their primes while loading
         const long n_small = (long)batch << hp.logN;
+        count_launch("sample_small_i8_kernel", stream, (double)n_small);
+        sample_small_i8_kernel<<<grid_for(ctx, n_small), kSampThreads, 0, stream>>>(reinterpret_cast<signed char *>(u), seeds, 32, 0, hp.logN,
+                                                                                   n_small);
+        LB_CUDA(cudaGetLastError());
         count_launch("sample_small_i8_kernel", stream, (double)n_small);
         sample_small_i8_kernel<<<grid_for(ctx, n_small), kSampThreads, 0, stream>>>(reinterpret_cast<signed char *>(e), seeds + 16, 32, 1,
                                                                                    hp.logN, n_small);
         LB_CUDA(cudaGetLastError());
         // u's transform stores its products with the two key polynomials straight away: cx[b][p][QP][N] = pk[p] * NTT(u[b])
         NttJob j;
-        j.src = u;
+        j.small = reinterpret_cast<const signed char *>(u);
         j.dst = cx;
         j.n_groups = batch;
         j.per_group = QP;
@@ -300,6 +304,7 @@ int encrypt_asymmetric(Context *ctx, const u64 *pk, const u64 *pt, int pt_is_coe
         j.mul2 = pk;
         if ((rc = ntt_forward(ctx, j, stream))) return rc;
     } else {
+        if ((rc = sample_small(ctx, 0, seeds, 32, batch, Q, P, u, stream))) return rc;
         if ((rc = sample_small(ctx, 1, seeds + 16, 32, batch, Q, P, e, stream))) return rc;
         NttJob j;
         j.src = u;
