@@ -119,7 +119,12 @@ struct IpArgs {
 };
 
 // grid: x over the coefficients of a limb (two per thread without a gather, one with), y = limb of
-// QlP, z = ciphertext; no index division, 16-byte accesses on the streaming path
+// QlP, z = blocks of ciphertexts (four with a gather, two without); no index division, 16-byte accesses on the streaming path.  A thread
+// applies every key word it loads to all ciphertexts of its block: the keys (and the permutation tables of a hoisting) come
+// from L2 once per block of ciphertexts instead of once per ciphertext, which was what bounded the hoisting sum
+// (15 steps x 2 digits of key per ciphertext: 17 GB of L2 reads per launch at 190 ciphertexts).
+template <bool GATHER>
+constexpr int ip_cts() { return GATHER ? 4 : 2; }
 template <bool GATHER>
 __global__ void __launch_bounds__(kKsThreads) inner_product_kernel(const u64 *__restrict__ digits, const u64 *__restrict__ own,
                                                                    const long own_stride, u64 *__restrict__ cx,
@@ -127,71 +132,98 @@ __global__ void __launch_bounds__(kKsThreads) inner_product_kernel(const u64 *__
                                                                    const int L, const int LP, const int size_Q, const int size_QP,
                                                                    const int alpha, const int beta, const int batch)
 {
-    constexpr int V = GATHER ? 1 : 2;
+    constexpr int V = GATHER ? 1 : 2, B = ip_cts<GATHER>();
     const long per_ct = (long)LP << logN;
     const int r = blockIdx.y;
     const int tbl = r < L ? r : size_Q + (r - L);
     const ModConst m = mc[tbl];
     const int own_digit = r < L ? r / alpha : -1;
     const long n = 1L << logN;
-    for (long b = blockIdx.z; b < batch; b += gridDim.z) {
-        const u64 *dig_b = digits + b * beta * per_ct;
-        const u64 *own_b = own + ((b * own_stride) << logN);
+    for (long b0 = (long)blockIdx.z * B; b0 < batch; b0 += (long)gridDim.z * B) {
+        const int nb = (int)min((long)B, batch - b0);
         for (long k = ((long)blockIdx.x * blockDim.x + threadIdx.x) * V; k < n; k += (long)gridDim.x * blockDim.x * V) {
-            u128d a0[V], a1[V];
-            u64 r0[V], r1[V];
+            u128d a0[B][V], a1[B][V];
+            u64 r0[B][V], r1[B][V];
 #pragma unroll
-            for (int v = 0; v < V; ++v) {
-                a0[v] = a1[v] = u128d{0, 0};
-                r0[v] = r1[v] = 0;
+            for (int c = 0; c < B; ++c) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    a0[c][v] = a1[c][v] = u128d{0, 0};
+                    r0[c][v] = r1[c][v] = 0;
+                }
             }
             int pending = 0;
             for (int s = 0; s < args.n_steps; ++s) {
                 const u64 *key = args.evk[s];
+                const long kk = GATHER && args.perm[s] ? (long)args.perm[s][k] : k;
                 for (int j = 0; j < beta; ++j) {
-                    const u64 *src = (j == own_digit) ? own_b + ((long)r << logN) : dig_b + (((long)j * LP + r) << logN);
                     const u64 *kb = key + ((((long)j * 2) * size_QP + tbl) << logN) + k;
-                    u64 d[V], k0[V], k1[V];
+                    u64 k0[V], k1[V];
                     if (GATHER) {
-                        d[0] = src[args.perm[s] ? (long)args.perm[s][k] : k];
                         k0[0] = kb[0];
                         k1[0] = kb[(long)size_QP << logN];
                     } else {
-                        const ulonglong2 dv = *reinterpret_cast<const ulonglong2 *>(src + k);
                         const ulonglong2 kv0 = *reinterpret_cast<const ulonglong2 *>(kb);
                         const ulonglong2 kv1 = *reinterpret_cast<const ulonglong2 *>(kb + ((long)size_QP << logN));
-                        d[0] = dv.x; d[V - 1] = dv.y;
                         k0[0] = kv0.x; k0[V - 1] = kv0.y;
                         k1[0] = kv1.x; k1[V - 1] = kv1.y;
                     }
+                    u64 d[B][V];
 #pragma unroll
-                    for (int v = 0; v < V; ++v) {
-                        mac_wide(a0[v], d[v], k0[v]);
-                        mac_wide(a1[v], d[v], k1[v]);
+                    for (int c = 0; c < B; ++c) {
+                        if (c < nb) {
+                            const long b = b0 + c;
+                            const u64 *src = (j == own_digit) ? own + ((b * own_stride) << logN) + ((long)r << logN)
+                                                              : digits + b * beta * per_ct + (((long)j * LP + r) << logN);
+                            if (GATHER) {
+                                d[c][0] = src[kk];
+                            } else {
+                                const ulonglong2 dv = *reinterpret_cast<const ulonglong2 *>(src + k);
+                                d[c][0] = dv.x; d[c][V - 1] = dv.y;
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int c = 0; c < B; ++c) {
+                        if (c < nb) {
+#pragma unroll
+                            for (int v = 0; v < V; ++v) {
+                                mac_wide(a0[c][v], d[c][v], k0[v]);
+                                mac_wide(a1[c][v], d[c][v], k1[v]);
+                            }
+                        }
                     }
                     if (++pending == 32) {
 #pragma unroll
-                        for (int v = 0; v < V; ++v) {
-                            r0[v] = add_mod(r0[v], barrett128(a0[v], m.q, m.r0, m.r1), m.q);
-                            r1[v] = add_mod(r1[v], barrett128(a1[v], m.q, m.r0, m.r1), m.q);
-                            a0[v] = a1[v] = u128d{0, 0};
+                        for (int c = 0; c < B; ++c) {
+#pragma unroll
+                            for (int v = 0; v < V; ++v) {
+                                r0[c][v] = add_mod(r0[c][v], barrett128(a0[c][v], m.q, m.r0, m.r1), m.q);
+                                r1[c][v] = add_mod(r1[c][v], barrett128(a1[c][v], m.q, m.r0, m.r1), m.q);
+                                a0[c][v] = a1[c][v] = u128d{0, 0};
+                            }
                         }
                         pending = 0;
                     }
                 }
             }
-            u64 *o0 = cx + 2 * b * per_ct + ((long)r << logN) + k, *o1 = o0 + per_ct;
 #pragma unroll
-            for (int v = 0; v < V; ++v) {
-                r0[v] = add_mod(r0[v], barrett128(a0[v], m.q, m.r0, m.r1), m.q);
-                r1[v] = add_mod(r1[v], barrett128(a1[v], m.q, m.r0, m.r1), m.q);
-            }
-            if (GATHER) {
-                o0[0] = r0[0];
-                o1[0] = r1[0];
-            } else {
-                *reinterpret_cast<ulonglong2 *>(o0) = make_ulonglong2(r0[0], r0[V - 1]);
-                *reinterpret_cast<ulonglong2 *>(o1) = make_ulonglong2(r1[0], r1[V - 1]);
+            for (int c = 0; c < B; ++c) {
+                if (c < nb) {
+                    u64 *o0 = cx + 2 * (b0 + c) * per_ct + ((long)r << logN) + k, *o1 = o0 + per_ct;
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        r0[c][v] = add_mod(r0[c][v], barrett128(a0[c][v], m.q, m.r0, m.r1), m.q);
+                        r1[c][v] = add_mod(r1[c][v], barrett128(a1[c][v], m.q, m.r0, m.r1), m.q);
+                    }
+                    if (GATHER) {
+                        o0[0] = r0[c][0];
+                        o1[0] = r1[c][0];
+                    } else {
+                        *reinterpret_cast<ulonglong2 *>(o0) = make_ulonglong2(r0[c][0], r0[c][V - 1]);
+                        *reinterpret_cast<ulonglong2 *>(o1) = make_ulonglong2(r1[c][0], r1[c][V - 1]);
+                    }
+                }
             }
         }
     }
@@ -207,7 +239,9 @@ static int inner_product_steps(Context *ctx, int L, int batch, const u64 *digits
     const long per_thread = gather ? 1 : 2;
     long gx = ((long)hp.N / per_thread + kKsThreads - 1) / kKsThreads;
     if (gx < 1) gx = 1;
-    const dim3 grid((unsigned)gx, (unsigned)LP, (unsigned)(batch < 65535 ? batch : 65535));
+    const int per_block = gather ? ip_cts<true>() : ip_cts<false>();
+    const int zb = (batch + per_block - 1) / per_block;
+    const dim3 grid((unsigned)gx, (unsigned)LP, (unsigned)(zb < 65535 ? zb : 65535));
     // digits (beta rows per output row, the own limbs included), both key polynomials per step and digit, two outputs
     count_launch("inner_product_kernel", stream,
                  8.0 * hp.N * LP * batch * (double)hp.level[L].beta + 8.0 * hp.N * LP * 2.0 * hp.level[L].beta * args.n_steps +

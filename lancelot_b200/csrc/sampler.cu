@@ -34,7 +34,9 @@ LB_D void prng_block(const uint32_t *__restrict__ seed, const u64 nonce, uint32_
     for (int i = 0; i < 6; ++i) j[10 + i] = seed[8 + i];
 #pragma unroll
     for (int i = 0; i < 16; ++i) x[i] = j[i];
-#pragma unroll 2
+    // unrolled in full: the small samplers use one or two words of the block, and only then can the compiler drop
+    // the quarter rounds of the last double round that do not reach them
+#pragma unroll
     for (int r = 0; r < 10; ++r) {
         LB_QR(0, 4, 8, 12) LB_QR(5, 9, 13, 1) LB_QR(10, 14, 2, 6) LB_QR(15, 3, 7, 11)
         LB_QR(0, 1, 2, 3) LB_QR(5, 6, 7, 4) LB_QR(10, 11, 8, 9) LB_QR(15, 12, 13, 14)
