@@ -152,60 +152,71 @@ __global__ void __launch_bounds__(kKsThreads) inner_product_kernel(const u64 *__
                     r0[c][v] = r1[c][v] = 0;
                 }
             }
-            int pending = 0;
-            for (int s = 0; s < args.n_steps; ++s) {
+            // one term = one digit of one step; the operands of term t + 1 are requested before term t is multiplied,
+            // so the loads of a term have the whole multiply-accumulate of its predecessor to arrive in
+            struct Term {
+                u64 k0[V], k1[V], d[B][V];
+            };
+            auto fetch = [&](const int t) {
+                Term x;
+                const int s = t / beta, j = t - s * beta;
                 const u64 *key = args.evk[s];
                 const long kk = GATHER && args.perm[s] ? (long)args.perm[s][k] : k;
-                for (int j = 0; j < beta; ++j) {
-                    const u64 *kb = key + ((((long)j * 2) * size_QP + tbl) << logN) + k;
-                    u64 k0[V], k1[V];
-                    if (GATHER) {
-                        k0[0] = kb[0];
-                        k1[0] = kb[(long)size_QP << logN];
+                const u64 *kb = key + ((((long)j * 2) * size_QP + tbl) << logN) + k;
+                if (GATHER) {
+                    x.k0[0] = kb[0];
+                    x.k1[0] = kb[(long)size_QP << logN];
+                } else {
+                    const ulonglong2 kv0 = *reinterpret_cast<const ulonglong2 *>(kb);
+                    const ulonglong2 kv1 = *reinterpret_cast<const ulonglong2 *>(kb + ((long)size_QP << logN));
+                    x.k0[0] = kv0.x; x.k0[V - 1] = kv0.y;
+                    x.k1[0] = kv1.x; x.k1[V - 1] = kv1.y;
+                }
+#pragma unroll
+                for (int c = 0; c < B; ++c) {
+                    if (c < nb) {
+                        const long b = b0 + c;
+                        const u64 *src = (j == own_digit) ? own + ((b * own_stride) << logN) + ((long)r << logN)
+                                                          : digits + b * beta * per_ct + (((long)j * LP + r) << logN);
+                        if (GATHER) {
+                            x.d[c][0] = src[kk];
+                        } else {
+                            const ulonglong2 dv = *reinterpret_cast<const ulonglong2 *>(src + k);
+                            x.d[c][0] = dv.x; x.d[c][V - 1] = dv.y;
+                        }
                     } else {
-                        const ulonglong2 kv0 = *reinterpret_cast<const ulonglong2 *>(kb);
-                        const ulonglong2 kv1 = *reinterpret_cast<const ulonglong2 *>(kb + ((long)size_QP << logN));
-                        k0[0] = kv0.x; k0[V - 1] = kv0.y;
-                        k1[0] = kv1.x; k1[V - 1] = kv1.y;
-                    }
-                    u64 d[B][V];
 #pragma unroll
-                    for (int c = 0; c < B; ++c) {
-                        if (c < nb) {
-                            const long b = b0 + c;
-                            const u64 *src = (j == own_digit) ? own + ((b * own_stride) << logN) + ((long)r << logN)
-                                                              : digits + b * beta * per_ct + (((long)j * LP + r) << logN);
-                            if (GATHER) {
-                                d[c][0] = src[kk];
-                            } else {
-                                const ulonglong2 dv = *reinterpret_cast<const ulonglong2 *>(src + k);
-                                d[c][0] = dv.x; d[c][V - 1] = dv.y;
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int c = 0; c < B; ++c) {
-                        if (c < nb) {
-#pragma unroll
-                            for (int v = 0; v < V; ++v) {
-                                mac_wide(a0[c][v], d[c][v], k0[v]);
-                                mac_wide(a1[c][v], d[c][v], k1[v]);
-                            }
-                        }
-                    }
-                    if (++pending == 32) {
-#pragma unroll
-                        for (int c = 0; c < B; ++c) {
-#pragma unroll
-                            for (int v = 0; v < V; ++v) {
-                                r0[c][v] = add_mod(r0[c][v], barrett128(a0[c][v], m.q, m.r0, m.r1), m.q);
-                                r1[c][v] = add_mod(r1[c][v], barrett128(a1[c][v], m.q, m.r0, m.r1), m.q);
-                                a0[c][v] = a1[c][v] = u128d{0, 0};
-                            }
-                        }
-                        pending = 0;
+                        for (int v = 0; v < V; ++v) x.d[c][v] = 0;
                     }
                 }
+                return x;
+            };
+            const int n_terms = args.n_steps * beta;
+            int pending = 0;
+            Term cur = fetch(0);
+            for (int t = 0; t < n_terms; ++t) {
+                const Term nxt = t + 1 < n_terms ? fetch(t + 1) : cur;
+#pragma unroll
+                for (int c = 0; c < B; ++c) {
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        mac_wide(a0[c][v], cur.d[c][v], cur.k0[v]);
+                        mac_wide(a1[c][v], cur.d[c][v], cur.k1[v]);
+                    }
+                }
+                if (++pending == 32) {
+#pragma unroll
+                    for (int c = 0; c < B; ++c) {
+#pragma unroll
+                        for (int v = 0; v < V; ++v) {
+                            r0[c][v] = add_mod(r0[c][v], barrett128(a0[c][v], m.q, m.r0, m.r1), m.q);
+                            r1[c][v] = add_mod(r1[c][v], barrett128(a1[c][v], m.q, m.r0, m.r1), m.q);
+                            a0[c][v] = a1[c][v] = u128d{0, 0};
+                        }
+                    }
+                    pending = 0;
+                }
+                cur = nxt;
             }
 #pragma unroll
             for (int c = 0; c < B; ++c) {
