@@ -217,6 +217,12 @@ LB_API int lb_gen_public_key(lb_context *ctx, const uint64_t *sk, const uint8_t 
 /* generate_one_kswitch_key (secretkey.cu:328): out[dnum][2][size_QP][N]; sk_target is s^2 for
  * a relinearization key, the permuted secret for a Galois key; seeds[dnum][2][64] (error, uniform) */
 LB_API int lb_gen_switch_key(lb_context *ctx, const uint64_t *sk, const uint64_t *sk_target, const uint8_t *seeds, uint64_t *out, void *stream);
+/* create_galois_keys (cahel-main/src/secretkey.cu:374-449) for several Galois elements of the context in one call:
+ * out[k][dnum][2][size_QP][N] = the switch key from sk rotated by element elt_indices[k] to sk, generated from
+ * seeds[k][2 dnum][64] exactly as lb_galois_permute + lb_gen_switch_key generate it, with every step launched once
+ * for all keys and digits. */
+LB_API int lb_gen_galois_keys(lb_context *ctx, const uint64_t *sk, int n_keys, const int *elt_indices, const uint8_t *seeds,
+                       uint64_t *out, void *stream);
 /* encrypt_asymmetric (secretkey.cu:47-249) for a batch: ct[b][2][size_Q][N] = moddown(pk u + e) + (pt[b], 0).
  * seeds[b][2][64] = (ternary seed, error seed); pt may be NULL (encryption of zero). */
 LB_API int lb_encrypt_asymmetric(lb_context *ctx, const uint64_t *pk, const uint64_t *pt, const uint8_t *seeds, int batch, uint64_t *ct, void *stream);

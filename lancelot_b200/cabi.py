@@ -336,6 +336,17 @@ class Context:
         check(lib.lb_gen_switch_key(self.h, _p(sk), _p(sk_target), sp, _p(out), self._stream()))
         return out
 
+    def gen_galois_keys(self, sk, elt_indices, seeds, out=None):
+        """switch keys of several Galois elements in one call -> [n][dnum][2][size_QP][N]; seeds: 2 dnum per key"""
+        dnum = self.size_Q // self.size_P
+        n = len(elt_indices)
+        s, sp = self._seed(seeds, 2 * dnum * n)
+        if out is None:
+            out = self.empty(n, dnum, 2, self.size_QP, self.N)
+        idx = (C.c_int * max(1, n))(*[int(e) for e in elt_indices])
+        check(lib.lb_gen_galois_keys(self.h, _p(sk), n, idx, sp, _p(out), self._stream()))
+        return out
+
     def encrypt_asymmetric(self, pk, pt, seeds, batch=1, out=None):
         s, sp = self._seed(seeds, 2 * batch)
         if out is not None:

@@ -645,6 +645,29 @@ int lb_gen_switch_key(lb_context *h, const uint64_t *sk, const uint64_t *sk_targ
     return gen_switch_key(c, sk, sk_target, ds, out, scratch, S(stream));
 }
 
+int lb_gen_galois_keys(lb_context *h, const uint64_t *sk, int n_keys, const int *elt_indices, const uint8_t *seeds, uint64_t *out,
+                       void *stream)
+{
+    int rc = bind(h);
+    if (rc) return rc;
+    REQUIRE(sk && seeds && out && n_keys >= 0 && (elt_indices || n_keys == 0), "operand is null");
+    if (n_keys == 0) return LB_OK;
+    Context *c = C(h);
+    REQUIRE(c->hp.size_P >= 1 && c->hp.size_Q % c->hp.size_P == 0, "special_modulus_size must divide the number of data primes");
+    for (int k = 0; k < n_keys; ++k)
+        REQUIRE(elt_indices[k] >= 0 && elt_indices[k] < (int)c->hp.galois_elts.size(), "Galois element index is out of range");
+    const int dnum = c->hp.size_Q / c->hp.size_P;
+    const size_t poly = (size_t)c->hp.size_QP << c->hp.logN;
+    uint32_t *ds;
+    u64 *scratch;
+    // scratch: the rotated secret keys [n][QP][N], then one error polynomial per key and digit
+    if ((rc = stage_seeds(c, seeds, 2 * dnum * n_keys, &ds, &scratch, poly * (size_t)n_keys * (1 + dnum), S(stream)))) return rc;
+    u64 *targets = scratch, *errors = scratch + poly * n_keys;
+    for (int k = 0; k < n_keys; ++k)
+        if ((rc = poly_galois(c, elt_indices[k], c->hp.size_QP, sk, targets + poly * k, S(stream)))) return rc;
+    return gen_switch_keys(c, sk, targets, n_keys, ds, out, errors, S(stream));
+}
+
 int lb_encrypt_asymmetric(lb_context *h, const uint64_t *pk, const uint64_t *pt, const uint8_t *seeds, int batch, uint64_t *ct, void *stream)
 {
     int rc = bind(h);

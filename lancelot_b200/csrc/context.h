@@ -165,10 +165,12 @@ int moddown(Context *ctx, int size_l, const u64 *cx, u64 *out, cudaStream_t stre
 int sample_small(Context *ctx, int kind, const uint32_t *d_seeds, int seed_stride, int batch, int size_l, int size_p, u64 *out,
                  cudaStream_t stream);
 int sample_uniform(Context *ctx, const uint32_t *d_seeds, int seed_stride, int batch, int size_l, int size_p, u64 *out,
-                   cudaStream_t stream);
+                   cudaStream_t stream, long out_stride = 0);
 int gen_public_key(Context *ctx, const u64 *sk, const uint32_t *d_seed_e, const uint32_t *d_seed_a, u64 *pk, u64 *scratch,
                    cudaStream_t stream);
 int gen_switch_key(Context *ctx, const u64 *sk, const u64 *skp, const uint32_t *d_seeds, u64 *out, u64 *scratch, cudaStream_t stream);
+int gen_switch_keys(Context *ctx, const u64 *sk, const u64 *targets, int n, const uint32_t *d_seeds, u64 *out, u64 *scratch,
+                    cudaStream_t stream);
 size_t encrypt_workspace_bytes(const Context *ctx, int batch);
 // encoder (encoder.cu)
 int encode(Context *ctx, int size_l, const void *values, int dtype, long value_stride, int n_values, int sparse_slots, int batch,

@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(kSampThreads) sample_small_kernel(u64 *__restr
 __global__ void __launch_bounds__(kSampThreads) sample_uniform_kernel(u64 *__restrict__ out, const uint32_t *__restrict__ seeds,
                                                                       const int seed_stride, const ModConst *__restrict__ mc, const int logN,
                                                                       const int size_l, const int size_p, const int size_Q,
-                                                                      const long total)
+                                                                      const long total, const long out_stride)
 {
     const int rows = size_l + size_p;
     const long blocks_per_poly = ((long)rows << logN) >> 3;
@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(kSampThreads) sample_uniform_kernel(u64 *__res
         uint32_t x[16];
         prng_block(seeds + seed_stride * b, (u64)t, x);
         u64 tries = 1;
-        u64 *o = out + b * (blocks_per_poly << 3) + (t << 3);
+        u64 *o = out + b * out_stride + (t << 3);
 #pragma unroll 1
         for (int w = 0; w < 8; ++w) {
             u64 v = (u64)x[2 * w] | (u64)x[2 * w + 1] << 32;
@@ -137,13 +137,15 @@ int sample_small(Context *ctx, int kind, const uint32_t *d_seeds, int seed_strid
     return LB_OK;
 }
 
-int sample_uniform(Context *ctx, const uint32_t *d_seeds, int seed_stride, int batch, int size_l, int size_p, u64 *out, cudaStream_t stream)
+int sample_uniform(Context *ctx, const uint32_t *d_seeds, int seed_stride, int batch, int size_l, int size_p, u64 *out, cudaStream_t stream,
+                   long out_stride)
 {
     const long total = ((long)batch * (size_l + size_p) << ctx->hp.logN) >> 3;
     if (total == 0) return LB_OK;
+    if (out_stride <= 0) out_stride = (long)(size_l + size_p) << ctx->hp.logN; // polynomials back to back
     count_launch("sample_uniform_kernel", stream);
     sample_uniform_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(out, d_seeds, seed_stride, ctx->d_mc, ctx->hp.logN, size_l, size_p,
-                                                                            ctx->hp.size_Q, total);
+                                                                            ctx->hp.size_Q, total, out_stride);
     LB_CUDA(cudaGetLastError());
     return LB_OK;
 }
@@ -214,6 +216,76 @@ int gen_switch_key(Context *ctx, const u64 *sk, const u64 *skp, const uint32_t *
     count_launch("ksk_add_kernel", stream);
     ksk_add_kernel<<<grid_for(ctx, total), kSampThreads, 0, stream>>>(out, skp, ctx->d_p_mod_q, ctx->d_p_mod_q_s, ctx->d_mc, hp.logN,
                                                                      hp.size_P, 2 * poly, total);
+    LB_CUDA(cudaGetLastError());
+    return LB_OK;
+}
+
+// The same two steps for a batch of key pairs / switch keys (grid y): pair t is (b, a) = (pairs + t * 2 poly, + poly),
+// its error e + t * poly; switch key k is dnum consecutive pairs and takes the target skp + k * poly.
+__global__ void __launch_bounds__(kSampThreads) pk_combine_batch_kernel(u64 *__restrict__ pairs, const u64 *__restrict__ s,
+                                                                        const u64 *__restrict__ e, const ModConst *__restrict__ mc,
+                                                                        const int logN, const long poly)
+{
+    u64 *b = pairs + (long)blockIdx.y * 2 * poly;
+    const u64 *a = b + poly, *eb = e + (long)blockIdx.y * poly;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < poly; i += (long)gridDim.x * blockDim.x) {
+        const ModConst m = mc[(int)(i >> logN)];
+        u128d acc = mul_wide(a[i], s[i]);
+        acc.lo += eb[i];
+        acc.hi += acc.lo < eb[i];
+        const u64 v = barrett128(acc, m.q, m.r0, m.r1);
+        b[i] = v ? m.q - v : 0;
+    }
+}
+
+__global__ void __launch_bounds__(kSampThreads) ksk_add_batch_kernel(u64 *__restrict__ keys, const u64 *__restrict__ skp,
+                                                                     const u64 *__restrict__ pmod, const u64 *__restrict__ pmod_s,
+                                                                     const ModConst *__restrict__ mc, const int logN, const int alpha,
+                                                                     const long key_words, const long poly, const long total)
+{
+    u64 *key = keys + (long)blockIdx.y * key_words;
+    const u64 *target = skp + (long)blockIdx.y * poly;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const int r = (int)(i >> logN);
+        const int j = r / alpha;
+        const u64 q = mc[r].q;
+        u64 *dst = key + j * 2 * poly + i;
+        *dst = add_mod(*dst, shoup_mul(target[i], pmod[r], pmod_s[r], q), q);
+    }
+}
+
+// n switch keys at once: the streams, and so the keys, are those of n calls of gen_switch_key with seeds
+// d_seeds + k * 32 * dnum, but every step is one launch over all keys and digits instead of one per key and digit.
+// targets: [n][QP][N]; out: [n][dnum][2][QP][N]; scratch: n * dnum polynomials.
+int gen_switch_keys(Context *ctx, const u64 *sk, const u64 *targets, int n, const uint32_t *d_seeds, u64 *out, u64 *scratch,
+                    cudaStream_t stream)
+{
+    const HostParams &hp = ctx->hp;
+    const int dnum = hp.size_Q / hp.size_P;
+    const long poly = (long)hp.size_QP << hp.logN;
+    const int pairs = n * dnum;
+    if (pairs == 0) return LB_OK;
+    if (pairs > 65535) { set_error("too many switch keys in one call"); return LB_ERR_INVALID_ARG; }
+    int rc;
+    if ((rc = sample_small(ctx, 1, d_seeds, 32, pairs, hp.size_Q, hp.size_P, scratch, stream))) return rc;
+    NttJob j;
+    j.src = scratch;
+    j.dst = scratch;
+    j.n_groups = pairs;
+    j.per_group = hp.size_QP;
+    j.size_l = hp.size_Q;
+    if ((rc = ntt_forward(ctx, j, stream))) return rc;
+    if ((rc = sample_uniform(ctx, d_seeds + 16, 32, pairs, hp.size_Q, hp.size_P, out + poly, stream, 2 * poly))) return rc;
+    long gx = (poly + kSampThreads - 1) / kSampThreads;
+    const long cap = (long)ctx->sm_count * 16;
+    if (gx > cap) gx = cap;
+    count_launch("pk_combine_kernel", stream);
+    pk_combine_batch_kernel<<<dim3((unsigned)gx, (unsigned)pairs), kSampThreads, 0, stream>>>(out, sk, scratch, ctx->d_mc, hp.logN, poly);
+    LB_CUDA(cudaGetLastError());
+    const long total = (long)hp.size_Q << hp.logN;
+    count_launch("ksk_add_kernel", stream);
+    ksk_add_batch_kernel<<<dim3((unsigned)grid_for(ctx, total), (unsigned)n), kSampThreads, 0, stream>>>(
+        out, targets, ctx->d_p_mod_q, ctx->d_p_mod_q_s, ctx->d_mc, hp.logN, hp.size_P, (long)dnum * 2 * poly, poly, total);
     LB_CUDA(cudaGetLastError());
     return LB_OK;
 }

@@ -438,12 +438,10 @@ class EncryptedKrum:
         key_words = int(np.prod(key_shape))
         everything = lb.empty(world_size, per, key_words)
         mine = everything[rank]
-        for i in range(n_keys):
-            seeds = cahel._seeds(2 * dnum)
-            if i % world_size != rank:
-                continue
-            rotated = lb.galois_permute(i, self.sk.data)
-            mine[i // world_size].copy_(lb.gen_switch_key(self.sk.data, rotated, seeds).reshape(-1))
+        all_seeds = [cahel._seeds(2 * dnum) for _ in range(n_keys)]  # every rank draws every key's seeds
+        own = list(range(rank, n_keys, world_size))
+        if own:
+            lb.gen_galois_keys(self.sk.data, own, np.concatenate([all_seeds[i] for i in own]), out=mine[: len(own)])
         dist.all_gather_into_tensor(everything.view(-1), mine.reshape(-1).clone(), group=group)
         self.glk.keys = [everything[i % world_size, i // world_size].view(key_shape) for i in range(n_keys)]
 

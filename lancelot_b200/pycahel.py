@@ -381,12 +381,14 @@ class secret_key:
     def create_galois_keys(self, ctx, glk, save_seed=False):
         self._need()
         dnum = ctx.size_Q // ctx.size_P
-        glk.keys = []
-        for i, elt in enumerate(ctx.galois_elts):
+        for elt in ctx.galois_elts:
             if not (elt & 1) or elt >= 2 * ctx.N:
                 raise ValueError("Galois element is not valid")
-            rotated = ctx.lb.galois_permute(i, self.data)
-            glk.keys.append(ctx.lb.gen_switch_key(self.data, rotated, _seeds(2 * dnum)))
+        # the seeds are drawn key by key, as separate calls would draw them; the keys come from one batched call
+        n = len(ctx.galois_elts)
+        seeds = np.concatenate([_seeds(2 * dnum) for _ in range(n)]) if n else np.zeros(0, dtype=np.uint8)
+        keys = ctx.lb.gen_galois_keys(self.data, list(range(n)), seeds) if n else []
+        glk.keys = [keys[i] for i in range(n)]
 
     def encrypt_symmetric(self, ctx, plain, save_seed=False):
         """cahel-main/src/secretkey.cu:451-560: (c0, c1) = (-(a s + e) + pt, a) at the plaintext's level."""

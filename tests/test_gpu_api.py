@@ -401,3 +401,36 @@ def test_round_entries_pair_sums_and_scores_equal_the_single_operations(n_client
     if len(pairs) > 1:
         with pytest.raises(ValueError):
             ek.lb.krum_pair_sums(3, cts, n_clients, [pairs[0], pairs[0]], acc)
+
+
+@pytest.mark.gpu
+def test_batched_galois_key_generation_equals_key_by_key():
+    """lb_gen_galois_keys against lb_galois_permute + lb_gen_switch_key per element with the same seeds, word for word
+    (the key-by-key path is the one the reference-made fixtures pin)"""
+    import torch
+
+    from lancelot_b200 import pycahel as cahel
+
+    n = 4096
+    params = cahel.params(cahel.scheme_type.ckks)
+    params.set_poly_modulus_degree(n)
+    params.set_coeff_modulus(cahel.coeff_modulus_create(n, [60, 40, 40, 40, 60, 60]))
+    params.set_special_modulus_size(2)  # four data primes, two special ones: dnum = 2, digits of two limbs
+    params.set_galois_elts(cahel.get_elts_from_steps([1, 2, 3, 5, 64], n))
+    ctx = cahel.context(params, True, cahel.sec_level_type.none)
+    cahel.set_seed_source(cahel.counter_seed_source(11))
+    try:
+        sk = cahel.secret_key(params)
+        sk.gen_secretkey(ctx)
+        dnum = ctx.size_Q // ctx.size_P
+        seeds = [cahel._seeds(2 * dnum) for _ in ctx.galois_elts]
+    finally:
+        cahel.set_seed_source(None)
+    lb = ctx.lb
+    single = [lb.gen_switch_key(sk.data, lb.galois_permute(i, sk.data), seeds[i]) for i in range(len(seeds))]
+    order = [3, 0, 4]  # any subset, any order
+    batched = lb.gen_galois_keys(sk.data, order, np.concatenate([seeds[i] for i in order]))
+    for k, i in enumerate(order):
+        assert torch.equal(batched[k], single[i]), "element %d" % i
+    every = lb.gen_galois_keys(sk.data, list(range(len(seeds))), np.concatenate(seeds))
+    assert all(torch.equal(every[i], single[i]) for i in range(len(seeds)))
