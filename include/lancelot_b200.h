@@ -184,10 +184,10 @@ LB_API int lb_krum_pair_sums(lb_context *ctx, int size_l, int n_clients, const u
  * rescale_to_next_inplace of acc [n_pairs][3][size_l][N] (overwritten), scores <- result [n_pairs][2][size_l-1][N],
  * scores += hoisting(scores, first steps), then scores += rotate(scores, step) for every further step in order.
  * first_keys / pow_keys: HOST arrays of device pointers to the Galois keys of first_elts / pow_elts (indices into
- * the context's Galois elements); scratch: device words of the size of scores. */
+ * the context's Galois elements). */
 LB_API int lb_krum_scores(lb_context *ctx, int size_l, int n_pairs, uint64_t *acc, const uint64_t *relin_key, int n_first,
                    const int *first_elts, const uint64_t *const *first_keys, int n_pow, const int *pow_elts,
-                   const uint64_t *const *pow_keys, uint64_t *scores, uint64_t *scratch, void *stream);
+                   const uint64_t *const *pow_keys, uint64_t *scores, void *stream);
 
 /* Mask multiplication of the aggregation phase (lancelot-main-GPU/utils/byzantine_fl.py:371-429):
  * out[c][3][size_l][N] = sum over clients k of ct_k[c] (x) mask_k (ckks_multiply + add_inplace per client

@@ -286,14 +286,12 @@ class Context:
         by first_elts added, then rotate + add for every element of pow_elts in order"""
         n_pairs = acc.numel() // (3 * size_l * self.N)
         scores = self.empty(n_pairs, 2, size_l - 1, self.N)
-        scratch = self.empty(n_pairs, 2, size_l - 1, self.N)
         nf, npw = len(first_elts), len(pow_elts)
         fe = (C.c_int * max(1, nf))(*first_elts)
         fk = (C.c_void_p * max(1, nf))(*[g.data_ptr() for g in first_keys])
         pe = (C.c_int * max(1, npw))(*pow_elts)
         pk = (C.c_void_p * max(1, npw))(*[g.data_ptr() for g in pow_keys])
-        check(lib.lb_krum_scores(self.h, size_l, n_pairs, _p(acc), _p(rlk), nf, fe, fk, npw, pe, pk, _p(scores), _p(scratch),
-                                 self._stream()))
+        check(lib.lb_krum_scores(self.h, size_l, n_pairs, _p(acc), _p(rlk), nf, fe, fk, npw, pe, pk, _p(scores), self._stream()))
         return scores
 
     def decrypt(self, size_l, ct, sk):

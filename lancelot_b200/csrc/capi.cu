@@ -493,31 +493,25 @@ int lb_krum_pair_sums(lb_context *h, int size_l, int n_clients, const uint64_t *
 // the first steps added to the ciphertext, then rotate_vector + add_inplace for every further step
 int lb_krum_scores(lb_context *h, int size_l, int n_pairs, uint64_t *acc, const uint64_t *relin_key, int n_first, const int *first_elts,
                    const uint64_t *const *first_keys, int n_pow, const int *pow_elts, const uint64_t *const *pow_keys, uint64_t *scores,
-                   uint64_t *scratch, void *stream)
+                   void *stream)
 {
     int rc = bind(h);
     if (rc) return rc;
     if ((rc = level_ok(C(h), size_l))) return rc;
     REQUIRE(size_l >= 2, "the pair sums must have a level to rescale to");
-    REQUIRE(acc && relin_key && scores && scratch && n_pairs >= 0 && n_first >= 0 && n_pow >= 0, "operand is null");
+    REQUIRE(acc && relin_key && scores && n_pairs >= 0 && n_first >= 0 && n_pow >= 0, "operand is null");
     REQUIRE((n_first == 0 || (first_elts && first_keys)) && (n_pow == 0 || (pow_elts && pow_keys)), "operand is null");
     if (n_pairs == 0) return LB_OK;
     Context *c = C(h);
     cudaStream_t st = S(stream);
     const int L = size_l - 1;
-    const size_t words = (size_t)n_pairs * 2 * L * c->hp.N;
     if ((rc = relinearize(c, size_l, n_pairs, acc, relin_key, st))) return rc;
     if ((rc = rescale(c, size_l, n_pairs, 2, acc, 3L * size_l, scores, st))) return rc;
-    if (n_first > 0) {
-        LB_CUDA(cudaMemcpyAsync(scratch, scores, words * sizeof(uint64_t), cudaMemcpyDeviceToDevice, st));
-        if ((rc = hoisting(c, L, n_pairs, scratch, n_first, first_elts, first_keys, st))) return rc;
-        if ((rc = poly_binary(c, OP_ADD, L, (long)n_pairs * 2 * L, scores, scratch, scores, st))) return rc;
-    }
-    for (int k = 0; k < n_pow; ++k) {
-        LB_CUDA(cudaMemcpyAsync(scratch, scores, words * sizeof(uint64_t), cudaMemcpyDeviceToDevice, st));
-        if ((rc = rotate(c, L, n_pairs, scratch, pow_elts[k], pow_keys[k], st))) return rc;
-        if ((rc = poly_binary(c, OP_ADD, L, (long)n_pairs * 2 * L, scores, scratch, scores, st))) return rc;
-    }
+    // scores += hoisting(scores), scores += rotate(scores, step): the sums are formed inside the key switch's closing
+    // transform (no copy of the batch, no separate addition)
+    if (n_first > 0 && (rc = hoisting(c, L, n_pairs, scores, n_first, first_elts, first_keys, st, true))) return rc;
+    for (int k = 0; k < n_pow; ++k)
+        if ((rc = rotate(c, L, n_pairs, scores, pow_elts[k], pow_keys[k], st, true))) return rc;
     return LB_OK;
 }
 

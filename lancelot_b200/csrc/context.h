@@ -110,6 +110,10 @@ struct NttJob {
     const u64 *add = nullptr; // optional addend rows; only groups with inner < add_inner have one
     long add_group_stride = -1, add_outer = -1;
     int add_inner = 0;
+    // the addend rows of the groups with inner == 1 when they sit in another buffer: add1 + outer * add1_outer rows
+    // (the second polynomial of ciphertexts that a rotation is added to in place); may alias dst
+    const u64 *add1 = nullptr;
+    long add1_outer = 0;
     // Forward epilogue, alternative: mul2[2][per_group][N] are two fixed rows per row position (the two polynomials of a
     // public key); group g stores NTT(x) * mul2[0] at dst rows (go * dst_outer + rr) and NTT(x) * mul2[1] per_group rows
     // further on, so dst_outer = 2 * per_group lays the products out as [group][2][per_group][N]
@@ -129,6 +133,8 @@ int poly_binary(Context *ctx, int op, int size_l, long rows, const u64 *a, const
 int poly_tensor(Context *ctx, int size_l, int batch, const u64 *a, const u64 *b, u64 *out, cudaStream_t stream);
 // dst[i] = src[perm[i]] for `rows` limbs
 int poly_galois(Context *ctx, int elt_idx, long rows, const u64 *src, u64 *dst, cudaStream_t stream);
+// the same for ciphertexts [batch][2][L][N], with the first polynomial of each added to its own image
+int poly_galois_plus_c0(Context *ctx, int elt_idx, int L, int batch, const u64 *src, u64 *dst, cudaStream_t stream);
 int poly_sum_groups(Context *ctx, int size_l, long n_rows, int n_groups, const int *h_offsets, const int *h_indices, const u64 *in,
                     u64 *out, cudaStream_t stream);
 // acc[3][L][N] (+)= sum_c square(b_c - a_c) over n_chunks ciphertext pairs [2][L][N]
@@ -151,11 +157,12 @@ int keyswitch(Context *ctx, int size_l, const u64 *cks, const u64 *evk, const u6
               cudaStream_t stream);
 int relinearize(Context *ctx, int size_l, int batch, u64 *ct3, const u64 *rlk, cudaStream_t stream);
 int rescale(Context *ctx, int size_l, int batch, int polys_per_ct, const u64 *in, long in_outer_rows, u64 *out, cudaStream_t stream);
-int rotate(Context *ctx, int size_l, int batch, u64 *ct, int elt_idx, const u64 *glk, cudaStream_t stream);
+// accumulate: ct <- ct + rotation (sum of rotations) of ct instead of ct <- rotation
+int rotate(Context *ctx, int size_l, int batch, u64 *ct, int elt_idx, const u64 *glk, cudaStream_t stream, bool accumulate = false);
 int rescale_static(Context *ctx, int size_l, int n_polys, const u64 *in, u64 *out, cudaStream_t stream); // rescale_static.cu
 size_t rescale_static_max_words();
 int hoisting(Context *ctx, int size_l, int batch, u64 *ct, int n_steps, const int *elt_idx, const u64 *const *glks,
-             cudaStream_t stream);
+             cudaStream_t stream, bool accumulate = false);
 // exposed pieces of the key switch for per-stage parity tests
 int modup(Context *ctx, int size_l, const u64 *cks, u64 *digits, cudaStream_t stream);
 int inner_product(Context *ctx, int size_l, const u64 *digits, const u64 *cks, const u64 *evk, u64 *cx, cudaStream_t stream);

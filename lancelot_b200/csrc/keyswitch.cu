@@ -275,7 +275,7 @@ struct Placement {
 };
 
 static int moddown_into(Context *ctx, int L, int batch, int ppc, const u64 *cx, u64 *pc, u64 *out, Placement po, const u64 *add,
-                        Placement pa, int add_inner, cudaStream_t stream)
+                        Placement pa, int add_inner, cudaStream_t stream, const u64 *add1 = nullptr, long add1_outer = 0)
 {
     const HostParams &hp = ctx->hp;
     const int P = hp.size_P, LP = L + P;
@@ -314,6 +314,8 @@ static int moddown_into(Context *ctx, int L, int batch, int ppc, const u64 *cx, 
     fwd.add_group_stride = pa.inner;
     fwd.add_outer = pa.outer;
     fwd.add_inner = add ? add_inner : 0;
+    fwd.add1 = add1;
+    fwd.add1_outer = add1_outer;
     return ntt_forward(ctx, fwd, stream);
 }
 
@@ -445,7 +447,7 @@ int rescale(Context *ctx, int L, int batch, int ppc, const u64 *in, long in_oute
 
 // cahel-main/src/evaluate.cu:2631-2686 for a batch of size-2 ciphertexts stored back to back:
 // permute both polynomials, then switch the permuted c1
-int rotate(Context *ctx, int L, int batch, u64 *ct, int elt_idx, const u64 *glk, cudaStream_t stream)
+int rotate(Context *ctx, int L, int batch, u64 *ct, int elt_idx, const u64 *glk, cudaStream_t stream, bool accumulate)
 {
     int rc = check_level(ctx, L);
     if (rc) return rc;
@@ -458,13 +460,17 @@ int rotate(Context *ctx, int L, int batch, u64 *ct, int elt_idx, const u64 *glk,
         KsWs w;
         if ((rc = get_ws(ctx, L, nb, w))) return rc;
         u64 *ct_b = ct + 2 * poly * b0;
-        if ((rc = poly_galois(ctx, elt_idx, 2L * L * nb, ct_b, w.tmp, stream))) return rc;
+        // accumulate: the image of c0 takes c0 along, and the closing transform adds the old c1 to the new one
+        if (accumulate) rc = poly_galois_plus_c0(ctx, elt_idx, L, nb, ct_b, w.tmp, stream);
+        else rc = poly_galois(ctx, elt_idx, 2L * L * nb, ct_b, w.tmp, stream);
+        if (rc) return rc;
         if ((rc = modup_into(ctx, L, nb, w.tmp + poly, 2L * L, w.coef, w.digits, stream))) return rc;
         IpArgs args = {};
         args.evk[0] = glk;
         args.n_steps = 1;
         if ((rc = inner_product_steps(ctx, L, nb, w.digits, w.tmp + poly, 2L * L, args, w.cx, stream))) return rc;
-        if ((rc = moddown_into(ctx, L, nb, 2, w.cx, w.pc, ct_b, p2, w.tmp, p2, 1, stream))) return rc;
+        if ((rc = moddown_into(ctx, L, nb, 2, w.cx, w.pc, ct_b, p2, w.tmp, p2, 1, stream, accumulate ? ct_b + poly : nullptr, 2L * L)))
+            return rc;
     }
     return LB_OK;
 }
@@ -472,7 +478,7 @@ int rotate(Context *ctx, int L, int batch, u64 *ct, int elt_idx, const u64 *glk,
 // sum over steps of the permuted c0 (cahel-main/src/evaluate.cu:2560-2568); c0 of ciphertext b at row b * ct_stride
 __global__ void __launch_bounds__(kKsThreads) galois_sum_kernel(const u64 *__restrict__ src, const long ct_stride, u64 *__restrict__ dst,
                                                                 const ModConst *__restrict__ mc, const IpArgs args, const int logN,
-                                                                const int L, const long total)
+                                                                const int L, const long total, const int plus_self)
 {
     const long n_mask = (1L << logN) - 1;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
@@ -480,7 +486,7 @@ __global__ void __launch_bounds__(kKsThreads) galois_sum_kernel(const u64 *__res
         const long b = row / L, r = row - b * L;
         const u64 q = mc[r].q;
         const u64 *s0 = src + ((b * ct_stride + r) << logN);
-        u64 acc = 0;
+        u64 acc = plus_self ? s0[k] : 0;
         for (int s = 0; s < args.n_steps; ++s) acc = add_mod(acc, s0[args.perm[s][k]], q);
         dst[i] = acc;
     }
@@ -488,7 +494,8 @@ __global__ void __launch_bounds__(kKsThreads) galois_sum_kernel(const u64 *__res
 
 // cahel-main/src/evaluate.cu:2412-2629 for a batch of size-2 ciphertexts stored back to back:
 // one mod-up, per step a permuted inner product, two mod-downs
-int hoisting(Context *ctx, int L, int batch, u64 *ct, int n_steps, const int *elt_idx, const u64 *const *glks, cudaStream_t stream)
+int hoisting(Context *ctx, int L, int batch, u64 *ct, int n_steps, const int *elt_idx, const u64 *const *glks, cudaStream_t stream,
+             bool accumulate)
 {
     int rc = check_level(ctx, L);
     if (rc) return rc;
@@ -515,9 +522,11 @@ int hoisting(Context *ctx, int L, int batch, u64 *ct, int n_steps, const int *el
         const long cap = (long)ctx->sm_count * 16;
         if (blocks > cap) blocks = cap;
         count_launch("galois_sum_kernel", stream);
-        galois_sum_kernel<<<(int)blocks, kKsThreads, 0, stream>>>(ct_b, 2L * L, w.tmp, ctx->d_mc, args, hp.logN, L, total);
+        galois_sum_kernel<<<(int)blocks, kKsThreads, 0, stream>>>(ct_b, 2L * L, w.tmp, ctx->d_mc, args, hp.logN, L, total, accumulate ? 1 : 0);
         LB_CUDA(cudaGetLastError());
-        if ((rc = moddown_into(ctx, L, nb, 2, w.cx, w.pc, ct_b, Placement{2L * L, L}, w.tmp, Placement{L, L}, 1, stream))) return rc;
+        if ((rc = moddown_into(ctx, L, nb, 2, w.cx, w.pc, ct_b, Placement{2L * L, L}, w.tmp, Placement{L, L}, 1, stream,
+                               accumulate ? ct_b + poly : nullptr, 2L * L)))
+            return rc;
     }
     return LB_OK;
 }

@@ -48,6 +48,8 @@ struct NttK {
     const u64 *bconv_mat;
     long mat_group_stride, mat_row_stride;
     const u64 *aux, *scal, *scal_s, *add, *fold;
+    const u64 *add1; // addend rows of the groups with inner == 1, if they sit elsewhere (see NttJob::add1)
+    long add1_outer;
     const u64 *mul2; // forward epilogue: two products per row (see NttJob::mul2)
     const u64 *presub, *presub_scal, *presub_scal_s;
     const signed char *esmall;
@@ -350,6 +352,7 @@ LB_D bool fwd_row_setup(const NttK &a, const int row, FwdRow &r)
     FwdEpi &epi = r.epi;
     epi.aux = a.aux ? a.aux + (((size_t)go * a.aux_outer + (size_t)gi * a.aux_group_stride + rr) << logN) : nullptr;
     epi.add = (a.add && gi < a.add_inner) ? a.add + (((size_t)go * a.add_outer + (size_t)gi * a.add_group_stride + rr) << logN) : nullptr;
+    if (a.add1 && gi == 1) epi.add = a.add1 + (((size_t)go * a.add1_outer + rr) << logN);
     epi.scal = a.aux ? a.scal[rr] : 0;
     epi.scal_s = a.aux ? a.scal_s[rr] : 0;
     epi.mul0 = a.mul2 ? a.mul2 + ((size_t)rr << logN) : nullptr;
@@ -1090,6 +1093,8 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     k.bconv_n = job.bconv_n;
     k.digit_alpha = job.digit_alpha;
     k.add_inner = job.add_inner;
+    k.add1 = job.add1;
+    k.add1_outer = job.add1_outer;
     k.bconv_mat = job.bconv_mat;
     k.mat_group_stride = job.mat_group_stride;
     k.mat_row_stride = job.mat_row_stride;
@@ -1130,6 +1135,7 @@ static int run(Context *ctx, const NttJob &job, bool forward, cudaStream_t strea
     const double outer = (double)job.n_groups / k.split;
     if (job.aux) bytes += out_rows * limb;
     if (job.add) bytes += outer * (job.add_inner < k.split ? job.add_inner : k.split) * live * limb;
+    if (job.add1) bytes += outer * live * limb;
     if (job.presub) bytes += outer * (k.presub_inner < k.split ? k.presub_inner : k.split) * live * limb;
     if (job.esmall) bytes += outer * (double)hp.N;
     if (job.mul2) bytes += out_rows * limb + 2.0 * job.per_group * limb; // a second output row per row, the two fixed rows once

@@ -132,6 +132,20 @@ __global__ void __launch_bounds__(kPolyThreads) galois_kernel(const u64 *__restr
     }
 }
 
+// ciphertexts [batch][2][L][N]: dst = image of src under the automorphism, the first polynomial plus itself
+__global__ void __launch_bounds__(kPolyThreads) galois_plus_c0_kernel(const u64 *__restrict__ src, u64 *__restrict__ dst,
+                                                                      const uint32_t *__restrict__ perm, const ModConst *__restrict__ mc,
+                                                                      const int logN, const int L, const long total)
+{
+    const long n_mask = (1L << logN) - 1;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long row = i >> logN;
+        const int r = (int)(row % (2 * L));
+        const u64 v = src[(row << logN) + perm[i & n_mask]];
+        dst[i] = r < L ? add_mod(v, src[i], mc[r].q) : v;
+    }
+}
+
 // out[g] = sum of the items in[idx] listed for group g (the reference's add_many over a chosen subset):
 // items are n_rows limbs each, row r uses prime r % size_l; lists in CSR form on the device
 __global__ void __launch_bounds__(kPolyThreads) sum_groups_kernel(const ulonglong2 *__restrict__ in, ulonglong2 *__restrict__ out,
@@ -185,6 +199,20 @@ int poly_galois(Context *ctx, int elt_idx, long rows, const u64 *src, u64 *dst, 
     count_launch("galois_kernel", stream);
     galois_kernel<<<grid_for(ctx, total, kPolyThreads), kPolyThreads, 0, stream>>>(
         src, dst, ctx->d_perm + ((size_t)elt_idx << ctx->hp.logN), ctx->hp.logN, total);
+    LB_CUDA(cudaGetLastError());
+    return LB_OK;
+}
+
+int poly_galois_plus_c0(Context *ctx, int elt_idx, int L, int batch, const u64 *src, u64 *dst, cudaStream_t stream)
+{
+    if (elt_idx < 0 || elt_idx >= (int)ctx->hp.galois_elts.size()) {
+        set_error("Galois key not present");
+        return LB_ERR_LOGIC;
+    }
+    const long total = ((long)batch * 2 * L) << ctx->hp.logN;
+    count_launch("galois_kernel", stream);
+    galois_plus_c0_kernel<<<grid_for(ctx, total, kPolyThreads), kPolyThreads, 0, stream>>>(
+        src, dst, ctx->d_perm + ((size_t)elt_idx << ctx->hp.logN), ctx->d_mc, ctx->hp.logN, L, total);
     LB_CUDA(cudaGetLastError());
     return LB_OK;
 }
