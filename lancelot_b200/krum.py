@@ -751,18 +751,17 @@ class EncryptedKrum:
         del acc
         if keep is not None:
             keep["scores"], keep["my_pairs"] = scores, mine
+        # every rank adds the scores of its own pairs into per-client sums (a client's sum is the sum over its pairs, so
+        # it splits over the ranks like the pairs do); the partial sums, residues below 2^60 from at most eight
+        # ranks, are added as 64-bit words on rank 0 and reduced once: 42 MB per rank instead of a gather of all scores
+        sums = self.client_sums(scores, mine, n_clients) if mine else self.lb.empty(n_clients, 2, 2, self.N).zero_()
         if world_size > 1:
-            send = scores
-            if len(mine) < block:
-                send = torch.zeros((block,) + tuple(scores.shape[1:]), dtype=scores.dtype, device=scores.device)
-                send[: len(mine)] = scores
-            recv = torch.empty((block * world_size,) + tuple(scores.shape[1:]), dtype=scores.dtype, device=scores.device)
-            dist.all_gather_into_tensor(recv.view(-1), send.contiguous().view(-1), group=group)
-            scores = recv[: len(pairs)]
+            dist.reduce(sums, dst=0 if group is None else dist.get_global_rank(group, 0), op=dist.ReduceOp.SUM, group=group)
+            if rank == 0:
+                self.lb.reduce_mod(2, sums)
         mark("gather_s")
         if rank != 0:
             return None, None
-        sums = self.client_sums(scores, pairs, n_clients)
         out = self.select(sums)
         mark("sum_decrypt_s")
         return out
