@@ -384,7 +384,7 @@ class NttWorkload:
         """arithmetic ceiling of the transform: the register-only butterfly rate converted to transform traffic"""
         per_limb = (self.N // 2) * self.logn
         to_gbs = lambda rate: rate / per_limb * 16 * self.N / 1e9
-        names = ["int_strict", "int_lazy", "fp64_assisted", "fp64"]
+        names = ["int_strict", "int_lazy", "fp64_50bit", "fp64_40bit"]
         out = {n: to_gbs(self.ctx.butterfly_rate(i)) for i, n in enumerate(names)}
         out["this_workload"] = to_gbs(self.ctx.butterfly_rate())  # the variant this workload's primes take
         return out

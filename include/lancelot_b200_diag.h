@@ -26,8 +26,9 @@ LB_API int lb_diag_kernel_report(char *buf, size_t capacity);
 /* Measures the register-only rate of one of the transform's butterfly variants on this GPU (butterflies per
  * second, synchronous, a few milliseconds): the arithmetic ceiling of any NTT schedule for primes of that size.
  * variant: 0 integer Shoup product with conditional subtraction (primes of 58 bits and more), 1 the same without
- * it (below 2^58), 2 quotient estimated on the FP64 pipe, the rest on the integer pipes (primes of [2^47, 2^50)),
- * 3 the whole butterfly on the FP64 pipe (primes below 2^47), -1 the variant the context's first prime takes.  One limb needs (N/2) log2 N butterflies for
+ * it (below 2^58), 2 the whole butterfly on the FP64 pipe with one centred reduction per element and pass (primes of
+ * [2^47, 2^50)), 3 the same at a 40-bit prime (primes below 2^47; the transform kernels skip most of those
+ * reductions there), -1 the variant the context's first prime takes.  One limb needs (N/2) log2 N butterflies for
  * its 16 N bytes. */
 LB_API int lb_probe_butterfly_rate(lb_context *ctx, int variant, double *butterflies_per_second);
 

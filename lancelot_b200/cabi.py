@@ -101,7 +101,7 @@ class Context:
         return out
 
     def butterfly_rate(self, variant=-1):
-        """register-only butterfly rate; variant 0..3 (integer strict / lazy, FP64-assisted strict / lazy), -1: the first prime's"""
+        """register-only butterfly rate; variant 0..3 (integer strict / lazy, FP64 pipe at a 50-bit / 40-bit prime), -1: the first prime's"""
         out = C.c_double()
         check(lib.lb_probe_butterfly_rate(self.h, int(variant), C.byref(out)))
         return float(out.value)

@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(kNttThreads, kNttMinBlocks) butterfly_probe_ke
     u64 v[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = (u64)threadIdx.x * 8 + i + blockIdx.x;
-    if (MODE == kF64) {
+    if (is_f64_mode(MODE)) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = bits_of(f64_from_u52(v[i]));
     }
@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(kNttThreads, kNttMinBlocks) butterfly_probe_ke
 #pragma unroll
             for (int b = 0; b < (1 << s); ++b) {
                 // twiddles that differ per thread and stage, so that nothing is hoisted out of the loop
-                const ulonglong2 w = MODE == kF64 ? make_ulonglong2(bits_of(f64_of(w0) + (double)(threadIdx.x + b)), bits_of(f64_of(ws0) * (double)(1 + s)))
+                const ulonglong2 w = is_f64_mode(MODE) ? make_ulonglong2(bits_of(f64_of(w0) + (double)(threadIdx.x + b)), bits_of(f64_of(ws0) * (double)(1 + s)))
                                                   : make_ulonglong2(w0 + threadIdx.x + b, ws0 + threadIdx.x + s);
 #pragma unroll
                 for (int i = 0; i < half; ++i) fwd_bf<MODE>(v[b * 2 * half + i], v[b * 2 * half + i + half], w, q1, q2);
@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(kNttThreads, kNttMinBlocks) butterfly_probe_ke
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] &= 0x03FFFFFFFFFFFFFFull;
         }
-        if (MODE == kF64) {
+        if (is_f64_mode(MODE)) { // one centred reduction per element and radix-8 pass: what the tight variant does
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] = bits_of(f64_centre(f64_of(v[i]), f64_of(q1), f64_of(q2)));
         }
@@ -104,13 +104,13 @@ __global__ void __launch_bounds__(kNttThreads, kNttMinBlocks) butterfly_probe_ke
     out[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = acc;
 }
 
-// mode: 0 integer strict, 1 integer lazy, 2 FP64-assisted (quotient on the FP64 pipe), 3 all on the FP64 pipe,
+// mode: 0 integer strict, 1 integer lazy, 2 all on the FP64 pipe at a 50-bit prime, 3 all on the FP64 pipe at a 40-bit prime,
 // -1 the variant the context's first prime takes.
 int probe_butterfly_rate(Context *ctx, int mode, double *butterflies_per_second)
 {
     if (mode < 0) {
         const u64 q0 = ctx->hp.q[0];
-        mode = q0 < kF64PrimeLimit ? kF64 : q0 < kFpPrimeLimit ? kFpStrict : (q0 >> 58) == 0 ? kIntLazy : kIntStrict;
+        mode = q0 < kF64PrimeLimit ? kF64 : q0 < kFpPrimeLimit ? kF64Tight : (q0 >> 58) == 0 ? kIntLazy : kIntStrict;
     }
     if (mode > kF64) {
         set_error("butterfly variant must be 0..3 or -1");
@@ -121,7 +121,7 @@ int probe_butterfly_rate(Context *ctx, int mode, double *butterflies_per_second)
     if (rc) return rc;
     u64 *out = reinterpret_cast<u64 *>(ctx->ws);
     // any odd modulus of the variant's size gives the variant's instruction stream
-    static const u64 size_of_mode[4] = {(u64(1) << 60) - 93, (u64(1) << 50) - 27, (u64(1) << 49) - 69, (u64(1) << 40) - 87};
+    static const u64 size_of_mode[4] = {(u64(1) << 60) - 93, (u64(1) << 57) - 13, (u64(1) << 50) - 27, (u64(1) << 40) - 87};
     const u64 q = size_of_mode[mode], w = h_twiddle_value(q / 3, q), ws = h_twiddle_quot(q / 3, q);
     cudaEvent_t e0, e1;
     LB_CUDA(cudaEventCreate(&e0));
@@ -133,7 +133,7 @@ int probe_butterfly_rate(Context *ctx, int mode, double *butterflies_per_second)
         switch (mode) {
         case kIntStrict: butterfly_probe_kernel<kIntStrict><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
         case kIntLazy: butterfly_probe_kernel<kIntLazy><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
-        case kFpStrict: butterfly_probe_kernel<kFpStrict><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
+        case kF64Tight: butterfly_probe_kernel<kF64Tight><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
         default: butterfly_probe_kernel<kF64><<<blocks, kNttThreads>>>(out, q, w, ws, iters); break;
         }
         LB_CUDA(cudaEventRecord(e1, 0));

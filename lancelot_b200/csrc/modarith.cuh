@@ -87,25 +87,14 @@ inline u64 h_fp_quot(u64 w, u64 q)
     return h_bits_of((double)w / (double)q); // both exact in double, so the quotient is correctly rounded
 }
 // the two words of a twiddle-table entry for the power w of a root modulo prime q
-inline u64 h_twiddle_value(u64 w, u64 q) { return q < kF64PrimeLimit ? h_bits_of((double)w) : w; }
+// (primes below 2^50 run their butterflies on the FP64 pipe: the power as a double, and its quotient by q)
+inline u64 h_twiddle_value(u64 w, u64 q) { return q < kFpPrimeLimit ? h_bits_of((double)w) : w; }
 inline u64 h_twiddle_quot(u64 w, u64 q) { return q < kFpPrimeLimit ? h_fp_quot(w, q) : h_shoup(w, q); }
 
 #if defined(__CUDACC__)
 // ---- device arithmetic ----------------------------------------------------------------
 
-// x * w - Q * q with Q within one of x w / q, as a two's-complement value in (-q, q).
-// Needs x < 2^52, w < q < 2^50 and wq = bits of the double nearest to w / q.  Error budget:
-// x is exact in double; the rounding of w / q moves the product by less than 2^52 * 2^-53 =
-// 0.5; the fused multiply-add into 2^52 rounds once to an integer, another 0.5 at most.
-LB_D u64 fp_mul_signed(u64 x, u64 w, u64 wq, u64 q)
-{
-    const double xd = __longlong_as_double((long long)(x | 0x4330000000000000ull)) - 4503599627370496.0;
-    const double u = __fma_rn(xd, __longlong_as_double((long long)wq), 4503599627370496.0);
-    const u64 Q = (u64)__double_as_longlong(u) & 0x000FFFFFFFFFFFFFull;
-    return x * w - Q * q;
-}
-
-// ---- residues as integer-valued doubles (primes below 2^47) --------------------------------------
+// ---- residues as integer-valued doubles (primes below 2^50) --------------------------------------
 LB_D double f64_of(u64 bits) { return __longlong_as_double((long long)bits); }
 LB_D u64 bits_of(double d) { return (u64)__double_as_longlong(d); }
 // an integer below 2^52 as a double: its bits under the exponent of 2^52, minus 2^52

@@ -73,6 +73,10 @@ LB_D void fwd_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ tw, const un
 #pragma unroll
     for (int u = 0; u < S; ++u) {
         const int half = 1 << (S - 1 - u);
+        if (MODE == kF64Tight && u == 3) { // three stages since the values were centred: centre them again
+#pragma unroll
+            for (int i = 0; i < (1 << S); ++i) v[i] = bits_of(f64_centre(f64_of(v[i]), f64_of(q), f64_of(q2)));
+        }
 #pragma unroll
         for (int b = 0; b < (1 << u); ++b) {
             const ulonglong2 w = __ldg(tw + ((t0 << u) + b));
@@ -93,13 +97,17 @@ LB_D void inv_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ itw, const u
 #pragma unroll
     for (int u = 0; u < S; ++u) {
         const int dist = 1 << u;
+        if (IM == kInvF64Tight && u > 0 && (u & 1) == 0) { // two stages since the values were centred
+#pragma unroll
+            for (int i = 0; i < (1 << S); ++i) v[i] = bits_of(f64_centre(f64_of(v[i]), f64_of(q), f64_of(q2)));
+        }
 #pragma unroll
         for (int b = 0; b < (1 << (S - 1 - u)); ++b) {
             if (CLOSE && u == S - 1) {
 #pragma unroll
                 for (int i = 0; i < dist; ++i) {
                     u64 &x = v[b * 2 * dist + i], &y = v[b * 2 * dist + i + dist];
-                    if (IM == kInvF64) {
+                    if (is_inv_f64(IM)) {
                         const double xd = f64_of(x), yd = f64_of(y), qd = f64_of(q), qi = f64_of(q2);
                         x = f64_canon(f64_mulmod(__dadd_rn(xd, yd), f64_of(cn), f64_of(cns), qd), qd, qi);
                         y = f64_canon(f64_mulmod(__dadd_rn(xd, -yd), f64_of(cw), f64_of(cws), qd), qd, qi);
@@ -237,7 +245,7 @@ LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, 
         if (from_global) {
 #pragma unroll
             for (int i = 0; i < R; ++i) v[i] = load_in(in, base + (i << logst));
-            if (MODE == kF64) {
+            if (is_f64_mode(MODE)) {
 #pragma unroll
                 for (int i = 0; i < R; ++i) v[i] = bits_of(f64_from_u52(v[i]));
             }
@@ -245,10 +253,14 @@ LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, 
 #pragma unroll
             for (int i = 0; i < R; ++i) v[i] = sm[sidx(base + (i << logst))];
         }
+        if (MODE == kF64Tight) {
+#pragma unroll
+            for (int i = 0; i < R; ++i) v[i] = bits_of(f64_centre(f64_of(v[i]), f64_of(q), f64_of(q2)));
+        }
         fwd_core<S, MODE>(v, tw, (cc << logm0) + hi, q, q2);
         if (gdst) { // closing pass: logst == 0, the 2^S results are contiguous
             const u64 qi = in.q; // the prime as an integer (q, q2 are the butterflies' scalars)
-            if (MODE == kF64) {
+            if (is_f64_mode(MODE)) {
 #pragma unroll
                 for (int i = 0; i < R; ++i) v[i] = f64_canon(f64_of(v[i]), f64_of(q), f64_of(q2));
             } else if (MODE == kIntLazy) {
@@ -376,7 +388,7 @@ __global__ void __launch_bounds__(kNttThreads, kNttMinBlocks) ntt_fwd_kernel(con
     const ulonglong2 *tw = fr.tw;
     const int mode = fr.mode;
     // the butterflies' two scalars: (q, 2q), or (double(q), double(1 / q)) when they run on the FP64 pipe
-    const u64 q = mode == kF64 ? bf_scalar_q<kF64>(fr.q) : fr.q, q2 = mode == kF64 ? bf_scalar_q2<kF64>(fr.q) : fr.q << 1;
+    const u64 q = is_f64_mode(mode) ? bf_scalar_q<kF64>(fr.q) : fr.q, q2 = is_f64_mode(mode) ? bf_scalar_q2<kF64>(fr.q) : fr.q << 1;
     const int logn_loc = a.logN - LOGC, n_loc = 1 << logn_loc;
 
     unsigned c = 0;
@@ -395,13 +407,17 @@ __global__ void __launch_bounds__(kNttThreads, kNttMinBlocks) ntt_fwd_kernel(con
             u64 v[C];
 #pragma unroll
             for (int k = 0; k < C; ++k) v[k] = load_in(in, j + k * n_loc);
-            if (mode == kF64) {
+            if (is_f64_mode(mode)) {
 #pragma unroll
                 for (int k = 0; k < C; ++k) v[k] = bits_of(f64_from_u52(v[k]));
             }
+            if (mode == kF64Tight) {
+#pragma unroll
+                for (int k = 0; k < C; ++k) v[k] = bits_of(f64_centre(f64_of(v[k]), f64_of(q), f64_of(q2)));
+            }
             switch (mode) {
             case kF64: fwd_core<LOGC, kF64>(v, tw, 1u, q, q2); break;
-            case kFpStrict: fwd_core<LOGC, kFpStrict>(v, tw, 1u, q, q2); break;
+            case kF64Tight: fwd_core<LOGC, kF64Tight>(v, tw, 1u, q, q2); break;
             case kIntLazy: fwd_core<LOGC, kIntLazy>(v, tw, 1u, q, q2); break;
             default: fwd_core<LOGC, kIntStrict>(v, tw, 1u, q, q2); break;
             }
@@ -428,7 +444,7 @@ __global__ void __launch_bounds__(kNttThreads, kNttMinBlocks) ntt_fwd_kernel(con
         const int wlog = p < a.nwide ? -1 : a.wlog;
         switch (mode) {
         case kF64: fwd_pass_any<kF64>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
-        case kFpStrict: fwd_pass_any<kFpStrict>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
+        case kF64Tight: fwd_pass_any<kF64Tight>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
         case kIntLazy: fwd_pass_any<kIntLazy>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
         default: fwd_pass_any<kIntStrict>(S, sm, from_global, gdst, in, logn_loc, logt, cc, tw, q, q2, epi, wlog); break;
         }
@@ -481,17 +497,17 @@ LB_D void inv_pass(u64 *sm, const u64 *gsrc, u64 *gdst, const int logn_loc, cons
         u64 v[R];
         if (gsrc) { // opening pass: logst == 0, contiguous
             load_contig<R>(v, gsrc + base);
-            if (IM == kInvF64) {
+            if (is_inv_f64(IM)) {
 #pragma unroll
                 for (int i = 0; i < R; ++i) v[i] = bits_of(f64_from_u52(v[i]));
             }
         } else {
 #pragma unroll
             for (int i = 0; i < R; ++i) v[i] = sm[sidx(base + (i << logst))];
-            if (IM == kInvF64 && reduce) {
+        }
+        if ((IM == kInvF64 && reduce && !gsrc) || IM == kInvF64Tight) {
 #pragma unroll
-                for (int i = 0; i < R; ++i) v[i] = bits_of(f64_centre(f64_of(v[i]), f64_of(q), f64_of(q2)));
-            }
+            for (int i = 0; i < R; ++i) v[i] = bits_of(f64_centre(f64_of(v[i]), f64_of(q), f64_of(q2)));
         }
         inv_core<S, CLOSE, IM>(v, itw, (cc << logm0) + (hi << (S - 1)), q, q2, cn, cns, cw, cws);
         if (gdst) {
@@ -522,7 +538,7 @@ struct InvConst {
 LB_D InvConst inv_constants(const int im, const u64 q, const u64 cn, const u64 cns, const u64 cw, const u64 cws)
 {
     InvConst k;
-    if (im == kInvF64) {
+    if (is_inv_f64(im)) {
         const double qd = (double)q;
         k.q = bits_of(qd);
         k.q2 = bits_of(1.0 / qd);
@@ -578,9 +594,9 @@ __global__ void __launch_bounds__(kNttThreads, kNttMinBlocks) ntt_inv_kernel(con
         if (im == kInvF64) {
             if (closing) inv_pass_any<true, kInvF64>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, ic.q, ic.q2, ic.cn, ic.cns, ic.cw, ic.cws, wlog, red);
             else inv_pass_any<false, kInvF64>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, ic.q, ic.q2, ic.cn, ic.cns, ic.cw, ic.cws, wlog, red);
-        } else if (im == kInvFp) {
-            if (closing) inv_pass_any<true, kInvFp>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, false);
-            else inv_pass_any<false, kInvFp>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, false);
+        } else if (im == kInvF64Tight) {
+            if (closing) inv_pass_any<true, kInvF64Tight>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, ic.q, ic.q2, ic.cn, ic.cns, ic.cw, ic.cws, wlog, true);
+            else inv_pass_any<false, kInvF64Tight>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, ic.q, ic.q2, ic.cn, ic.cns, ic.cw, ic.cws, wlog, true);
         } else {
             if (closing) inv_pass_any<true, kInvInt>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, false);
             else inv_pass_any<false, kInvInt>(S, sm, gsrc, gdst, logn_loc, logt, cc, itw, q, q2, cn, cns, cw, cws, wlog, false);
@@ -606,8 +622,10 @@ __global__ void __launch_bounds__(kNttThreads, kNttMinBlocks) ntt_inv_kernel(con
                     for (int kk = 0; kk < C; ++kk) v[kk] = bits_of(f64_centre(f64_of(v[kk]), f64_of(ic.q), f64_of(ic.q2)));
                 }
                 inv_core<LOGC, true, kInvF64>(v, itw, C / 2, ic.q, ic.q2, ic.cn, ic.cns, ic.cw, ic.cws);
-            } else if (im == kInvFp) {
-                inv_core<LOGC, true, kInvFp>(v, itw, C / 2, q, q2, cn, cns, cw, cws);
+            } else if (im == kInvF64Tight) {
+#pragma unroll
+                for (int kk = 0; kk < C; ++kk) v[kk] = bits_of(f64_centre(f64_of(v[kk]), f64_of(ic.q), f64_of(ic.q2)));
+                inv_core<LOGC, true, kInvF64Tight>(v, itw, C / 2, ic.q, ic.q2, ic.cn, ic.cns, ic.cw, ic.cws);
             } else {
                 inv_core<LOGC, true, kInvInt>(v, itw, C / 2, q, q2, cn, cns, cw, cws);
             }
@@ -737,9 +755,13 @@ LB_D void fwd_first_fixed(u64 *sm, const FwdIn &in, const unsigned c, const ulon
 #pragma unroll
             for (int k = 0; k < R0; ++k) v[k] = load_in(in, j + k * kHalfLoc);
         }
-        if (MODE == kF64) {
+        if (is_f64_mode(MODE)) {
 #pragma unroll
             for (int k = 0; k < R0; ++k) v[k] = bits_of(f64_from_u52(v[k]));
+        }
+        if (MODE == kF64Tight) {
+#pragma unroll
+            for (int k = 0; k < R0; ++k) v[k] = bits_of(f64_centre(f64_of(v[k]), f64_of(bq), f64_of(bq2)));
         }
         fwd_core<F, MODE>(v, tw, 1u, bq, bq2);
         const int s0 = sidx(j);
@@ -777,9 +799,13 @@ LB_D void fwd_pass_fixed(u64 *sm, u64 *gdst, const unsigned cc, const ulonglong2
         if (CLOSING && !PLAIN && epi.aux) load_contig<8>(t, epi.aux + base); // in flight during the butterflies
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = p[pad_off<LOGST>(i)];
+        if (MODE == kF64Tight) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = bits_of(f64_centre(f64_of(v[i]), f64_of(q), f64_of(q2)));
+        }
         fwd_core<3, MODE>(v, tw, (cc << (12 - LOGT)) + hi, q, q2);
         if constexpr (CLOSING) {
-            if (MODE == kF64) {
+            if (is_f64_mode(MODE)) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] = f64_canon(f64_of(v[i]), f64_of(q), f64_of(q2));
             } else if (MODE == kIntLazy) {
@@ -850,7 +876,7 @@ __global__ void __launch_bounds__(256, kNttMinBlocks) ntt_fwd_fixed_kernel(const
     }
     switch (fr.mode) {
     case kF64: fwd_body_fixed<LOGC, kF64, PLAIN>(sm, fr, c); break;
-    case kFpStrict: fwd_body_fixed<LOGC, kFpStrict, PLAIN>(sm, fr, c); break;
+    case kF64Tight: fwd_body_fixed<LOGC, kF64Tight, PLAIN>(sm, fr, c); break;
     case kIntLazy: fwd_body_fixed<LOGC, kIntLazy, PLAIN>(sm, fr, c); break;
     default: fwd_body_fixed<LOGC, kIntStrict, PLAIN>(sm, fr, c); break;
     }
@@ -869,17 +895,17 @@ LB_D void inv_pass_fixed(u64 *sm, const u64 *gsrc, const unsigned cc, const ulon
         u64 v[8];
         if constexpr (OPENING) {
             load_contig<8>(v, gsrc + base);
-            if (IM == kInvF64) {
+            if (is_inv_f64(IM)) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] = bits_of(f64_from_u52(v[i]));
             }
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] = p[pad_off<LOGT>(i)];
-            if (IM == kInvF64 && reduce) {
+        }
+        if ((IM == kInvF64 && reduce && !OPENING) || IM == kInvF64Tight) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = bits_of(f64_centre(f64_of(v[i]), f64_of(q), f64_of(q2)));
-            }
+            for (int i = 0; i < 8; ++i) v[i] = bits_of(f64_centre(f64_of(v[i]), f64_of(q), f64_of(q2)));
         }
         inv_core<3, false, IM>(v, itw, (cc << (12 - LOGT)) + (hi << 2), q, q2, 0, 0, 0, 0);
 #pragma unroll
@@ -908,7 +934,7 @@ LB_D void inv_last_fixed(u64 *sm, u64 *dst, const unsigned c, const ulonglong2 *
                 v[2 * r + 1] = ld_cluster(ra + 8u * kHalfLocPad);
             }
         }
-        if (IM == kInvF64 && reduce) {
+        if ((IM == kInvF64 && reduce) || IM == kInvF64Tight) {
 #pragma unroll
             for (int k = 0; k < R0; ++k) v[k] = bits_of(f64_centre(f64_of(v[k]), f64_of(q), f64_of(q2)));
         }
@@ -963,7 +989,7 @@ __global__ void __launch_bounds__(256, kNttMinBlocks) ntt_inv_fixed_kernel(const
     unsigned c = 0;
     if constexpr (LOGC > 0) c = cg::this_cluster().block_rank();
     if (mc.q < kF64PrimeLimit) inv_body_fixed<LOGC, kInvF64>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
-    else if (mc.q < kFpPrimeLimit) inv_body_fixed<LOGC, kInvFp>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
+    else if (mc.q < kFpPrimeLimit) inv_body_fixed<LOGC, kInvF64Tight>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
     else inv_body_fixed<LOGC, kInvInt>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
 }
 

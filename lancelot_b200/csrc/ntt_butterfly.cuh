@@ -10,62 +10,63 @@ namespace lb {
 //   integer, lazy:   the prime is below 2^58, so x may grow by 2q per stage over all seventeen
 //                    possible stages (bound 35q < 2^64) and the per-butterfly conditional
 //                    subtraction is dropped; the closing pass reduces once;
-//   FP64-assisted:   primes of [2^47, 2^50), quotient estimated on the FP64 pipe (fp_mul_signed),
-//                    which takes the 64 x 64 -> 128 bit product off the integer multiplier;
 //   FP64:            primes below 2^47, the whole butterfly on the FP64 pipe (f64_mulmod): eight
 //                    double-precision operations and nothing on the integer pipes.  The 64-bit
 //                    words then hold the bit patterns of integer-valued doubles; in this mode the
-//                    scalars q and q2 of the butterfly functions carry double(q) and double(1 / q).
+//                    scalars q and q2 of the butterfly functions carry double(q) and double(1 / q);
+//   FP64, tight:     the same butterflies for primes of [2^47, 2^50).  The multiplicand of a butterfly
+//                    must stay below 2^51 (hardly more than 2q here) and a value grows by up to 0.75 q
+//                    per stage, so every element is brought back to the residue nearest zero when a
+//                    pass loads it (|v| <= q / 2, at most 2q before the third stage) and once more
+//                    inside a pass of four stages.
 // Every variant leaves the same canonical residues in memory.
-enum { kIntStrict = 0, kIntLazy = 1, kFpStrict = 2, kF64 = 3 };
+enum { kIntStrict = 0, kIntLazy = 1, kF64Tight = 2, kF64 = 3 };
+LB_D constexpr bool is_f64_mode(const int mode) { return mode == kF64 || mode == kF64Tight; }
 
 LB_D int butterfly_mode(const u64 q)
 {
     if (q < kF64PrimeLimit) return kF64;
-    if (q < kFpPrimeLimit) return kFpStrict;
+    if (q < kFpPrimeLimit) return kF64Tight;
     return (q >> 58) == 0 ? kIntLazy : kIntStrict;
 }
 
 // the two scalars the butterflies of a mode take: (q, 2q), or (double(q), double(1 / q)) as bit patterns
 template <int MODE>
-LB_D u64 bf_scalar_q(const u64 q) { return MODE == kF64 ? bits_of((double)q) : q; }
+LB_D u64 bf_scalar_q(const u64 q) { return is_f64_mode(MODE) ? bits_of((double)q) : q; }
 template <int MODE>
-LB_D u64 bf_scalar_q2(const u64 q) { return MODE == kF64 ? bits_of(1.0 / (double)q) : q << 1; }
+LB_D u64 bf_scalar_q2(const u64 q) { return is_f64_mode(MODE) ? bits_of(1.0 / (double)q) : q << 1; }
 
 template <int MODE>
 LB_D void fwd_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
 {
-    if (MODE == kF64) {
+    if (is_f64_mode(MODE)) {
         const double xd = f64_of(x), r = f64_mulmod(f64_of(y), f64_of(w.x), f64_of(w.y), f64_of(q));
         y = bits_of(__dadd_rn(xd, -r));
         x = bits_of(__dadd_rn(xd, r));
         return;
     }
-    if (MODE == kIntStrict || MODE == kFpStrict) x = csub(x, q2);
-    if (MODE == kFpStrict) {
-        const u64 r = fp_mul_signed(y, w.x, w.y, q), xq = x + q; // r in (-q, q)
-        y = xq - r;
-        x = xq + r;
-    } else {
-        const u64 t = shoup_lazy(y, w.x, w.y, q);
-        y = x + q2 - t;
-        x = x + t;
-    }
+    if (MODE == kIntStrict) x = csub(x, q2);
+    const u64 t = shoup_lazy(y, w.x, w.y, q);
+    y = x + q2 - t;
+    x = x + t;
 }
 
-// inverse butterfly kinds: the integer Shoup product, the FP64-assisted one, all on the FP64 pipe
-enum { kInvInt = 0, kInvFp = 1, kInvF64 = 2 };
+// inverse butterfly kinds: the integer Shoup product, or all on the FP64 pipe
+// kInvF64Tight: kInvF64 for primes of [2^47, 2^50): the sums double per stage and the difference that is multiplied
+// must stay below 2^51, so the values are centred when a pass loads them and again after every second stage
+enum { kInvInt = 0, kInvF64Tight = 1, kInvF64 = 2 };
+LB_D constexpr bool is_inv_f64(const int im) { return im == kInvF64 || im == kInvF64Tight; }
 
-LB_D int inverse_mode(const u64 q) { return q < kF64PrimeLimit ? kInvF64 : q < kFpPrimeLimit ? kInvFp : kInvInt; }
+LB_D int inverse_mode(const u64 q) { return q < kF64PrimeLimit ? kInvF64 : q < kFpPrimeLimit ? kInvF64Tight : kInvInt; }
 template <int IM>
-LB_D u64 inv_scalar_q(const u64 q) { return IM == kInvF64 ? bits_of((double)q) : q; }
+LB_D u64 inv_scalar_q(const u64 q) { return is_inv_f64(IM) ? bits_of((double)q) : q; }
 template <int IM>
-LB_D u64 inv_scalar_q2(const u64 q) { return IM == kInvF64 ? bits_of(1.0 / (double)q) : q << 1; }
+LB_D u64 inv_scalar_q2(const u64 q) { return is_inv_f64(IM) ? bits_of(1.0 / (double)q) : q << 1; }
 
 template <int IM>
 LB_D void inv_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
 {
-    if (IM == kInvF64) {
+    if (is_inv_f64(IM)) {
         // the sum doubles its magnitude per stage: the passes reduce where 2^51 comes into reach
         const double xd = f64_of(x), yd = f64_of(y);
         x = bits_of(__dadd_rn(xd, yd));
@@ -75,7 +76,7 @@ LB_D void inv_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
     const u64 s = csub(x + y, q2);
     const u64 d = x + q2 - y; // below 4q
     x = s;
-    y = IM == kInvFp ? fp_mul_signed(d, w.x, w.y, q) + q : shoup_lazy(d, w.x, w.y, q);
+    y = shoup_lazy(d, w.x, w.y, q);
 }
 
 } // namespace lb
