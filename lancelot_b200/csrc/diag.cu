@@ -110,7 +110,7 @@ int probe_butterfly_rate(Context *ctx, int mode, double *butterflies_per_second)
 {
     if (mode < 0) {
         const u64 q0 = ctx->hp.q[0];
-        mode = q0 < kF64PrimeLimit ? kF64 : q0 < kFpPrimeLimit ? kF64Tight : (q0 >> 58) == 0 ? kIntLazy : kIntStrict;
+        mode = q0 < kF64PrimeLimit ? kF64 : q0 < kF64TightPrimeLimit ? kF64Tight : (q0 >> 58) == 0 ? kIntLazy : kIntStrict;
     }
     if (mode > kF64) {
         set_error("butterfly variant must be 0..3 or -1");

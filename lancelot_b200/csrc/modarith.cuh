@@ -65,14 +65,12 @@ inline u64 h_shoup(u64 w, u64 q) { return (u64)(((u128)w << 64) / q); }
 #endif
 
 // ---- the FP64 pipe in the transform kernels -----------------------------------------------------
-// Primes of [2^47, 2^50): the quotient floor(x w / q) is estimated with one double-precision fused
-// multiply-add instead of a 64 x 64 -> 128 bit integer product; the integer multiplier then only has
-// to produce the two low products x w and Q q.  Their twiddle entries are (w, double(w / q)).
-// Primes below 2^47: the whole butterfly runs on the FP64 pipe.  Residues travel through the
+// Primes below 2^50: the whole butterfly runs on the FP64 pipe.  Residues travel through the
 // transform as integer-valued doubles (their bit patterns sit in the same 64-bit words), products
-// are formed error-free with fused multiply-adds, and values may grow over all stages without a
-// reduction (13 q < 2^51).  Their twiddle entries are (double(w), double(w / q)).
-constexpr u64 kFpPrimeLimit = u64(1) << 50; // operands stay below 4q <= 2^52, the exact-integer range of the estimate
+// are formed error-free with fused multiply-adds.  Below 2^47 values may grow over all forward stages
+// without a reduction (13 q < 2^51); from 2^47 up they are centred once per pass (ntt_butterfly.cuh).
+// Their twiddle entries are (double(w), double(w / q)).
+constexpr u64 kF64TightPrimeLimit = u64(1) << 50; // below it the butterflies run on the FP64 pipe: 2q stays below 2^51
 constexpr u64 kF64PrimeLimit = u64(1) << 47;
 
 inline u64 h_bits_of(double d)
@@ -88,8 +86,8 @@ inline u64 h_fp_quot(u64 w, u64 q)
 }
 // the two words of a twiddle-table entry for the power w of a root modulo prime q
 // (primes below 2^50 run their butterflies on the FP64 pipe: the power as a double, and its quotient by q)
-inline u64 h_twiddle_value(u64 w, u64 q) { return q < kFpPrimeLimit ? h_bits_of((double)w) : w; }
-inline u64 h_twiddle_quot(u64 w, u64 q) { return q < kFpPrimeLimit ? h_fp_quot(w, q) : h_shoup(w, q); }
+inline u64 h_twiddle_value(u64 w, u64 q) { return q < kF64TightPrimeLimit ? h_bits_of((double)w) : w; }
+inline u64 h_twiddle_quot(u64 w, u64 q) { return q < kF64TightPrimeLimit ? h_fp_quot(w, q) : h_shoup(w, q); }
 
 #if defined(__CUDACC__)
 // ---- device arithmetic ----------------------------------------------------------------

@@ -989,7 +989,7 @@ __global__ void __launch_bounds__(256, kNttMinBlocks) ntt_inv_fixed_kernel(const
     unsigned c = 0;
     if constexpr (LOGC > 0) c = cg::this_cluster().block_rank();
     if (mc.q < kF64PrimeLimit) inv_body_fixed<LOGC, kInvF64>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
-    else if (mc.q < kFpPrimeLimit) inv_body_fixed<LOGC, kInvF64Tight>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
+    else if (mc.q < kF64TightPrimeLimit) inv_body_fixed<LOGC, kInvF64Tight>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
     else inv_body_fixed<LOGC, kInvInt>(sm, src, dst, c, itw, mc.q, cn, cns, cw, cws);
 }
 

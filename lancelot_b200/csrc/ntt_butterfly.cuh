@@ -26,7 +26,7 @@ LB_D constexpr bool is_f64_mode(const int mode) { return mode == kF64 || mode ==
 LB_D int butterfly_mode(const u64 q)
 {
     if (q < kF64PrimeLimit) return kF64;
-    if (q < kFpPrimeLimit) return kF64Tight;
+    if (q < kF64TightPrimeLimit) return kF64Tight;
     return (q >> 58) == 0 ? kIntLazy : kIntStrict;
 }
 
@@ -57,7 +57,7 @@ LB_D void fwd_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
 enum { kInvInt = 0, kInvF64Tight = 1, kInvF64 = 2 };
 LB_D constexpr bool is_inv_f64(const int im) { return im == kInvF64 || im == kInvF64Tight; }
 
-LB_D int inverse_mode(const u64 q) { return q < kF64PrimeLimit ? kInvF64 : q < kFpPrimeLimit ? kInvF64Tight : kInvInt; }
+LB_D int inverse_mode(const u64 q) { return q < kF64PrimeLimit ? kInvF64 : q < kF64TightPrimeLimit ? kInvF64Tight : kInvInt; }
 template <int IM>
 LB_D u64 inv_scalar_q(const u64 q) { return is_inv_f64(IM) ? bits_of((double)q) : q; }
 template <int IM>

@@ -292,22 +292,6 @@ int gen_switch_keys(Context *ctx, const u64 *sk, const u64 *targets, int n, cons
 
 // ---- public-key encryption (cahel-main/src/secretkey.cu:47-170) -----------------------------
 
-// cx[b][p][QP][N] = pk[p] * u[b]   (the error term joins inside the mod-down transform)
-// two coefficients per thread through 16-byte accesses; blockIdx.y is the ciphertext
-__global__ void __launch_bounds__(kSampThreads) encrypt_product_kernel(ulonglong2 *__restrict__ cx, const ulonglong2 *__restrict__ pk,
-                                                                       const ulonglong2 *__restrict__ u, const ModConst *__restrict__ mc,
-                                                                       const int log_half_n, const long half_poly, const int batch)
-{
-    for (long b = blockIdx.y; b < batch; b += gridDim.y) {
-        for (long k = (long)blockIdx.x * blockDim.x + threadIdx.x; k < half_poly; k += (long)gridDim.x * blockDim.x) {
-            const ModConst m = mc[(int)(k >> log_half_n)];
-            const ulonglong2 uu = u[b * half_poly + k], p0 = pk[k], p1 = pk[half_poly + k];
-            cx[2 * b * half_poly + k] = make_ulonglong2(mul_mod(uu.x, p0.x, m.q, m.r0, m.r1), mul_mod(uu.y, p0.y, m.q, m.r0, m.r1));
-            cx[(2 * b + 1) * half_poly + k] = make_ulonglong2(mul_mod(uu.x, p1.x, m.q, m.r0, m.r1), mul_mod(uu.y, p1.y, m.q, m.r0, m.r1));
-        }
-    }
-}
-
 // cx[b][p][QP][N] = pk[p] * u[b] + e[b]   (u and e already in NTT form; e0 == e1)
 __global__ void __launch_bounds__(kSampThreads) encrypt_combine_kernel(u64 *__restrict__ cx, const u64 *__restrict__ pk,
                                                                        const u64 *__restrict__ u, const u64 *__restrict__ e,
