@@ -133,6 +133,16 @@ LB_D u64 shoup_lazy(u64 x, u64 w, u64 ws, u64 q)
     return x * w - hi * q;
 }
 
+// The same with the high product formed from three 32 x 32 multiplications instead of four: the quotient comes out at
+// most two too small (the product of the low halves and the carries of the cross terms are dropped, each worth less
+// than one), so the result is congruent to x w and lies in [0, 4q).  For the butterflies, which only need a bound.
+LB_D u64 shoup_lazy4(u64 x, u64 w, u64 ws, u64 q)
+{
+    const unsigned xh = (unsigned)(x >> 32), xl = (unsigned)x, sh = (unsigned)(ws >> 32), sl = (unsigned)ws;
+    const u64 hi = (u64)xh * sh + __umulhi(xh, sl) + __umulhi(xl, sh);
+    return x * w - hi * q;
+}
+
 LB_D u64 shoup_mul(u64 x, u64 w, u64 ws, u64 q)
 {
     u64 r = shoup_lazy(x, w, ws, q);

@@ -112,7 +112,7 @@ LB_D void inv_core(u64 (&v)[1 << S], const ulonglong2 *__restrict__ itw, const u
                         x = f64_canon(f64_mulmod(__dadd_rn(xd, yd), f64_of(cn), f64_of(cns), qd), qd, qi);
                         y = f64_canon(f64_mulmod(__dadd_rn(xd, -yd), f64_of(cw), f64_of(cws), qd), qd, qi);
                     } else {
-                        const u64 s = x + y, d = x + q2 - y;
+                        const u64 s = x + y, d = x + (q2 << 1) - y; // inputs below 4q
                         x = shoup_mul(s, cn, cns, q);
                         y = shoup_mul(d, cw, cws, q);
                     }
@@ -268,7 +268,7 @@ LB_D void fwd_pass(u64 *sm, const bool from_global, u64 *gdst, const FwdIn &in, 
                 for (int i = 0; i < R; ++i) v[i] = barrett64(v[i], qi, in.r1);
             } else {
 #pragma unroll
-                for (int i = 0; i < R; ++i) v[i] = csub(csub(v[i], q2), q);
+                for (int i = 0; i < R; ++i) v[i] = csub(csub(csub(v[i], q2 << 1), q2), q);
             }
             if (epi.aux) {
                 u64 t[R];
@@ -813,7 +813,7 @@ LB_D void fwd_pass_fixed(u64 *sm, u64 *gdst, const unsigned cc, const ulonglong2
                 for (int i = 0; i < 8; ++i) v[i] = barrett64(v[i], qi, r1);
             } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = csub(csub(v[i], q2), q);
+                for (int i = 0; i < 8; ++i) v[i] = csub(csub(csub(v[i], q2 << 1), q2), q);
             }
             if (!PLAIN && epi.aux) {
 #pragma unroll

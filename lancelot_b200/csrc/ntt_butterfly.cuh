@@ -6,7 +6,8 @@
 namespace lb {
 
 // Butterfly variants, chosen per prime:
-//   integer, strict: Shoup product on the integer multiplier, values kept in [0, 4q);
+//   integer, strict: Shoup product on the integer multiplier with a three-multiplication high part
+//                    (shoup_lazy4), values kept in [0, 8q);
 //   integer, lazy:   the prime is below 2^58, so x may grow by 2q per stage over all seventeen
 //                    possible stages (bound 35q < 2^64) and the per-butterfly conditional
 //                    subtraction is dropped; the closing pass reduces once;
@@ -45,7 +46,15 @@ LB_D void fwd_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
         x = bits_of(__dadd_rn(xd, r));
         return;
     }
-    if (MODE == kIntStrict) x = csub(x, q2);
+    if (MODE == kIntStrict) {
+        // values below 8q between stages: x is brought below 4q, the product is below 4q (shoup_lazy4)
+        const u64 q4 = q2 << 1;
+        x = csub(x, q4);
+        const u64 t = shoup_lazy4(y, w.x, w.y, q);
+        y = x + q4 - t;
+        x = x + t;
+        return;
+    }
     const u64 t = shoup_lazy(y, w.x, w.y, q);
     y = x + q2 - t;
     x = x + t;
@@ -73,10 +82,12 @@ LB_D void inv_bf(u64 &x, u64 &y, const ulonglong2 w, const u64 q, const u64 q2)
         y = bits_of(f64_mulmod(__dadd_rn(xd, -yd), f64_of(w.x), f64_of(w.y), f64_of(q)));
         return;
     }
-    const u64 s = csub(x + y, q2);
-    const u64 d = x + q2 - y; // below 4q
+    // values below 4q between stages: the sum is brought back below 4q, the product is below 4q (shoup_lazy4)
+    const u64 q4 = q2 << 1;
+    const u64 s = csub(x + y, q4);
+    const u64 d = x + q4 - y; // below 8q
     x = s;
-    y = shoup_lazy(d, w.x, w.y, q);
+    y = shoup_lazy4(d, w.x, w.y, q);
 }
 
 } // namespace lb
